@@ -1,0 +1,184 @@
+"""ctypes binding of ``libqlin_b200.so`` (declared in ``include/qlin_b200.h``).
+
+The structures below mirror the header field for field.  There is no fallback: if the library is
+missing or a call fails, a ``RuntimeError`` with the library's own message is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = PKG_DIR / "lib" / "libqlin_b200.so"
+
+# qlin_status
+OK = 0
+ERR_BAD_SHAPE, ERR_BAD_ALIGN, ERR_BAD_DTYPE, ERR_UNSUPPORTED = -1, -2, -3, -4
+ERR_LAUNCH, ERR_TIMEOUT, ERR_NULL, ERR_DEVICE, ERR_TOO_LARGE = -5, -6, -7, -8, -9
+
+# qlin_dtype
+DT_NONE, DT_I8, DT_U8, DT_I32, DT_F32, DT_F16, DT_BF16, DT_F8E4M3 = range(8)
+
+# qlin_epilogue
+EPI_RAW, EPI_SCALE_PROD, EPI_SCALE_SEQ = 0, 1, 2
+
+# qlin_quant_mode
+Q_I8_DYN, Q_I8_STATIC, Q_I8_STATIC_CLAMP_FIRST, Q_F8_DYN, Q_I8_GIVEN_SCALE = range(5)
+
+# qlin_wq_mode
+W_SAWB, W_MAX, W_GIVEN = 0, 1, 2
+
+EXPORTED_SYMBOLS = (
+    "qlin_version",
+    "qlin_last_error_string",
+    "qlin_device_supported",
+    "qlin_gemm",
+    "qlin_act_quant",
+    "qlin_pact2_fwd",
+    "qlin_pact2_bwd",
+    "qlin_pact2_bwd_workspace_bytes",
+    "qlin_weight_fq_perch",
+)
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p),
+        ("b", C.c_void_p),
+        ("c", C.c_void_p),
+        ("d", C.c_void_p),
+        ("row_scale", C.c_void_p),
+        ("col_scale", C.c_void_p),
+        ("bias", C.c_void_p),
+        ("status", C.c_void_p),
+        ("lda", C.c_int64),
+        ("ldb", C.c_int64),
+        ("ldc", C.c_int64),
+        ("ldd", C.c_int64),
+        ("M", C.c_int32),
+        ("N", C.c_int32),
+        ("K", C.c_int32),
+        ("kind", C.c_int32),
+        ("chunk_k", C.c_int32),
+        ("trun_bits", C.c_int32),
+        ("max_acc_bits", C.c_int32),
+        ("trunc_then_acc", C.c_int32),
+        ("clamp_dl16", C.c_int32),
+        ("epilogue", C.c_int32),
+        ("row_scale_stride", C.c_int32),
+        ("col_scale_stride", C.c_int32),
+        ("scale_round", C.c_int32),
+        ("mid_round", C.c_int32),
+        ("acc_round", C.c_int32),
+        ("out_dtype", C.c_int32),
+    ]
+
+
+class QuantArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p),
+        ("smooth", C.c_void_p),
+        ("scale_in", C.c_void_p),
+        ("codes", C.c_void_p),
+        ("scale_out", C.c_void_p),
+        ("dq_out", C.c_void_p),
+        ("status", C.c_void_p),
+        ("ldx", C.c_int64),
+        ("ldq", C.c_int64),
+        ("lddq", C.c_int64),
+        ("rows", C.c_int32),
+        ("cols", C.c_int32),
+        ("x_dtype", C.c_int32),
+        ("mode", C.c_int32),
+        ("native_chain", C.c_int32),
+        ("smooth_mul", C.c_int32),
+        ("clamp_codes", C.c_int32),
+        ("qmax_levels", C.c_int32),
+        ("dl8_flush", C.c_int32),
+        ("scale_in_stride", C.c_int32),
+        ("scale0", C.c_float),
+        ("zp0", C.c_float),
+        ("lo", C.c_float),
+        ("hi", C.c_float),
+        ("shift", C.c_float),
+        ("add2", C.c_float),
+    ]
+
+
+class Pact2Args(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p),
+        ("grad_out", C.c_void_p),
+        ("out", C.c_void_p),
+        ("clip_val", C.c_void_p),
+        ("clip_valn", C.c_void_p),
+        ("grad_clip", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("numel", C.c_int64),
+        ("dtype", C.c_int32),
+        ("num_bits", C.c_int32),
+        ("align_zero", C.c_int32),
+    ]
+
+
+class WfqArgs(C.Structure):
+    _fields_ = [
+        ("w", C.c_void_p),
+        ("smooth", C.c_void_p),
+        ("dq_out", C.c_void_p),
+        ("codes", C.c_void_p),
+        ("clip_io", C.c_void_p),
+        ("ldw", C.c_int64),
+        ("ldo", C.c_int64),
+        ("ldq", C.c_int64),
+        ("rows", C.c_int32),
+        ("cols", C.c_int32),
+        ("dtype", C.c_int32),
+        ("num_bits", C.c_int32),
+        ("mode", C.c_int32),
+        ("native_mul", C.c_int32),
+        ("c0", C.c_float),
+        ("c1", C.c_float),
+    ]
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the library once and declares the prototypes.  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m fms_model_optimizer_b200.build_ext` "
+            "(there is no fallback implementation)"
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    lib.qlin_version.restype = C.c_int
+    lib.qlin_last_error_string.restype = C.c_char_p
+    lib.qlin_device_supported.argtypes = [C.c_int]
+    lib.qlin_device_supported.restype = C.c_int
+    for name, struct in (
+        ("qlin_gemm", GemmArgs),
+        ("qlin_act_quant", QuantArgs),
+        ("qlin_pact2_fwd", Pact2Args),
+        ("qlin_pact2_bwd", Pact2Args),
+        ("qlin_weight_fq_perch", WfqArgs),
+    ):
+        fn = getattr(lib, name)
+        fn.argtypes = [C.POINTER(struct), C.c_void_p]
+        fn.restype = C.c_int
+    lib.qlin_pact2_bwd_workspace_bytes.argtypes = [C.c_int64]
+    lib.qlin_pact2_bwd_workspace_bytes.restype = C.c_size_t
+    _lib = lib
+    return lib
+
+
+def check(rc: int, what: str) -> None:
+    """Turns a negative qlin_status into a RuntimeError carrying the library's message."""
+    if rc != OK:
+        msg = load().qlin_last_error_string()
+        raise RuntimeError(f"{what} failed with status {rc}: {msg.decode() if msg else ''}")

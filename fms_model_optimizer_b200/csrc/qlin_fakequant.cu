@@ -1,0 +1,222 @@
+// qlin_pact2_fwd / qlin_pact2_bwd: PACT+ two-sided fake quantisation for QAT activations.
+//
+// Elementwise, HBM-bound: fwd reads x and writes y (2*s bytes per element); bwd reads x and
+// grad_out and writes grad_x (3*s bytes per element) and reduces the two clip-value gradients.
+// The reduction is two-stage and ordered: every block writes its pair of partial sums to the
+// workspace, a one-block kernel adds them in index order, so results repeat bit for bit from run
+// to run.  The quantiser parameters are derived on the device from the clip values, exactly in
+// the order the reference derives them, so no host synchronisation is needed.
+#include "qlin_internal.h"
+#include "qlin_rows.cuh"
+
+namespace qlin {
+
+constexpr int kFqThreads = 256;
+
+struct PactParams {
+  const void* x;
+  const void* g;
+  void* out;
+  const float* cv;
+  const float* cvn;
+  float* grad_clip;
+  float* ws;
+  int64_t numel;
+  int32_t num_bits, align_zero;
+};
+
+struct PactScalars {
+  float cv, cvn, step, zp, n;
+};
+
+template <typename XT>
+__device__ __forceinline__ PactScalars pact_scalars(const PactParams& p) {
+  PactScalars s;
+  s.cv = Elem<XT>::rnd(*p.cv);
+  s.cvn = Elem<XT>::rnd(*p.cvn);
+  s.n = static_cast<float>((1 << p.num_bits) - 1);
+  const float scale = Elem<XT>::rnd(__fdiv_rn(s.n, Elem<XT>::rnd(__fsub_rn(s.cv, s.cvn))));
+  s.step = Elem<XT>::rnd(__fdiv_rn(1.0f, scale));
+  s.zp = Elem<XT>::rnd(__fmul_rn(s.cvn, scale));
+  if (p.align_zero) s.zp = rintf(s.zp);
+  return s;
+}
+
+template <typename XT>
+__device__ __forceinline__ float pact_fwd_one(const PactScalars& s, float x) {
+  float y = fminf(x, s.cv);
+  y = fmaxf(y, s.cvn);
+  float t = Elem<XT>::rnd(__fdiv_rn(y, s.step));
+  t = Elem<XT>::rnd(__fsub_rn(t, s.zp));
+  const float q = rintf(t);
+  return Elem<XT>::rnd(__fmul_rn(Elem<XT>::rnd(__fadd_rn(q, s.zp)), s.step));
+}
+
+template <typename XT>
+__device__ __forceinline__ float pact_bwd_one(const PactScalars& s, float x, float g, float& ga, float& gan) {
+  const float z = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fsub_rn(x, s.cvn)), s.step));
+  const float delz = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fsub_rn(z, rintf(z))), s.n));
+  const float inner = Elem<XT>::rnd(__fmul_rn(-g, delz));
+  const bool hi = x >= s.cv, lo = x <= s.cvn;
+  ga += hi ? g : (lo ? 0.0f : inner);
+  gan += lo ? g : (hi ? 0.0f : -inner);
+  return (hi || lo) ? 0.0f : g;
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(kFqThreads) pact2_fwd_kernel(const PactParams p) {
+  const PactScalars s = pact_scalars<XT>(p);
+  const XT* x = reinterpret_cast<const XT*>(p.x);
+  XT* out = reinterpret_cast<XT*>(p.out);
+  const bool vec = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+  const int64_t nvec = vec ? (p.numel >> 4) : 0;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float v[16];
+    load16(x + i * 16, v);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = pact_fwd_one<XT>(s, v[j]);
+    store16(out + i * 16, v);
+  }
+  for (int64_t i = nvec * 16 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.numel; i += stride)
+    store1(out + i, pact_fwd_one<XT>(s, load1(x + i)));
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(kFqThreads) pact2_bwd_kernel(const PactParams p) {
+  __shared__ float red[2][32];
+  const PactScalars s = pact_scalars<XT>(p);
+  const XT* x = reinterpret_cast<const XT*>(p.x);
+  const XT* g = reinterpret_cast<const XT*>(p.g);
+  XT* out = reinterpret_cast<XT*>(p.out);
+  const bool vec =
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+  const int64_t nvec = vec ? (p.numel >> 4) : 0;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  float ga = 0.0f, gan = 0.0f;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float v[16], gv[16];
+    load16(x + i * 16, v);
+    load16(g + i * 16, gv);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = pact_bwd_one<XT>(s, v[j], gv[j], ga, gan);
+    store16(out + i * 16, v);
+  }
+  for (int64_t i = nvec * 16 + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.numel; i += stride)
+    store1(out + i, pact_bwd_one<XT>(s, load1(x + i), load1(g + i), ga, gan));
+  ga = block_reduce<OpSum>(ga, red[0], 0.0f);
+  gan = block_reduce<OpSum>(gan, red[1], 0.0f);
+  if (threadIdx.x == 0) {
+    p.ws[2 * blockIdx.x] = ga;
+    p.ws[2 * blockIdx.x + 1] = gan;
+  }
+}
+
+// Adds the per-block partial sums in index order.
+__global__ void __launch_bounds__(kFqThreads) pact2_bwd_finish_kernel(const float* ws, int nblocks, float* grad_clip) {
+  __shared__ float red[2][32];
+  float ga = 0.0f, gan = 0.0f;
+  for (int i = threadIdx.x; i < nblocks; i += blockDim.x) {
+    ga += ws[2 * i];
+    gan += ws[2 * i + 1];
+  }
+  ga = block_reduce<OpSum>(ga, red[0], 0.0f);
+  gan = block_reduce<OpSum>(gan, red[1], 0.0f);
+  if (threadIdx.x == 0) {
+    grad_clip[0] = ga;
+    grad_clip[1] = gan;
+  }
+}
+
+// Grid of the elementwise kernels: a function of numel only, so the reduction order is fixed.
+static int fq_grid(int64_t numel) {
+  const int64_t per_block = static_cast<int64_t>(kFqThreads) * 16;
+  int64_t blocks = (numel + per_block - 1) / per_block;
+  const int64_t cap = 148 * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return static_cast<int>(blocks);
+}
+
+static int check_pact(const qlin_pact2_args* a, bool bwd, const char* name) {
+  if (a == nullptr) return fail(QLIN_ERR_NULL, "%s: args is NULL", name);
+  if (a->x == nullptr || a->out == nullptr || a->clip_val == nullptr || a->clip_valn == nullptr)
+    return fail(QLIN_ERR_NULL, "%s: x, out, clip_val or clip_valn is NULL", name);
+  if (bwd && (a->grad_out == nullptr || a->grad_clip == nullptr || a->workspace == nullptr))
+    return fail(QLIN_ERR_NULL, "%s: grad_out, grad_clip or workspace is NULL", name);
+  if (a->numel < 0) return fail(QLIN_ERR_BAD_SHAPE, "%s: negative numel", name);
+  if (a->num_bits < 2 || a->num_bits > 16) return fail(QLIN_ERR_UNSUPPORTED, "%s: num_bits must be in [2, 16]", name);
+  if (a->dtype != QLIN_DT_F32 && a->dtype != QLIN_DT_F16 && a->dtype != QLIN_DT_BF16)
+    return fail(QLIN_ERR_BAD_DTYPE, "%s: dtype must be F32, F16 or BF16", name);
+  return QLIN_OK;
+}
+
+static PactParams to_params(const qlin_pact2_args* a) {
+  PactParams p;
+  p.x = a->x;
+  p.g = a->grad_out;
+  p.out = a->out;
+  p.cv = a->clip_val;
+  p.cvn = a->clip_valn;
+  p.grad_clip = a->grad_clip;
+  p.ws = static_cast<float*>(a->workspace);
+  p.numel = a->numel;
+  p.num_bits = a->num_bits;
+  p.align_zero = a->align_zero != 0;
+  return p;
+}
+
+}  // namespace qlin
+
+using namespace qlin;
+
+extern "C" size_t qlin_pact2_bwd_workspace_bytes(int64_t numel) {
+  return static_cast<size_t>(fq_grid(numel < 0 ? 0 : numel)) * 2 * sizeof(float);
+}
+
+extern "C" int qlin_pact2_fwd(const qlin_pact2_args* a, void* stream) {
+  int rc = check_pact(a, false, "qlin_pact2_fwd");
+  if (rc != QLIN_OK) return rc;
+  if (a->numel == 0) return QLIN_OK;
+  const PactParams p = to_params(a);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = fq_grid(a->numel);
+  switch (a->dtype) {
+    case QLIN_DT_F32:
+      pact2_fwd_kernel<float><<<grid, kFqThreads, 0, s>>>(p);
+      break;
+    case QLIN_DT_F16:
+      pact2_fwd_kernel<__half><<<grid, kFqThreads, 0, s>>>(p);
+      break;
+    default:
+      pact2_fwd_kernel<__nv_bfloat16><<<grid, kFqThreads, 0, s>>>(p);
+      break;
+  }
+  QLIN_CHECK_LAUNCH("qlin_pact2_fwd");
+  return QLIN_OK;
+}
+
+extern "C" int qlin_pact2_bwd(const qlin_pact2_args* a, void* stream) {
+  int rc = check_pact(a, true, "qlin_pact2_bwd");
+  if (rc != QLIN_OK) return rc;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const PactParams p = to_params(a);
+  const int grid = fq_grid(a->numel);
+  if (a->numel > 0) {
+    switch (a->dtype) {
+      case QLIN_DT_F32:
+        pact2_bwd_kernel<float><<<grid, kFqThreads, 0, s>>>(p);
+        break;
+      case QLIN_DT_F16:
+        pact2_bwd_kernel<__half><<<grid, kFqThreads, 0, s>>>(p);
+        break;
+      default:
+        pact2_bwd_kernel<__nv_bfloat16><<<grid, kFqThreads, 0, s>>>(p);
+        break;
+    }
+    QLIN_CHECK_LAUNCH("qlin_pact2_bwd");
+  }
+  pact2_bwd_finish_kernel<<<1, kFqThreads, 0, s>>>(p.ws, a->numel > 0 ? grid : 0, p.grad_clip);
+  QLIN_CHECK_LAUNCH("qlin_pact2_bwd(finish)");
+  return QLIN_OK;
+}

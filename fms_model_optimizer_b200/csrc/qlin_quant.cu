@@ -1,0 +1,548 @@
+// qlin_act_quant and qlin_weight_fq_perch: single-pass, row-per-block quantise kernels.
+//
+// A block owns one row at a time (grid-stride over rows).  Each thread keeps its 16-element slices
+// of the row in registers between the statistics pass (absmax, or mean|w| and mean w^2) and the
+// quantise pass, so a row is read from HBM once and written once:
+//   activation quantise : read s*cols (+4*cols smooth), write cols codes + 4 bytes scale
+//   weight fake-quantise: read s*cols, write s*cols (and / or cols codes) + 4 bytes clip
+// Rows longer than the register budget fall back to re-reading the row (from L2) in the second
+// pass; rows whose length or alignment rules out 16-byte vectors take a scalar path with the same
+// arithmetic.
+//
+// Arithmetic follows the reference's eager tensor expressions operation by operation: every
+// division, multiplication and addition is a separately rounded fp32 operation, optionally rounded
+// again to the tensor dtype ("native chain") where the reference computes in bf16 / fp16.
+#include <cuda_fp8.h>
+
+#include "qlin_internal.h"
+#include "qlin_rows.cuh"
+
+namespace qlin {
+
+struct QuantParams {
+  const void* x;
+  const float* smooth;
+  const float* scale_in;
+  uint8_t* codes;
+  float* scale_out;
+  void* dq_out;
+  int64_t ldx, ldq, lddq;
+  int32_t rows, cols;
+  int32_t mode, native, smooth_mul, clamp_codes, levels, dl8_flush, scale_in_stride;
+  float scale0, zp0, lo, hi, shift, add2;
+};
+
+template <typename XT>
+__device__ __forceinline__ float smooth_apply(const QuantParams& p, float x, float sm) {
+  const float v = p.smooth_mul ? __fmul_rn(x, sm) : __fdiv_rn(x, sm);
+  return rnd_if<XT>(v, p.native);
+}
+
+// Row scale from the row's absmax.
+template <typename XT>
+__device__ __forceinline__ float dyn_scale(const QuantParams& p, float amax) {
+  const float eps = rnd_if<XT>(1e-5f, p.native);
+  if (p.mode == QLIN_Q_F8_DYN) {
+    const float a = rnd_if<XT>(__fdiv_rn(amax, 448.0f), p.native);
+    return fmaxf(a, eps);
+  }
+  const float a = fmaxf(amax, eps);
+  return rnd_if<XT>(__fdiv_rn(a, static_cast<float>(p.levels)), p.native);
+}
+
+// torch's float -> float8_e4m3fn conversion: round to nearest even, NaN above 464.
+__device__ __forceinline__ uint8_t to_e4m3(float v) {
+  if (!(fabsf(v) <= 464.0f)) return static_cast<uint8_t>(0x7F | (signbit(v) ? 0x80 : 0));
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+__device__ __forceinline__ float from_e4m3(uint8_t c) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(c), __NV_E4M3);
+  return __half2float(*reinterpret_cast<const __half*>(&h));
+}
+
+// One element: value after smoothing -> code byte, and the fake-quantised value for dq_out.
+template <typename XT>
+__device__ __forceinline__ uint8_t quant_one(const QuantParams& p, float v, float s, float& dq) {
+  const bool nat = p.native;
+  switch (p.mode) {
+    case QLIN_Q_I8_DYN:
+    case QLIN_Q_I8_GIVEN_SCALE: {
+      const float r = rintf(rnd_if<XT>(__fdiv_rn(v, s), nat));
+      dq = rnd_if<XT>(__fmul_rn(r, s), nat);
+      float c = r;
+      if (p.mode == QLIN_Q_I8_GIVEN_SCALE) c = rnd_if<XT>(__fadd_rn(c, p.zp0), nat);
+      int q = static_cast<int>(c);
+      if (p.clamp_codes) q = max(-p.levels, min(p.levels, q));
+      return static_cast<uint8_t>(q & 0xFF);
+    }
+    case QLIN_Q_I8_STATIC: {
+      float t = rnd_if<XT>(__fdiv_rn(v, p.scale0), nat);
+      t = rnd_if<XT>(__fadd_rn(t, p.zp0), nat);
+      t = rnd_if<XT>(__fsub_rn(t, p.shift), nat);
+      t = rnd_if<XT>(__fadd_rn(t, p.add2), nat);
+      const float r = fminf(fmaxf(rintf(t), -128.0f), 127.0f);
+      dq = r;
+      return static_cast<uint8_t>(static_cast<int>(r) & 0xFF);
+    }
+    case QLIN_Q_I8_STATIC_CLAMP_FIRST: {
+      float t = fminf(fmaxf(v, p.lo), p.hi);
+      t = rnd_if<XT>(__fdiv_rn(t, p.scale0), nat);
+      t = rnd_if<XT>(__fsub_rn(t, p.zp0), nat);
+      const float r = rnd_if<XT>(__fsub_rn(rintf(t), p.shift), nat);
+      dq = r;
+      return static_cast<uint8_t>(static_cast<int>(r) & 0xFF);
+    }
+    default: {  // QLIN_Q_F8_DYN
+      const float t = rnd_if<XT>(__fdiv_rn(v, s), nat);
+      uint8_t c = to_e4m3(t);
+      float f = from_e4m3(c);
+      if (p.dl8_flush && fabsf(f) < 0.0087890625f) {
+        c = 0;
+        f = 0.0f;
+      }
+      dq = f;
+      return c;
+    }
+  }
+}
+
+__device__ __forceinline__ bool is_dynamic(int mode) { return mode == QLIN_Q_I8_DYN || mode == QLIN_Q_F8_DYN; }
+
+template <typename XT>
+__device__ __forceinline__ float row_scale_of(const QuantParams& p, int row, float amax) {
+  if (is_dynamic(p.mode)) return dyn_scale<XT>(p, amax);
+  if (p.mode == QLIN_Q_I8_GIVEN_SCALE) return p.scale_in[static_cast<int64_t>(row) * p.scale_in_stride];
+  return p.scale0;
+}
+
+// Vector path: cols % 16 == 0 and every row start 16-byte aligned.  MAXC = register-resident
+// 16-element slices per thread; MAXC == 0 re-reads the row in the second pass.
+template <typename XT, int MAXC>
+__global__ void __launch_bounds__(1024) act_quant_vec_kernel(const QuantParams p) {
+  __shared__ float red[2][32];
+  const int nchunks = p.cols >> 4;
+  const bool has_smooth = p.smooth != nullptr;
+  constexpr int NREG = MAXC > 0 ? MAXC : 1;
+  int iter = 0;
+  for (int row = blockIdx.x; row < p.rows; row += gridDim.x, ++iter) {
+    const XT* xr = reinterpret_cast<const XT*>(p.x) + static_cast<int64_t>(row) * p.ldx;
+    float v[NREG][16];
+    float amax = 0.0f;
+    if (MAXC > 0) {
+#pragma unroll
+      for (int c = 0; c < NREG; ++c) {
+        const int ch = threadIdx.x + c * blockDim.x;
+        if (ch < nchunks) {
+          load16(xr + ch * 16, v[c]);
+          if (has_smooth) {
+            float sm[16];
+            load16(p.smooth + ch * 16, sm);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[c][i] = smooth_apply<XT>(p, v[c][i], sm[i]);
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[c][i]));
+        }
+      }
+    } else if (is_dynamic(p.mode)) {
+      for (int ch = threadIdx.x; ch < nchunks; ch += blockDim.x) {
+        load16(xr + ch * 16, v[0]);
+        if (has_smooth) {
+          float sm[16];
+          load16(p.smooth + ch * 16, sm);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[0][i] = smooth_apply<XT>(p, v[0][i], sm[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[0][i]));
+      }
+    }
+    if (is_dynamic(p.mode)) amax = block_reduce<OpMax>(amax, red[iter & 1], 0.0f);
+    const float s = row_scale_of<XT>(p, row, amax);
+    if (threadIdx.x == 0 && p.scale_out != nullptr) p.scale_out[row] = s;
+
+    auto emit = [&](int ch, const float (&val)[16]) {
+      float dq[16];
+      uint32_t w[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t c = quant_one<XT>(p, val[i], s, dq[i]);
+        w[i >> 2] |= c << (8 * (i & 3));
+      }
+      if (p.codes != nullptr)
+        *reinterpret_cast<uint4*>(p.codes + static_cast<int64_t>(row) * p.ldq + ch * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      if (p.dq_out != nullptr) store16(reinterpret_cast<XT*>(p.dq_out) + static_cast<int64_t>(row) * p.lddq + ch * 16, dq);
+    };
+    if (MAXC > 0) {
+#pragma unroll
+      for (int c = 0; c < NREG; ++c) {
+        const int ch = threadIdx.x + c * blockDim.x;
+        if (ch < nchunks) emit(ch, v[c]);
+      }
+    } else {
+      for (int ch = threadIdx.x; ch < nchunks; ch += blockDim.x) {
+        load16(xr + ch * 16, v[0]);
+        if (has_smooth) {
+          float sm[16];
+          load16(p.smooth + ch * 16, sm);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[0][i] = smooth_apply<XT>(p, v[0][i], sm[i]);
+        }
+        emit(ch, v[0]);
+      }
+    }
+  }
+}
+
+// Scalar path for any shape / alignment.
+template <typename XT>
+__global__ void __launch_bounds__(256) act_quant_scalar_kernel(const QuantParams p) {
+  __shared__ float red[2][32];
+  const bool has_smooth = p.smooth != nullptr;
+  int iter = 0;
+  for (int row = blockIdx.x; row < p.rows; row += gridDim.x, ++iter) {
+    const XT* xr = reinterpret_cast<const XT*>(p.x) + static_cast<int64_t>(row) * p.ldx;
+    float amax = 0.0f;
+    if (is_dynamic(p.mode)) {
+      for (int c = threadIdx.x; c < p.cols; c += blockDim.x) {
+        float v = load1(xr + c);
+        if (has_smooth) v = smooth_apply<XT>(p, v, p.smooth[c]);
+        amax = fmaxf(amax, fabsf(v));
+      }
+      amax = block_reduce<OpMax>(amax, red[iter & 1], 0.0f);
+    }
+    const float s = row_scale_of<XT>(p, row, amax);
+    if (threadIdx.x == 0 && p.scale_out != nullptr) p.scale_out[row] = s;
+    for (int c = threadIdx.x; c < p.cols; c += blockDim.x) {
+      float v = load1(xr + c);
+      if (has_smooth) v = smooth_apply<XT>(p, v, p.smooth[c]);
+      float dq;
+      const uint8_t code = quant_one<XT>(p, v, s, dq);
+      if (p.codes != nullptr) p.codes[static_cast<int64_t>(row) * p.ldq + c] = code;
+      if (p.dq_out != nullptr) store1(reinterpret_cast<XT*>(p.dq_out) + static_cast<int64_t>(row) * p.lddq + c, dq);
+    }
+  }
+}
+
+template <typename XT>
+static int launch_act_quant(const QuantParams& p, cudaStream_t stream) {
+  const int es = static_cast<int>(sizeof(XT));
+  bool vec = (p.cols % 16 == 0) && aligned16(p.x) && ((p.ldx * es) % 16 == 0);
+  if (p.smooth != nullptr) vec = vec && aligned16(p.smooth);
+  if (p.codes != nullptr) vec = vec && aligned16(p.codes) && (p.ldq % 16 == 0);
+  if (p.dq_out != nullptr) vec = vec && aligned16(p.dq_out) && ((p.lddq * es) % 16 == 0);
+  const int max_blocks = sm_count() * 16;
+  if (!vec) {
+    const int grid = p.rows < max_blocks ? p.rows : max_blocks;
+    act_quant_scalar_kernel<XT><<<grid, 256, 0, stream>>>(p);
+    QLIN_CHECK_LAUNCH("qlin_act_quant");
+    return QLIN_OK;
+  }
+  const int nchunks = p.cols / 16;
+  int threads = ((nchunks + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  const int blocks_per_sm = 2048 / threads;
+  int grid = sm_count() * (blocks_per_sm > 0 ? blocks_per_sm : 1);
+  if (grid > p.rows) grid = p.rows;
+  if (nchunks <= threads) {
+    act_quant_vec_kernel<XT, 1><<<grid, threads, 0, stream>>>(p);
+  } else if (nchunks <= 2 * threads) {
+    act_quant_vec_kernel<XT, 2><<<grid, threads, 0, stream>>>(p);
+  } else {
+    act_quant_vec_kernel<XT, 0><<<grid, threads, 0, stream>>>(p);
+  }
+  QLIN_CHECK_LAUNCH("qlin_act_quant");
+  return QLIN_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Per-output-channel weight fake quantisation (SAWB+ / max), statistics and quantise in one pass.
+// ------------------------------------------------------------------------------------------------
+struct WfqParams {
+  const void* w;
+  const float* smooth;
+  void* dq_out;
+  int8_t* codes;
+  float* clip_io;
+  int64_t ldw, ldo, ldq;
+  int32_t rows, cols, num_bits, mode, native_mul;
+  float c0, c1;
+};
+
+template <typename XT>
+__device__ __forceinline__ float wfq_clip(const WfqParams& p, float sum_abs, float sum_sq, float amax, int row) {
+  if (p.mode == QLIN_W_GIVEN) return p.clip_io[row];
+  if (p.mode == QLIN_W_MAX) return amax;
+  // clip = c1 * mean|w| + c0 * sqrt(mean w^2), every step rounded to the weight dtype.
+  const float n = static_cast<float>(p.cols);
+  const float mu = Elem<XT>::rnd(__fdiv_rn(sum_abs, n));
+  const float sd = Elem<XT>::rnd(__fsqrt_rn(Elem<XT>::rnd(__fdiv_rn(sum_sq, n))));
+  const float a = Elem<XT>::rnd(__fmul_rn(p.c1, mu));
+  const float b = Elem<XT>::rnd(__fmul_rn(p.c0, sd));
+  return Elem<XT>::rnd(__fadd_rn(a, b));
+}
+
+// torch.fake_quantize_per_channel_affine with zero_point 0:
+//   q = clamp(nearbyint(w * (1 / scale)), -L, L);  out = q * scale.
+__device__ __forceinline__ float wfq_one(float w, float inv_scale, float scale, float lim, int& q) {
+  float r = nearbyintf(__fmul_rn(w, inv_scale));
+  r = fminf(fmaxf(r, -lim), lim);
+  q = static_cast<int>(r);
+  return __fmul_rn(r, scale);
+}
+
+template <typename XT, int MAXC>
+__global__ void __launch_bounds__(1024) wfq_vec_kernel(const WfqParams p) {
+  __shared__ float red[2][3][32];
+  const int nchunks = p.cols >> 4;
+  const bool has_smooth = p.smooth != nullptr;
+  constexpr int NREG = MAXC > 0 ? MAXC : 1;
+  const float lim = static_cast<float>((1 << (p.num_bits - 1)) - 1);
+  const float nspace = static_cast<float>((1 << p.num_bits) - 2);
+  int iter = 0;
+  for (int row = blockIdx.x; row < p.rows; row += gridDim.x, ++iter) {
+    const XT* wr = reinterpret_cast<const XT*>(p.w) + static_cast<int64_t>(row) * p.ldw;
+    float v[NREG][16];
+    float sa = 0.0f, sq = 0.0f, am = 0.0f;
+    auto fetch = [&](int ch, float (&dst)[16]) {
+      load16(wr + ch * 16, dst);
+      if (has_smooth) {
+        float sm[16];
+        load16(p.smooth + ch * 16, sm);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dst[i] = rnd_if<XT>(__fmul_rn(dst[i], sm[i]), p.native_mul);
+      }
+    };
+    auto stats = [&](const float (&val)[16]) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float a = fabsf(val[i]);
+        sa += a;
+        sq += Elem<XT>::rnd(__fmul_rn(val[i], val[i]));
+        am = fmaxf(am, a);
+      }
+    };
+    if (MAXC > 0) {
+#pragma unroll
+      for (int c = 0; c < NREG; ++c) {
+        const int ch = threadIdx.x + c * blockDim.x;
+        if (ch < nchunks) {
+          fetch(ch, v[c]);
+          stats(v[c]);
+        }
+      }
+    } else if (p.mode != QLIN_W_GIVEN) {
+      for (int ch = threadIdx.x; ch < nchunks; ch += blockDim.x) {
+        fetch(ch, v[0]);
+        stats(v[0]);
+      }
+    }
+    if (p.mode == QLIN_W_SAWB) {
+      sa = block_reduce<OpSum>(sa, red[iter & 1][0], 0.0f);
+      // the second reduction may reuse the barrier of the first: distinct slot
+      sq = block_reduce<OpSum>(sq, red[iter & 1][1], 0.0f);
+    } else if (p.mode == QLIN_W_MAX) {
+      am = block_reduce<OpMax>(am, red[iter & 1][2], 0.0f);
+    }
+    const float clip = wfq_clip<XT>(p, sa, sq, am, row);
+    if (threadIdx.x == 0 && p.mode != QLIN_W_GIVEN) p.clip_io[row] = clip;
+    // scale = clip * 2 / nspace in the weight dtype, then widened
+    const float scale = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fmul_rn(clip, 2.0f)), nspace));
+    const float inv_scale = __fdiv_rn(1.0f, scale);
+    auto emit = [&](int ch, const float (&val)[16]) {
+      float dq[16];
+      uint32_t wds[4] = {0, 0, 0, 0};
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        int q;
+        dq[i] = wfq_one(val[i], inv_scale, scale, lim, q);
+        wds[i >> 2] |= static_cast<uint32_t>(q & 0xFF) << (8 * (i & 3));
+      }
+      if (p.codes != nullptr)
+        *reinterpret_cast<uint4*>(p.codes + static_cast<int64_t>(row) * p.ldq + ch * 16) =
+            make_uint4(wds[0], wds[1], wds[2], wds[3]);
+      if (p.dq_out != nullptr) store16(reinterpret_cast<XT*>(p.dq_out) + static_cast<int64_t>(row) * p.ldo + ch * 16, dq);
+    };
+    if (MAXC > 0) {
+#pragma unroll
+      for (int c = 0; c < NREG; ++c) {
+        const int ch = threadIdx.x + c * blockDim.x;
+        if (ch < nchunks) emit(ch, v[c]);
+      }
+    } else {
+      for (int ch = threadIdx.x; ch < nchunks; ch += blockDim.x) {
+        fetch(ch, v[0]);
+        emit(ch, v[0]);
+      }
+    }
+  }
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(256) wfq_scalar_kernel(const WfqParams p) {
+  __shared__ float red[2][3][32];
+  const bool has_smooth = p.smooth != nullptr;
+  const float lim = static_cast<float>((1 << (p.num_bits - 1)) - 1);
+  const float nspace = static_cast<float>((1 << p.num_bits) - 2);
+  int iter = 0;
+  for (int row = blockIdx.x; row < p.rows; row += gridDim.x, ++iter) {
+    const XT* wr = reinterpret_cast<const XT*>(p.w) + static_cast<int64_t>(row) * p.ldw;
+    float sa = 0.0f, sq = 0.0f, am = 0.0f;
+    if (p.mode != QLIN_W_GIVEN) {
+      for (int c = threadIdx.x; c < p.cols; c += blockDim.x) {
+        float v = load1(wr + c);
+        if (has_smooth) v = rnd_if<XT>(__fmul_rn(v, p.smooth[c]), p.native_mul);
+        const float a = fabsf(v);
+        sa += a;
+        sq += Elem<XT>::rnd(__fmul_rn(v, v));
+        am = fmaxf(am, a);
+      }
+      if (p.mode == QLIN_W_SAWB) {
+        sa = block_reduce<OpSum>(sa, red[iter & 1][0], 0.0f);
+        sq = block_reduce<OpSum>(sq, red[iter & 1][1], 0.0f);
+      } else {
+        am = block_reduce<OpMax>(am, red[iter & 1][2], 0.0f);
+      }
+    }
+    const float clip = wfq_clip<XT>(p, sa, sq, am, row);
+    if (threadIdx.x == 0 && p.mode != QLIN_W_GIVEN) p.clip_io[row] = clip;
+    const float scale = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fmul_rn(clip, 2.0f)), nspace));
+    const float inv_scale = __fdiv_rn(1.0f, scale);
+    for (int c = threadIdx.x; c < p.cols; c += blockDim.x) {
+      float v = load1(wr + c);
+      if (has_smooth) v = rnd_if<XT>(__fmul_rn(v, p.smooth[c]), p.native_mul);
+      int q;
+      const float dq = wfq_one(v, inv_scale, scale, lim, q);
+      if (p.codes != nullptr) p.codes[static_cast<int64_t>(row) * p.ldq + c] = static_cast<int8_t>(q);
+      if (p.dq_out != nullptr) store1(reinterpret_cast<XT*>(p.dq_out) + static_cast<int64_t>(row) * p.ldo + c, dq);
+    }
+  }
+}
+
+template <typename XT>
+static int launch_wfq(const WfqParams& p, cudaStream_t stream) {
+  const int es = static_cast<int>(sizeof(XT));
+  bool vec = (p.cols % 16 == 0) && aligned16(p.w) && ((p.ldw * es) % 16 == 0);
+  if (p.smooth != nullptr) vec = vec && aligned16(p.smooth);
+  if (p.codes != nullptr) vec = vec && aligned16(p.codes) && (p.ldq % 16 == 0);
+  if (p.dq_out != nullptr) vec = vec && aligned16(p.dq_out) && ((p.ldo * es) % 16 == 0);
+  const int max_blocks = sm_count() * 16;
+  if (!vec) {
+    const int grid = p.rows < max_blocks ? p.rows : max_blocks;
+    wfq_scalar_kernel<XT><<<grid, 256, 0, stream>>>(p);
+    QLIN_CHECK_LAUNCH("qlin_weight_fq_perch");
+    return QLIN_OK;
+  }
+  const int nchunks = p.cols / 16;
+  int threads = ((nchunks + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  const int blocks_per_sm = 2048 / threads;
+  int grid = sm_count() * (blocks_per_sm > 0 ? blocks_per_sm : 1);
+  if (grid > p.rows) grid = p.rows;
+  if (nchunks <= threads) {
+    wfq_vec_kernel<XT, 1><<<grid, threads, 0, stream>>>(p);
+  } else if (nchunks <= 2 * threads) {
+    wfq_vec_kernel<XT, 2><<<grid, threads, 0, stream>>>(p);
+  } else {
+    wfq_vec_kernel<XT, 0><<<grid, threads, 0, stream>>>(p);
+  }
+  QLIN_CHECK_LAUNCH("qlin_weight_fq_perch");
+  return QLIN_OK;
+}
+
+}  // namespace qlin
+
+using namespace qlin;
+
+extern "C" int qlin_act_quant(const qlin_quant_args* a, void* stream) {
+  if (a == nullptr) return fail(QLIN_ERR_NULL, "qlin_act_quant: args is NULL");
+  if (a->x == nullptr) return fail(QLIN_ERR_NULL, "qlin_act_quant: x is NULL");
+  if (a->codes == nullptr && a->dq_out == nullptr && a->scale_out == nullptr)
+    return fail(QLIN_ERR_NULL, "qlin_act_quant: no output requested");
+  if (a->rows < 0 || a->cols < 0) return fail(QLIN_ERR_BAD_SHAPE, "qlin_act_quant: negative dimension");
+  if (a->rows == 0 || a->cols == 0) return QLIN_OK;
+  if (a->ldx < a->cols || (a->codes != nullptr && a->ldq < a->cols) || (a->dq_out != nullptr && a->lddq < a->cols))
+    return fail(QLIN_ERR_BAD_SHAPE, "qlin_act_quant: leading dimension smaller than the row length");
+  if (a->mode < QLIN_Q_I8_DYN || a->mode > QLIN_Q_I8_GIVEN_SCALE)
+    return fail(QLIN_ERR_UNSUPPORTED, "qlin_act_quant: unknown mode %d", a->mode);
+  if (a->mode == QLIN_Q_I8_GIVEN_SCALE && a->scale_in == nullptr)
+    return fail(QLIN_ERR_NULL, "qlin_act_quant: scale_in is required by QLIN_Q_I8_GIVEN_SCALE");
+  if ((a->mode == QLIN_Q_I8_DYN || a->mode == QLIN_Q_I8_GIVEN_SCALE) && (a->qmax_levels < 1 || a->qmax_levels > 127))
+    return fail(QLIN_ERR_UNSUPPORTED, "qlin_act_quant: qmax_levels must be in [1, 127]");
+  QuantParams p;
+  p.x = a->x;
+  p.smooth = a->smooth;
+  p.scale_in = a->scale_in;
+  p.codes = static_cast<uint8_t*>(a->codes);
+  p.scale_out = a->scale_out;
+  p.dq_out = a->dq_out;
+  p.ldx = a->ldx;
+  p.ldq = a->ldq;
+  p.lddq = a->lddq;
+  p.rows = a->rows;
+  p.cols = a->cols;
+  p.mode = a->mode;
+  p.native = a->native_chain != 0;
+  p.smooth_mul = a->smooth_mul != 0;
+  p.clamp_codes = a->clamp_codes != 0;
+  p.levels = a->qmax_levels;
+  p.dl8_flush = a->dl8_flush != 0;
+  p.scale_in_stride = a->scale_in_stride != 0 ? 1 : 0;
+  p.scale0 = a->scale0;
+  p.zp0 = a->zp0;
+  p.lo = a->lo;
+  p.hi = a->hi;
+  p.shift = a->shift;
+  p.add2 = a->add2;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (a->x_dtype) {
+    case QLIN_DT_F32:
+      return launch_act_quant<float>(p, s);
+    case QLIN_DT_F16:
+      return launch_act_quant<__half>(p, s);
+    case QLIN_DT_BF16:
+      return launch_act_quant<__nv_bfloat16>(p, s);
+    default:
+      return fail(QLIN_ERR_BAD_DTYPE, "qlin_act_quant: x_dtype must be F32, F16 or BF16");
+  }
+}
+
+extern "C" int qlin_weight_fq_perch(const qlin_wfq_args* a, void* stream) {
+  if (a == nullptr) return fail(QLIN_ERR_NULL, "qlin_weight_fq_perch: args is NULL");
+  if (a->w == nullptr || a->clip_io == nullptr) return fail(QLIN_ERR_NULL, "qlin_weight_fq_perch: w or clip_io is NULL");
+  if (a->dq_out == nullptr && a->codes == nullptr) return fail(QLIN_ERR_NULL, "qlin_weight_fq_perch: no output requested");
+  if (a->rows < 0 || a->cols < 0) return fail(QLIN_ERR_BAD_SHAPE, "qlin_weight_fq_perch: negative dimension");
+  if (a->rows == 0 || a->cols == 0) return QLIN_OK;
+  if (a->num_bits != 2 && a->num_bits != 4 && a->num_bits != 8)
+    return fail(QLIN_ERR_UNSUPPORTED, "qlin_weight_fq_perch: num_bits must be 2, 4 or 8");
+  if (a->mode < QLIN_W_SAWB || a->mode > QLIN_W_GIVEN) return fail(QLIN_ERR_UNSUPPORTED, "qlin_weight_fq_perch: unknown mode");
+  if (a->ldw < a->cols || (a->dq_out != nullptr && a->ldo < a->cols) || (a->codes != nullptr && a->ldq < a->cols))
+    return fail(QLIN_ERR_BAD_SHAPE, "qlin_weight_fq_perch: leading dimension smaller than the row length");
+  WfqParams p;
+  p.w = a->w;
+  p.smooth = a->smooth;
+  p.dq_out = a->dq_out;
+  p.codes = static_cast<int8_t*>(a->codes);
+  p.clip_io = a->clip_io;
+  p.ldw = a->ldw;
+  p.ldo = a->ldo;
+  p.ldq = a->ldq;
+  p.rows = a->rows;
+  p.cols = a->cols;
+  p.num_bits = a->num_bits;
+  p.mode = a->mode;
+  p.native_mul = a->native_mul != 0;
+  p.c0 = a->c0;
+  p.c1 = a->c1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (a->dtype) {
+    case QLIN_DT_F32:
+      return launch_wfq<float>(p, s);
+    case QLIN_DT_F16:
+      return launch_wfq<__half>(p, s);
+    case QLIN_DT_BF16:
+      return launch_wfq<__nv_bfloat16>(p, s);
+    default:
+      return fail(QLIN_ERR_BAD_DTYPE, "qlin_weight_fq_perch: dtype must be F32, F16 or BF16");
+  }
+}

@@ -1,0 +1,405 @@
+"""Tensor-level entry points over the C ABI of ``libqlin_b200.so``.
+
+Every function here takes CUDA tensors, allocates its outputs with PyTorch's caching allocator,
+passes raw device pointers plus the current CUDA stream to the library and returns tensors.  There
+is no CPU path and no fallback kernel: a CPU tensor or a missing library is an error.
+
+The functions are also registered as torch custom ops in the ``qlin_b200`` namespace (see the end
+of the file) so that modules call ``torch.ops.qlin_b200.*`` the way the reference's modules call
+``torch.ops.fms_mo.*`` (fms_mo/custom_ext_kernels/utils.py:642-802).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib as L
+
+_DT = {
+    torch.int8: L.DT_I8,
+    torch.uint8: L.DT_U8,
+    torch.int32: L.DT_I32,
+    torch.float32: L.DT_F32,
+    torch.float16: L.DT_F16,
+    torch.bfloat16: L.DT_BF16,
+    torch.float8_e4m3fn: L.DT_F8E4M3,
+}
+_ROUND = {None: L.DT_NONE, torch.float32: L.DT_F32, torch.float16: L.DT_F16, torch.bfloat16: L.DT_BF16}
+
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def _require_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("qlin_b200 ops run on CUDA tensors only (there is no CPU path)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"tensors on different devices: {dev} and {t.device}")
+    if dev is None:
+        raise RuntimeError("no tensor given")
+    return dev
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(dev: torch.device) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def status_word(dev: torch.device) -> torch.Tensor:
+    """Per-device int32 status word handed to the GEMM; stays 0 unless a kernel gave up a wait."""
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx not in _status_words:
+        _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return _status_words[idx]
+
+
+def check_status(dev: Optional[torch.device] = None) -> None:
+    """Synchronises and raises if any GEMM on ``dev`` reported a timed-out wait."""
+    dev = dev if dev is not None else torch.device("cuda", torch.cuda.current_device())
+    word = status_word(dev)
+    val = int(word.item())
+    if val != 0:
+        word.zero_()
+        raise RuntimeError(f"qlin_gemm reported device status {val} (a bounded wait ran out)")
+
+
+def _f32(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    if t is None:
+        return None
+    t = t.reshape(-1)
+    if t.dtype != torch.float32:
+        t = t.float()
+    return t.contiguous()
+
+
+def _pad_k(t: torch.Tensor) -> torch.Tensor:
+    """Returns a K-contiguous 2-D view/copy whose row stride and base are 16-byte aligned."""
+    es = t.element_size()
+    if t.stride(1) == 1 and (t.stride(0) * es) % 16 == 0 and t.data_ptr() % 16 == 0 and t.stride(0) >= t.shape[1]:
+        return t
+    rows, k = t.shape
+    kp = (k * es + 15) // 16 * 16 // es
+    buf = torch.zeros((rows, kp), dtype=t.dtype, device=t.device)
+    buf[:, :k] = t
+    return buf[:, :k]
+
+
+# --------------------------------------------------------------------------------------------------
+# GEMM
+# --------------------------------------------------------------------------------------------------
+def gemm(
+    a: torch.Tensor,
+    b_nk: torch.Tensor,
+    *,
+    c: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    chunk_k: int = 0,
+    trun_bits: int = 0,
+    max_acc_bits: int = 32,
+    trunc_then_acc: bool = True,
+    clamp_dl16: bool = False,
+    epilogue: int = L.EPI_RAW,
+    row_scale: Optional[torch.Tensor] = None,
+    col_scale: Optional[torch.Tensor] = None,
+    bias: Optional[torch.Tensor] = None,
+    scale_round: Optional[torch.dtype] = None,
+    mid_round: Optional[torch.dtype] = None,
+    acc_round: Optional[torch.dtype] = None,
+    out_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """``D[M,N] = epilogue(C + sum_chunks f(A_c @ B_c^T))`` with A ``[M,K]`` and B ``[N,K]`` (both
+    K-contiguous, int8 or float8_e4m3fn).  See ``qlin_gemm`` in include/qlin_b200.h for the
+    chunk and epilogue semantics (tl_matmul_chunk_truncate, fms_mo/custom_ext_kernels/triton_kernels.py:468)."""
+    dev = _require_cuda(a, b_nk, c, out, row_scale, col_scale, bias)
+    if a.dim() != 2 or b_nk.dim() != 2 or a.shape[1] != b_nk.shape[1]:
+        raise RuntimeError(f"incompatible shapes {tuple(a.shape)} x {tuple(b_nk.shape)}^T")
+    if a.dtype != b_nk.dtype or a.dtype not in (torch.int8, torch.float8_e4m3fn):
+        raise RuntimeError(f"operands must both be int8 or float8_e4m3fn, got {a.dtype} and {b_nk.dtype}")
+    f8 = a.dtype == torch.float8_e4m3fn
+    M, K = a.shape
+    N = b_nk.shape[0]
+    raw_dtype = torch.float32 if f8 else torch.int32
+    if epilogue == L.EPI_RAW:
+        out_dtype = raw_dtype
+    elif out_dtype is None:
+        out_dtype = torch.float32
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=dev)
+    elif out.dtype != out_dtype or out.shape != (M, N) or out.stride(1) != 1:
+        raise RuntimeError("out has the wrong dtype, shape or layout")
+    if M == 0 or N == 0:
+        return out
+    if K == 0:
+        raise RuntimeError("K must be positive")
+    a = _pad_k(a)
+    b_nk = _pad_k(b_nk)
+    if c is not None:
+        if c.dtype != raw_dtype or c.shape != (M, N):
+            raise RuntimeError("c must be an [M,N] tensor of the accumulator dtype")
+        if c.stride(1) != 1:
+            c = c.contiguous()
+    rs, cs, bs = _f32(row_scale), _f32(col_scale), _f32(bias)
+    if rs is not None and rs.numel() not in (1, M):
+        raise RuntimeError("row_scale must have 1 or M elements")
+    if cs is not None and cs.numel() not in (1, N):
+        raise RuntimeError("col_scale must have 1 or N elements")
+    if bs is not None and bs.numel() != N:
+        raise RuntimeError("bias must have N elements")
+    args = L.GemmArgs(
+        a=_ptr(a), b=_ptr(b_nk), c=_ptr(c), d=_ptr(out),
+        row_scale=_ptr(rs), col_scale=_ptr(cs), bias=_ptr(bs), status=_ptr(status_word(dev)),
+        lda=a.stride(0), ldb=b_nk.stride(0), ldc=(c.stride(0) if c is not None else 0), ldd=out.stride(0),
+        M=M, N=N, K=K, kind=_DT[a.dtype],
+        chunk_k=int(chunk_k), trun_bits=int(trun_bits), max_acc_bits=int(max_acc_bits),
+        trunc_then_acc=int(bool(trunc_then_acc)), clamp_dl16=int(bool(clamp_dl16)), epilogue=int(epilogue),
+        row_scale_stride=(0 if rs is None or rs.numel() == 1 else 1),
+        col_scale_stride=(0 if cs is None or cs.numel() == 1 else 1),
+        scale_round=_ROUND[scale_round], mid_round=_ROUND[mid_round], acc_round=_ROUND[acc_round],
+        out_dtype=_DT[out_dtype],
+    )  # fmt: skip
+    with torch.cuda.device(dev):
+        L.check(L.load().qlin_gemm(C.byref(args), _stream(dev)), "qlin_gemm")
+    return out
+
+
+def _as_nk(m2: torch.Tensor) -> torch.Tensor:
+    """The reference passes B as a ``[k,n]`` tensor, normally the ``.t()`` view of a row-major
+    ``[n,k]`` weight.  Returns the ``[n,k]`` K-contiguous operand, copying only when ``m2`` is not
+    such a view."""
+    nk = m2.t()
+    return nk if nk.stride(1) == 1 else nk.contiguous()
+
+
+def imatmul(m1: torch.Tensor, m2: torch.Tensor) -> torch.Tensor:
+    """``fms_mo::imatmul`` contract (fms_mo/custom_ext_kernels/utils.py:690-720): int8 ``m1 [..,k]``
+    times int8 ``m2 [k,n]`` -> int32 ``[..,n]``."""
+    lead = m1.shape[:-1]
+    out = gemm(m1.reshape(-1, m1.shape[-1]), _as_nk(m2))
+    return out.reshape(*lead, m2.shape[1])
+
+
+_MIN_CHUNK_8BIT = 32
+
+
+def tl_matmul_chunk_truncate(
+    a,
+    b,
+    c=None,
+    activation="",
+    chunk_trun_bits=0,
+    chunk_size=16,
+    max_acc_bits=32,
+    truncate_then_accumulate=True,
+    cast_output_to_input_dtype=None,
+    clamp_acc_to_dl16=False,
+):
+    """Drop-in for ``tl_matmul_chunk_truncate`` (fms_mo/custom_ext_kernels/triton_kernels.py:468-621)
+    for int8 and float8_e4m3fn operands: ``a [m,k]`` contiguous, ``b [k,n]``; returns int32 for int8
+    and float32 for fp8 (the reference does not cast 8-bit results back).  ``c``, if given, is the
+    initial accumulator.  The chunk size is normalised exactly as the reference does: a power of
+    two is raised to at least 32, anything else becomes 32; ``chunk_size == 8`` is emulated there by
+    zero-interleaving both operands and is reproduced here the same way."""
+    assert a.shape[1] == b.shape[0], "Incompatible dimensions"
+    assert a.is_contiguous(), "Matrix A must be contiguous"
+    assert a.dtype == b.dtype, "Input dtypes inconsistent"
+    if a.dtype not in (torch.int8, torch.float8_e4m3fn):
+        raise RuntimeError(
+            f"tl_matmul_chunk_truncate on B200 takes int8 or float8_e4m3fn operands, got {a.dtype}"
+        )
+    if activation not in ("", None):
+        raise RuntimeError(f"activation {activation!r} is not supported")
+    if cast_output_to_input_dtype:
+        raise RuntimeError("8-bit results are returned in the accumulator dtype")
+    f8 = a.dtype == torch.float8_e4m3fn
+    if chunk_size == 8:
+        ratio = _MIN_CHUNK_8BIT // chunk_size
+        a_p = torch.zeros(a.shape[0], a.shape[1] * ratio, dtype=a.dtype, device=a.device)
+        a_p.view(torch.int8)[:, ::ratio] = a.view(torch.int8)
+        b_nk = _as_nk(b)
+        b_p = torch.zeros(b_nk.shape[0], b_nk.shape[1] * ratio, dtype=b.dtype, device=b.device)
+        b_p.view(torch.int8)[:, ::ratio] = b_nk.view(torch.int8)
+        a, b_nk = a_p, b_p
+        chunk_size = _MIN_CHUNK_8BIT
+    else:
+        b_nk = _as_nk(b)
+        pow2 = chunk_size > 0 and (chunk_size & (chunk_size - 1)) == 0
+        chunk_size = max(chunk_size, _MIN_CHUNK_8BIT) if pow2 else _MIN_CHUNK_8BIT
+    if f8:
+        assert chunk_trun_bits < 23, "FP32 accumulator only has 23 mantissa bits"
+        if clamp_acc_to_dl16:
+            chunk_trun_bits = 14
+    acc_dtype = torch.float32 if f8 else torch.int32
+    c_in = None
+    if c is not None:
+        assert c.shape[0] == a.shape[0] and c.shape[1] == b.shape[1], "C shape is inconsistent with A B."
+        c_in = c.to(acc_dtype)
+    return gemm(
+        a,
+        b_nk,
+        c=c_in,
+        chunk_k=chunk_size,
+        trun_bits=chunk_trun_bits,
+        max_acc_bits=max_acc_bits,
+        trunc_then_acc=truncate_then_accumulate,
+        clamp_dl16=bool(clamp_acc_to_dl16) and f8,
+    )
+
+
+# --------------------------------------------------------------------------------------------------
+# Row-wise quantisation
+# --------------------------------------------------------------------------------------------------
+def act_quant(
+    x: torch.Tensor,
+    *,
+    mode: int = L.Q_I8_DYN,
+    smooth: Optional[torch.Tensor] = None,
+    smooth_mul: bool = False,
+    native_chain: bool = False,
+    clamp_codes: bool = False,
+    levels: int = 127,
+    want_codes: bool = True,
+    want_dq: bool = False,
+    scale_in: Optional[torch.Tensor] = None,
+    dl8_flush: bool = False,
+    scale0: float = 1.0,
+    zp0: float = 0.0,
+    lo: float = 0.0,
+    hi: float = 0.0,
+    shift: float = 0.0,
+    add2: float = 0.0,
+) -> Tuple[Optional[torch.Tensor], torch.Tensor, Optional[torch.Tensor]]:
+    """Row-wise 8-bit quantisation of a 2-D tensor; returns ``(codes, scale[rows], dq)``.
+    See ``qlin_act_quant`` in include/qlin_b200.h for the modes."""
+    dev = _require_cuda(x, smooth, scale_in)
+    if x.dim() != 2:
+        raise RuntimeError("act_quant takes a 2-D tensor")
+    if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise RuntimeError(f"unsupported activation dtype {x.dtype}")
+    if x.stride(1) != 1:
+        x = x.contiguous()
+    rows, cols = x.shape
+    code_dtype = torch.float8_e4m3fn if mode == L.Q_F8_DYN else torch.int8
+    codes = torch.empty((rows, cols), dtype=code_dtype, device=dev) if want_codes else None
+    dq = torch.empty((rows, cols), dtype=x.dtype, device=dev) if want_dq else None
+    scale = torch.empty((rows,), dtype=torch.float32, device=dev)
+    sm = _f32(smooth)
+    if sm is not None and sm.numel() != cols:
+        raise RuntimeError("smooth must have one entry per column")
+    si = _f32(scale_in)
+    if rows == 0 or cols == 0:
+        return codes, scale, dq
+    args = L.QuantArgs(
+        x=_ptr(x), smooth=_ptr(sm), scale_in=_ptr(si), codes=_ptr(codes), scale_out=_ptr(scale), dq_out=_ptr(dq),
+        status=None, ldx=x.stride(0), ldq=cols, lddq=cols, rows=rows, cols=cols, x_dtype=_DT[x.dtype], mode=mode,
+        native_chain=int(bool(native_chain)), smooth_mul=int(bool(smooth_mul)), clamp_codes=int(bool(clamp_codes)),
+        qmax_levels=int(levels), dl8_flush=int(bool(dl8_flush)),
+        scale_in_stride=(0 if si is None or si.numel() == 1 else 1),
+        scale0=scale0, zp0=zp0, lo=lo, hi=hi, shift=shift, add2=add2,
+    )  # fmt: skip
+    with torch.cuda.device(dev):
+        L.check(L.load().qlin_act_quant(C.byref(args), _stream(dev)), "qlin_act_quant")
+    return codes, scale, dq
+
+
+def weight_fq_perch(
+    w: torch.Tensor,
+    *,
+    num_bits: int = 8,
+    mode: int = L.W_SAWB,
+    clip: Optional[torch.Tensor] = None,
+    smooth: Optional[torch.Tensor] = None,
+    native_mul: bool = True,
+    want_dq: bool = True,
+    want_codes: bool = False,
+    c0: float = 0.0,
+    c1: float = 0.0,
+) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor], torch.Tensor]:
+    """Per-output-channel symmetric fake quantisation of ``w [rows, cols]``; returns
+    ``(dq, codes, clip[rows])``.  See ``qlin_weight_fq_perch`` in include/qlin_b200.h."""
+    dev = _require_cuda(w, clip, smooth)
+    if w.dim() != 2:
+        w = w.reshape(w.shape[0], -1)
+    if w.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise RuntimeError(f"unsupported weight dtype {w.dtype}")
+    if w.stride(1) != 1:
+        w = w.contiguous()
+    rows, cols = w.shape
+    if mode == L.W_GIVEN:
+        if clip is None or clip.numel() != rows:
+            raise RuntimeError("W_GIVEN needs one clip value per row")
+        clip_io = _f32(clip).clone()
+    else:
+        clip_io = torch.empty((rows,), dtype=torch.float32, device=dev)
+    dq = torch.empty((rows, cols), dtype=w.dtype, device=dev) if want_dq else None
+    codes = torch.empty((rows, cols), dtype=torch.int8, device=dev) if want_codes else None
+    sm = _f32(smooth)
+    if rows == 0 or cols == 0:
+        return dq, codes, clip_io
+    args = L.WfqArgs(
+        w=_ptr(w), smooth=_ptr(sm), dq_out=_ptr(dq), codes=_ptr(codes), clip_io=_ptr(clip_io),
+        ldw=w.stride(0), ldo=cols, ldq=cols, rows=rows, cols=cols, dtype=_DT[w.dtype], num_bits=int(num_bits),
+        mode=int(mode), native_mul=int(bool(native_mul)), c0=float(c0), c1=float(c1),
+    )  # fmt: skip
+    with torch.cuda.device(dev):
+        L.check(L.load().qlin_weight_fq_perch(C.byref(args), _stream(dev)), "qlin_weight_fq_perch")
+    return dq, codes, clip_io
+
+
+# --------------------------------------------------------------------------------------------------
+# PACT+ two-sided fake quantisation
+# --------------------------------------------------------------------------------------------------
+def _clip_f32(t: torch.Tensor, dev: torch.device) -> torch.Tensor:
+    t = t.detach().reshape(-1)[:1]
+    if t.dtype != torch.float32 or t.device != dev:
+        t = t.to(device=dev, dtype=torch.float32)
+    return t.contiguous()
+
+
+def pact2_fwd(x: torch.Tensor, clip_val: torch.Tensor, clip_valn: torch.Tensor, num_bits: int, align_zero: bool) -> torch.Tensor:
+    """PACTplus2STE.forward with dequantize=True (fms_mo/quant/quantizers.py:1949-2055)."""
+    dev = _require_cuda(x)
+    xc = x.contiguous()
+    out = torch.empty_like(xc)
+    cv, cvn = _clip_f32(clip_val, dev), _clip_f32(clip_valn, dev)
+    args = L.Pact2Args(
+        x=_ptr(xc), grad_out=None, out=_ptr(out), clip_val=_ptr(cv), clip_valn=_ptr(cvn), grad_clip=None,
+        workspace=None, numel=xc.numel(), dtype=_DT[xc.dtype], num_bits=int(num_bits), align_zero=int(bool(align_zero)),
+    )  # fmt: skip
+    with torch.cuda.device(dev):
+        L.check(L.load().qlin_pact2_fwd(C.byref(args), _stream(dev)), "qlin_pact2_fwd")
+    return out
+
+
+def pact2_bwd(
+    x: torch.Tensor, grad_out: torch.Tensor, clip_val: torch.Tensor, clip_valn: torch.Tensor, num_bits: int, align_zero: bool
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """PACTplus2STE.backward (fms_mo/quant/quantizers.py:2058-2102): returns ``(grad_x, [grad_cv, grad_cvn])``."""
+    dev = _require_cuda(x, grad_out)
+    xc = x.contiguous()
+    gc = grad_out.contiguous()
+    if gc.dtype != xc.dtype:
+        gc = gc.to(xc.dtype)
+    gx = torch.empty_like(xc)
+    cv, cvn = _clip_f32(clip_val, dev), _clip_f32(clip_valn, dev)
+    lib = L.load()
+    ws = torch.empty((max(1, lib.qlin_pact2_bwd_workspace_bytes(xc.numel()) // 4),), dtype=torch.float32, device=dev)
+    grads = torch.empty((2,), dtype=torch.float32, device=dev)
+    args = L.Pact2Args(
+        x=_ptr(xc), grad_out=_ptr(gc), out=_ptr(gx), clip_val=_ptr(cv), clip_valn=_ptr(cvn), grad_clip=_ptr(grads),
+        workspace=_ptr(ws), numel=xc.numel(), dtype=_DT[xc.dtype], num_bits=int(num_bits),
+        align_zero=int(bool(align_zero)),
+    )  # fmt: skip
+    with torch.cuda.device(dev):
+        L.check(lib.qlin_pact2_bwd(C.byref(args), _stream(dev)), "qlin_pact2_bwd")
+    return gx, grads

@@ -1,0 +1,261 @@
+/*
+ * qlin_b200.h -- C ABI of libqlin_b200.so: the quantized-Linear hot path of
+ * fms-model-optimizer, written for NVIDIA B200 (sm_100a).
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless a comment says otherwise.
+ *   - `stream` is a cudaStream_t passed as void*; NULL is the legacy default stream.
+ *   - The library never allocates, frees or keeps device memory; the caller owns all
+ *     inputs, outputs and workspaces.  Calls are asynchronous on `stream`.
+ *   - Return value: 0 (QLIN_OK) or a negative qlin_status.  The text of the last error
+ *     on the calling host thread is available from qlin_last_error_string().
+ *   - Kernels never trap.  A kernel that gives up a bounded wait writes a negative
+ *     qlin_status to `*status` (when the caller passed one) and returns.
+ *
+ * Each entry point names the fms-model-optimizer interface it stands in for
+ * (paths relative to that project's root).
+ */
+#ifndef QLIN_B200_H
+#define QLIN_B200_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QLIN_VERSION 100
+
+typedef enum qlin_status {
+  QLIN_OK = 0,
+  QLIN_ERR_BAD_SHAPE = -1,
+  QLIN_ERR_BAD_ALIGN = -2,
+  QLIN_ERR_BAD_DTYPE = -3,
+  QLIN_ERR_UNSUPPORTED = -4,
+  QLIN_ERR_LAUNCH = -5,
+  QLIN_ERR_TIMEOUT = -6,
+  QLIN_ERR_NULL = -7,
+  QLIN_ERR_DEVICE = -8,
+  QLIN_ERR_TOO_LARGE = -9
+} qlin_status;
+
+typedef enum qlin_dtype {
+  QLIN_DT_NONE = 0,
+  QLIN_DT_I8 = 1,
+  QLIN_DT_U8 = 2,
+  QLIN_DT_I32 = 3,
+  QLIN_DT_F32 = 4,
+  QLIN_DT_F16 = 5,
+  QLIN_DT_BF16 = 6,
+  QLIN_DT_F8E4M3 = 7
+} qlin_dtype;
+
+/* ------------------------------------------------------------------------------------------------
+ * Library / device queries
+ * ---------------------------------------------------------------------------------------------- */
+int qlin_version(void);
+const char* qlin_last_error_string(void);
+/* 1 when `device` has compute capability 10.x (tcgen05 + TMA), 0 otherwise, <0 on error. */
+int qlin_device_supported(int device);
+
+/* ------------------------------------------------------------------------------------------------
+ * qlin_gemm -- 8-bit tensor-core GEMM  D[M,N] = epilogue( C + sum_chunks f(A_chunk . B_chunk^T) )
+ *
+ * Replaces: tl_matmul_chunk_truncate / imatmul_kernel / matmul_kernel(_DABC)
+ *           (fms_mo/custom_ext_kernels/triton_kernels.py:468, :212, :97, :306),
+ *           cutlass_mm.run (fms_mo/custom_ext_kernels/cutlass_i8i32gemm.cpp:34,
+ *           cutlass_i8i32gemm.cu:67-120), cublas_gemm::gemm_nt_i8i32
+ *           (fms_mo/custom_ext_kernels/ext_kernel_cublas.cpp:103-195, :295) and the dequantise
+ *           chain of QLinearINT8Deploy.iaddmm_int (fms_mo/modules/linear.py:1115-1188),
+ *           fms_mo::iaddmm / q_iaddmm_dq (fms_mo/custom_ext_kernels/utils.py:729-790) and
+ *           LinearFuncFPxFwdBwd.forward (fms_mo/modules/linear.py:1958-1973).
+ *
+ * Operands: A is [M,K], B is [N,K], both with K contiguous ("NT"; B is the `.t()` view the
+ * reference passes as its [k,n] operand).  kind = QLIN_DT_I8 (int32 accumulation) or
+ * QLIN_DT_F8E4M3 (fp32 accumulation).  a, b must be 16-byte aligned, lda/ldb multiples of 16.
+ *
+ * Chunked accumulation (K1/K2 semantics): K is cut into chunks of `chunk_k` elements (a multiple
+ * of 32; <=0 means one chunk).  Per chunk p = A_c . B_c^T; integer kinds: clamp p to
+ * max_acc_bits (if < 32), then p = ((p + (1 << (t-1))) >> t) << t with t = trun_bits;
+ * float kinds: bits(p) = (bits(p) + (1 << (t-1))) & ~((1 << t) - 1), then the optional DL16
+ * clamp/flush.  trunc_then_acc != 0 applies f to each chunk product and adds it to the
+ * running sum; == 0 applies f to (running sum + product).  The K tail is zero-filled.
+ *
+ * Epilogue, per element with acc the final accumulator (converted to fp32 for the scaled
+ * modes), rs = row_scale[m * row_scale_stride] (1 if NULL), cs likewise:
+ *   QLIN_EPI_RAW        d = acc                             (out_dtype I32 for I8, F32 for F8)
+ *   QLIN_EPI_SCALE_PROD s = round(rs * cs, scale_round); y = acc * s; y = y + bias[n];
+ *                       y = round(y, acc_round); d = cast(y, out_dtype)
+ *   QLIN_EPI_SCALE_SEQ  y = (acc * rs) * cs; y = round(y, mid_round); y = y + bias[n];
+ *                       y = round(y, acc_round); d = cast(y, out_dtype)
+ * round(.., QLIN_DT_NONE/F32) is the identity; F16 / BF16 round to nearest even and widen back.
+ * Every multiply and add is a separately rounded fp32 operation (no FMA contraction), which is
+ * what the reference's eager tensor expressions compute.
+ * ---------------------------------------------------------------------------------------------- */
+typedef enum qlin_epilogue {
+  QLIN_EPI_RAW = 0,
+  QLIN_EPI_SCALE_PROD = 1,
+  QLIN_EPI_SCALE_SEQ = 2
+} qlin_epilogue;
+
+typedef struct qlin_gemm_args {
+  const void* a;
+  const void* b;
+  const void* c;          /* optional [M,N] initial accumulator (int32 / fp32); may alias d */
+  void* d;
+  const float* row_scale; /* optional */
+  const float* col_scale; /* optional */
+  const float* bias;      /* optional [N] */
+  int32_t* status;        /* optional device status word, written only on failure */
+  int64_t lda, ldb, ldc, ldd; /* leading dimensions in elements */
+  int32_t M, N, K;
+  int32_t kind;             /* qlin_dtype of A and B */
+  int32_t chunk_k;
+  int32_t trun_bits;
+  int32_t max_acc_bits;     /* 32 = no clamp (integer kinds only) */
+  int32_t trunc_then_acc;
+  int32_t clamp_dl16;       /* float kinds only */
+  int32_t epilogue;         /* qlin_epilogue */
+  int32_t row_scale_stride; /* 0 = one scalar, 1 = per row */
+  int32_t col_scale_stride; /* 0 = one scalar, 1 = per column */
+  int32_t scale_round;      /* qlin_dtype */
+  int32_t mid_round;        /* qlin_dtype */
+  int32_t acc_round;        /* qlin_dtype */
+  int32_t out_dtype;        /* qlin_dtype */
+} qlin_gemm_args;
+
+int qlin_gemm(const qlin_gemm_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * qlin_act_quant -- row-wise (per-token / per-channel) dynamic 8-bit quantisation in one pass.
+ *
+ * Replaces: `x / smoothq_scale` + QLinearINT8Deploy.qa_dynamic_max_qfunc
+ *           (fms_mo/modules/linear.py:1331-1334, :1085-1100), QMaxDynamic.forward / PerTokenMax
+ *           (fms_mo/quant/quantizers.py:3531-3534, :3479-3501), the static quantisers
+ *           qa_raw_qfunc / qa_fmo_mo_qfunc (fms_mo/modules/linear.py:1061-1083), fms_mo::q_per_t_sym
+ *           (fms_mo/custom_ext_kernels/utils.py:792-802), the FP8 scaling of
+ *           LinearFuncFPxFwdBwd.forward (fms_mo/modules/linear.py:1935-1953) and the weight
+ *           quantisation of QLinearINT8Deploy.from_fms_mo (fms_mo/modules/linear.py:859-871).
+ *
+ * x is [rows, cols] with cols contiguous; `smooth` (optional, [cols] fp32) divides
+ * (smooth_mul == 0) or multiplies (smooth_mul != 0) every row first.
+ *   QLIN_Q_I8_DYN     amax per row; scale = max(amax, 1e-5) / qmax_levels; code = rint(v / scale)
+ *                     cast to int8 with two's-complement wrap (the reference does not clamp) or
+ *                     clamped to +-qmax_levels when clamp_codes != 0.
+ *   QLIN_Q_I8_STATIC  code = clamp(rint(((v / scale0 + zp0) - shift) + add2), -128, 127)
+ *                     (qa_raw_qfunc: zp0 = input_zp, shift = 128, add2 = useSymAct)
+ *   QLIN_Q_I8_STATIC_CLAMP_FIRST
+ *                     code = rint(clamp(v, lo, hi) / scale0 - zp0) - shift, wrapped to int8
+ *                     (qa_fmo_mo_qfunc: scale0 = quant_stepsize, zp0 = quant_zero_point)
+ *   QLIN_Q_F8_DYN     scale = max(amax / 448, 1e-5); code = e4m3(v / scale), optional DL8 flush
+ *   QLIN_Q_I8_GIVEN_SCALE
+ *                     scale = scale_in[row * scale_in_stride]; code = rint(v / scale) + zp0,
+ *                     wrapped to int8 or clamped to +-qmax_levels
+ * native_chain != 0 rounds every intermediate to the dtype of x (what the reference computes when
+ * it is handed bf16 / fp16 tensors); 0 evaluates the same formulas in fp32.
+ * Outputs: codes [rows, cols] (1 byte each), scale_out [rows] fp32 (optional),
+ * dq_out (optional, dtype of x): the fake-quantised value code * scale, QMaxDynamic's output.
+ * ---------------------------------------------------------------------------------------------- */
+typedef enum qlin_quant_mode {
+  QLIN_Q_I8_DYN = 0,
+  QLIN_Q_I8_STATIC = 1,
+  QLIN_Q_I8_STATIC_CLAMP_FIRST = 2,
+  QLIN_Q_F8_DYN = 3,
+  QLIN_Q_I8_GIVEN_SCALE = 4
+} qlin_quant_mode;
+
+typedef struct qlin_quant_args {
+  const void* x;
+  const float* smooth;    /* optional [cols] */
+  const float* scale_in;  /* QLIN_Q_I8_GIVEN_SCALE: [rows] */
+  void* codes;            /* optional [rows, cols] int8 / e4m3 */
+  float* scale_out;       /* optional [rows] */
+  void* dq_out;           /* optional [rows, cols], dtype of x */
+  int32_t* status;
+  int64_t ldx, ldq, lddq; /* leading dimensions in elements */
+  int32_t rows, cols;
+  int32_t x_dtype;        /* F32 / F16 / BF16 */
+  int32_t mode;           /* qlin_quant_mode */
+  int32_t native_chain;
+  int32_t smooth_mul;
+  int32_t clamp_codes;
+  int32_t qmax_levels;    /* 127 for int8 */
+  int32_t dl8_flush;      /* QLIN_Q_F8_DYN: flush |code| < 0.0087890625 to 0 */
+  int32_t scale_in_stride;/* QLIN_Q_I8_GIVEN_SCALE: 0 = one scalar, 1 = per row */
+  float scale0, zp0, lo, hi, shift, add2; /* static modes */
+} qlin_quant_args;
+
+int qlin_act_quant(const qlin_quant_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * qlin_pact2_fwd / qlin_pact2_bwd -- PACT+ two-sided fake quantisation (QAT activations).
+ *
+ * Replaces: PACT2.forward -> PACTplus2STE.forward / .backward
+ *           (fms_mo/quant/quantizers.py:1465-1476, :1949-2102).
+ * fwd:  y = clamp(x, cvn, cv); q = rint(y / step - zp); out = (q + zp) * step
+ *       with n = 2^bits - 1, scale = n / (cv - cvn), step = 1 / scale, zp = cvn * scale,
+ *       zp = rint(zp) when align_zero.  cv / cvn are read from device memory ([1] fp32).
+ * bwd:  z = (x - cvn) / step; delz = (z - rint(z)) / n;
+ *       grad_x = g where cvn < x < cv else 0;
+ *       grad_cv  = sum( x >= cv ? g : (x <= cvn ? 0 : -g * delz) );
+ *       grad_cvn = sum( x <= cvn ? g : (x >= cv ? 0 :  g * delz) ).
+ *       The two sums are reduced in a fixed order (run-to-run deterministic) through a
+ *       caller-provided workspace of qlin_pact2_bwd_workspace_bytes(numel) bytes.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct qlin_pact2_args {
+  const void* x;
+  const void* grad_out;   /* bwd only */
+  void* out;              /* fwd: y ; bwd: grad_x */
+  const float* clip_val;  /* [1] */
+  const float* clip_valn; /* [1] */
+  float* grad_clip;       /* bwd: [2] = {grad_cv, grad_cvn} */
+  void* workspace;        /* bwd */
+  int64_t numel;
+  int32_t dtype;          /* F32 / F16 / BF16 (x, out, grad_out) */
+  int32_t num_bits;
+  int32_t align_zero;
+} qlin_pact2_args;
+
+int qlin_pact2_fwd(const qlin_pact2_args* args, void* stream);
+int qlin_pact2_bwd(const qlin_pact2_args* args, void* stream);
+size_t qlin_pact2_bwd_workspace_bytes(int64_t numel);
+
+/* ------------------------------------------------------------------------------------------------
+ * qlin_weight_fq_perch -- per-output-channel symmetric weight fake quantisation with the
+ * clip value computed in the same pass.
+ *
+ * Replaces: SAWB.forward -> SAWBPlusZeroPerChSTE.forward + sawb_params_code(perCh=True)
+ *           (fms_mo/quant/quantizers.py:434-446, :503-567, :633-655) and
+ *           Qmax.forward -> QmaxPerChSTE.forward (fms_mo/quant/quantizers.py:3048-3141, :3190-3220).
+ * w is [rows, cols] (one row per output channel), optionally multiplied by smooth[cols] first.
+ *   QLIN_W_SAWB  clip = c1 * mean|w| + c0 * sqrt(mean w^2)   (c0, c1 given by the caller)
+ *   QLIN_W_MAX   clip = max|w|
+ *   QLIN_W_GIVEN clip read from clip_io
+ * scale = clip * 2 / (2^bits - 2); q = clamp(nearbyint(w / scale), -(2^(bits-1) - 1), +..);
+ * out = q * scale (dq_out, dtype of w) and / or q as int8 (codes).  clip_io [rows] fp32 is
+ * written for SAWB / MAX and read for GIVEN.
+ * ---------------------------------------------------------------------------------------------- */
+typedef enum qlin_wq_mode { QLIN_W_SAWB = 0, QLIN_W_MAX = 1, QLIN_W_GIVEN = 2 } qlin_wq_mode;
+
+typedef struct qlin_wfq_args {
+  const void* w;
+  const float* smooth;  /* optional [cols] */
+  void* dq_out;         /* optional [rows, cols] */
+  void* codes;          /* optional [rows, cols] int8 */
+  float* clip_io;       /* [rows] */
+  int64_t ldw, ldo, ldq;
+  int32_t rows, cols;
+  int32_t dtype;        /* F32 / F16 / BF16 */
+  int32_t num_bits;
+  int32_t mode;         /* qlin_wq_mode */
+  int32_t native_mul;   /* round w * smooth to dtype before use (reference multiplies in the weight dtype) */
+  float c0, c1;
+} qlin_wfq_args;
+
+int qlin_weight_fq_perch(const qlin_wfq_args* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QLIN_B200_H */
