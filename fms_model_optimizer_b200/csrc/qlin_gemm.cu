@@ -34,6 +34,19 @@ constexpr int kMmaWarp = 9;
 constexpr int kThreads = 320;
 constexpr int kGroupM = 16;       // m-blocks per raster group
 constexpr int kTmemCols = 512;
+constexpr int kStageOutBytes = 4096;  // per epilogue warp: 32 rows x 128 bytes of output
+
+struct Aux {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tfull[4];
+  uint64_t tempty[4];
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort_flag;
+  float cs[256];
+  float bias[256];
+};
 
 template <bool CHUNKED>
 struct Cfg {
@@ -44,9 +57,11 @@ struct Cfg {
   static constexpr int B_BYTES = BN * kBK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int COLS_PER_WARP = BN / 2;  // each epilogue warp: 32 rows x BN/2 columns
-  static constexpr int AUX_BYTES = 4096;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + AUX_BYTES + 1024;
+  static constexpr int OUT_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int AUX_OFFSET = OUT_OFFSET + kEpiWarps * kStageOutBytes;
+  static constexpr int SMEM_BYTES = AUX_OFFSET + static_cast<int>(sizeof(Aux));
 };
+static_assert(Cfg<false>::SMEM_BYTES <= 232448 && Cfg<true>::SMEM_BYTES <= 232448, "shared memory budget");
 
 struct GemmParams {
   const void* c;
@@ -63,19 +78,6 @@ struct GemmParams {
   int32_t epilogue, rs_stride, cs_stride, scale_round, mid_round, acc_round, out_dtype;
   int32_t num_m, num_n;
 };
-
-struct Aux {
-  uint64_t full[8];
-  uint64_t empty[8];
-  uint64_t tfull[4];
-  uint64_t tempty[4];
-  uint64_t drain;
-  uint32_t tmem_base;
-  int abort_flag;
-  float cs[256];
-  float bias[256];
-};
-static_assert(sizeof(Aux) <= 4096, "aux block too large");
 
 __device__ __forceinline__ float round_to(float y, int dt) {
   if (dt == QLIN_DT_F16) return __half2float(__float2half_rn(y));
@@ -126,82 +128,84 @@ __device__ __forceinline__ void tile_coords(int t, int num_m, int num_n, int& mb
   nb = r / gsz;
 }
 
-// Converts, scales and stores NC consecutive columns of one output row held by this thread.
+// Accumulator -> output value (fp32, already rounded the way the epilogue mode asks).
+template <bool F8>
+__device__ __forceinline__ float dequant_one(const GemmParams& p, uint32_t v, float rs, float cs, float bias,
+                                             bool prod, bool has_bias) {
+  const float a = F8 ? __uint_as_float(v) : __int2float_rn(static_cast<int32_t>(v));
+  float t;
+  if (prod) {
+    const float s = round_to(__fmul_rn(rs, cs), p.scale_round);
+    t = __fmul_rn(a, s);
+  } else {
+    t = round_to(__fmul_rn(__fmul_rn(a, rs), cs), p.mid_round);
+  }
+  if (has_bias) t = __fadd_rn(t, bias);
+  return round_to(t, p.acc_round);
+}
+
+__device__ __forceinline__ uint32_t pack16(const GemmParams& p, float lo, float hi) {
+  if (p.out_dtype == QLIN_DT_BF16) {
+    return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) |
+           (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);
+  }
+  return static_cast<uint32_t>(__half_as_ushort(__float2half_rn(lo))) |
+         (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(hi))) << 16);
+}
+
+// Direct (uncoalesced, bounds-checked) store of NC consecutive columns of one row held by this
+// thread: the path for ragged right edges and for outputs that rule out 16-byte vectors.
 template <bool F8, int NC>
-__device__ __forceinline__ void store_row(const GemmParams& p, const uint32_t (&v)[NC], int row, int col0,
-                                          const float* s_cs, const float* s_bias, int s_off, float rs,
-                                          bool vec_ok) {
+__device__ __forceinline__ void store_row_direct(const GemmParams& p, const uint32_t (&v)[NC], int row, int col0,
+                                                 const float* s_cs, const float* s_bias, int s_off, float rs) {
   if (row >= p.M) return;
   const int ncol = min(NC, p.N - col0);
   if (ncol <= 0) return;
-  if (p.epilogue == QLIN_EPI_RAW) {
-    uint32_t* out = reinterpret_cast<uint32_t*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0;
-    if (vec_ok && ncol == NC) {
-#pragma unroll
-      for (int j = 0; j < NC; j += 4) {
-        *reinterpret_cast<uint4*>(out + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < NC; ++j)
-        if (j < ncol) out[j] = v[j];
-    }
-    return;
-  }
-  float y[NC];
   const bool prod = p.epilogue == QLIN_EPI_SCALE_PROD;
   const bool has_bias = p.bias != nullptr;
+  const int64_t off = static_cast<int64_t>(row) * p.ldd + col0;
 #pragma unroll
   for (int j = 0; j < NC; ++j) {
-    const float a = F8 ? __uint_as_float(v[j]) : __int2float_rn(static_cast<int32_t>(v[j]));
-    const float cs = s_cs[s_off + j];
-    float t;
-    if (prod) {
-      float s = round_to(__fmul_rn(rs, cs), p.scale_round);
-      t = __fmul_rn(a, s);
-    } else {
-      t = round_to(__fmul_rn(__fmul_rn(a, rs), cs), p.mid_round);
-    }
-    if (has_bias) t = __fadd_rn(t, s_bias[s_off + j]);
-    y[j] = round_to(t, p.acc_round);
-  }
-  if (p.out_dtype == QLIN_DT_F32) {
-    float* out = reinterpret_cast<float*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0;
-    if (vec_ok && ncol == NC) {
-#pragma unroll
-      for (int j = 0; j < NC; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(y[j], y[j + 1], y[j + 2], y[j + 3]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < NC; ++j)
-        if (j < ncol) out[j] = y[j];
-    }
-  } else {
-    uint16_t h[NC];
-#pragma unroll
-    for (int j = 0; j < NC; ++j) {
-      if (p.out_dtype == QLIN_DT_BF16) {
-        h[j] = __bfloat16_as_ushort(__float2bfloat16_rn(y[j]));
+    if (j < ncol) {
+      if (p.epilogue == QLIN_EPI_RAW) {
+        reinterpret_cast<uint32_t*>(p.d)[off + j] = v[j];
       } else {
-        h[j] = __half_as_ushort(__float2half_rn(y[j]));
+        const float y = dequant_one<F8>(p, v[j], rs, s_cs[s_off + j], s_bias[s_off + j], prod, has_bias);
+        if (p.out_dtype == QLIN_DT_F32) {
+          reinterpret_cast<float*>(p.d)[off + j] = y;
+        } else {
+          reinterpret_cast<uint16_t*>(p.d)[off + j] = static_cast<uint16_t>(pack16(p, y, 0.0f) & 0xFFFFu);
+        }
       }
-    }
-    uint16_t* out = reinterpret_cast<uint16_t*>(p.d) + static_cast<int64_t>(row) * p.ldd + col0;
-    if (vec_ok && ncol == NC) {
-#pragma unroll
-      for (int j = 0; j < NC; j += 8) {
-        uint4 w;
-        w.x = h[j] | (static_cast<uint32_t>(h[j + 1]) << 16);
-        w.y = h[j + 2] | (static_cast<uint32_t>(h[j + 3]) << 16);
-        w.z = h[j + 4] | (static_cast<uint32_t>(h[j + 5]) << 16);
-        w.w = h[j + 6] | (static_cast<uint32_t>(h[j + 7]) << 16);
-        *reinterpret_cast<uint4*>(out + j) = w;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < NC; ++j)
-        if (j < ncol) out[j] = h[j];
     }
   }
+}
+
+// Coalesced store through this warp's 32 x 128-byte staging tile.  `w` holds this thread's row as
+// 32 packed 32-bit words (128 bytes).  The tile is written with a 16-byte-chunk XOR swizzle so both
+// the row-per-lane writes and the row-contiguous reads are bank-conflict free; every global store
+// instruction then covers four full 128-byte lines.
+__device__ __forceinline__ void store_tile_coalesced(uint8_t* stage, const uint32_t (&w)[32], uint8_t* gbase,
+                                                     int64_t row_pitch_bytes, int rows_valid, int lane) {
+  const uint32_t sbase = smem_u32(stage);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const uint32_t addr = sbase + lane * 128 + ((c ^ (lane & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[4 * c]), "r"(w[4 * c + 1]),
+                 "r"(w[4 * c + 2]), "r"(w[4 * c + 3])
+                 : "memory");
+  }
+  __syncwarp();
+  const int c = lane & 7;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = i * 4 + (lane >> 3);
+    uint32_t x0, x1, x2, x3;
+    const uint32_t addr = sbase + r * 128 + ((c ^ (r & 7)) << 4);
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(addr) : "memory");
+    if (r < rows_valid) *reinterpret_cast<uint4*>(gbase + r * row_pitch_bytes + c * 16) = make_uint4(x0, x1, x2, x3);
+  }
+  __syncwarp();
 }
 
 // Loads NC columns of the optional initial accumulator C for one row (zeros when absent / outside).
@@ -216,19 +220,68 @@ __device__ __forceinline__ void load_c_row(const GemmParams& p, uint32_t (&v)[NC
     if (col0 + j < p.N) v[j] = src[j];
 }
 
+// Emits 64 accumulator columns [col0, col0+64) of this thread's row.  `vec_ok` says the output
+// allows 16-byte row-contiguous stores.
+template <bool F8>
+__device__ __forceinline__ void emit64(const GemmParams& p, const uint32_t (&v)[64], int row0, int lane, int col0,
+                                       const float* s_cs, const float* s_bias, int s_off, float rs, bool vec_ok,
+                                       uint8_t* stage) {
+  const int row = row0 + lane;
+  const bool prod = p.epilogue == QLIN_EPI_SCALE_PROD;
+  const bool has_bias = p.bias != nullptr;
+  const int rows_valid = p.M - row0;
+  if (!vec_ok || col0 + 64 > p.N) {
+    store_row_direct<F8, 64>(p, v, row, col0, s_cs, s_bias, s_off, rs);
+    return;
+  }
+  if (p.epilogue != QLIN_EPI_RAW && p.out_dtype != QLIN_DT_F32) {
+    // 2-byte outputs: 64 columns = one 128-byte staging row
+    uint32_t w[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float y0 = dequant_one<F8>(p, v[2 * j], rs, s_cs[s_off + 2 * j], s_bias[s_off + 2 * j], prod, has_bias);
+      const float y1 =
+          dequant_one<F8>(p, v[2 * j + 1], rs, s_cs[s_off + 2 * j + 1], s_bias[s_off + 2 * j + 1], prod, has_bias);
+      w[j] = pack16(p, y0, y1);
+    }
+    uint8_t* g = reinterpret_cast<uint8_t*>(p.d) + (static_cast<int64_t>(row0) * p.ldd + col0) * 2;
+    store_tile_coalesced(stage, w, g, p.ldd * 2, rows_valid, lane);
+  } else {
+    // 4-byte outputs: two staging passes of 32 columns
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t w[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int k = h * 32 + j;
+        w[j] = p.epilogue == QLIN_EPI_RAW
+                   ? v[k]
+                   : __float_as_uint(dequant_one<F8>(p, v[k], rs, s_cs[s_off + k], s_bias[s_off + k], prod, has_bias));
+      }
+      uint8_t* g = reinterpret_cast<uint8_t*>(p.d) + (static_cast<int64_t>(row0) * p.ldd + col0 + h * 32) * 4;
+      store_tile_coalesced(stage, w, g, p.ldd * 4, rows_valid, lane);
+    }
+  }
+}
+
 template <bool F8, bool CHUNKED>
 __global__ void __launch_bounds__(kThreads, 1)
 qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
   using C = Cfg<CHUNKED>;
-  extern __shared__ uint8_t smem_raw[];
-  // 1024-byte alignment is required by the 128-byte swizzle atoms.
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  Aux* aux = reinterpret_cast<Aux*>(smem + C::STAGES * C::STAGE_BYTES);
+  extern __shared__ __align__(1024) uint8_t smem[];
+  Aux* aux = reinterpret_cast<Aux*>(smem + C::AUX_OFFSET);
   volatile int* abort_flag = &aux->abort_flag;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+
+  // The 128-byte swizzle atoms need a 1024-byte aligned base; dynamic shared memory starts at the
+  // base of the CTA's window, so this only guards against a toolchain that would place it elsewhere.
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, static_cast<int32_t>(QLIN_ERR_BAD_ALIGN));
+    return;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -264,25 +317,30 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------------ TMA producer
-    // The whole warp walks the loop (so it stays converged for the final barrier); lane 0 issues.
-    uint32_t it = 0;
+    // The whole warp walks the loop converged; one elected lane issues.  The next stage's
+    // barrier is polled (non-blocking) before the current stage is issued, which takes the
+    // barrier round trip off the loop's critical path.
+    uint32_t s = 0, ph = 0, issued = 0;
     bool ok = true;
+    bool ready = false;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
       tile_coords(t, p.num_m, p.num_n, mb, nb);
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const uint32_t s = it % C::STAGES;
-        const uint32_t ph = (it / C::STAGES) & 1u;
-        ok = __all_sync(0xffffffffu, mbar_wait(&aux->empty[s], ph ^ 1u, abort_flag));
-        if (!ok) break;
-        if (lane == 0) {
-          uint8_t* sa = smem + s * C::STAGE_BYTES;
-          uint8_t* sb = sa + C::A_BYTES;
-          mbar_arrive_expect_tx(&aux->full[s], C::STAGE_BYTES);
-          tma_load_2d(sa, &tmap_a, &aux->full[s], kb * kBK, mb * kBM);
-          tma_load_2d(sb, &tmap_b, &aux->full[s], kb * kBK, nb * C::BN);
+      const int ya = mb * kBM, yb = nb * C::BN;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!ready) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&aux->empty[s], ph ^ 1u, abort_flag));
+          if (!ok) break;
         }
-        __syncwarp();
+        const uint32_t ns = (s + 1 == C::STAGES) ? 0u : s + 1;
+        const uint32_t nph = (ns == 0u) ? (ph ^ 1u) : ph;
+        const bool peek = mbar_test_wait(&aux->empty[ns], nph ^ 1u);
+        uint8_t* sa = smem + s * C::STAGE_BYTES;
+        tma_issue_stage(&aux->full[s], C::STAGE_BYTES, sa, &tmap_a, ya, sa + C::A_BYTES, &tmap_b, yb, kb * kBK);
+        ++issued;
+        ready = __all_sync(0xffffffffu, peek);
+        s = ns;
+        ph = nph;
       }
     }
     if (!ok) {
@@ -291,69 +349,104 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         *abort_flag = 1;
       }
       // Let the copies already issued land before the CTA gives its shared memory back.
-      const uint32_t issued = it;
-      for (uint32_t s = 0; s < static_cast<uint32_t>(C::STAGES); ++s) {
-        if (issued <= s) continue;
-        const uint32_t last = ((issued - 1 - s) / C::STAGES);  // index of the last fill of stage s
-        mbar_wait_drain(&aux->full[s], last & 1u);
+      for (uint32_t st = 0; st < static_cast<uint32_t>(C::STAGES); ++st) {
+        if (issued <= st) continue;
+        const uint32_t last = ((issued - 1 - st) / C::STAGES);  // index of the last fill of stage st
+        mbar_wait_drain(&aux->full[st], last & 1u);
       }
     }
     __syncwarp();
   } else if (warp == kMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
+    // One instruction stream feeds the tensor pipe, so this loop is latency-critical: no
+    // divisions, positions carried as counters, a whole 128-byte K block issued by one fused
+    // statement, and the next stage's barrier polled before the current block is issued.
     constexpr uint32_t idesc = F8 ? make_idesc(1u, 0u, kBM, C::BN) : make_idesc(2u, 1u, kBM, C::BN);
-    uint32_t it = 0, acc_it = 0;
+    const uint64_t adesc0 = make_smem_desc_sw128(smem_u32(smem));
+    const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(smem) + C::A_BYTES);
+    uint32_t s = 0, ph = 0;          // smem stage and its phase
+    uint32_t buf = 0, bph = 0;       // TMEM accumulator buffer to use next and its phase
     bool ok = true;
+    bool ready = false;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-      uint32_t buf = 0, accumulate = 0;
-      for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
-        const uint32_t s = it % C::STAGES;
-        const uint32_t ph = (it / C::STAGES) & 1u;
-        ok = __all_sync(0xffffffffu, mbar_wait(&aux->full[s], ph, abort_flag));
-        if (!ok) break;
+      uint32_t accumulate = 0, cur = 0;
+      int chunk_pos = 0;
+      int k32_left = total_k32;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        if (!ready) {
+          ok = __all_sync(0xffffffffu, mbar_wait(&aux->full[s], ph, abort_flag));
+          if (!ok) break;
+        }
         tc_fence_after();
-        const uint32_t sa = smem_u32(smem + s * C::STAGE_BYTES);
-        const uint64_t adesc = make_smem_desc_sw128(sa);
-        const uint64_t bdesc = make_smem_desc_sw128(sa + C::A_BYTES);
-        const int nsteps = min(4, total_k32 - kb * 4);
-        for (int j = 0; j < nsteps; ++j) {
-          const int kk = kb * 4 + j;
-          if (kk % p.chunk_k32 == 0) {
-            buf = acc_it % C::NBUF;
-            const uint32_t bph = (acc_it / C::NBUF) & 1u;
+        const uint32_t ns = (s + 1 == C::STAGES) ? 0u : s + 1;
+        const uint32_t nph = (ns == 0u) ? (ph ^ 1u) : ph;
+        const bool peek = mbar_test_wait(&aux->full[ns], nph);
+        const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
+        const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
+        if (!CHUNKED && k32_left >= 4 && (kb > 0 || true)) {
+          if (kb == 0) {
             ok = __all_sync(0xffffffffu, mbar_wait(&aux->tempty[buf], bph ^ 1u, abort_flag));
             if (!ok) break;
             tc_fence_after();
-            accumulate = 0;
+            cur = buf;
+            if (++buf == C::NBUF) {
+              buf = 0;
+              bph ^= 1u;
+            }
           }
-          const bool last_of_chunk = (kk + 1) % p.chunk_k32 == 0 || kk + 1 == total_k32;
-          if (lane == 0) {
-            tc_mma<F8 ? 1 : 0>(tmem_base + buf * C::BN, adesc + static_cast<uint64_t>(j * 2),
-                               bdesc + static_cast<uint64_t>(j * 2), idesc, accumulate);
-            if (last_of_chunk) tc_commit(&aux->tfull[buf]);
-          }
+          tc_mma4_release<F8 ? 1 : 0>(tmem_base + cur * C::BN, adesc, bdesc, idesc, accumulate, &aux->empty[s]);
           accumulate = 1;
-          if (last_of_chunk) ++acc_it;
+          k32_left -= 4;
+          if (k32_left == 0) tc_commit_elect(&aux->tfull[cur]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (k32_left > 0 && ok) {
+              if (chunk_pos == 0 && (CHUNKED || accumulate == 0)) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&aux->tempty[buf], bph ^ 1u, abort_flag));
+                if (ok) {
+                  tc_fence_after();
+                  cur = buf;
+                  accumulate = 0;
+                  if (++buf == C::NBUF) {
+                    buf = 0;
+                    bph ^= 1u;
+                  }
+                }
+              }
+              if (ok) {
+                ++chunk_pos;
+                --k32_left;
+                const bool last_of_chunk = chunk_pos == p.chunk_k32 || k32_left == 0;
+                tc_mma1<F8 ? 1 : 0>(tmem_base + cur * C::BN, adesc + static_cast<uint64_t>(j * 2),
+                                    bdesc + static_cast<uint64_t>(j * 2), idesc, accumulate);
+                if (last_of_chunk) tc_commit_elect(&aux->tfull[cur]);
+                accumulate = 1;
+                if (last_of_chunk) chunk_pos = 0;
+              }
+            }
+          }
+          if (ok) tc_commit_elect(&aux->empty[s]);
         }
-        if (ok && lane == 0) tc_commit(&aux->empty[s]);
-        __syncwarp();
+        ready = __all_sync(0xffffffffu, peek);
+        s = ns;
+        ph = nph;
       }
     }
-    if (lane == 0) {
-      if (!ok) {
-        timed_out = !*abort_flag;
-        *abort_flag = 1;
-      }
-      // Nothing may still be reading shared memory or writing TMEM when the CTA retires.
-      tc_commit(&aux->drain);
-      mbar_wait_drain(&aux->drain, 0);
+    if (!ok && lane == 0) {
+      timed_out = !*abort_flag;
+      *abort_flag = 1;
     }
+    // Nothing may still be reading shared memory or writing TMEM when the CTA retires.
+    tc_commit_elect(&aux->drain);
+    mbar_wait_drain(&aux->drain, 0);
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int q = warp & 3;
     const int half = warp >> 2;
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+    uint8_t* stage = smem + C::OUT_OFFSET + warp * kStageOutBytes;
     const int elt = (p.out_dtype == QLIN_DT_F16 || p.out_dtype == QLIN_DT_BF16) ? 2 : 4;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.d) & 15u) == 0) && ((p.ldd * elt) % 16 == 0);
     const bool clamp = !F8 && p.max_acc_bits < 32;
@@ -363,12 +456,13 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t mask = p.trun_bits > 0 ? ~((1u << p.trun_bits) - 1u) : 0xFFFFFFFFu;
     const bool dl16 = F8 && p.clamp_dl16;
     const bool scaled = p.epilogue != QLIN_EPI_RAW;
-    uint32_t acc_it = 0;
+    uint32_t ebuf = 0, ebph = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
       tile_coords(t, p.num_m, p.num_n, mb, nb);
-      const int row = mb * kBM + q * 32 + lane;
+      const int row0 = mb * kBM + q * 32;
+      const int row = row0 + lane;
       const int col_w = nb * C::BN + half * C::COLS_PER_WARP;
       float rs = 1.0f;
       if (scaled) {
@@ -383,25 +477,27 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (p.rs != nullptr && row < p.M) rs = p.rs[static_cast<int64_t>(row) * p.rs_stride];
       }
       if constexpr (!CHUNKED) {
-        const uint32_t buf = acc_it % C::NBUF;
-        const uint32_t bph = (acc_it / C::NBUF) & 1u;
-        ++acc_it;
+        const uint32_t buf = ebuf, bph = ebph;
+        if (++ebuf == C::NBUF) {
+          ebuf = 0;
+          ebph ^= 1u;
+        }
         if (!mbar_wait(&aux->tfull[buf], bph, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
 #pragma unroll 1
-        for (int j = 0; j < C::COLS_PER_WARP; j += 32) {
-          uint32_t v[32];
-          tmem_ld32(tmem_base + lane_base + buf * C::BN + half * C::COLS_PER_WARP + j, v);
+        for (int j = 0; j < C::COLS_PER_WARP; j += 64) {
+          uint32_t v[64];
+          tmem_ld64(tmem_base + lane_base + buf * C::BN + half * C::COLS_PER_WARP + j, v);
           if (p.c != nullptr) {
-            uint32_t cv[32];
-            load_c_row<32>(p, cv, row, col_w + j);
+            uint32_t cv[64];
+            load_c_row<64>(p, cv, row, col_w + j);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = acc_add<F8>(cv[i], v[i]);
+            for (int i = 0; i < 64; ++i) v[i] = acc_add<F8>(cv[i], v[i]);
           }
-          store_row<F8, 32>(p, v, row, col_w + j, aux->cs, aux->bias, half * C::COLS_PER_WARP + j, rs, vec_ok);
+          emit64<F8>(p, v, row0, lane, col_w + j, aux->cs, aux->bias, half * C::COLS_PER_WARP + j, rs, vec_ok, stage);
         }
         tc_fence_before();
         __syncwarp();
@@ -409,12 +505,15 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       } else {
         uint32_t run[C::COLS_PER_WARP];
         load_c_row<C::COLS_PER_WARP>(p, run, row, col_w);
-        const int num_chunks = (total_k32 + p.chunk_k32 - 1) / p.chunk_k32;
+        int k32_left = total_k32;
 #pragma unroll 1
-        for (int ch = 0; ch < num_chunks; ++ch) {
-          const uint32_t buf = acc_it % C::NBUF;
-          const uint32_t bph = (acc_it / C::NBUF) & 1u;
-          ++acc_it;
+        while (k32_left > 0) {
+          k32_left -= p.chunk_k32;
+          const uint32_t buf = ebuf, bph = ebph;
+          if (++ebuf == C::NBUF) {
+            ebuf = 0;
+            ebph ^= 1u;
+          }
           if (!mbar_wait(&aux->tfull[buf], bph, abort_flag)) {
             ok = false;
             break;
@@ -436,8 +535,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
         if (!ok) break;
-        store_row<F8, C::COLS_PER_WARP>(p, run, row, col_w, aux->cs, aux->bias, half * C::COLS_PER_WARP, rs,
-                                        vec_ok);
+        emit64<F8>(p, run, row0, lane, col_w, aux->cs, aux->bias, half * C::COLS_PER_WARP, rs, vec_ok, stage);
       }
     }
     if (!ok && lane == 0) {

@@ -43,6 +43,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Budget of a bounded wait.  The first polls spin; after that every miss sleeps 64 ns and checks
 // the CTA's abort flag and the wall clock (%globaltimer, nanoseconds).
 constexpr uint32_t kSpinFast = 2048;
@@ -161,6 +175,94 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
   }
+}
+
+// The issue helpers below are executed by a whole converged warp; one elected lane issues (guard
+// predicate from elect.sync), so the surrounding loop stays free of divergent branches and its
+// operands stay warp-uniform.
+
+// One stage of the TMA producer: arm the barrier with the byte count, then load the A and B boxes.
+__device__ __forceinline__ void tma_issue_stage(uint64_t* full_bar, uint32_t bytes, void* smem_a, const void* tmap_a,
+                                                int32_t ya, void* smem_b, const void* tmap_b, int32_t yb, int32_t x) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pe;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "@pe mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t"
+      "@pe cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%2], [%3, {%8, %4}], [%0];\n\t"
+      "@pe cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%5], [%6, {%8, %7}], [%0];\n\t"
+      "}" ::"r"(smem_u32(full_bar)),
+      "r"(bytes), "r"(smem_u32(smem_a)), "l"(reinterpret_cast<uint64_t>(tmap_a)), "r"(ya), "r"(smem_u32(smem_b)),
+      "l"(reinterpret_cast<uint64_t>(tmap_b)), "r"(yb), "r"(x)
+      : "memory");
+}
+
+// One full 128-byte K block: four K=32-byte MMAs into the same accumulator (the first one
+// overwrites it when `accumulate` is 0), then release the shared-memory stage through `empty_bar`.
+template <int KIND_F8>
+__device__ __forceinline__ void tc_mma4_release(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate, uint64_t* empty_bar) {
+#define QLIN_MMA4(KIND)                                                                         \
+  asm volatile(                                                                                 \
+      "{\n\t"                                                                                   \
+      ".reg .pred pe, pa, pt;\n\t"                                                              \
+      ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"                                                   \
+      "elect.sync _|pe, 0xffffffff;\n\t"                                                        \
+      "setp.ne.b32 pa, %4, 0;\n\t"                                                              \
+      "setp.ne.b32 pt, %3, 0;\n\t"                                                              \
+      "add.s64 a1, %1, 2;\n\t"                                                                  \
+      "add.s64 b1, %2, 2;\n\t"                                                                  \
+      "add.s64 a2, %1, 4;\n\t"                                                                  \
+      "add.s64 b2, %2, 4;\n\t"                                                                  \
+      "add.s64 a3, %1, 6;\n\t"                                                                  \
+      "add.s64 b3, %2, 6;\n\t"                                                                  \
+      "@pe tcgen05.mma.cta_group::1.kind::" KIND " [%0], %1, %2, %3, pa;\n\t"                   \
+      "@pe tcgen05.mma.cta_group::1.kind::" KIND " [%0], a1, b1, %3, pt;\n\t"                   \
+      "@pe tcgen05.mma.cta_group::1.kind::" KIND " [%0], a2, b2, %3, pt;\n\t"                   \
+      "@pe tcgen05.mma.cta_group::1.kind::" KIND " [%0], a3, b3, %3, pt;\n\t"                   \
+      "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%5];\n\t"     \
+      "}" ::"r"(d_tmem),                                                                        \
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(smem_u32(empty_bar))             \
+      : "memory")
+  if (KIND_F8) {
+    QLIN_MMA4("f8f6f4");
+  } else {
+    QLIN_MMA4("i8");
+  }
+#undef QLIN_MMA4
+}
+
+// A single K=32-byte MMA, elected-lane form.
+template <int KIND_F8>
+__device__ __forceinline__ void tc_mma1(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+#define QLIN_MMA1(KIND)                                                               \
+  asm volatile(                                                                       \
+      "{\n\t"                                                                         \
+      ".reg .pred pe, pa;\n\t"                                                        \
+      "elect.sync _|pe, 0xffffffff;\n\t"                                              \
+      "setp.ne.b32 pa, %4, 0;\n\t"                                                    \
+      "@pe tcgen05.mma.cta_group::1.kind::" KIND " [%0], %1, %2, %3, pa;\n\t"         \
+      "}" ::"r"(d_tmem),                                                              \
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)                             \
+      : "memory")
+  if (KIND_F8) {
+    QLIN_MMA1("f8f6f4");
+  } else {
+    QLIN_MMA1("i8");
+  }
+#undef QLIN_MMA1
+}
+
+// tcgen05.commit, elected-lane form.
+__device__ __forceinline__ void tc_commit_elect(uint64_t* bar) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pe;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}" ::"r"(smem_u32(bar))
+      : "memory");
 }
 
 // Reads 32 consecutive 32-bit columns of this warp's 32 TMEM lanes (lane i of the warp gets TMEM
