@@ -68,6 +68,7 @@ class GemmArgs(C.Structure):
         ("epilogue", C.c_int32),
         ("row_scale_stride", C.c_int32),
         ("col_scale_stride", C.c_int32),
+        ("prod_round", C.c_int32),
         ("scale_round", C.c_int32),
         ("mid_round", C.c_int32),
         ("acc_round", C.c_int32),
@@ -138,6 +139,7 @@ class WfqArgs(C.Structure):
         ("num_bits", C.c_int32),
         ("mode", C.c_int32),
         ("native_mul", C.c_int32),
+        ("clip_f32", C.c_int32),
         ("c0", C.c_float),
         ("c1", C.c_float),
     ]

@@ -35,7 +35,10 @@ __device__ __forceinline__ PactScalars pact_scalars(const PactParams& p) {
   s.cv = Elem<XT>::rnd(*p.cv);
   s.cvn = Elem<XT>::rnd(*p.cvn);
   s.n = static_cast<float>((1 << p.num_bits) - 1);
-  const float scale = Elem<XT>::rnd(__fdiv_rn(s.n, Elem<XT>::rnd(__fsub_rn(s.cv, s.cvn))));
+  // `n_levels / (cv - cvn)` and `1.0 / scale` have a Python scalar on the left: torch evaluates
+  // them as reciprocal(tensor) * scalar, each step rounded to the tensor dtype.
+  const float inv = Elem<XT>::rnd(__fdiv_rn(1.0f, Elem<XT>::rnd(__fsub_rn(s.cv, s.cvn))));
+  const float scale = Elem<XT>::rnd(__fmul_rn(inv, s.n));
   s.step = Elem<XT>::rnd(__fdiv_rn(1.0f, scale));
   s.zp = Elem<XT>::rnd(__fmul_rn(s.cvn, scale));
   if (p.align_zero) s.zp = rintf(s.zp);

@@ -75,7 +75,7 @@ struct GemmParams {
   int32_t kbytes;      // K in bytes
   int32_t chunk_k32;   // 32-byte MMA steps per accumulation chunk
   int32_t trun_bits, max_acc_bits, trunc_then_acc, clamp_dl16;
-  int32_t epilogue, rs_stride, cs_stride, scale_round, mid_round, acc_round, out_dtype;
+  int32_t epilogue, rs_stride, cs_stride, prod_round, scale_round, mid_round, acc_round, out_dtype;
   int32_t num_m, num_n;
 };
 
@@ -135,7 +135,7 @@ __device__ __forceinline__ float dequant_one(const GemmParams& p, uint32_t v, fl
   const float a = F8 ? __uint_as_float(v) : __int2float_rn(static_cast<int32_t>(v));
   float t;
   if (prod) {
-    const float s = round_to(__fmul_rn(rs, cs), p.scale_round);
+    const float s = round_to(round_to(__fmul_rn(rs, cs), p.prod_round), p.scale_round);
     t = __fmul_rn(a, s);
   } else {
     t = round_to(__fmul_rn(__fmul_rn(a, rs), cs), p.mid_round);
@@ -634,7 +634,7 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   } else if (a->epilogue == QLIN_EPI_SCALE_PROD || a->epilogue == QLIN_EPI_SCALE_SEQ) {
     if (a->out_dtype != QLIN_DT_F32 && a->out_dtype != QLIN_DT_F16 && a->out_dtype != QLIN_DT_BF16)
       return fail(QLIN_ERR_BAD_DTYPE, "qlin_gemm: scaled output must be fp32, fp16 or bf16");
-    if (!is_round_dtype(a->scale_round) || !is_round_dtype(a->mid_round) || !is_round_dtype(a->acc_round))
+    if (!is_round_dtype(a->prod_round) || !is_round_dtype(a->scale_round) || !is_round_dtype(a->mid_round) || !is_round_dtype(a->acc_round))
       return fail(QLIN_ERR_BAD_DTYPE, "qlin_gemm: rounding dtypes must be NONE, F32, F16 or BF16");
     if ((a->row_scale_stride != 0 && a->row_scale_stride != 1) || (a->col_scale_stride != 0 && a->col_scale_stride != 1))
       return fail(QLIN_ERR_BAD_SHAPE, "qlin_gemm: scale strides must be 0 or 1");
@@ -674,6 +674,7 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   p.epilogue = a->epilogue;
   p.rs_stride = a->row_scale_stride;
   p.cs_stride = a->col_scale_stride;
+  p.prod_round = a->prod_round;
   p.scale_round = a->scale_round;
   p.mid_round = a->mid_round;
   p.acc_round = a->acc_round;

@@ -28,14 +28,14 @@ struct QuantParams {
   void* dq_out;
   int64_t ldx, ldq, lddq;
   int32_t rows, cols;
-  int32_t mode, native, smooth_mul, clamp_codes, levels, dl8_flush, scale_in_stride;
+  int32_t mode, native, native_smooth, smooth_mul, clamp_codes, levels, dl8_flush, scale_in_stride;
   float scale0, zp0, lo, hi, shift, add2;
 };
 
 template <typename XT>
 __device__ __forceinline__ float smooth_apply(const QuantParams& p, float x, float sm) {
   const float v = p.smooth_mul ? __fmul_rn(x, sm) : __fdiv_rn(x, sm);
-  return rnd_if<XT>(v, p.native);
+  return rnd_if<XT>(v, p.native_smooth);
 }
 
 // Row scale from the row's absmax.
@@ -265,7 +265,7 @@ struct WfqParams {
   int8_t* codes;
   float* clip_io;
   int64_t ldw, ldo, ldq;
-  int32_t rows, cols, num_bits, mode, native_mul;
+  int32_t rows, cols, num_bits, mode, native_mul, clip_f32;
   float c0, c1;
 };
 
@@ -347,7 +347,8 @@ __global__ void __launch_bounds__(1024) wfq_vec_kernel(const WfqParams p) {
     const float clip = wfq_clip<XT>(p, sa, sq, am, row);
     if (threadIdx.x == 0 && p.mode != QLIN_W_GIVEN) p.clip_io[row] = clip;
     // scale = clip * 2 / nspace in the weight dtype, then widened
-    const float scale = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fmul_rn(clip, 2.0f)), nspace));
+    const float scale = p.clip_f32 ? __fdiv_rn(__fmul_rn(clip, 2.0f), nspace)
+                                   : Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fmul_rn(clip, 2.0f)), nspace));
     const float inv_scale = __fdiv_rn(1.0f, scale);
     auto emit = [&](int ch, const float (&val)[16]) {
       float dq[16];
@@ -406,7 +407,8 @@ __global__ void __launch_bounds__(256) wfq_scalar_kernel(const WfqParams p) {
     }
     const float clip = wfq_clip<XT>(p, sa, sq, am, row);
     if (threadIdx.x == 0 && p.mode != QLIN_W_GIVEN) p.clip_io[row] = clip;
-    const float scale = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fmul_rn(clip, 2.0f)), nspace));
+    const float scale = p.clip_f32 ? __fdiv_rn(__fmul_rn(clip, 2.0f), nspace)
+                                   : Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fmul_rn(clip, 2.0f)), nspace));
     const float inv_scale = __fdiv_rn(1.0f, scale);
     for (int c = threadIdx.x; c < p.cols; c += blockDim.x) {
       float v = load1(wr + c);
@@ -482,7 +484,8 @@ extern "C" int qlin_act_quant(const qlin_quant_args* a, void* stream) {
   p.rows = a->rows;
   p.cols = a->cols;
   p.mode = a->mode;
-  p.native = a->native_chain != 0;
+  p.native = (a->native_chain & 2) != 0;
+  p.native_smooth = (a->native_chain & 1) != 0;
   p.smooth_mul = a->smooth_mul != 0;
   p.clamp_codes = a->clamp_codes != 0;
   p.levels = a->qmax_levels;
@@ -532,6 +535,7 @@ extern "C" int qlin_weight_fq_perch(const qlin_wfq_args* a, void* stream) {
   p.num_bits = a->num_bits;
   p.mode = a->mode;
   p.native_mul = a->native_mul != 0;
+  p.clip_f32 = a->clip_f32 != 0;
   p.c0 = a->c0;
   p.c1 = a->c1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

@@ -113,6 +113,7 @@ def gemm(
     row_scale: Optional[torch.Tensor] = None,
     col_scale: Optional[torch.Tensor] = None,
     bias: Optional[torch.Tensor] = None,
+    prod_round: Optional[torch.dtype] = None,
     scale_round: Optional[torch.dtype] = None,
     mid_round: Optional[torch.dtype] = None,
     acc_round: Optional[torch.dtype] = None,
@@ -165,7 +166,7 @@ def gemm(
         trunc_then_acc=int(bool(trunc_then_acc)), clamp_dl16=int(bool(clamp_dl16)), epilogue=int(epilogue),
         row_scale_stride=(0 if rs is None or rs.numel() == 1 else 1),
         col_scale_stride=(0 if cs is None or cs.numel() == 1 else 1),
-        scale_round=_ROUND[scale_round], mid_round=_ROUND[mid_round], acc_round=_ROUND[acc_round],
+        prod_round=_ROUND[prod_round], scale_round=_ROUND[scale_round], mid_round=_ROUND[mid_round], acc_round=_ROUND[acc_round],
         out_dtype=_DT[out_dtype],
     )  # fmt: skip
     with torch.cuda.device(dev):
@@ -265,7 +266,7 @@ def act_quant(
     mode: int = L.Q_I8_DYN,
     smooth: Optional[torch.Tensor] = None,
     smooth_mul: bool = False,
-    native_chain: bool = False,
+    native_chain: int = 0,
     clamp_codes: bool = False,
     levels: int = 127,
     want_codes: bool = True,
@@ -302,7 +303,7 @@ def act_quant(
     args = L.QuantArgs(
         x=_ptr(x), smooth=_ptr(sm), scale_in=_ptr(si), codes=_ptr(codes), scale_out=_ptr(scale), dq_out=_ptr(dq),
         status=None, ldx=x.stride(0), ldq=cols, lddq=cols, rows=rows, cols=cols, x_dtype=_DT[x.dtype], mode=mode,
-        native_chain=int(bool(native_chain)), smooth_mul=int(bool(smooth_mul)), clamp_codes=int(bool(clamp_codes)),
+        native_chain=int(native_chain), smooth_mul=int(bool(smooth_mul)), clamp_codes=int(bool(clamp_codes)),
         qmax_levels=int(levels), dl8_flush=int(bool(dl8_flush)),
         scale_in_stride=(0 if si is None or si.numel() == 1 else 1),
         scale0=scale0, zp0=zp0, lo=lo, hi=hi, shift=shift, add2=add2,
@@ -320,6 +321,7 @@ def weight_fq_perch(
     clip: Optional[torch.Tensor] = None,
     smooth: Optional[torch.Tensor] = None,
     native_mul: bool = True,
+    clip_f32: bool = False,
     want_dq: bool = True,
     want_codes: bool = False,
     c0: float = 0.0,
@@ -349,7 +351,7 @@ def weight_fq_perch(
     args = L.WfqArgs(
         w=_ptr(w), smooth=_ptr(sm), dq_out=_ptr(dq), codes=_ptr(codes), clip_io=_ptr(clip_io),
         ldw=w.stride(0), ldo=cols, ldq=cols, rows=rows, cols=cols, dtype=_DT[w.dtype], num_bits=int(num_bits),
-        mode=int(mode), native_mul=int(bool(native_mul)), c0=float(c0), c1=float(c1),
+        mode=int(mode), native_mul=int(bool(native_mul)), clip_f32=int(bool(clip_f32)), c0=float(c0), c1=float(c1),
     )  # fmt: skip
     with torch.cuda.device(dev):
         L.check(L.load().qlin_weight_fq_perch(C.byref(args), _stream(dev)), "qlin_weight_fq_perch")
@@ -403,3 +405,40 @@ def pact2_bwd(
     with torch.cuda.device(dev):
         L.check(lib.qlin_pact2_bwd(C.byref(args), _stream(dev)), "qlin_pact2_bwd")
     return gx, grads
+
+
+# --------------------------------------------------------------------------------------------------
+# torch custom ops (namespace qlin_b200), the counterpart of the reference's fms_mo::* registrations
+# (fms_mo/custom_ext_kernels/utils.py:674-802).  Fake implementations give shapes and dtypes so the
+# ops can be traced.
+# --------------------------------------------------------------------------------------------------
+@torch.library.custom_op("qlin_b200::imatmul", mutates_args=())
+def _imatmul_op(m1: torch.Tensor, m2: torch.Tensor) -> torch.Tensor:
+    return imatmul(m1, m2)
+
+
+@_imatmul_op.register_fake
+def _(m1, m2):
+    return m1.new_empty((*m1.shape[:-1], m2.shape[1]), dtype=torch.int32)
+
+
+@torch.library.custom_op("qlin_b200::act_quant_i8", mutates_args=())
+def _act_quant_i8_op(x: torch.Tensor, smooth: Optional[torch.Tensor], native_chain: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    codes, scale, _ = act_quant(x.reshape(-1, x.shape[-1]), mode=L.Q_I8_DYN, smooth=smooth, native_chain=native_chain)
+    return codes.reshape(x.shape), scale
+
+
+@_act_quant_i8_op.register_fake
+def _(x, smooth, native_chain):
+    return x.new_empty(x.shape, dtype=torch.int8), x.new_empty((x.numel() // x.shape[-1],), dtype=torch.float32)
+
+
+@torch.library.custom_op("qlin_b200::iaddmm", mutates_args=())
+def _iaddmm_op(bias: torch.Tensor, m1: torch.Tensor, m2: torch.Tensor, scale_i: torch.Tensor, scale_w: torch.Tensor) -> torch.Tensor:
+    """fms_mo::iaddmm (fms_mo/custom_ext_kernels/utils.py:729-746): ``scale_i.float() * imatmul(m1, m2) * scale_w + bias``."""
+    return gemm(m1, _as_nk(m2), epilogue=L.EPI_SCALE_SEQ, row_scale=scale_i, col_scale=scale_w, bias=bias, out_dtype=torch.float32)
+
+
+@_iaddmm_op.register_fake
+def _(bias, m1, m2, scale_i, scale_w):
+    return m1.new_empty((m1.shape[0], m2.shape[1]), dtype=torch.float32)

@@ -85,7 +85,7 @@ int qlin_device_supported(int device);
  * Epilogue, per element with acc the final accumulator (converted to fp32 for the scaled
  * modes), rs = row_scale[m * row_scale_stride] (1 if NULL), cs likewise:
  *   QLIN_EPI_RAW        d = acc                             (out_dtype I32 for I8, F32 for F8)
- *   QLIN_EPI_SCALE_PROD s = round(rs * cs, scale_round); y = acc * s; y = y + bias[n];
+ *   QLIN_EPI_SCALE_PROD s = round(round(rs * cs, prod_round), scale_round); y = acc * s; y = y + bias[n];
  *                       y = round(y, acc_round); d = cast(y, out_dtype)
  *   QLIN_EPI_SCALE_SEQ  y = (acc * rs) * cs; y = round(y, mid_round); y = y + bias[n];
  *                       y = round(y, acc_round); d = cast(y, out_dtype)
@@ -119,6 +119,7 @@ typedef struct qlin_gemm_args {
   int32_t epilogue;         /* qlin_epilogue */
   int32_t row_scale_stride; /* 0 = one scalar, 1 = per row */
   int32_t col_scale_stride; /* 0 = one scalar, 1 = per column */
+  int32_t prod_round;       /* qlin_dtype: dtype the reference forms input_scale * w_scale in */
   int32_t scale_round;      /* qlin_dtype */
   int32_t mid_round;        /* qlin_dtype */
   int32_t acc_round;        /* qlin_dtype */
@@ -152,8 +153,9 @@ int qlin_gemm(const qlin_gemm_args* args, void* stream);
  *   QLIN_Q_I8_GIVEN_SCALE
  *                     scale = scale_in[row * scale_in_stride]; code = rint(v / scale) + zp0,
  *                     wrapped to int8 or clamped to +-qmax_levels
- * native_chain != 0 rounds every intermediate to the dtype of x (what the reference computes when
- * it is handed bf16 / fp16 tensors); 0 evaluates the same formulas in fp32.
+ * native_chain is a bit mask: bit 0 rounds the smoothed value to the dtype of x, bit 1 rounds every
+ * later intermediate to the dtype of x (what the reference computes when the tensors involved are
+ * bf16 / fp16); 0 evaluates the same formulas in fp32 on the widened inputs.
  * Outputs: codes [rows, cols] (1 byte each), scale_out [rows] fp32 (optional),
  * dq_out (optional, dtype of x): the fake-quantised value code * scale, QMaxDynamic's output.
  * ---------------------------------------------------------------------------------------------- */
@@ -250,6 +252,8 @@ typedef struct qlin_wfq_args {
   int32_t num_bits;
   int32_t mode;         /* qlin_wq_mode */
   int32_t native_mul;   /* round w * smooth to dtype before use (reference multiplies in the weight dtype) */
+  int32_t clip_f32;     /* the clip values live in an fp32 tensor: form scale = clip * 2 / (2^bits - 2) in fp32
+                           instead of the weight dtype (QLIN_W_GIVEN with an fp32 clip_val buffer) */
   float c0, c1;
 } qlin_wfq_args;
 

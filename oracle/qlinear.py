@@ -1,0 +1,134 @@
+"""Oracle for the quantized Linear modules (test infrastructure, see ``oracle/__init__.py``).
+
+Restates, on CPU tensors, the forward passes of ``QLinear`` (fake-quant path),
+``QLinearINT8Deploy`` (integer path) and ``LinearFPxAcc`` (FP8 path) of
+``fms_mo/modules/linear.py``.  The matmuls go through ``oracle.gemm``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import gemm as G
+from . import quantizers as Q
+
+
+def smoothq_scale(act_scale: torch.Tensor, weight: torch.Tensor, alpha: float, dtype: torch.dtype) -> torch.Tensor:
+    """QLinear.get_smoothq_scale (fms_mo/modules/linear.py:345-368); the deploy copy is
+    linear.py:799-817.  All-zero activation scales mean "no smoothing" (scale 1)."""
+    if act_scale.sum().item() == 0.0:
+        return torch.tensor([1.0]).to(dtype)
+    weight_scale = weight.abs().max(dim=0, keepdim=True)[0].clamp(min=1e-5)
+    return (act_scale.pow(alpha) / weight_scale.pow(1.0 - alpha)).clamp(min=1e-5).to(dtype)
+
+
+def qmax_clip_after_first_train_forward(w_smoothed: torch.Tensor, buffer_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """The clip_val buffer of Qmax(perCh) after one training-mode forward
+    (fms_mo/quant/quantizers.py:3098-3128): the fresh per-row absmax is copied into the buffer and
+    then passed through the moving average ``buf * (1 - 0.1) + cv_new * 0.1``.  The buffer is fp32
+    unless the owning module was cast (``QLinear.to(dtype)`` casts it along)."""
+    buffer_dtype = buffer_dtype if buffer_dtype is not None else w_smoothed.dtype
+    cv_new = torch.max(w_smoothed.abs().reshape([w_smoothed.shape[0], -1]), dim=1).values
+    buf = cv_new.to(buffer_dtype)
+    return (buf * (1.0 - 0.1) + cv_new * 0.1).to(buffer_dtype)
+
+
+def qlinear_fakequant_forward(
+    x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], sq_scale: torch.Tensor, w_clip: torch.Tensor,
+    num_bits: int = 8,
+) -> torch.Tensor:  # fmt: skip
+    """QLinear.forward (fms_mo/modules/linear.py:248-305) in eval mode with
+    ``qa_mode="pertokenmax"`` (QMaxDynamic) and ``qw_mode="maxperCh"`` (Qmax per channel with the
+    stored clip values): ``F.linear(Qa(x / s), Qw(W * s), bias)``."""
+    qinput = Q.qmax_dynamic(x / sq_scale, num_bits).to(x.dtype)
+    qweight = Q.perch_fake_quant(weight * sq_scale, w_clip, num_bits).to((weight * sq_scale).dtype).to(weight.dtype)
+    return F.linear(qinput, qweight, bias)
+
+
+@dataclass
+class DeployState:
+    """Buffers of a QLinearINT8Deploy built by from_fms_mo with per-token dynamic activations."""
+
+    weight: torch.Tensor  # int8 [N, K]
+    w_scale: torch.Tensor  # [N]
+    smoothq_scale: torch.Tensor  # [1, K] or [1]
+    bias: torch.Tensor  # [N], weight dtype
+    input_zp: torch.Tensor
+    corr_term: torch.Tensor
+
+
+def deploy_from_fms_mo(
+    weight: torch.Tensor, bias: Optional[torch.Tensor], w_cv: torch.Tensor, act_scale: Optional[torch.Tensor],
+    alpha: float = 0.5, nbits_w: int = 8,
+) -> DeployState:  # fmt: skip
+    """QLinearINT8Deploy.from_fms_mo (fms_mo/modules/linear.py:780-911) for a symmetric dynamic
+    activation quantiser (``use_dynamic_max_act_Qfunc=-1``) and a non-SAWB weight quantiser:
+    SmoothQuant scale, ``w_scale = w_cv * 2 / 254``, int8 weights
+    ``round((W * sq).t() / w_scale).clamp(-127, 127).t()``, zero correction term."""
+    w_levels = 2**nbits_w - 2
+    sq = torch.tensor([1.0], dtype=weight.dtype)
+    if act_scale is not None:
+        w_sq = weight.abs().max(dim=0, keepdim=True)[0].clamp(min=1e-5)
+        # the module keeps alpha as a one-element buffer, so both powers are tensor-tensor pows
+        # (not the sqrt fast path a Python scalar 0.5 would take)
+        alpha_t = torch.tensor([alpha], dtype=torch.float32).to(act_scale.dtype)
+        if torch.all(act_scale != 0).item():
+            sq = (act_scale**alpha_t / w_sq ** (1.0 - alpha_t)).clamp(min=1e-5).to(act_scale.dtype)
+    w_scale = w_cv * 2 / w_levels
+    w_int8 = torch.round((weight * sq).t() / w_scale).clamp(-w_levels / 2, w_levels / 2).t().to(torch.int).to(torch.int8)
+    corr_term = 0 * w_scale.float() * torch.tensor(1.0).float()
+    new_bias = bias.float() - corr_term if bias is not None else -corr_term
+    return DeployState(w_int8, w_scale, sq, new_bias.to(weight.dtype), torch.tensor(127, dtype=torch.int), corr_term)
+
+
+def deploy_forward(
+    st: DeployState, x: torch.Tensor, truncate_lsb: int = 0, chunk_size: int = 100000, max_acc_bits: int = 32,
+    acc_dtype: torch.dtype = torch.float16, return_parts: bool = False,
+):  # fmt: skip
+    """QLinearINT8Deploy.forward with a kernel that chunks internally, i.e. the
+    ``use_int_kernel="triton"`` branch (fms_mo/modules/linear.py:1309-1338, :1115-1188):
+    ``x / smoothq_scale`` -> per-token int8 codes -> chunk-truncating int matmul ->
+    ``(acc.float() * (input_scale * w_scale).to(fp16) + bias).to(acc_dtype)`` -> input dtype."""
+    org_dtype = x.dtype
+    tar_shape = tuple(x.shape[:-1]) + (st.weight.shape[0],)
+    x2 = x.view(-1, x.shape[-1])
+    if torch.all(st.smoothq_scale != 1).item():
+        x2 = x2 / st.smoothq_scale
+    codes, input_scale = Q.qa_dynamic_max_qfunc(x2)
+    acc = G.imatmul_chunk_truncate(
+        codes, st.weight.t(), chunk_trun_bits=truncate_lsb, chunk_size=chunk_size, max_acc_bits=max_acc_bits
+    )
+    out = (acc.float() * (input_scale * st.w_scale).to(torch.float16) + st.bias).to(acc_dtype)
+    out = out.reshape(tar_shape).to(org_dtype)
+    if return_parts:
+        return out, codes, input_scale, acc
+    return out
+
+
+def linear_fpx_forward(
+    x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], trun_bits: int = 0, chunk_size: int = 16,
+    fp8_dyn="per_token", clamp_acc_to_dl16: bool = False, return_parts: bool = False,
+):  # fmt: skip
+    """LinearFuncFPxFwdBwd.forward (fms_mo/modules/linear.py:1902-1975) with dynamic FP8 scaling:
+    e4m3 quantisation of x (per token) and W (per output channel), fp32-accumulated matmul with
+    optional chunk truncation, ``* x_scale * w_scale.t()``, cast to the input dtype, ``+ bias``."""
+    org_dtype = x.dtype
+    target_shape = x.shape[:-1] + (weight.shape[0],)
+    x2 = x.reshape(-1, x.shape[-1])
+    per_tensor = fp8_dyn == "per_tensor"
+    xq, x_scale = Q.fp8_dyn_quant(x2, per_tensor, clamp_acc_to_dl16)
+    wq, w_scale = Q.fp8_dyn_quant(weight, per_tensor, clamp_acc_to_dl16)
+    acc = G.fmatmul_chunk_truncate(
+        xq.to(torch.float32), wq.to(torch.float32).t(), chunk_trun_bits=trun_bits, chunk_size=chunk_size,
+        clamp_acc_to_dl16=clamp_acc_to_dl16,
+    )  # fmt: skip
+    out = (acc * x_scale * w_scale.t()).to(org_dtype).reshape(target_shape)
+    if bias is not None:
+        out = out + bias.to(org_dtype)
+    if return_parts:
+        return out, xq, x_scale, wq, w_scale, acc
+    return out

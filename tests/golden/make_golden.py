@@ -1,0 +1,236 @@
+"""Generates the golden fixtures under tests/golden/ by running fms-model-optimizer itself.
+
+Run once, in a container that has the reference source tree, as
+
+    python tests/golden/make_golden.py /path/to/fms-model-optimizer
+
+It imports ``fms_mo`` from that tree, drives the reference's own classes on CPU with small seeded
+inputs and stores inputs and outputs as ``.pt`` files next to this script.  The tests never import
+the reference; they only read these files.
+
+Where the reference needs a CUDA device (its Triton matmuls), the reference's Python code is run
+unchanged and only the matmul callable is replaced by ``oracle.gemm`` (stated per case below), so
+those files pin the reference's quantise / dequantise chains, not the matmul.
+"""
+
+from __future__ import annotations
+
+import importlib.metadata
+import sys
+from pathlib import Path
+
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+sys.path.insert(0, str(REF))
+sys.path.insert(0, str(ROOT))
+
+_orig_version = importlib.metadata.version
+
+
+def _version(name):  # the reference asks for its own installed version; it runs from source here
+    return "0.0.0" if name == "fms-model-optimizer" else _orig_version(name)
+
+
+importlib.metadata.version = _version
+
+from fms_mo.custom_ext_kernels.utils import imatmul_ops_reg  # noqa: E402
+from fms_mo.modules import linear as ref_linear  # noqa: E402
+from fms_mo.quant import quantizers as ref_q  # noqa: E402
+
+from oracle import gemm as OG  # noqa: E402
+
+
+def save(name, obj):
+    torch.save(obj, HERE / name)
+    print(f"wrote {name}")
+
+
+def gen_quantizers():
+    torch.manual_seed(23)
+    out = {}
+    # PACT+ two-sided, forward and backward
+    cases = []
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        for nbits in (8, 4):
+            for cv, cvn in ((2.5, -2.5), (3.55, -1.75), (6.0, -6.0)):
+                x = (torch.randn(37, 96) * 3).to(dtype).requires_grad_(True)
+                q = ref_q.PACT2(nbits, init_clip_valn=cvn, init_clip_val=cv, dequantize=True, pact_plus=True, align_zero=True)
+                y = q(x)
+                g = torch.randn(37, 96).to(dtype)
+                y.backward(g)
+                cases.append(
+                    dict(dtype=dtype, nbits=nbits, cv=cv, cvn=cvn, x=x.detach().clone(), y=y.detach().clone(), g=g,
+                         gx=x.grad.clone(), gcv=q.clip_val.grad.clone(), gcvn=q.clip_valn.grad.clone())
+                )  # fmt: skip
+    out["pact2"] = cases
+    # SAWB+ per channel (training mode) and Qmax per channel
+    cases = []
+    for dtype in (torch.float32, torch.bfloat16):
+        for nbits in (8, 4):
+            w = (torch.randn(48, 80) * 0.05).to(dtype)
+            q = ref_q.SAWB(nbits, dequantize=True, align_zero=True, perCh=48)
+            q.train()
+            y = q(w)
+            q2 = ref_q.SAWB(nbits, dequantize=False, align_zero=True, perCh=48)
+            q2.train()
+            codes = q2(w.float())
+            cases.append(dict(dtype=dtype, nbits=nbits, w=w, y=y.clone(), clip=q.clip_val.clone(), codes=codes.clone(),
+                              clip_f32=q2.clip_val.clone()))  # fmt: skip
+    out["sawb_perch"] = cases
+    cases = []
+    for dtype in (torch.float32, torch.bfloat16):
+        w = (torch.randn(48, 80) * 0.05).to(dtype)
+        q = ref_q.Qmax(8, align_zero=True, perCh=48)
+        q.train()
+        y = q(w)
+        clip_after_train = q.clip_val.clone()
+        q.eval()
+        y_eval = q(w)
+        cases.append(dict(dtype=dtype, w=w, y_train=y.clone(), clip_after_train=clip_after_train, y_eval=y_eval.clone()))
+    out["qmax_perch"] = cases
+    # per-token dynamic max (fake quant)
+    cases = []
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        x = torch.randn(33, 80).to(dtype)
+        x[5] = 0
+        x[7] *= 1e-7
+        x[:, 11] *= 20
+        q = ref_q.QMaxDynamic(8, dim=-1)
+        cases.append(dict(dtype=dtype, x=x, y=q(x).clone()))
+    out["qmax_dynamic"] = cases
+    save("quantizers.pt", out)
+
+
+def build_ref_qlinear(K, N, dtype, x_cal, alpha=0.5, bias=True):
+    qcfg = {"smoothq": True, "smoothq_alpha": alpha}
+    lin = ref_linear.QLinear(K, N, bias=bias, num_bits_feature=8, qa_mode="pertokenmax", num_bits_weight=8,
+                             qw_mode="maxperCh", qcfg=qcfg, device="cpu")  # fmt: skip
+    with torch.no_grad():
+        lin.weight.copy_(torch.randn(N, K) * 0.02)
+        if bias:
+            lin.bias.copy_(torch.randn(N) * 0.01)
+    lin = lin.to(dtype)
+    lin.set_act_scale(x_cal.float().abs().amax(0))
+    return lin
+
+
+def make_x(M, K, dtype):
+    x = torch.randn(M, K)
+    cols = torch.randperm(K)[: max(1, K // 100)]
+    x[:, cols] *= 20
+    return x.to(dtype)
+
+
+def gen_qlinear():
+    torch.manual_seed(0)
+    cases = []
+    for dtype in (torch.float32, torch.bfloat16):
+        M, K, N = 40, 128, 96
+        x = make_x(M, K, dtype)
+        lin = build_ref_qlinear(K, N, dtype, x)
+        lin.train()
+        with torch.no_grad():
+            y_train = lin(x)
+        lin.eval()
+        with torch.no_grad():
+            y_eval = lin(x)
+            sq = lin.get_smoothq_scale(x)
+        cases.append(dict(dtype=dtype, x=x, weight=lin.weight.detach().clone(), bias=lin.bias.detach().clone(),
+                          act_scale=lin.smoothq_act_scale.clone(), alpha=0.5, sq=sq.clone(),
+                          w_clip=lin.quantize_weight.clip_val.clone(), y_train=y_train.clone(), y_eval=y_eval.clone()))  # fmt: skip
+    save("qlinear_fakequant.pt", dict(cases=cases))
+
+
+_mm = {"fn": None}
+
+
+def _dispatch_mm(m1, m2):
+    return _mm["fn"](m1, m2)
+
+
+def gen_deploy():
+    """QLinearINT8Deploy.from_fms_mo + forward.  fms_mo::imatmul is registered with a dispatcher:
+    (a) ``kernel``: the reference runs its use_int_kernel="triton" code path and the matmul callable
+        is oracle.gemm.imatmul_chunk_truncate (the Triton kernel cannot run without a GPU);
+    (b) ``torch_loop``: the reference's own PyTorch chunk loop (iaddmm_int) with a plain integer
+        matmul as callable -- entirely reference arithmetic."""
+    torch.manual_seed(1)
+    imatmul_ops_reg("triton", mm_func=_dispatch_mm)
+    cases = []
+    for dtype in (torch.float32, torch.bfloat16):
+        M, K, N = 40, 256, 96
+        x = make_x(M, K, dtype)
+        lin = build_ref_qlinear(K, N, dtype, x)
+        lin.train()
+        with torch.no_grad():
+            lin(x)
+        lin.eval()
+        for trun, chunk, accb in ((0, 100000, 32), (8, 64, 32), (4, 32, 32), (8, 64, 20)):
+            dep = ref_linear.QLinearINT8Deploy.from_fms_mo(
+                lin, use_int_kernel="triton", use_dynamic_max_act_Qfunc=-1, truncate_lsb=trun, chunk_size=chunk,
+                max_acc_bits=accb, target_device="cpu",
+            )  # fmt: skip
+            # (a) kernel path
+            dep.use_int_kernel = "triton"
+            dep.iaddmm = dep.iaddmm_int
+            _mm["fn"] = lambda m1, m2: OG.imatmul_chunk_truncate(m1, m2, chunk_trun_bits=trun, chunk_size=chunk, max_acc_bits=accb)
+            y_kernel = dep(x.reshape(5, 8, K))
+            # (b) reference torch loop
+            dep.use_int_kernel = "cutlass"
+            _mm["fn"] = lambda m1, m2: (m1.double() @ m2.double()).to(torch.int32)
+            y_loop = dep(x.reshape(5, 8, K))
+            cases.append(dict(dtype=dtype, x=x, weight=lin.weight.detach().clone(), bias=lin.bias.detach().clone(),
+                              act_scale=lin.smoothq_act_scale.clone(), w_cv=lin.quantize_weight.clip_val.clone(),
+                              trun=trun, chunk=chunk, accb=accb, w_int8=dep.weight.detach().clone(),
+                              w_scale=dep.w_scale.clone(), smoothq_scale=dep.smoothq_scale.clone(),
+                              dep_bias=dep.bias.clone(), y_kernel=y_kernel.clone(), y_loop=y_loop.clone()))  # fmt: skip
+    save("deploy_int8.pt", dict(cases=cases))
+
+
+def gen_fp8():
+    """LinearFPxAcc forward: the reference's autograd function runs unchanged; its ``tl_matmul``
+    callable is replaced by oracle.gemm.fmatmul_chunk_truncate."""
+    torch.manual_seed(2)
+
+    def tl_matmul(a, b, chunk_trun_bits=0, chunk_size=16, clamp_acc_to_dl16=False, **kw):
+        return OG.fmatmul_chunk_truncate(a, b, chunk_trun_bits=chunk_trun_bits, chunk_size=chunk_size,
+                                         clamp_acc_to_dl16=clamp_acc_to_dl16)  # fmt: skip
+
+    ref_linear.tl_matmul = tl_matmul
+    cases = []
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        for trun, chunk, dl16, bias in ((0, 16, False, False), (0, 64, False, True), (8, 64, False, True), (0, 64, True, False)):
+            M, K, N = 24, 192, 80
+            x = torch.randn(M, K).to(dtype)
+            x[3] = 0
+            nn_lin = torch.nn.Linear(K, N, bias=bias).to(dtype)
+            with torch.no_grad():
+                nn_lin.weight.copy_(torch.randn(N, K).to(dtype))
+            lin = ref_linear.LinearFPxAcc.from_nn(nn_lin, trun_bits=trun, chunk_size=chunk, dynamic_fp8="per_token",
+                                                  clamp_acc_to_dl16=dl16, target_device="cpu")  # fmt: skip
+            with torch.no_grad():
+                y = lin(x.reshape(2, 12, K))
+            cases.append(dict(dtype=dtype, trun=trun, chunk=chunk, dl16=dl16, x=x, weight=nn_lin.weight.detach().clone(),
+                              bias=None if not bias else nn_lin.bias.detach().clone(), y=y.clone()))  # fmt: skip
+    save("linear_fp8.pt", dict(cases=cases))
+
+
+def gen_aiu_vectors():
+    """The six W8A8 golden vectors of the reference's test-suite (tests/artifacts/aiu_addons),
+    re-saved as one file: inputs and expected output of fms_mo::i8i8_aiu with smoothquant off."""
+    out = {}
+    art = REF / "tests" / "artifacts" / "aiu_addons"
+    for f in sorted(art.glob("ref_w-*_a-*_sq-N.pt")):
+        out[f.stem] = torch.load(f, weights_only=True)
+    save("aiu_i8i8_vectors.pt", out)
+
+
+if __name__ == "__main__":
+    gen_quantizers()
+    gen_qlinear()
+    gen_deploy()
+    gen_fp8()
+    gen_aiu_vectors()

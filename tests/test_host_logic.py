@@ -1,0 +1,71 @@
+"""CPU tests of the host-side logic: module construction mirrors the reference's buffers, the chunk
+normalisation matches, and modules refuse to run without a CUDA device."""
+
+import pytest
+import torch
+
+from conftest import load_golden
+from fms_model_optimizer_b200.modules import QLinear, QLinearINT8Deploy
+from fms_model_optimizer_b200.modules.linear import _normalised_chunk
+from oracle import gemm as OG
+
+
+class _RefLikeQmax(torch.nn.Module):
+    def __init__(self, clip):
+        super().__init__()
+        self.register_buffer("clip_val", clip)
+
+    def forward(self, w):
+        return w
+
+
+class _RefLikeQLinear(torch.nn.Linear):
+    """Carries the attributes from_fms_mo reads from the reference's QLinear."""
+
+    def __init__(self, c):
+        N, K = c["weight"].shape
+        super().__init__(K, N, bias=True)
+        with torch.no_grad():
+            self.weight = torch.nn.Parameter(c["weight"].clone())
+            self.bias = torch.nn.Parameter(c["bias"].clone())
+        self.num_bits_feature = 8
+        self.num_bits_weight = 8
+        self.qa_mode = "pertokenmax"
+        self.qw_mode = "maxperCh"
+        self.quantize_feature = torch.nn.Identity()
+        self.quantize_weight = _RefLikeQmax(c["w_cv"].clone())
+        self.smoothq = True
+        self.register_buffer("smoothq_act_scale", c["act_scale"].clone())
+        self.register_buffer("smoothq_alpha", torch.tensor([0.5], dtype=torch.float32).to(c["act_scale"].dtype))
+
+
+def test_from_fms_mo_reproduces_reference_buffers():
+    for c in load_golden("deploy_int8.pt")["cases"]:
+        q = QLinearINT8Deploy.from_fms_mo(
+            _RefLikeQLinear(c), use_dynamic_max_act_Qfunc=-1, truncate_lsb=c["trun"], chunk_size=c["chunk"],
+            max_acc_bits=c["accb"], target_device="cpu",
+        )
+        assert q.weight.dtype == torch.int8 and torch.equal(q.weight, c["w_int8"])
+        assert torch.equal(q.w_scale, c["w_scale"])
+        assert torch.equal(q.smoothq_scale, c["smoothq_scale"])
+        assert torch.equal(q.bias, c["dep_bias"])
+        assert set(dict(q.named_buffers())) >= {"input_scale", "input_zp", "w_scale", "w_zp", "smoothq_scale", "corr_term", "bias"}
+        with pytest.raises(RuntimeError, match="CUDA"):
+            q(c["x"])
+
+
+def test_chunk_normalisation_matches_oracle_statement():
+    for cs in (1, 8, 16, 31, 32, 33, 48, 64, 100, 128, 1000, 4096, 100000):
+        if cs == 8:
+            continue
+        assert _normalised_chunk(cs) == OG.normalise_chunk_size(cs)
+
+
+def test_qlinear_constructs_on_cpu_and_refuses_to_run():
+    lin = QLinear(64, 32, num_bits_feature=8, qa_mode="pact+", num_bits_weight=8, qw_mode="sawb+perCh",
+                  qcfg={"smoothq": False}, device="cpu", act_clip_init_val=6.0, act_clip_init_valn=-6.0)
+    assert type(lin.quantize_feature).__name__ == "PACT2"
+    assert type(lin.quantize_weight).__name__ == "SAWB"
+    assert float(lin.quantize_feature.clip_val) == 6.0 and float(lin.quantize_feature.clip_valn) == -6.0
+    with pytest.raises(RuntimeError):
+        lin(torch.randn(4, 64))

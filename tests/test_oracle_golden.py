@@ -1,0 +1,161 @@
+"""The oracle against outputs of fms-model-optimizer itself (tests/golden/*.pt, produced by
+tests/golden/make_golden.py) and against the reference test-suite's own W8A8 golden vectors."""
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from conftest import load_golden
+from oracle import gemm as OG
+from oracle import qlinear as OL
+from oracle import quantizers as OQ
+
+
+def test_pact2_fwd_bwd_matches_reference():
+    for c in load_golden("quantizers.pt")["pact2"]:
+        cv, cvn = torch.tensor([c["cv"]]), torch.tensor([c["cvn"]])
+        y = OQ.pact2plus_fwd(c["x"], cv, cvn, c["nbits"], True)
+        assert torch.equal(y, c["y"]), (c["dtype"], c["nbits"], c["cv"])
+        gx, gcv, gcvn = OQ.pact2plus_bwd(c["x"], c["g"], cv, cvn, c["nbits"], True)
+        assert torch.equal(gx, c["gx"])
+        assert torch.equal(gcv.reshape(1).float(), c["gcv"].float())
+        assert torch.equal(gcvn.reshape(1).float(), c["gcvn"].float())
+
+
+def test_sawb_perch_matches_reference():
+    for c in load_golden("quantizers.pt")["sawb_perch"]:
+        y, clip = OQ.sawb_perch(c["w"], c["nbits"], dequantize=True)
+        assert torch.equal(clip, c["clip"])
+        assert torch.equal(y, c["y"])
+        codes, clip32 = OQ.sawb_perch(c["w"].float(), c["nbits"], dequantize=False)
+        assert torch.equal(clip32, c["clip_f32"])
+        assert torch.equal(codes, c["codes"])
+
+
+def test_qmax_perch_matches_reference():
+    for c in load_golden("quantizers.pt")["qmax_perch"]:
+        y, clip = OQ.qmax_perch(c["w"], 8)
+        assert torch.equal(y, c["y_train"])
+        latched = OL.qmax_clip_after_first_train_forward(c["w"], torch.float32)
+        assert torch.equal(latched, c["clip_after_train"])
+        y_eval = OQ.perch_fake_quant(c["w"], latched, 8).to(c["w"].dtype)
+        assert torch.equal(y_eval, c["y_eval"])
+
+
+def test_qmax_dynamic_matches_reference():
+    for c in load_golden("quantizers.pt")["qmax_dynamic"]:
+        assert torch.equal(OQ.qmax_dynamic(c["x"], 8), c["y"])
+
+
+def test_qlinear_fakequant_matches_reference():
+    for c in load_golden("qlinear_fakequant.pt")["cases"]:
+        sq = OL.smoothq_scale(c["act_scale"], c["weight"], c["alpha"], c["x"].dtype)
+        assert torch.equal(sq, c["sq"])
+        w_clip = OL.qmax_clip_after_first_train_forward(c["weight"] * sq)
+        assert torch.equal(w_clip, c["w_clip"])
+        y = OL.qlinear_fakequant_forward(c["x"], c["weight"], c["bias"], sq, w_clip)
+        assert torch.equal(y, c["y_eval"])
+
+
+def test_deploy_matches_reference():
+    for c in load_golden("deploy_int8.pt")["cases"]:
+        st = OL.deploy_from_fms_mo(c["weight"], c["bias"], c["w_cv"], c["act_scale"], 0.5)
+        assert torch.equal(st.weight, c["w_int8"])
+        assert torch.equal(st.w_scale, c["w_scale"])
+        assert torch.equal(st.smoothq_scale, c["smoothq_scale"])
+        assert torch.equal(st.bias, c["dep_bias"])
+        x3 = c["x"].reshape(5, 8, -1)
+        y, codes, in_scale, acc = OL.deploy_forward(
+            st, x3, truncate_lsb=c["trun"], chunk_size=c["chunk"], max_acc_bits=c["accb"], return_parts=True
+        )
+        assert torch.equal(y, c["y_kernel"])
+        # The reference's own PyTorch chunk loop (iaddmm_int, linear.py:1142-1175) keeps the
+        # accumulator shifted right by t bits and rescales by 2^t at the end; when chunking is
+        # active its output must follow from the oracle's truncated accumulator.
+        K = c["x"].shape[-1]
+        if K > c["chunk"]:
+            chunk = c["chunk"]
+            acc_loop = torch.zeros_like(acc)
+            rb = (1 << (c["trun"] - 1)) if c["trun"] > 0 else 0
+            lo, hi = -(1 << (c["accb"] - 1)), (1 << (c["accb"] - 1)) - 1
+            for k0 in range(0, K, chunk):
+                p = (codes[:, k0 : k0 + chunk].double() @ st.weight.t()[k0 : k0 + chunk].double()).to(torch.int32)
+                if c["accb"] < 32:
+                    p = p.clamp(lo, hi)
+                if c["trun"] > 0:
+                    p = torch.bitwise_right_shift(p + rb, c["trun"])
+                acc_loop += p
+            assert torch.equal(acc_loop << c["trun"], acc), "oracle chunk GEMM differs from the torch-loop arithmetic"
+            y_loop = (acc_loop * ((1 << c["trun"]) * in_scale * st.w_scale) + st.bias).to(torch.float16)
+            y_loop = y_loop.reshape(5, 8, -1).to(c["x"].dtype)
+            assert torch.equal(y_loop, c["y_loop"])
+
+
+def test_linear_fp8_matches_reference():
+    for c in load_golden("linear_fp8.pt")["cases"]:
+        y = OL.linear_fpx_forward(
+            c["x"].reshape(2, 12, -1), c["weight"], c["bias"], trun_bits=c["trun"], chunk_size=c["chunk"],
+            clamp_acc_to_dl16=c["dl16"],
+        )
+        assert torch.equal(y, c["y"]), (c["dtype"], c["trun"], c["chunk"], c["dl16"])
+
+
+def _aiu_i8i8(x, weight, bias, qdata, wtype, atype):
+    """fms_mo::i8i8_aiu (fms_mo/aiu_addons/i8i8/i8i8_aiu_op.py:180-231) with smoothquant off, restated
+    through the oracle's pieces: activations quantised symmetric per tensor / per token with codes
+    clamped to +-127, int8 weights dequantised with w_cv / 127, fp16 linear."""
+    out_feat, in_feat = weight.shape
+    n_w = 1 if wtype == "per_tensor" else out_feat
+    w_cv = qdata[:n_w]
+    a_cv, a_cvn = qdata[2 * n_w : 2 * n_w + 1], qdata[2 * n_w + 1 : 2 * n_w + 2]
+    sq = qdata[-1:]
+    if atype == "per_tensor_symm":
+        scale_x = 127 / a_cv
+        x_dq = torch.round(x / sq * scale_x).clamp(-127, 127).to(torch.int8).div(scale_x).mul(sq)
+    elif atype == "per_tensor_asymm":
+        scale_x = 255 / (a_cv - a_cvn)
+        zp_x = a_cvn * scale_x
+        x_dq = torch.round(x / sq * scale_x - zp_x).clamp(0, 255).add(zp_x).div(scale_x).mul(sq)
+    else:
+        x_sq = x / sq
+        scale_x = 127 / x_sq.abs().max(dim=-1, keepdim=True)[0]
+        x_dq = torch.round(x_sq * scale_x).clamp(-127, 127).div(scale_x).mul(sq)
+    w = weight * (w_cv if wtype == "per_tensor" else w_cv.unsqueeze(1)) / 127 / sq
+    return F.linear(x_dq.to(x.dtype), w.to(x.dtype), bias.to(x.dtype))
+
+
+def test_reference_w8a8_golden_vectors():
+    vecs = load_golden("aiu_i8i8_vectors.pt")
+    assert len(vecs) == 6
+    for name, d in vecs.items():
+        wtype = "per_tensor" if "w-per_tensor" in name else "per_channel"
+        atype = name.split("_a-")[1].split("_sq")[0]
+        x = d["x"].to(torch.float16)
+        out = _aiu_i8i8(x, d["w_int"], d["bias"], d["qdata"].to(torch.float16), wtype, atype)
+        assert torch.all((out - d["reference_out"]).abs() < 1e-4), name
+        if atype == "per_token":
+            # the per-token codes of this sibling definition equal the deploy quantiser's codes
+            # wherever multiply-by-reciprocal and divide round alike (checked, not assumed)
+            codes, _ = OQ.qa_dynamic_max_qfunc(x.reshape(-1, x.shape[-1]).float())
+            x2 = x.reshape(-1, x.shape[-1]).float()
+            alt = torch.round(x2 * (127 / x2.abs().max(dim=-1, keepdim=True)[0])).clamp(-127, 127).to(torch.int8)
+            assert (codes != alt).float().mean() < 0.05
+
+
+def test_chunk_gemm_properties():
+    """Properties the reference's own GPU tests state for the truncating matmul
+    (tests/triton_kernels/test_triton_mm.py:85-123), on the oracle."""
+    torch.manual_seed(0)
+    a = torch.randint(-128, 127, (64, 256), dtype=torch.int8)
+    b = torch.randint(-128, 127, (256, 64), dtype=torch.int8)
+    exact = (a.double() @ b.double())
+    plain = OG.imatmul_chunk_truncate(a, b, chunk_size=32).double()
+    assert torch.equal(plain, exact)
+
+    def rel(t):
+        return (torch.norm(t.double() - exact) / torch.norm(exact)).item()
+
+    e32 = rel(OG.imatmul_chunk_truncate(a, b, chunk_trun_bits=8, chunk_size=32))
+    e128 = rel(OG.imatmul_chunk_truncate(a, b, chunk_trun_bits=8, chunk_size=128))
+    assert e32 < 1e-2 and e128 < 1e-2
+    assert rel(OG.imatmul_chunk_truncate(a, b, max_acc_bits=18, chunk_size=32)) < 1e-2
