@@ -1,0 +1,467 @@
+"""Benchmark of the W8A8 quantized-Linear hot path on B200.
+
+Default workload ("c5"): prefill of a Llama-3-8B-shaped decoder (32 layers, hidden 4096, 32 q / 8 kv
+heads of 128, SwiGLU FFN 14336, RMSNorm, RoPE theta 5e5, vocab 128256) whose every Linear inside the
+decoder layers is W8A8 SmoothQuant INT8 (alpha 0.5, per-channel weights, per-token activations), on a
+batch of 8 x 2048 random token ids.  With N > 1 GPUs the Linears are sharded column / row parallel
+(tensor parallel), one process per GPU, NCCL all-reduce at the row-parallel boundaries; the total
+work is fixed, so scaling is "strong".
+
+    python bench.py --gpus N --steps K --warmup W                  # this implementation
+    python bench.py --impl reference --gpus N --steps K --warmup W # reference CPU fake-quant path
+
+One JSON line is printed by rank 0.  `value` is tokens/s of the whole job with the token ids
+already on the device; `e2e` is the same with the ids copied from pinned host memory and the
+next-token ids copied back inside the timed region.  `roofline` is the int8 GEMM kernel (all its
+launches in the timed region, timed with CUDA events on the launching stream); `cpu_baseline` is
+the reference's CPU fake-quant arithmetic (QLinear.forward: per-token / per-channel fake quantise +
+F.linear) for one decoder layer on a bounded token sample, extrapolated to the 32 layers.
+
+Other workloads, for single kernels: --workload c1 | c2 | c3 (TOPS of one quantized Linear / GEMM).
+Weights and activations are synthetic (seeded); nothing is read from disk.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LLAMA = dict(layers=32, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=128256, rope_theta=500000.0,
+             batch=8, seq=2048)  # fmt: skip
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm=d["hbm_gbs"], bf16=d["bf16_tflops"], bf16_sustained=d["bf16_tflops_sustained"], src="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, src="fallback")
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")  # fmt: skip
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )  # fmt: skip
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        busy = [v for v in sm if smax and v > 0.3 * smax] or sm
+        med = busy[len(busy) // 2] if busy else None
+        return {"sm_mhz": med, "sm_max_mhz": smax, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# synthetic W8A8 decoder
+# ------------------------------------------------------------------------------------------------
+def synth_w8a8(n, k, seed, dev, dtype=torch.bfloat16):
+    """Random-init Linear [n, k] (N(0, 0.02)) turned into W8A8 SmoothQuant buffers the way
+    QLinearINT8Deploy.from_fms_mo does it (fms_mo/modules/linear.py:799-871): synthetic activation
+    scales (1% outlier channels x20), smoothing scale with alpha 0.5, per-channel max weight scale,
+    int8 codes."""
+    g = torch.Generator(device=dev).manual_seed(seed)
+    w = (torch.randn(n, k, generator=g, device=dev) * 0.02).to(dtype)
+    act = torch.full((k,), 4.0, device=dev)
+    idx = torch.randperm(k, generator=g, device=dev)[: max(1, k // 100)]
+    act[idx] *= 20
+    act = act.to(dtype)
+    w_sq = w.abs().max(dim=0, keepdim=True)[0].clamp(min=1e-5)
+    smooth = (act**0.5 / w_sq**0.5).clamp(min=1e-5).to(dtype)
+    ws = w * smooth
+    w_cv = ws.abs().max(dim=1).values
+    w_scale = w_cv * 2 / 254
+    codes = torch.round(ws.t() / w_scale).clamp(-127, 127).t().to(torch.int8).contiguous()
+    return codes, w_scale.float(), smooth.reshape(-1).float()
+
+
+class Decoder:
+    """Llama-shaped decoder whose Linears are ``tp.W8A8Linear``; norms, RoPE, attention and SwiGLU
+    are plain PyTorch ops on the device (they are not part of the quantized-Linear path)."""
+
+    def __init__(self, cfg, dev, world, rank, layers=None):
+        from fms_model_optimizer_b200 import tp
+
+        self.cfg = cfg
+        self.dev = dev
+        self.world = world
+        H, hd = cfg["hidden"], cfg["head_dim"]
+        self.nq, self.nkv = cfg["q_heads"] // world, cfg["kv_heads"] // world
+        nl = layers if layers is not None else cfg["layers"]
+        self.layers = []
+        for li in range(nl):
+            lin = {}
+            for ni, (name, (n, k, mode)) in enumerate(dict(
+                q=(cfg["q_heads"] * hd, H, "column"), k=(cfg["kv_heads"] * hd, H, "column"), v=(cfg["kv_heads"] * hd, H, "column"),
+                o=(H, cfg["q_heads"] * hd, "row"), gate=(cfg["ffn"], H, "column"), up=(cfg["ffn"], H, "column"),
+                down=(H, cfg["ffn"], "row"),
+            ).items()):  # fmt: skip
+                codes, w_scale, smooth = synth_w8a8(n, k, 1000 * li + ni, dev)
+                wt, sc, sm, _ = tp.shard_w8a8(codes, w_scale, smooth, None, mode, world, rank)
+                lin[name] = tp.W8A8Linear(wt, sc, sm, None, mode=mode if world > 1 else "replicate")
+                del codes
+            lin["ln1"] = torch.ones(H, device=dev, dtype=torch.bfloat16)
+            lin["ln2"] = torch.ones(H, device=dev, dtype=torch.bfloat16)
+            self.layers.append(lin)
+        g = torch.Generator(device=dev).manual_seed(4)
+        self.embed = (torch.randn(cfg["vocab"], H, generator=g, device=dev) * 0.02).bfloat16()
+        self.lm_head = (torch.randn(cfg["vocab"], H, generator=g, device=dev) * 0.02).bfloat16()
+        self.norm = torch.ones(H, device=dev, dtype=torch.bfloat16)
+        S = cfg["seq"]
+        inv = 1.0 / (cfg["rope_theta"] ** (torch.arange(0, hd, 2, device=dev).float() / hd))
+        ang = torch.outer(torch.arange(S, device=dev).float(), inv)
+        self.cos = torch.cat([ang.cos(), ang.cos()], -1).bfloat16()[None, None]
+        self.sin = torch.cat([ang.sin(), ang.sin()], -1).bfloat16()[None, None]
+
+    def _rope(self, x):
+        x1, x2 = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2 :]
+        return x * self.cos + torch.cat((-x2, x1), dim=-1) * self.sin
+
+    @torch.no_grad()
+    def forward(self, ids):
+        cfg = self.cfg
+        B, S = ids.shape
+        hd = cfg["head_dim"]
+        x = F.embedding(ids, self.embed).view(B * S, -1)
+        for lin in self.layers:
+            h = F.rms_norm(x, (x.shape[-1],), lin["ln1"], 1e-5)
+            q = lin["q"](h).view(B, S, self.nq, hd).transpose(1, 2)
+            k = lin["k"](h).view(B, S, self.nkv, hd).transpose(1, 2)
+            v = lin["v"](h).view(B, S, self.nkv, hd).transpose(1, 2)
+            q, k = self._rope(q), self._rope(k)
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+            a = a.transpose(1, 2).reshape(B * S, self.nq * hd)
+            x = x + lin["o"](a)
+            h = F.rms_norm(x, (x.shape[-1],), lin["ln2"], 1e-5)
+            m = F.silu(lin["gate"](h)) * lin["up"](h)
+            x = x + lin["down"](m)
+        last = F.rms_norm(x.view(B, S, -1)[:, -1], (x.shape[-1],), self.norm, 1e-5)
+        logits = last @ self.lm_head.t()
+        return logits.argmax(-1)
+
+
+def decoder_linear_ops(cfg, tokens, layers=None):
+    hd, H = cfg["head_dim"], cfg["hidden"]
+    per_layer = H * (cfg["q_heads"] * hd) * 2 + 2 * H * (cfg["kv_heads"] * hd) + 3 * H * cfg["ffn"]
+    return 2.0 * per_layer * tokens * (layers if layers is not None else cfg["layers"])
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline: the reference's fake-quant QLinear arithmetic (oracle port)
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_layer_tokens_per_s(tokens: int, steps: int, warmup: int, cfg=LLAMA):
+    """Times the seven QLinear fake-quant forwards of one decoder layer (QLinear.forward,
+    fms_mo/modules/linear.py:248-305, with qa_mode pertokenmax / qw_mode maxperCh / SmoothQuant) on
+    `tokens` tokens with all host threads and returns (tokens/s of a 32-layer prefill, seconds per
+    step, threads).  Only the quantized Linears are timed, as they are the path being replaced."""
+    from oracle import qlinear as OL
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    hd, H = cfg["head_dim"], cfg["hidden"]
+    shapes = [(cfg["q_heads"] * hd, H), (cfg["kv_heads"] * hd, H), (cfg["kv_heads"] * hd, H), (H, cfg["q_heads"] * hd),
+              (cfg["ffn"], H), (cfg["ffn"], H), (H, cfg["ffn"])]  # fmt: skip
+    g = torch.Generator().manual_seed(4)
+    mods = []
+    for n, k in shapes:
+        w = (torch.randn(n, k, generator=g) * 0.02).bfloat16()
+        act = torch.full((k,), 4.0).bfloat16()
+        sq = OL.smoothq_scale(act, w, 0.5, torch.bfloat16)
+        clip = OL.qmax_clip_after_first_train_forward(w * sq)
+        x = torch.randn(tokens, k, generator=g).bfloat16()
+        mods.append((x, w, sq, clip))
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        for x, w, sq, clip in mods:
+            OL.qlinear_fakequant_forward(x, w, None, sq, clip)
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+    per_step = sum(times) / len(times)
+    return tokens / (per_step * cfg["layers"]), per_step, torch.get_num_threads()
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    tokens = 256
+    tps, per_step, threads = cpu_reference_layer_tokens_per_s(tokens, args.steps, max(1, min(args.warmup, 1)))
+    sample = (f"one decoder layer (7 QLinear fake-quant forwards, bf16) on {tokens} tokens per step, "
+              f"tokens/s = {tokens} / (step time x 32 layers)")  # fmt: skip
+    line = {
+        "impl": "reference", "metric": "w8a8_llama3_8b_prefill_tokens_per_s", "value": tps, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "c5: Llama-3-8B-shaped W8A8 prefill 8x2048", "hardware": "host CPU"},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
+def run_c5(args, rank, world, dev):
+    from fms_model_optimizer_b200 import ops
+
+    cfg = dict(LLAMA)
+    model = Decoder(cfg, dev, world, rank, layers=args.layers)
+    nl = len(model.layers)
+    B, S = cfg["batch"], cfg["seq"]
+    tokens = B * S
+    g = torch.Generator().manual_seed(4)
+    ids_host = torch.randint(0, cfg["vocab"], (B, S), generator=g).pin_memory()
+    ids_dev = ids_host.to(dev)
+    out_host = torch.empty(B, dtype=torch.int64).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        model.forward(ids_dev)
+    barrier()
+    ops.check_status(dev)
+
+    # ---- timed region: device-resident inputs; every GEMM launch bracketed by events
+    sampler = ClockSampler(dev.index)
+    if rank == 0:
+        sampler.start()
+    ops.PROFILE = []
+    ops.LAUNCHES = 0
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        model.forward(ids_dev)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    prof, ops.PROFILE = ops.PROFILE, None
+    launches = ops.LAUNCHES
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.item()
+
+    # ---- end to end: ids from pinned host memory, next-token ids back to the host, every step
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        ids_d = ids_host.to(dev, non_blocking=True)
+        out = model.forward(ids_d)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_e2e = t.item()
+    ops.check_status(dev)
+    if rank != 0:
+        return
+
+    pk = peaks()
+    gemm_ms = sum(a.elapsed_time(b) for (name, a, b, work) in prof if name == "gemm")
+    gemm_ops = sum(work for (name, a, b, work) in prof if name == "gemm")
+    n_gemm = sum(1 for p in prof if p[0] == "gemm")
+    quant_ms = sum(a.elapsed_time(b) for (name, a, b, work) in prof if name == "act_quant")
+    quant_bytes = sum(work for (name, a, b, work) in prof if name == "act_quant")
+    achieved = gemm_ops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    peak = 2.0 * pk["bf16_sustained"]
+    line = {
+        "metric": "w8a8_llama3_8b_prefill_tokens_per_s", "value": tokens * args.steps / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {
+            "workload": "c5: Llama-3-8B-shaped decoder, all decoder Linears W8A8 SmoothQuant INT8, prefill 8x2048",
+            "layers": nl, "global_batch": B, "seq_len": S, "parallelism": f"tp{world}",
+            "l2": "inputs larger than L2 (activations 134 MB per Linear, weights 7 GB)",
+            "linear_tops": decoder_linear_ops(cfg, tokens, nl) * args.steps / (ms * 1e-3) / 1e12,
+        },
+        "roofline": {
+            "bound": "tensor", "kernel": "qlin_gemm_kernel<int8>", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": achieved / peak if peak else None, "traffic": None, "launches": n_gemm,
+            "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({pk['src']}); no 8-bit peak was measured; "
+                           f"datasheet dense int8 4500 TOPS -> frac {achieved / 4500.0:.3f}",
+            "gemm_share_of_step": gemm_ms / ms if ms else None,
+            "act_quant_gbs": quant_bytes / (quant_ms * 1e-3) / 1e9 if quant_ms > 0 else None,
+            "act_quant_share_of_step": quant_ms / ms if ms else None,
+        },
+        "e2e": {"value": tokens * args.steps / (ms_e2e * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": ids_host.numel() * ids_host.element_size(), "d2h_bytes_per_step": out_host.numel() * 8},
+        "gpu_launches": launches,
+        "clocks": clocks,
+    }  # fmt: skip
+    if world == 1 and not args.no_cpu_baseline:
+        tok = 256
+        tps, per_step, threads = cpu_reference_layer_tokens_per_s(tok, 2, 1)
+        line["cpu_baseline"] = {
+            "value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"one decoder layer (7 QLinear fake-quant forwards, bf16) on {tok} tokens, {per_step:.2f} s per step, "
+                      f"extrapolated to 32 layers",
+        }  # fmt: skip
+    print(json.dumps(line), flush=True)
+
+
+def run_kernel_workload(args, dev):
+    """Single-kernel workloads: c1 (W8A8 Linear 2048x4096x4096), c2 (chunk-truncated int8 GEMM
+    4096x8192x4096, chunk 64, 8 bits), c3 (FP8 Linear sweep).  Prints one JSON line per shape."""
+    from fms_model_optimizer_b200 import _lib as L, ops
+
+    pk = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timeit(fn, steps, warmup):
+        for _ in range(max(warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        tot = 0.0
+        for _ in range(steps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            tot += e0.elapsed_time(e1)
+        return tot / steps
+
+    cases = []
+    if args.workload == "c1":
+        torch.manual_seed(0)
+        M, K, N = 2048, 4096, 4096
+        x = torch.randn(M, K, device=dev).bfloat16()
+        codes, w_scale, smooth = synth_w8a8(N, K, 0, dev)
+        from fms_model_optimizer_b200 import tp
+
+        lin = tp.W8A8Linear(codes, w_scale, smooth, torch.zeros(N, device=dev))
+        cases.append((f"c1 W8A8 INT8 Linear {M}x{K}x{N} (quantise + GEMM + dequantise)", 2.0 * M * N * K, lambda: lin(x), "int8"))
+    elif args.workload == "c2":
+        torch.manual_seed(1)
+        M, K, N = 4096, 8192, 4096
+        a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
+        b = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev)
+        out = torch.empty((M, N), dtype=torch.int32, device=dev)
+        cases.append((f"c2 int8 chunk-truncated GEMM {M}x{K}x{N}, chunk 64, 8 bits", 2.0 * M * N * K,
+                      lambda: ops.gemm(a, b, out=out, chunk_k=64, trun_bits=8), "int8"))  # fmt: skip
+    else:
+        torch.manual_seed(2)
+        from fms_model_optimizer_b200.modules import LinearFPxAcc
+
+        for M, K, N in ((1, 4096, 14336), (128, 4096, 4096), (8192, 4096, 14336), (8192, 14336, 4096)):
+            x = torch.randn(M, K, device=dev).bfloat16()
+            lin = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
+            q = LinearFPxAcc.from_nn(lin, trun_bits=0, chunk_size=64, dynamic_fp8="per_token")
+            with torch.no_grad():
+                q(x)
+            cases.append((f"c3 FP8 e4m3 Linear {M}x{K}x{N}", 2.0 * M * N * K, (lambda q=q, x=x: q(x)), "fp8"))
+    for name, work, fn, dt in cases:
+        with torch.no_grad():
+            ms = timeit(fn, args.steps, args.warmup)
+        tops = work / (ms * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "quantized_linear_tops", "value": tops, "unit": "TOPS", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": dt, "data": "synthetic", "config": {"workload": name, "l2": "256 MB flush between timed launches"},
+            "roofline": {"bound": "tensor", "achieved": tops, "peak": 2.0 * pk["bf16"], "unit": "TFLOP/s",
+                         "frac": tops / (2.0 * pk["bf16"]), "traffic": None,
+                         "peak_source": f"2 x bf16_tflops (burst) of MEASURED_PEAKS.json ({pk['src']})"},
+        }), flush=True)  # fmt: skip
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c5", choices=["c5", "c1", "c2", "c3"])
+    ap.add_argument("--layers", type=int, default=None, help="development only: fewer decoder layers")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path); use --impl reference for the CPU baseline")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    try:
+        if args.workload == "c5":
+            run_c5(args, rank, world, dev)
+        else:
+            run_kernel_workload(args, dev)
+    finally:
+        if world > 1:
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -31,6 +31,26 @@ _ROUND = {None: L.DT_NONE, torch.float32: L.DT_F32, torch.float16: L.DT_F16, tor
 
 _status_words: dict[int, torch.Tensor] = {}
 
+# Measurement hooks used by bench.py: LAUNCHES counts kernel launches made through this module;
+# when PROFILE is a list, every launch is bracketed by CUDA events on the launching stream and
+# (name, start, end, work) is appended (work = operations for the GEMM, bytes for the others).
+LAUNCHES = 0
+PROFILE = None
+
+
+def _timed(name: str, work: float, dev: torch.device, call):
+    global LAUNCHES
+    LAUNCHES += 1
+    if PROFILE is None:
+        return call()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    st = torch.cuda.current_stream(dev)
+    e0.record(st)
+    rc = call()
+    e1.record(st)
+    PROFILE.append((name, e0, e1, work))
+    return rc
+
 
 def _require_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
     dev = None
@@ -170,7 +190,8 @@ def gemm(
         out_dtype=_DT[out_dtype],
     )  # fmt: skip
     with torch.cuda.device(dev):
-        L.check(L.load().qlin_gemm(C.byref(args), _stream(dev)), "qlin_gemm")
+        rc = _timed("gemm", 2.0 * M * N * K, dev, lambda: L.load().qlin_gemm(C.byref(args), _stream(dev)))
+        L.check(rc, "qlin_gemm")
     return out
 
 
@@ -308,8 +329,11 @@ def act_quant(
         scale_in_stride=(0 if si is None or si.numel() == 1 else 1),
         scale0=scale0, zp0=zp0, lo=lo, hi=hi, shift=shift, add2=add2,
     )  # fmt: skip
+    nbytes = rows * cols * (x.element_size() + (1 if want_codes else 0) + (x.element_size() if want_dq else 0)) + 4 * rows
+    nbytes += 4 * cols if sm is not None else 0
     with torch.cuda.device(dev):
-        L.check(L.load().qlin_act_quant(C.byref(args), _stream(dev)), "qlin_act_quant")
+        rc = _timed("act_quant", float(nbytes), dev, lambda: L.load().qlin_act_quant(C.byref(args), _stream(dev)))
+        L.check(rc, "qlin_act_quant")
     return codes, scale, dq
 
 
@@ -353,8 +377,10 @@ def weight_fq_perch(
         ldw=w.stride(0), ldo=cols, ldq=cols, rows=rows, cols=cols, dtype=_DT[w.dtype], num_bits=int(num_bits),
         mode=int(mode), native_mul=int(bool(native_mul)), clip_f32=int(bool(clip_f32)), c0=float(c0), c1=float(c1),
     )  # fmt: skip
+    nbytes = rows * cols * (w.element_size() * (2 if want_dq else 1) + (1 if want_codes else 0)) + 4 * rows
     with torch.cuda.device(dev):
-        L.check(L.load().qlin_weight_fq_perch(C.byref(args), _stream(dev)), "qlin_weight_fq_perch")
+        rc = _timed("weight_fq", float(nbytes), dev, lambda: L.load().qlin_weight_fq_perch(C.byref(args), _stream(dev)))
+        L.check(rc, "qlin_weight_fq_perch")
     return dq, codes, clip_io
 
 
@@ -379,7 +405,8 @@ def pact2_fwd(x: torch.Tensor, clip_val: torch.Tensor, clip_valn: torch.Tensor, 
         workspace=None, numel=xc.numel(), dtype=_DT[xc.dtype], num_bits=int(num_bits), align_zero=int(bool(align_zero)),
     )  # fmt: skip
     with torch.cuda.device(dev):
-        L.check(L.load().qlin_pact2_fwd(C.byref(args), _stream(dev)), "qlin_pact2_fwd")
+        rc = _timed("pact2_fwd", 2.0 * xc.numel() * xc.element_size(), dev, lambda: L.load().qlin_pact2_fwd(C.byref(args), _stream(dev)))
+        L.check(rc, "qlin_pact2_fwd")
     return out
 
 
@@ -403,7 +430,8 @@ def pact2_bwd(
         align_zero=int(bool(align_zero)),
     )  # fmt: skip
     with torch.cuda.device(dev):
-        L.check(lib.qlin_pact2_bwd(C.byref(args), _stream(dev)), "qlin_pact2_bwd")
+        rc = _timed("pact2_bwd", 3.0 * xc.numel() * xc.element_size(), dev, lambda: lib.qlin_pact2_bwd(C.byref(args), _stream(dev)))
+        L.check(rc, "qlin_pact2_bwd")
     return gx, grads
 
 

@@ -1,0 +1,105 @@
+"""W8A8 Linear layers sharded column- or row-parallel across the GPUs of one node.
+
+The sharding follows the tables the reference registers for its int8 Linear
+(fms_mo/aiu_addons/i8i8/i8i8_aiu_linear.py:304-389): a column-parallel layer splits the output
+features (int8 weight rows, per-channel weight scales, bias) and replicates the SmoothQuant scale;
+a row-parallel layer splits the input features (weight columns and the SmoothQuant scale),
+replicates the weight scales and keeps the bias on rank 0.  One process drives one GPU; the only
+data-path collectives are the ones at the shard boundary of a row-parallel layer:
+
+  * an all-reduce(MAX) of the per-token quantisation scales ([tokens] fp32), so that the int8
+    activation codes are the ones the unsharded layer would produce, and
+  * an all-reduce(SUM) of the dequantised partial outputs.
+
+Everything else is the single-GPU path of ``ops``: one row-quantise kernel and one tcgen05 GEMM with
+the dequantise epilogue per layer.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib as L
+from . import ops
+
+
+def shard_range(total: int, world: int, rank: int) -> slice:
+    """Contiguous equal split; ``total`` must divide by ``world``."""
+    if total % world != 0:
+        raise ValueError(f"cannot shard {total} over {world} ranks")
+    step = total // world
+    return slice(rank * step, (rank + 1) * step)
+
+
+def shard_w8a8(weight_i8: torch.Tensor, w_scale: torch.Tensor, smooth: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+               mode: str, world: int, rank: int):
+    """Returns this rank's ``(weight, w_scale, smooth, bias)`` of an unsharded W8A8 Linear.
+    ``mode`` is ``"column"`` (split out features), ``"row"`` (split in features) or ``"replicate"``."""
+    if mode == "replicate" or world == 1:
+        return weight_i8, w_scale, smooth, bias
+    n, k = weight_i8.shape
+    if mode == "column":
+        r = shard_range(n, world, rank)
+        return weight_i8[r].contiguous(), w_scale[r].contiguous(), smooth, (bias[r].contiguous() if bias is not None else None)
+    if mode == "row":
+        r = shard_range(k, world, rank)
+        return (weight_i8[:, r].contiguous(), w_scale, (smooth[r].contiguous() if smooth is not None else None),
+                (bias if rank == 0 else None))  # fmt: skip
+    raise ValueError(f"unknown shard mode {mode!r}")
+
+
+class W8A8Linear:
+    """A (possibly sharded) W8A8 Linear with per-token dynamic activation quantisation, SmoothQuant
+    and per-channel weight scales: the arithmetic of QLinearINT8Deploy.forward
+    (fms_mo/modules/linear.py:1309-1338, :1115-1188) for bf16 / fp16 activations.
+
+    ``quant_fn`` / ``gemm_fn`` default to the CUDA kernels; tests of the sharding logic on CPU ranks
+    substitute the oracle's arithmetic."""
+
+    def __init__(self, weight_i8, w_scale, smooth=None, bias=None, mode="replicate", group=None,
+                 quant_fn: Optional[Callable] = None, gemm_fn: Optional[Callable] = None):  # fmt: skip
+        self.weight = weight_i8
+        self.w_scale = w_scale.float().contiguous()
+        self.smooth = smooth.float().contiguous() if smooth is not None else None
+        self.bias = bias.float().contiguous() if bias is not None else None
+        self.mode = mode
+        self.group = group
+        self.world = dist.get_world_size(group) if (group is not None or (dist.is_available() and dist.is_initialized())) else 1
+        self.quant_fn = quant_fn or _cuda_quant
+        self.gemm_fn = gemm_fn or _cuda_gemm
+
+    def quantise(self, x2: torch.Tensor):
+        """Per-token int8 codes and scales of ``x2 / smooth``.  For a row-parallel shard the scale is
+        the maximum over the ranks, which is the unsharded layer's scale."""
+        if self.mode == "row" and self.world > 1:
+            _, scale = self.quant_fn(x2, self.smooth, None)
+            dist.all_reduce(scale, op=dist.ReduceOp.MAX, group=self.group)
+            codes, _ = self.quant_fn(x2, self.smooth, scale)
+            return codes, scale
+        return self.quant_fn(x2, self.smooth, None)
+
+    def __call__(self, x2: torch.Tensor, quantised=None) -> torch.Tensor:
+        codes, scale = quantised if quantised is not None else self.quantise(x2)
+        out = self.gemm_fn(codes, self.weight, scale, self.w_scale, self.bias, x2.dtype)
+        if self.mode == "row" and self.world > 1:
+            dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
+        return out
+
+
+def _cuda_quant(x2, smooth, given_scale):
+    native = 0 if x2.dtype == torch.float32 else 3
+    if given_scale is None:
+        codes, scale, _ = ops.act_quant(x2, mode=L.Q_I8_DYN, smooth=smooth, native_chain=native)
+    else:
+        codes, scale, _ = ops.act_quant(x2, mode=L.Q_I8_GIVEN_SCALE, smooth=smooth, native_chain=native, scale_in=given_scale)
+        scale = given_scale
+    return codes, scale
+
+
+def _cuda_gemm(codes, weight, scale, w_scale, bias, out_dtype):
+    # (acc.float() * (input_scale * w_scale).to(fp16) + bias).to(fp16).to(out_dtype), linear.py:1185-1188, :1338
+    return ops.gemm(codes, weight, epilogue=L.EPI_SCALE_PROD, row_scale=scale, col_scale=w_scale, bias=bias,
+                    prod_round=None, scale_round=torch.float16, acc_round=torch.float16, out_dtype=out_dtype)  # fmt: skip
