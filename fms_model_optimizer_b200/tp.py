@@ -62,6 +62,9 @@ class W8A8Linear:
     def __init__(self, weight_i8, w_scale, smooth=None, bias=None, mode="replicate", group=None,
                  quant_fn: Optional[Callable] = None, gemm_fn: Optional[Callable] = None):  # fmt: skip
         self.weight = weight_i8
+        # dtype the reference's buffer would have: `input_scale * w_scale` is formed in the promoted
+        # dtype of the two before it is cast to fp16 (linear.py:1186)
+        self.w_scale_dtype = w_scale.dtype
         self.w_scale = w_scale.float().contiguous()
         self.smooth = smooth.float().contiguous() if smooth is not None else None
         self.bias = bias.float().contiguous() if bias is not None else None
@@ -83,7 +86,8 @@ class W8A8Linear:
 
     def __call__(self, x2: torch.Tensor, quantised=None) -> torch.Tensor:
         codes, scale = quantised if quantised is not None else self.quantise(x2)
-        out = self.gemm_fn(codes, self.weight, scale, self.w_scale, self.bias, x2.dtype)
+        prod_dtype = torch.promote_types(x2.dtype, self.w_scale_dtype)
+        out = self.gemm_fn(codes, self.weight, scale, self.w_scale, self.bias, x2.dtype, prod_dtype)
         if self.mode == "row" and self.world > 1:
             dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
         return out
@@ -99,7 +103,8 @@ def _cuda_quant(x2, smooth, given_scale):
     return codes, scale
 
 
-def _cuda_gemm(codes, weight, scale, w_scale, bias, out_dtype):
+def _cuda_gemm(codes, weight, scale, w_scale, bias, out_dtype, prod_dtype):
     # (acc.float() * (input_scale * w_scale).to(fp16) + bias).to(fp16).to(out_dtype), linear.py:1185-1188, :1338
     return ops.gemm(codes, weight, epilogue=L.EPI_SCALE_PROD, row_scale=scale, col_scale=w_scale, bias=bias,
-                    prod_round=None, scale_round=torch.float16, acc_round=torch.float16, out_dtype=out_dtype)  # fmt: skip
+                    prod_round=(None if prod_dtype == torch.float32 else prod_dtype), scale_round=torch.float16,
+                    acc_round=torch.float16, out_dtype=out_dtype)  # fmt: skip

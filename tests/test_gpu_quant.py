@@ -140,10 +140,11 @@ def test_sawb_perch_vs_reference_golden(cuda_dev):
         _, codes, _ = ops.weight_fq_perch(c["w"].float().to(cuda_dev), num_bits=c["nbits"], mode=L.W_GIVEN,
                                           clip=c["clip_f32"].to(cuda_dev), want_dq=False, want_codes=True)
         assert torch.equal(codes.cpu(), c["codes"])
-        # eval mode reuses the stored clip
+        # eval mode reuses the stored (fp32) clip buffer: the scale is then formed in fp32
         q.eval()
         q.clip_val.copy_(c["clip"].to(cuda_dev))
-        assert torch.equal(q(c["w"].to(cuda_dev)).cpu(), c["y"])
+        want_eval = OQ.perch_fake_quant(c["w"], c["clip"], c["nbits"]).to(c["w"].dtype)
+        assert torch.equal(q(c["w"].to(cuda_dev)).cpu(), want_eval)
 
 
 def test_qmax_perch_vs_reference_golden(cuda_dev):
