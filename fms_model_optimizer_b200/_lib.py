@@ -38,6 +38,8 @@ EXPORTED_SYMBOLS = (
     "qlin_pact2_fwd",
     "qlin_pact2_bwd",
     "qlin_pact2_bwd_workspace_bytes",
+    "qlin_pact2_bwd_noalloc",
+    "qlin_pact2_bwd_noalloc_max_numel",
     "qlin_weight_fq_perch",
 )
 
@@ -168,6 +170,7 @@ def load() -> C.CDLL:
         ("qlin_act_quant", QuantArgs),
         ("qlin_pact2_fwd", Pact2Args),
         ("qlin_pact2_bwd", Pact2Args),
+        ("qlin_pact2_bwd_noalloc", Pact2Args),
         ("qlin_weight_fq_perch", WfqArgs),
     ):
         fn = getattr(lib, name)
@@ -175,6 +178,7 @@ def load() -> C.CDLL:
         fn.restype = C.c_int
     lib.qlin_pact2_bwd_workspace_bytes.argtypes = [C.c_int64]
     lib.qlin_pact2_bwd_workspace_bytes.restype = C.c_size_t
+    lib.qlin_pact2_bwd_noalloc_max_numel.restype = C.c_int64
     _lib = lib
     return lib
 

@@ -223,3 +223,91 @@ extern "C" int qlin_pact2_bwd(const qlin_pact2_args* a, void* stream) {
   QLIN_CHECK_LAUNCH("qlin_pact2_bwd(finish)");
   return QLIN_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// qlin_pact2_bwd_noalloc: the PACT+ backward for callers that have no device memory to lend.
+//
+// qlin_pact2_bwd needs a small workspace for the per-block partial sums of the two clip-value
+// gradients, and the caller has to get it from somewhere.  Some callers cannot: a host runtime whose
+// device pool is carved up once at start-up and sealed, an autograd hook that is handed nothing but
+// its input and output buffers, a step loop that must not call cudaMalloc because it may fail under
+// a fixed memory budget or stall the device in the middle of a step.  For them the same two kernels
+// run with the partial sums in a fixed array that is part of the library image: every GPU that loads
+// the library holds these kNoAllocScratchFloats * 4 bytes until the process exits.
+//
+// In host code the array's name is only a handle; the device address is looked up once per device
+// with cudaGetSymbolAddress, while that device is current, and that pointer is what the kernels
+// receive.  The look-up happens in the first call on each device, so make that first call outside
+// any stream capture.  Nothing in the array has to start at zero: each call writes every slot that
+// its second kernel reads.  All calls on a device share the array, so two calls whose kernels can
+// overlap on the GPU (different streams without an ordering between them) race on it.
+// ------------------------------------------------------------------------------------------------
+namespace qlin {
+
+constexpr int kNoAllocMaxBlocks = 148 * 8;                 // the grid cap of the elementwise kernels
+constexpr int kNoAllocScratchFloats = 2 * kNoAllocMaxBlocks;  // 9472 bytes
+constexpr int64_t kNoAllocMaxNumel = int64_t(1) << 31;     // elements per call
+
+static __device__ __align__(256) float g_pact2_noalloc_scratch[kNoAllocScratchFloats];
+
+// Device address of the scratch array on the current device, looked up once per device.
+static int noalloc_scratch_ptr(float** out) {
+  static float* cached[64] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(QLIN_ERR_DEVICE, "qlin_pact2_bwd_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(QLIN_ERR_DEVICE, "qlin_pact2_bwd_noalloc: device ordinal %d out of range", dev);
+  if (cached[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_pact2_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(QLIN_ERR_DEVICE, "qlin_pact2_bwd_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return QLIN_OK;
+}
+
+}  // namespace qlin
+
+extern "C" int64_t qlin_pact2_bwd_noalloc_max_numel(void) { return qlin::kNoAllocMaxNumel; }
+
+extern "C" int qlin_pact2_bwd_noalloc(const qlin_pact2_args* a, void* stream) {
+  const char* name = "qlin_pact2_bwd_noalloc";
+  if (a == nullptr) return fail(QLIN_ERR_NULL, "%s: args is NULL", name);
+  if (a->x == nullptr || a->out == nullptr || a->clip_val == nullptr || a->clip_valn == nullptr ||
+      a->grad_out == nullptr || a->grad_clip == nullptr)
+    return fail(QLIN_ERR_NULL, "%s: x, grad_out, out, clip_val, clip_valn or grad_clip is NULL", name);
+  if (a->numel < 0) return fail(QLIN_ERR_BAD_SHAPE, "%s: negative numel", name);
+  if (a->numel > kNoAllocMaxNumel)
+    return fail(QLIN_ERR_TOO_LARGE, "%s: numel %lld exceeds the built-in scratch limit of %lld elements per call", name,
+                static_cast<long long>(a->numel), static_cast<long long>(kNoAllocMaxNumel));
+  if (a->num_bits < 2 || a->num_bits > 16) return fail(QLIN_ERR_UNSUPPORTED, "%s: num_bits must be in [2, 16]", name);
+  if (a->dtype != QLIN_DT_F32 && a->dtype != QLIN_DT_F16 && a->dtype != QLIN_DT_BF16)
+    return fail(QLIN_ERR_BAD_DTYPE, "%s: dtype must be F32, F16 or BF16", name);
+  const int grid = fq_grid(a->numel);
+  if (grid > kNoAllocMaxBlocks) return fail(QLIN_ERR_TOO_LARGE, "%s: grid %d exceeds the built-in scratch", name, grid);
+  float* scratch = nullptr;
+  int rc = noalloc_scratch_ptr(&scratch);
+  if (rc != QLIN_OK) return rc;
+  PactParams p = to_params(a);
+  p.ws = scratch;  // the looked-up device address, never the host-side symbol
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (a->numel > 0) {
+    switch (a->dtype) {
+      case QLIN_DT_F32:
+        pact2_bwd_kernel<float><<<grid, kFqThreads, 0, s>>>(p);
+        break;
+      case QLIN_DT_F16:
+        pact2_bwd_kernel<__half><<<grid, kFqThreads, 0, s>>>(p);
+        break;
+      default:
+        pact2_bwd_kernel<__nv_bfloat16><<<grid, kFqThreads, 0, s>>>(p);
+        break;
+    }
+    QLIN_CHECK_LAUNCH("qlin_pact2_bwd_noalloc");
+  }
+  pact2_bwd_finish_kernel<<<1, kFqThreads, 0, s>>>(scratch, a->numel > 0 ? grid : 0, p.grad_clip);
+  QLIN_CHECK_LAUNCH("qlin_pact2_bwd_noalloc(finish)");
+  return QLIN_OK;
+}

@@ -223,6 +223,24 @@ int qlin_pact2_fwd(const qlin_pact2_args* args, void* stream);
 int qlin_pact2_bwd(const qlin_pact2_args* args, void* stream);
 size_t qlin_pact2_bwd_workspace_bytes(int64_t numel);
 
+/* qlin_pact2_bwd_noalloc -- qlin_pact2_bwd without a caller-provided workspace.
+ *
+ * No counterpart in fms-model-optimizer: this entry point exists only for hosts of this library.
+ * It is for callers that cannot hand over scratch memory -- a runtime whose device pool is sealed
+ * after start-up, a hook that receives only its input and output buffers, a step loop that must not
+ * call cudaMalloc because it can fail under a fixed budget or stall the device.  `workspace` in the
+ * argument block is ignored; the partial sums of the two clip gradients go to a 9472-byte array that
+ * is part of the library image and stays resident on every GPU that loads the library.  The call
+ * allocates and frees nothing.  Results are identical to qlin_pact2_bwd.
+ *   - numel above qlin_pact2_bwd_noalloc_max_numel() (2^31 elements) is rejected with
+ *     QLIN_ERR_TOO_LARGE.
+ *   - The first call on each device looks up the array's device address; make that call while the
+ *     device is current and before any stream capture.
+ *   - All calls on a device share the array: calls that may overlap on the GPU race on it.  Nothing
+ *     needs clearing between calls (each call writes every slot it later reads). */
+int qlin_pact2_bwd_noalloc(const qlin_pact2_args* args, void* stream);
+int64_t qlin_pact2_bwd_noalloc_max_numel(void);
+
 /* ------------------------------------------------------------------------------------------------
  * qlin_weight_fq_perch -- per-output-channel symmetric weight fake quantisation with the
  * clip value computed in the same pass.
