@@ -82,6 +82,7 @@ class QuantArgs(C.Structure):
     _fields_ = [
         ("x", C.c_void_p),
         ("smooth", C.c_void_p),
+        ("smooth_rcp", C.c_void_p),
         ("scale_in", C.c_void_p),
         ("codes", C.c_void_p),
         ("scale_out", C.c_void_p),

@@ -31,6 +31,51 @@ __device__ __forceinline__ float rnd_if(float v, bool native) {
   return native ? Elem<T>::rnd(v) : v;
 }
 
+// ---- rounding on the FMA / ALU pipes ---------------------------------------------------------------
+// The conversion instructions (float -> bf16, rint, float -> int) issue on the quarter-rate
+// conversion pipe and bound the quantise kernels.  These produce the same results with additions:
+// adding and subtracting 1.5 * 2^k makes the hardware's round-to-nearest-even act at 2^(k-23).
+template <typename T>
+__device__ __forceinline__ float fast_rnd(float v) {
+  return Elem<T>::rnd(v);
+}
+// bf16 keeps 8 significant bits: for |v| in [2^e, 2^(e+1)) round at 2^(e-7), i.e. k = e + 16.
+// Valid for normal v up to 2^110 (callers bound their values far below that).
+template <>
+__device__ __forceinline__ float fast_rnd<__nv_bfloat16>(float v) {
+  const float m = __uint_as_float((__float_as_uint(v) & 0x7F800000u) + 0x08400000u);
+  return __fsub_rn(__fadd_rn(v, m), m);
+}
+// rint for |v| < 2^22, and the integer itself from the low bits of the biased sum.
+__device__ __forceinline__ float fast_rint(float v, int& as_int) {
+  const float t = __fadd_rn(v, 12582912.0f);
+  as_int = __float_as_int(t) - 0x4B400000;
+  return __fsub_rn(t, 12582912.0f);
+}
+
+// ---- exact division through a precomputed reciprocal ---------------------------------------------
+// RN(x / s) from r = RN(1 / s) with three fused operations (Markstein): q = RN(x r), the exact
+// remainder rem = x - s q (one FMA), q' = RN(q + rem r).  q' is the correctly rounded quotient when
+// r is the correctly rounded reciprocal and s's significand is not all ones; callers pass r = NaN
+// for such s.  Results outside a comfortable normal range (where the remainder could be subnormal),
+// NaN and infinities take the ordinary IEEE division.
+__device__ __forceinline__ float div_exact(float x, float s, float r) {
+  const float q = __fmul_rn(x, r);
+  const float rem = __fmaf_rn(-s, q, x);
+  const float q2 = __fmaf_rn(rem, r, q);
+  if (x == 0.0f) return q;  // keeps the sign of a zero quotient
+  const float a = fabsf(q2);
+  if (!(a > 1e-15f && a < 1e15f)) return __fdiv_rn(x, s);
+  return q2;
+}
+// r for div_exact: RN(1 / s), or NaN when the shortcut is not proven for this s.
+__device__ __forceinline__ float rcp_for_div(float s) {
+  const uint32_t bits = __float_as_uint(s);
+  const float a = fabsf(s);
+  if ((bits & 0x7FFFFFu) == 0x7FFFFFu || !(a > 1e-15f && a < 1e15f)) return __int_as_float(0x7fc00000);
+  return __frcp_rn(s);
+}
+
 // ---- 16 consecutive elements <-> 16 floats --------------------------------------------------
 __device__ __forceinline__ void load16(const float* p, float (&v)[16]) {
 #pragma unroll
@@ -117,6 +162,17 @@ __device__ __forceinline__ float warp_reduce(float v) {
 // Reduces `v` over the block in a fixed order and returns the result to every thread.  `slot`
 // points at 32 floats of shared memory; callers alternate between two slots from one call to the
 // next so that a single __syncthreads() per call is enough.
+// block_reduce that also ORs a per-thread flag over the block through the same barrier.
+template <typename Op>
+__device__ __forceinline__ float block_reduce_flag(float v, float* slot, float identity, bool flag, bool& any_flag) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_reduce<Op>(v);
+  if (lane == 0) slot[warp] = v;
+  any_flag = __syncthreads_or(flag ? 1 : 0) != 0;
+  float r = lane < nwarps ? slot[lane] : identity;
+  return warp_reduce<Op>(r);
+}
+
 template <typename Op>
 __device__ __forceinline__ float block_reduce(float v, float* slot, float identity) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;

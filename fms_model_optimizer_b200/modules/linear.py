@@ -207,6 +207,7 @@ class QLinearINT8Deploy(nn.Linear):
                     w_scale=self.w_scale.detach().float().reshape(-1).contiguous(),
                     bias=self.bias.detach().float().reshape(-1).contiguous(),
                     smooth=(sq.detach().float().reshape(-1).contiguous() if use_sq else None),
+                    smooth_rcp=(ops.smooth_reciprocal(sq.detach().float()) if use_sq else None),
                 ),
             )
         return self._cache[1]
@@ -252,20 +253,23 @@ class QLinearINT8Deploy(nn.Linear):
                 native = (1 if (smooth is not None and chain == x2.dtype and chain != torch.float32) else 0) | (
                     2 if (chain == x2.dtype and chain != torch.float32) else 0
                 )
+                if smooth is None or self.smoothq_scale.dtype == x2.dtype:
+                    native |= 4  # the smoothing scales are values of the activation dtype
                 codes, in_scale, _ = ops.act_quant(
-                    x2, mode=L.Q_I8_DYN, smooth=smooth, native_chain=native, levels=2 ** (self.nbits_a - 1) - 1
+                    x2, mode=L.Q_I8_DYN, smooth=smooth, smooth_rcp=prep["smooth_rcp"], native_chain=native,
+                    levels=2 ** (self.nbits_a - 1) - 1
                 )
                 scale_dtype = chain
             elif self.usePTnativeQfunc:
                 codes, in_scale, _ = ops.act_quant(
-                    x2, mode=L.Q_I8_STATIC, smooth=smooth, scale0=float(self.input_scale), zp0=float(self.input_zp),
+                    x2, mode=L.Q_I8_STATIC, smooth=smooth, smooth_rcp=prep["smooth_rcp"], scale0=float(self.input_scale), zp0=float(self.input_zp),
                     shift=128.0, add2=float(self.useSymAct),
                 )  # fmt: skip
                 in_scale = self.input_scale.detach().float().reshape(-1)
                 scale_dtype = self.input_scale.dtype
             else:
                 codes, in_scale, _ = ops.act_quant(
-                    x2, mode=L.Q_I8_STATIC_CLAMP_FIRST, smooth=smooth, scale0=float(self.quant_stepsize),
+                    x2, mode=L.Q_I8_STATIC_CLAMP_FIRST, smooth=smooth, smooth_rcp=prep["smooth_rcp"], scale0=float(self.quant_stepsize),
                     zp0=float(self.quant_zero_point), lo=float(self.cvs[1]), hi=float(self.cvs[0]),
                     shift=float(128 - self.useSymAct),
                 )  # fmt: skip

@@ -281,11 +281,22 @@ def tl_matmul_chunk_truncate(
 # --------------------------------------------------------------------------------------------------
 # Row-wise quantisation
 # --------------------------------------------------------------------------------------------------
+def smooth_reciprocal(smooth_f32: torch.Tensor) -> torch.Tensor:
+    """The ``smooth_rcp`` operand of qlin_act_quant: the IEEE fp32 reciprocal of every smoothing scale,
+    NaN where the kernel's three-operation exact division is not proven (significand all ones, or a
+    magnitude outside [1e-15, 1e15]) so that those columns take the ordinary division."""
+    s = smooth_f32.float().reshape(-1).contiguous()
+    r = torch.reciprocal(s)
+    bad = ((s.view(torch.int32) & 0x7FFFFF) == 0x7FFFFF) | ~((s.abs() > 1e-15) & (s.abs() < 1e15))
+    return torch.where(bad, torch.full_like(r, float("nan")), r).contiguous()
+
+
 def act_quant(
     x: torch.Tensor,
     *,
     mode: int = L.Q_I8_DYN,
     smooth: Optional[torch.Tensor] = None,
+    smooth_rcp: Optional[torch.Tensor] = None,
     smooth_mul: bool = False,
     native_chain: int = 0,
     clamp_codes: bool = False,
@@ -318,11 +329,14 @@ def act_quant(
     sm = _f32(smooth)
     if sm is not None and sm.numel() != cols:
         raise RuntimeError("smooth must have one entry per column")
+    rsm = None
+    if sm is not None and not smooth_mul:
+        rsm = _f32(smooth_rcp) if smooth_rcp is not None else smooth_reciprocal(sm)
     si = _f32(scale_in)
     if rows == 0 or cols == 0:
         return codes, scale, dq
     args = L.QuantArgs(
-        x=_ptr(x), smooth=_ptr(sm), scale_in=_ptr(si), codes=_ptr(codes), scale_out=_ptr(scale), dq_out=_ptr(dq),
+        x=_ptr(x), smooth=_ptr(sm), smooth_rcp=_ptr(rsm), scale_in=_ptr(si), codes=_ptr(codes), scale_out=_ptr(scale), dq_out=_ptr(dq),
         status=None, ldx=x.stride(0), ldq=cols, lddq=cols, rows=rows, cols=cols, x_dtype=_DT[x.dtype], mode=mode,
         native_chain=int(native_chain), smooth_mul=int(bool(smooth_mul)), clamp_codes=int(bool(clamp_codes)),
         qmax_levels=int(levels), dl8_flush=int(bool(dl8_flush)),

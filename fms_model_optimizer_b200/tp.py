@@ -67,6 +67,9 @@ class W8A8Linear:
         self.w_scale_dtype = w_scale.dtype
         self.w_scale = w_scale.float().contiguous()
         self.smooth = smooth.float().contiguous() if smooth is not None else None
+        self.smooth_rcp = ops.smooth_reciprocal(self.smooth) if (self.smooth is not None and self.smooth.is_cuda) else None
+        # true when every smoothing scale is a bf16 value (the reference casts it to the activation dtype)
+        self.smooth_is_bf16 = bool(((self.smooth.view(torch.int32) & 0xFFFF) == 0).all().item()) if self.smooth is not None else True
         self.bias = bias.float().contiguous() if bias is not None else None
         self.mode = mode
         self.group = group
@@ -74,15 +77,20 @@ class W8A8Linear:
         self.quant_fn = quant_fn or _cuda_quant
         self.gemm_fn = gemm_fn or _cuda_gemm
 
+    def _q(self, x2, given_scale):
+        if self.quant_fn is _cuda_quant:
+            return _cuda_quant(x2, self.smooth, given_scale, self.smooth_rcp, self.smooth_is_bf16)
+        return self.quant_fn(x2, self.smooth, given_scale)
+
     def quantise(self, x2: torch.Tensor):
         """Per-token int8 codes and scales of ``x2 / smooth``.  For a row-parallel shard the scale is
         the maximum over the ranks, which is the unsharded layer's scale."""
         if self.mode == "row" and self.world > 1:
-            _, scale = self.quant_fn(x2, self.smooth, None)
+            _, scale = self._q(x2, None)
             dist.all_reduce(scale, op=dist.ReduceOp.MAX, group=self.group)
-            codes, _ = self.quant_fn(x2, self.smooth, scale)
+            codes, _ = self._q(x2, scale)
             return codes, scale
-        return self.quant_fn(x2, self.smooth, None)
+        return self._q(x2, None)
 
     def __call__(self, x2: torch.Tensor, quantised=None) -> torch.Tensor:
         codes, scale = quantised if quantised is not None else self.quantise(x2)
@@ -93,12 +101,15 @@ class W8A8Linear:
         return out
 
 
-def _cuda_quant(x2, smooth, given_scale):
+def _cuda_quant(x2, smooth, given_scale, smooth_rcp=None, smooth_is_bf16=False):
     native = 0 if x2.dtype == torch.float32 else 3
+    if x2.dtype == torch.bfloat16 and smooth_is_bf16:
+        native |= 4
     if given_scale is None:
-        codes, scale, _ = ops.act_quant(x2, mode=L.Q_I8_DYN, smooth=smooth, native_chain=native)
+        codes, scale, _ = ops.act_quant(x2, mode=L.Q_I8_DYN, smooth=smooth, smooth_rcp=smooth_rcp, native_chain=native)
     else:
-        codes, scale, _ = ops.act_quant(x2, mode=L.Q_I8_GIVEN_SCALE, smooth=smooth, native_chain=native, scale_in=given_scale)
+        codes, scale, _ = ops.act_quant(x2, mode=L.Q_I8_GIVEN_SCALE, smooth=smooth, smooth_rcp=smooth_rcp, native_chain=native,
+                                        scale_in=given_scale)
         scale = given_scale
     return codes, scale
 

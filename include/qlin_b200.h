@@ -155,7 +155,10 @@ int qlin_gemm(const qlin_gemm_args* args, void* stream);
  *                     wrapped to int8 or clamped to +-qmax_levels
  * native_chain is a bit mask: bit 0 rounds the smoothed value to the dtype of x, bit 1 rounds every
  * later intermediate to the dtype of x (what the reference computes when the tensors involved are
- * bf16 / fp16); 0 evaluates the same formulas in fp32 on the widened inputs.
+ * bf16 / fp16); 0 evaluates the same formulas in fp32 on the widened inputs.  Bit 2 is a promise by the
+ * caller that every smooth[c] is exactly representable in the dtype of x (the reference casts its
+ * SmoothQuant scale to that dtype); with bits 0-2 set on bf16 rows the kernel uses a shorter, still
+ * bit-identical instruction sequence.
  * Outputs: codes [rows, cols] (1 byte each), scale_out [rows] fp32 (optional),
  * dq_out (optional, dtype of x): the fake-quantised value code * scale, QMaxDynamic's output.
  * ---------------------------------------------------------------------------------------------- */
@@ -170,6 +173,9 @@ typedef enum qlin_quant_mode {
 typedef struct qlin_quant_args {
   const void* x;
   const float* smooth;    /* optional [cols] */
+  const float* smooth_rcp;/* [cols], required when smooth divides: the correctly rounded fp32 reciprocal of
+                             smooth[c], or NaN to make column c take the plain IEEE division.  The kernel
+                             derives the exact quotient x / smooth[c] from it with three fused operations. */
   const float* scale_in;  /* QLIN_Q_I8_GIVEN_SCALE: [rows] */
   void* codes;            /* optional [rows, cols] int8 / e4m3 */
   float* scale_out;       /* optional [rows] */
