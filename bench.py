@@ -166,12 +166,14 @@ class Decoder:
         S = cfg["seq"]
         inv = 1.0 / (cfg["rope_theta"] ** (torch.arange(0, hd, 2, device=dev).float() / hd))
         ang = torch.outer(torch.arange(S, device=dev).float(), inv)
-        self.cos = torch.cat([ang.cos(), ang.cos()], -1).bfloat16()[None, None]
-        self.sin = torch.cat([ang.sin(), ang.sin()], -1).bfloat16()[None, None]
+        # [1, S, 1, hd] tables for activations laid out [B, S, heads, hd]; rotate_half(x) is a roll by
+        # hd/2 with the sign folded into the sine table: x*cos + roll(x)*sin_signed (3 passes)
+        self.cos = torch.cat([ang.cos(), ang.cos()], -1).bfloat16()[None, :, None, :]
+        self.sin = torch.cat([-ang.sin(), ang.sin()], -1).bfloat16()[None, :, None, :]
+        self.half = hd // 2
 
     def _rope(self, x):
-        x1, x2 = x[..., : x.shape[-1] // 2], x[..., x.shape[-1] // 2 :]
-        return x * self.cos + torch.cat((-x2, x1), dim=-1) * self.sin
+        return torch.addcmul(x * self.cos, x.roll(self.half, -1), self.sin)
 
     @torch.no_grad()
     def forward(self, ids):
@@ -181,10 +183,9 @@ class Decoder:
         x = F.embedding(ids, self.embed).view(B * S, -1)
         for lin in self.layers:
             h = F.rms_norm(x, (x.shape[-1],), lin["ln1"], 1e-5)
-            q = lin["q"](h).view(B, S, self.nq, hd).transpose(1, 2)
-            k = lin["k"](h).view(B, S, self.nkv, hd).transpose(1, 2)
+            q = self._rope(lin["q"](h).view(B, S, self.nq, hd)).transpose(1, 2)
+            k = self._rope(lin["k"](h).view(B, S, self.nkv, hd)).transpose(1, 2)
             v = lin["v"](h).view(B, S, self.nkv, hd).transpose(1, 2)
-            q, k = self._rope(q), self._rope(k)
             a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
             a = a.transpose(1, 2).reshape(B * S, self.nq * hd)
             x = x + lin["o"](a)

@@ -329,16 +329,16 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int ya = mb * kBM, yb = nb * C::BN;
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!ready) {
-          ok = __all_sync(0xffffffffu, mbar_wait(&aux->empty[s], ph ^ 1u, abort_flag));
+          ok = warp_mbar_wait(&aux->empty[s], ph ^ 1u, abort_flag);
           if (!ok) break;
         }
         const uint32_t ns = (s + 1 == C::STAGES) ? 0u : s + 1;
         const uint32_t nph = (ns == 0u) ? (ph ^ 1u) : ph;
-        const bool peek = mbar_test_wait(&aux->empty[ns], nph ^ 1u);
+        const bool peek = warp_mbar_test(&aux->empty[ns], nph ^ 1u);
         uint8_t* sa = smem + s * C::STAGE_BYTES;
         tma_issue_stage(&aux->full[s], C::STAGE_BYTES, sa, &tmap_a, ya, sa + C::A_BYTES, &tmap_b, yb, kb * kBK);
         ++issued;
-        ready = __all_sync(0xffffffffu, peek);
+        ready = peek;
         s = ns;
         ph = nph;
       }
@@ -374,18 +374,18 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int k32_left = total_k32;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         if (!ready) {
-          ok = __all_sync(0xffffffffu, mbar_wait(&aux->full[s], ph, abort_flag));
+          ok = warp_mbar_wait(&aux->full[s], ph, abort_flag);
           if (!ok) break;
         }
         tc_fence_after();
         const uint32_t ns = (s + 1 == C::STAGES) ? 0u : s + 1;
         const uint32_t nph = (ns == 0u) ? (ph ^ 1u) : ph;
-        const bool peek = mbar_test_wait(&aux->full[ns], nph);
+        const bool peek = warp_mbar_test(&aux->full[ns], nph);
         const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
         const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
         if (!CHUNKED && k32_left >= 4 && (kb > 0 || true)) {
           if (kb == 0) {
-            ok = __all_sync(0xffffffffu, mbar_wait(&aux->tempty[buf], bph ^ 1u, abort_flag));
+            ok = warp_mbar_wait(&aux->tempty[buf], bph ^ 1u, abort_flag);
             if (!ok) break;
             tc_fence_after();
             cur = buf;
@@ -403,7 +403,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           for (int j = 0; j < 4; ++j) {
             if (k32_left > 0 && ok) {
               if (chunk_pos == 0 && (CHUNKED || accumulate == 0)) {
-                ok = __all_sync(0xffffffffu, mbar_wait(&aux->tempty[buf], bph ^ 1u, abort_flag));
+                ok = warp_mbar_wait(&aux->tempty[buf], bph ^ 1u, abort_flag);
                 if (ok) {
                   tc_fence_after();
                   cur = buf;
@@ -428,7 +428,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           if (ok) tc_commit_elect(&aux->empty[s]);
         }
-        ready = __all_sync(0xffffffffu, peek);
+        ready = peek;
         s = ns;
         ph = nph;
       }
@@ -482,7 +482,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           ebuf = 0;
           ebph ^= 1u;
         }
-        if (!mbar_wait(&aux->tfull[buf], bph, abort_flag)) {
+        if (!warp_mbar_wait(&aux->tfull[buf], bph, abort_flag)) {
           ok = false;
           break;
         }
@@ -514,7 +514,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             ebuf = 0;
             ebph ^= 1u;
           }
-          if (!mbar_wait(&aux->tfull[buf], bph, abort_flag)) {
+          if (!warp_mbar_wait(&aux->tfull[buf], bph, abort_flag)) {
             ok = false;
             break;
           }

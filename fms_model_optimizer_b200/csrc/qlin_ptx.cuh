@@ -83,6 +83,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// Warp-level forms: mbarrier operations on one address are processed lane by lane, so a whole warp
+// polling costs ~32x the latency of a single lane.  One lane polls, the result is broadcast; the
+// warp is converged again when these return.
+__device__ __forceinline__ bool warp_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  uint32_t ok = 0;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1u : 0u;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+__device__ __forceinline__ bool warp_mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok = 0;
+  if ((threadIdx.x & 31) == 0) ok = mbar_test_wait(bar, parity) ? 1u : 0u;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // Bounded wait used while winding down: ignores the abort flag and uses a shorter budget.
 __device__ __forceinline__ bool mbar_wait_drain(uint64_t* bar, uint32_t parity) {
   const uint64_t t0 = global_timer_ns();
