@@ -17,7 +17,8 @@ launches in the timed region, timed with CUDA events on the launching stream); `
 the reference's CPU fake-quant arithmetic (QLinear.forward: per-token / per-channel fake quantise +
 F.linear) for one decoder layer on a bounded token sample, extrapolated to the 32 layers.
 
-Other workloads, for single kernels: --workload c1 | c2 | c3 (TOPS of one quantized Linear / GEMM).
+Other workloads, for single kernels: --workload c1 | c2 | c3 | c5lin (TOPS of one quantized Linear / GEMM;
+c5lin is one 16384 x 4096 x 4096 Linear of the c5 decoder).
 Weights and activations are synthetic (seeded); nothing is read from disk.
 """
 
@@ -390,15 +391,15 @@ def run_kernel_workload(args, dev):
         return tot / steps
 
     cases = []
-    if args.workload == "c1":
+    if args.workload in ("c1", "c5lin"):
         torch.manual_seed(0)
-        M, K, N = 2048, 4096, 4096
+        M, K, N = (2048, 4096, 4096) if args.workload == "c1" else (16384, 4096, 4096)
         x = torch.randn(M, K, device=dev).bfloat16()
         codes, w_scale, smooth = synth_w8a8(N, K, 0, dev)
         from fms_model_optimizer_b200 import tp
 
         lin = tp.W8A8Linear(codes, w_scale, smooth, torch.zeros(N, device=dev))
-        cases.append((f"c1 W8A8 INT8 Linear {M}x{K}x{N} (quantise + GEMM + dequantise)", 2.0 * M * N * K, lambda: lin(x), "int8"))
+        cases.append((f"{args.workload} W8A8 INT8 Linear {M}x{K}x{N} (quantise + GEMM + dequantise)", 2.0 * M * N * K, lambda: lin(x), "int8"))
     elif args.workload == "c2":
         torch.manual_seed(1)
         M, K, N = 4096, 8192, 4096
@@ -438,7 +439,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c5", choices=["c5", "c1", "c2", "c3"])
+    ap.add_argument("--workload", default="c5", choices=["c5", "c1", "c2", "c3", "c5lin"])
     ap.add_argument("--layers", type=int, default=None, help="development only: fewer decoder layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
