@@ -5,11 +5,11 @@
 // Both operands are K-major ("NT"), which is the layout the reference hands to its Triton / CUTLASS
 // kernels (activations [m,k]; weight [n,k] passed as its .t() view).
 //
-// Per CTA (one per SM, 320 threads):
-//   warp 8      TMA producer: 128-byte-swizzled [128 x 128B] A tile and [BN x 128B] B tile per stage
-//   warp 9      MMA issuer: tcgen05.mma.cta_group::1 (M=128, N=BN, K=32 bytes per instruction),
+// Per CTA (one per SM, 320 or 576 threads):
+//   warp E      TMA producer (E = number of epilogue warps: 8 unchunked, 16 chunked): 128-byte-swizzled [128 x 128B] A tile and [BN x 128B] B tile per stage
+//   warp E+1    MMA issuer: tcgen05.mma.cta_group::1 (M=128, N=BN, K=32 bytes per instruction),
 //               accumulators in tensor memory; owns the TMEM allocation
-//   warps 0-7   epilogue: tcgen05.ld of the accumulator, chunk rounding / running sum, dequantise,
+//   warps 0..E-1 epilogue: tcgen05.ld of the accumulator, chunk rounding / running sum, dequantise,
 //               global stores.  Warp w reads TMEM lanes 32*(w%4).. and column half w/4.
 // Unchunked: BN=256, two 256-column accumulators so the epilogue of tile i overlaps the mainloop of
 // tile i+1.  Chunked: BN=128, four 128-column accumulators; every K-chunk is a fresh accumulation
@@ -28,10 +28,6 @@ namespace qlin {
 
 constexpr int kBM = 128;          // rows of A per tile = MMA M
 constexpr int kBK = 128;          // bytes of K per pipeline stage = one swizzle row
-constexpr int kEpiWarps = 8;
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
-constexpr int kThreads = 320;
 constexpr int kGroupM = 16;       // m-blocks per raster group
 constexpr int kTmemCols = 512;
 constexpr int kStageOutBytes = 4096;  // per epilogue warp: 32 rows x 128 bytes of output
@@ -52,13 +48,20 @@ template <bool CHUNKED>
 struct Cfg {
   static constexpr int BN = CHUNKED ? 128 : 256;
   static constexpr int NBUF = CHUNKED ? 4 : 2;
-  static constexpr int STAGES = CHUNKED ? 6 : 4;
+  static constexpr int STAGES = CHUNKED ? 5 : 4;
+  // Epilogue warps: w % 4 selects the 32 TMEM lanes a warp may read, w / 4 its column slice.  The
+  // chunked kernel drains an accumulator per K-chunk, a chain of short dependent steps, and hides
+  // that latency with twice as many, narrower warps.
+  static constexpr int EPI_WARPS = CHUNKED ? 16 : 8;
+  static constexpr int PRODUCER_WARP = EPI_WARPS;
+  static constexpr int MMA_WARP = EPI_WARPS + 1;
+  static constexpr int THREADS = (EPI_WARPS + 2) * 32;
   static constexpr int A_BYTES = kBM * kBK;
   static constexpr int B_BYTES = BN * kBK;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int COLS_PER_WARP = BN / 2;  // each epilogue warp: 32 rows x BN/2 columns
+  static constexpr int COLS_PER_WARP = BN / (EPI_WARPS / 4);  // 128 (unchunked) or 32 (chunked) columns
   static constexpr int OUT_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr int AUX_OFFSET = OUT_OFFSET + kEpiWarps * kStageOutBytes;
+  static constexpr int AUX_OFFSET = OUT_OFFSET + EPI_WARPS * kStageOutBytes;
   static constexpr int SMEM_BYTES = AUX_OFFSET + static_cast<int>(sizeof(Aux));
 };
 static_assert(Cfg<false>::SMEM_BYTES <= 232448 && Cfg<true>::SMEM_BYTES <= 232448, "shared memory budget");
@@ -264,8 +267,31 @@ __device__ __forceinline__ void emit64(const GemmParams& p, const uint32_t (&v)[
   }
 }
 
+// Emits 32 accumulator columns of this thread's row (the chunked kernel's final store): 4-byte
+// outputs go through the coalescing tile, 2-byte outputs (64 bytes per row) are stored directly.
+template <bool F8>
+__device__ __forceinline__ void emit32(const GemmParams& p, const uint32_t (&v)[32], int row0, int lane, int col0,
+                                       const float* s_cs, const float* s_bias, int s_off, float rs, bool vec_ok,
+                                       uint8_t* stage) {
+  const bool four_byte = p.epilogue == QLIN_EPI_RAW || p.out_dtype == QLIN_DT_F32;
+  if (!vec_ok || col0 + 32 > p.N || !four_byte) {
+    store_row_direct<F8, 32>(p, v, row0 + lane, col0, s_cs, s_bias, s_off, rs);
+    return;
+  }
+  const bool prod = p.epilogue == QLIN_EPI_SCALE_PROD;
+  const bool has_bias = p.bias != nullptr;
+  uint32_t w[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j)
+    w[j] = p.epilogue == QLIN_EPI_RAW
+               ? v[j]
+               : __float_as_uint(dequant_one<F8>(p, v[j], rs, s_cs[s_off + j], s_bias[s_off + j], prod, has_bias));
+  uint8_t* g = reinterpret_cast<uint8_t*>(p.d) + (static_cast<int64_t>(row0) * p.ldd + col0) * 4;
+  store_tile_coalesced(stage, w, g, p.ldd * 4, p.M - row0, lane);
+}
+
 template <bool F8, bool CHUNKED>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(Cfg<CHUNKED>::THREADS, 1)
 qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
   using C = Cfg<CHUNKED>;
@@ -290,18 +316,18 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int b = 0; b < C::NBUF; ++b) {
       mbar_init(&aux->tfull[b], 1);
-      mbar_init(&aux->tempty[b], kEpiWarps);
+      mbar_init(&aux->tempty[b], C::EPI_WARPS);
     }
     mbar_init(&aux->drain, 1);
     aux->abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async();
   }
-  if (warp == kMmaWarp) {
+  if (warp == C::MMA_WARP) {
     tmem_alloc(&aux->tmem_base, kTmemCols);
     tmem_relinquish();
   }
-  if (warp == kProducerWarp && lane == 0) {
+  if (warp == C::PRODUCER_WARP && lane == 0) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
   }
@@ -315,7 +341,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int total_k32 = (p.kbytes + 31) / 32;
   bool timed_out = false;
 
-  if (warp == kProducerWarp) {
+  if (warp == C::PRODUCER_WARP) {
     // ------------------------------------------------------------------ TMA producer
     // The whole warp walks the loop converged; one elected lane issues.  The next stage's
     // barrier is polled (non-blocking) before the current stage is issued, which takes the
@@ -334,11 +360,11 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         const uint32_t ns = (s + 1 == C::STAGES) ? 0u : s + 1;
         const uint32_t nph = (ns == 0u) ? (ph ^ 1u) : ph;
-        const bool peek = warp_mbar_test(&aux->empty[ns], nph ^ 1u);
+        const uint32_t peek = warp_mbar_test_begin(&aux->empty[ns], nph ^ 1u);
         uint8_t* sa = smem + s * C::STAGE_BYTES;
         tma_issue_stage(&aux->full[s], C::STAGE_BYTES, sa, &tmap_a, ya, sa + C::A_BYTES, &tmap_b, yb, kb * kBK);
         ++issued;
-        ready = peek;
+        ready = warp_mbar_test_end(peek);
         s = ns;
         ph = nph;
       }
@@ -356,7 +382,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     }
     __syncwarp();
-  } else if (warp == kMmaWarp) {
+  } else if (warp == C::MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     // One instruction stream feeds the tensor pipe, so this loop is latency-critical: no
     // divisions, positions carried as counters, a whole 128-byte K block issued by one fused
@@ -368,6 +394,9 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t buf = 0, bph = 0;       // TMEM accumulator buffer to use next and its phase
     bool ok = true;
     bool ready = false;
+    bool tready = false;  // next accumulator buffer known to be drained
+    // chunks that tile a 128-byte K block exactly (32, 64 or 128 elements, K a multiple of 128)
+    const bool chunk_fast = CHUNKED && (p.chunk_k32 == 1 || p.chunk_k32 == 2 || p.chunk_k32 == 4) && (total_k32 % 4 == 0);
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       uint32_t accumulate = 0, cur = 0;
       int chunk_pos = 0;
@@ -380,7 +409,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tc_fence_after();
         const uint32_t ns = (s + 1 == C::STAGES) ? 0u : s + 1;
         const uint32_t nph = (ns == 0u) ? (ph ^ 1u) : ph;
-        const bool peek = warp_mbar_test(&aux->full[ns], nph);
+        const uint32_t peek = warp_mbar_test_begin(&aux->full[ns], nph);
         const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
         const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
         if (!CHUNKED && k32_left >= 4 && (kb > 0 || true)) {
@@ -398,6 +427,34 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           accumulate = 1;
           k32_left -= 4;
           if (k32_left == 0) tc_commit_elect(&aux->tfull[cur]);
+        } else if (CHUNKED && chunk_fast && k32_left >= 4) {
+          // whole chunks inside this 128-byte K block: one fused statement per chunk, the next
+          // accumulator's "empty" barrier polled before the current chunk is issued
+          const int cpk = 4 / p.chunk_k32;
+          for (int c = 0; c < cpk && ok; ++c) {
+            if (!tready) {
+              ok = warp_mbar_wait(&aux->tempty[buf], bph ^ 1u, abort_flag);
+              if (!ok) break;
+            }
+            tc_fence_after();
+            const uint32_t nb = (buf + 1 == C::NBUF) ? 0u : buf + 1;
+            const uint32_t nbph = (nb == 0u) ? (bph ^ 1u) : bph;
+            const uint32_t tpeek = warp_mbar_test_begin(&aux->tempty[nb], nbph ^ 1u);
+            const uint64_t off = static_cast<uint64_t>(c * p.chunk_k32 * 2);
+            const uint32_t d = tmem_base + buf * C::BN;
+            if (p.chunk_k32 == 1) {
+              tc_mma_chunk<F8 ? 1 : 0, 1>(d, adesc + off, bdesc + off, idesc, &aux->tfull[buf]);
+            } else if (p.chunk_k32 == 2) {
+              tc_mma_chunk<F8 ? 1 : 0, 2>(d, adesc + off, bdesc + off, idesc, &aux->tfull[buf]);
+            } else {
+              tc_mma_chunk<F8 ? 1 : 0, 4>(d, adesc + off, bdesc + off, idesc, &aux->tfull[buf]);
+            }
+            tready = warp_mbar_test_end(tpeek);
+            buf = nb;
+            bph = nbph;
+          }
+          k32_left -= 4;
+          if (ok) tc_commit_elect(&aux->empty[s]);
         } else {
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -428,7 +485,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           if (ok) tc_commit_elect(&aux->empty[s]);
         }
-        ready = peek;
+        ready = warp_mbar_test_end(peek);
         s = ns;
         ph = nph;
       }
@@ -444,7 +501,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int q = warp & 3;
-    const int half = warp >> 2;
+    const int half = warp >> 2;  // column slice of this warp
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
     uint8_t* stage = smem + C::OUT_OFFSET + warp * kStageOutBytes;
     const int elt = (p.out_dtype == QLIN_DT_F16 || p.out_dtype == QLIN_DT_BF16) ? 2 : 4;
@@ -457,6 +514,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const bool dl16 = F8 && p.clamp_dl16;
     const bool scaled = p.epilogue != QLIN_EPI_RAW;
     uint32_t ebuf = 0, ebph = 0;
+    bool eready = false;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
@@ -467,13 +525,13 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       float rs = 1.0f;
       if (scaled) {
         // Stage this tile's column scales and bias once; all lanes then read them as broadcasts.
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        for (int i = threadIdx.x; i < C::BN; i += kEpiWarps * 32) {
+        asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
+        for (int i = threadIdx.x; i < C::BN; i += C::EPI_WARPS * 32) {
           const int n = nb * C::BN + i;
           aux->cs[i] = (p.cs != nullptr && n < p.N) ? p.cs[static_cast<int64_t>(n) * p.cs_stride] : 1.0f;
           aux->bias[i] = (p.bias != nullptr && n < p.N) ? p.bias[n] : 0.0f;
         }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
         if (p.rs != nullptr && row < p.M) rs = p.rs[static_cast<int64_t>(row) * p.rs_stride];
       }
       if constexpr (!CHUNKED) {
@@ -514,17 +572,23 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             ebuf = 0;
             ebph ^= 1u;
           }
-          if (!warp_mbar_wait(&aux->tfull[buf], bph, abort_flag)) {
+          if (!eready && !warp_mbar_wait(&aux->tfull[buf], bph, abort_flag)) {
             ok = false;
             break;
           }
           tc_fence_after();
           uint32_t v[C::COLS_PER_WARP];
-          tmem_ld64(tmem_base + lane_base + buf * C::BN + half * C::COLS_PER_WARP, v);
+          tmem_ld32(tmem_base + lane_base + buf * C::BN + half * C::COLS_PER_WARP, v);
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&aux->tempty[buf]);
-          if (p.trunc_then_acc) {
+          // poll the next chunk's barrier now; the answer is consumed after this chunk's arithmetic
+          const uint32_t epeek = warp_mbar_test_begin(&aux->tfull[ebuf], ebph);
+          if (p.trunc_then_acc && !clamp && !dl16) {
+            // the common case, kept free of per-element predicates: run += (p + rb) & mask
+#pragma unroll
+            for (int i = 0; i < C::COLS_PER_WARP; ++i) run[i] = acc_add<F8>(run[i], (v[i] + rb) & mask);
+          } else if (p.trunc_then_acc) {
 #pragma unroll
             for (int i = 0; i < C::COLS_PER_WARP; ++i)
               run[i] = acc_add<F8>(run[i], chunk_round<F8>(v[i], clamp, lo, hi, rb, mask, dl16));
@@ -533,9 +597,10 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int i = 0; i < C::COLS_PER_WARP; ++i)
               run[i] = chunk_round<F8>(acc_add<F8>(run[i], v[i]), clamp, lo, hi, rb, mask, dl16);
           }
+          eready = warp_mbar_test_end(epeek);
         }
         if (!ok) break;
-        emit64<F8>(p, run, row0, lane, col_w, aux->cs, aux->bias, half * C::COLS_PER_WARP, rs, vec_ok, stage);
+        emit32<F8>(p, run, row0, lane, col_w, aux->cs, aux->bias, half * C::COLS_PER_WARP, rs, vec_ok, stage);
       }
     }
     if (!ok && lane == 0) {
@@ -547,7 +612,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (timed_out && p.status != nullptr) atomicExch(p.status, static_cast<int32_t>(QLIN_ERR_TIMEOUT));
   tc_fence_before();
   __syncthreads();
-  if (warp == kMmaWarp) {
+  if (warp == C::MMA_WARP) {
     __syncwarp();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -602,7 +667,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   }
   const int tiles = p.num_m * p.num_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  qlin_gemm_kernel<F8, CHUNKED><<<grid, kThreads, C::SMEM_BYTES, stream>>>(ta, tb, p);
+  qlin_gemm_kernel<F8, CHUNKED><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
   QLIN_CHECK_LAUNCH("qlin_gemm");
   return QLIN_OK;
 }

@@ -91,10 +91,26 @@ __device__ __forceinline__ bool warp_mbar_wait(uint64_t* bar, uint32_t parity, v
   if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1u : 0u;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
-__device__ __forceinline__ bool warp_mbar_test(uint64_t* bar, uint32_t parity) {
+// Split form of a non-blocking poll: `begin` issues the test in lane 0 and returns a per-lane token
+// without consuming the result, `end` broadcasts it.  Work placed between the two overlaps the
+// barrier round trip (the warp issues in order and only stalls where the result is first read).
+__device__ __forceinline__ uint32_t warp_mbar_test_begin(uint64_t* bar, uint32_t parity) {
   uint32_t ok = 0;
-  if ((threadIdx.x & 31) == 0) ok = mbar_test_wait(bar, parity) ? 1u : 0u;
-  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+  if ((threadIdx.x & 31) == 0) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+  }
+  return ok;
+}
+__device__ __forceinline__ bool warp_mbar_test_end(uint32_t token) {
+  return __shfl_sync(0xffffffffu, token, 0) != 0;
 }
 
 // Bounded wait used while winding down: ignores the abort flag and uses a shorter budget.
@@ -244,6 +260,50 @@ __device__ __forceinline__ void tc_mma4_release(uint32_t d_tmem, uint64_t adesc,
     QLIN_MMA4("i8");
   }
 #undef QLIN_MMA4
+}
+
+// One accumulation chunk of NMMA (1, 2 or 4) K=32-byte MMAs into a fresh accumulator (the first MMA
+// overwrites it), then the "accumulator full" commit on `tfull_bar`.
+template <int KIND_F8, int NMMA>
+__device__ __forceinline__ void tc_mma_chunk(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint64_t* tfull_bar) {
+#define QLIN_CHUNK_HEAD                                   \
+  "{\n\t"                                                 \
+  ".reg .pred pe, pf, pt;\n\t"                            \
+  ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"                 \
+  "elect.sync _|pe, 0xffffffff;\n\t"                      \
+  "setp.ne.b32 pt, %3, 0;\n\t"                            \
+  "setp.eq.b32 pf, %3, 0;\n\t"                            \
+  "add.s64 a1, %1, 2;\n\t"                                \
+  "add.s64 b1, %2, 2;\n\t"                                \
+  "add.s64 a2, %1, 4;\n\t"                                \
+  "add.s64 b2, %2, 4;\n\t"                                \
+  "add.s64 a3, %1, 6;\n\t"                                \
+  "add.s64 b3, %2, 6;\n\t"
+#define QLIN_CHUNK_TAIL                                                                        \
+  "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%4];\n\t"        \
+  "}" ::"r"(d_tmem),                                                                           \
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(smem_u32(tfull_bar))                             \
+      : "memory"
+#define QLIN_M(KIND, A, B, P) "@pe tcgen05.mma.cta_group::1.kind::" KIND " [%0], " A ", " B ", %3, " P ";\n\t"
+#define QLIN_CHUNK(KIND)                                                                                         \
+  if (NMMA == 1) {                                                                                               \
+    asm volatile(QLIN_CHUNK_HEAD QLIN_M(KIND, "%1", "%2", "pf") QLIN_CHUNK_TAIL);                                \
+  } else if (NMMA == 2) {                                                                                        \
+    asm volatile(QLIN_CHUNK_HEAD QLIN_M(KIND, "%1", "%2", "pf") QLIN_M(KIND, "a1", "b1", "pt") QLIN_CHUNK_TAIL); \
+  } else {                                                                                                       \
+    asm volatile(QLIN_CHUNK_HEAD QLIN_M(KIND, "%1", "%2", "pf") QLIN_M(KIND, "a1", "b1", "pt")                   \
+                     QLIN_M(KIND, "a2", "b2", "pt") QLIN_M(KIND, "a3", "b3", "pt") QLIN_CHUNK_TAIL);             \
+  }
+  if (KIND_F8) {
+    QLIN_CHUNK("f8f6f4")
+  } else {
+    QLIN_CHUNK("i8")
+  }
+#undef QLIN_CHUNK
+#undef QLIN_M
+#undef QLIN_CHUNK_TAIL
+#undef QLIN_CHUNK_HEAD
 }
 
 // A single K=32-byte MMA, elected-lane form.
