@@ -26,6 +26,9 @@ EPI_RAW, EPI_SCALE_PROD, EPI_SCALE_SEQ = 0, 1, 2
 # qlin_quant_mode
 Q_I8_DYN, Q_I8_STATIC, Q_I8_STATIC_CLAMP_FIRST, Q_F8_DYN, Q_I8_GIVEN_SCALE = range(5)
 
+# qlin_pact_variant
+PACT_TWO_SIDED, PACT_ONE_SIDED, PACT_SYMMETRIC = 0, 1, 2
+
 # qlin_wq_mode
 W_SAWB, W_MAX, W_GIVEN = 0, 1, 2
 
@@ -107,6 +110,7 @@ class QuantArgs(C.Structure):
         ("hi", C.c_float),
         ("shift", C.c_float),
         ("add2", C.c_float),
+        ("dyn_eps", C.c_float),
     ]
 
 
@@ -123,6 +127,7 @@ class Pact2Args(C.Structure):
         ("dtype", C.c_int32),
         ("num_bits", C.c_int32),
         ("align_zero", C.c_int32),
+        ("variant", C.c_int32),
     ]
 
 

@@ -22,47 +22,95 @@ struct PactParams {
   float* grad_clip;
   float* ws;
   int64_t numel;
-  int32_t num_bits, align_zero;
+  int32_t num_bits, align_zero, variant;
 };
 
 struct PactScalars {
   float cv, cvn, step, zp, n;
+  int variant;
 };
 
 template <typename XT>
 __device__ __forceinline__ PactScalars pact_scalars(const PactParams& p) {
   PactScalars s;
+  s.variant = p.variant;
   s.cv = Elem<XT>::rnd(*p.cv);
-  s.cvn = Elem<XT>::rnd(*p.cvn);
-  s.n = static_cast<float>((1 << p.num_bits) - 1);
-  // `n_levels / (cv - cvn)` and `1.0 / scale` have a Python scalar on the left: torch evaluates
-  // them as reciprocal(tensor) * scalar, each step rounded to the tensor dtype.
-  const float inv = Elem<XT>::rnd(__fdiv_rn(1.0f, Elem<XT>::rnd(__fsub_rn(s.cv, s.cvn))));
-  const float scale = Elem<XT>::rnd(__fmul_rn(inv, s.n));
-  s.step = Elem<XT>::rnd(__fdiv_rn(1.0f, scale));
-  s.zp = Elem<XT>::rnd(__fmul_rn(s.cvn, scale));
-  if (p.align_zero) s.zp = rintf(s.zp);
+  // `n_levels / tensor` and `1.0 / scale` have a Python scalar on the left: torch evaluates them as
+  // reciprocal(tensor) * scalar, each step rounded to the tensor dtype.
+  if (p.variant == QLIN_PACT_TWO_SIDED) {
+    s.cvn = Elem<XT>::rnd(*p.cvn);
+    s.n = static_cast<float>((1 << p.num_bits) - 1);
+    const float inv = Elem<XT>::rnd(__fdiv_rn(1.0f, Elem<XT>::rnd(__fsub_rn(s.cv, s.cvn))));
+    const float scale = Elem<XT>::rnd(__fmul_rn(inv, s.n));
+    s.step = Elem<XT>::rnd(__fdiv_rn(1.0f, scale));
+    s.zp = Elem<XT>::rnd(__fmul_rn(s.cvn, scale));
+    if (p.align_zero) s.zp = rintf(s.zp);
+  } else if (p.variant == QLIN_PACT_ONE_SIDED) {
+    s.cvn = 0.0f;
+    s.zp = 0.0f;
+    s.n = static_cast<float>((1 << p.num_bits) - 1);
+    const float scale = Elem<XT>::rnd(__fmul_rn(Elem<XT>::rnd(__fdiv_rn(1.0f, s.cv)), s.n));
+    s.step = Elem<XT>::rnd(__fdiv_rn(1.0f, scale));
+  } else {  // symmetric: levels 2^b - 2 when the zero point is integral
+    s.cvn = -s.cv;
+    s.zp = 0.0f;
+    s.n = static_cast<float>((1 << p.num_bits) - (p.align_zero ? 2 : 1));
+    const float two_cv = Elem<XT>::rnd(__fmul_rn(2.0f, s.cv));
+    const float scale = Elem<XT>::rnd(__fmul_rn(Elem<XT>::rnd(__fdiv_rn(1.0f, two_cv)), s.n));
+    s.step = Elem<XT>::rnd(__fdiv_rn(1.0f, scale));
+  }
   return s;
 }
 
 template <typename XT>
 __device__ __forceinline__ float pact_fwd_one(const PactScalars& s, float x) {
-  float y = fminf(x, s.cv);
-  y = fmaxf(y, s.cvn);
-  float t = Elem<XT>::rnd(__fdiv_rn(y, s.step));
-  t = Elem<XT>::rnd(__fsub_rn(t, s.zp));
-  const float q = rintf(t);
-  return Elem<XT>::rnd(__fmul_rn(Elem<XT>::rnd(__fadd_rn(q, s.zp)), s.step));
+  if (s.variant == QLIN_PACT_TWO_SIDED) {
+    float y = fminf(x, s.cv);
+    y = fmaxf(y, s.cvn);
+    float t = Elem<XT>::rnd(__fdiv_rn(y, s.step));
+    t = Elem<XT>::rnd(__fsub_rn(t, s.zp));
+    const float q = rintf(t);
+    return Elem<XT>::rnd(__fmul_rn(Elem<XT>::rnd(__fadd_rn(q, s.zp)), s.step));
+  }
+  if (s.variant == QLIN_PACT_ONE_SIDED) {
+    // PACTplusSTE.forward: round(clamp(x, 0, cv) / step) * step
+    const float y = fminf(fmaxf(x, 0.0f), s.cv);
+    return Elem<XT>::rnd(__fmul_rn(rintf(Elem<XT>::rnd(__fdiv_rn(y, s.step))), s.step));
+  }
+  // PACTplusSymSTE_rev1.forward: round((clamp(x, -cv, cv) + cv) / step) * step - cv
+  float y = x > s.cv ? s.cv : x;
+  y = y < -s.cv ? -s.cv : y;
+  const float q = rintf(Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fadd_rn(y, s.cv)), s.step)));
+  return Elem<XT>::rnd(__fsub_rn(Elem<XT>::rnd(__fmul_rn(q, s.step)), s.cv));
 }
 
 template <typename XT>
 __device__ __forceinline__ float pact_bwd_one(const PactScalars& s, float x, float g, float& ga, float& gan) {
-  const float z = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fsub_rn(x, s.cvn)), s.step));
-  const float delz = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fsub_rn(z, rintf(z))), s.n));
-  const float inner = Elem<XT>::rnd(__fmul_rn(-g, delz));
-  const bool hi = x >= s.cv, lo = x <= s.cvn;
-  ga += hi ? g : (lo ? 0.0f : inner);
-  gan += lo ? g : (hi ? 0.0f : -inner);
+  if (s.variant == QLIN_PACT_TWO_SIDED) {
+    const float z = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fsub_rn(x, s.cvn)), s.step));
+    const float delz = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fsub_rn(z, rintf(z))), s.n));
+    const float inner = Elem<XT>::rnd(__fmul_rn(-g, delz));
+    const bool hi = x >= s.cv, lo = x <= s.cvn;
+    ga += hi ? g : (lo ? 0.0f : inner);
+    gan += lo ? g : (hi ? 0.0f : -inner);
+    return (hi || lo) ? 0.0f : g;
+  }
+  if (s.variant == QLIN_PACT_ONE_SIDED) {
+    // PACTplusSTE.backward: z = x / step; delz = (z - round(z)) / n
+    const float z = Elem<XT>::rnd(__fdiv_rn(x, s.step));
+    const float delz = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fsub_rn(z, rintf(z))), s.n));
+    const float inner = Elem<XT>::rnd(__fmul_rn(-g, delz));
+    const bool hi = x >= s.cv, lo = x <= 0.0f;
+    ga += hi ? g : (lo ? 0.0f : inner);
+    return (hi || lo) ? 0.0f : g;
+  }
+  // PACTplusSymSTE_rev1.backward: z = (x + cv) / step; delz = 2 (round(z) - z) / n; +-1 outside
+  const float z = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fadd_rn(x, s.cv)), s.step));
+  const float d0 = Elem<XT>::rnd(__fsub_rn(rintf(z), z));
+  const float delz = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fmul_rn(2.0f, d0)), s.n));
+  const bool hi = x >= s.cv, lo = x <= -s.cv;
+  const float w = hi ? 1.0f : (lo ? -1.0f : delz);
+  ga += Elem<XT>::rnd(__fmul_rn(w, g));
   return (hi || lo) ? 0.0f : g;
 }
 
@@ -143,8 +191,11 @@ static int fq_grid(int64_t numel) {
 
 static int check_pact(const qlin_pact2_args* a, bool bwd, const char* name) {
   if (a == nullptr) return fail(QLIN_ERR_NULL, "%s: args is NULL", name);
-  if (a->x == nullptr || a->out == nullptr || a->clip_val == nullptr || a->clip_valn == nullptr)
+  if (a->x == nullptr || a->out == nullptr || a->clip_val == nullptr ||
+      (a->variant == QLIN_PACT_TWO_SIDED && a->clip_valn == nullptr))
     return fail(QLIN_ERR_NULL, "%s: x, out, clip_val or clip_valn is NULL", name);
+  if (a->variant < QLIN_PACT_TWO_SIDED || a->variant > QLIN_PACT_SYMMETRIC)
+    return fail(QLIN_ERR_UNSUPPORTED, "%s: unknown variant %d", name, a->variant);
   if (bwd && (a->grad_out == nullptr || a->grad_clip == nullptr || a->workspace == nullptr))
     return fail(QLIN_ERR_NULL, "%s: grad_out, grad_clip or workspace is NULL", name);
   if (a->numel < 0) return fail(QLIN_ERR_BAD_SHAPE, "%s: negative numel", name);
@@ -166,6 +217,7 @@ static PactParams to_params(const qlin_pact2_args* a) {
   p.numel = a->numel;
   p.num_bits = a->num_bits;
   p.align_zero = a->align_zero != 0;
+  p.variant = a->variant;
   return p;
 }
 
@@ -275,8 +327,8 @@ extern "C" int64_t qlin_pact2_bwd_noalloc_max_numel(void) { return qlin::kNoAllo
 extern "C" int qlin_pact2_bwd_noalloc(const qlin_pact2_args* a, void* stream) {
   const char* name = "qlin_pact2_bwd_noalloc";
   if (a == nullptr) return fail(QLIN_ERR_NULL, "%s: args is NULL", name);
-  if (a->x == nullptr || a->out == nullptr || a->clip_val == nullptr || a->clip_valn == nullptr ||
-      a->grad_out == nullptr || a->grad_clip == nullptr)
+  if (a->x == nullptr || a->out == nullptr || a->clip_val == nullptr ||
+      (a->variant == QLIN_PACT_TWO_SIDED && a->clip_valn == nullptr) || a->grad_out == nullptr || a->grad_clip == nullptr)
     return fail(QLIN_ERR_NULL, "%s: x, grad_out, out, clip_val, clip_valn or grad_clip is NULL", name);
   if (a->numel < 0) return fail(QLIN_ERR_BAD_SHAPE, "%s: negative numel", name);
   if (a->numel > kNoAllocMaxNumel)

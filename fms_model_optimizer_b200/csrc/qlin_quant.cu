@@ -35,7 +35,7 @@ struct QuantParams {
   int32_t rows, cols;
   int32_t smooth_exact;  // smoothing scales are exactly representable in the dtype of x
   int32_t mode, native, native_smooth, smooth_mul, clamp_codes, levels, dl8_flush, scale_in_stride;
-  float scale0, zp0, lo, hi, shift, add2;
+  float scale0, zp0, lo, hi, shift, add2, dyn_eps;
 };
 
 template <typename XT>
@@ -47,7 +47,7 @@ __device__ __forceinline__ float smooth_apply(const QuantParams& p, float x, flo
 // Row scale from the row's absmax.
 template <typename XT>
 __device__ __forceinline__ float dyn_scale(const QuantParams& p, float amax) {
-  const float eps = rnd_if<XT>(1e-5f, p.native);
+  const float eps = rnd_if<XT>(p.dyn_eps, p.native);
   if (p.mode == QLIN_Q_F8_DYN) {
     const float a = rnd_if<XT>(__fdiv_rn(amax, 448.0f), p.native);
     return fmaxf(a, eps);
@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(TPB) act_quant_fast_kernel(const QuantParams p
       }
     }
   }
-  const float eps = NATIVE ? Elem<XT>::rnd(1e-5f) : 1e-5f;
+  const float eps = NATIVE ? Elem<XT>::rnd(p.dyn_eps) : p.dyn_eps;
 
   for (int i = 0; i < my_rows; ++i) {
     const int slot = i % stages;
@@ -489,7 +489,7 @@ __global__ void __launch_bounds__(TPB) act_quant_bf16_kernel(const QuantParams p
 #pragma unroll
   for (int j = 0; j < 16; ++j) mreg[j] = 1.0f;
   if (SMREG && has_smooth && static_cast<int>(threadIdx.x) < nchunks) load16(mulvec + threadIdx.x * 16, mreg);
-  const float eps = Elem<__nv_bfloat16>::rnd(1e-5f);
+  const float eps = Elem<__nv_bfloat16>::rnd(p.dyn_eps);
 
   for (int i = 0; i < my_rows; ++i) {
     const int slot = i % stages;
@@ -992,6 +992,7 @@ extern "C" int qlin_act_quant(const qlin_quant_args* a, void* stream) {
   p.hi = a->hi;
   p.shift = a->shift;
   p.add2 = a->add2;
+  p.dyn_eps = a->dyn_eps;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (a->x_dtype) {
     case QLIN_DT_F32:

@@ -361,6 +361,72 @@ class LinearFPxAcc(nn.Linear):
         return s + f",chunk_size={self.chunk_size}"
 
 
+class _LinearINT8FwdFP32Bwd(torch.autograd.Function):
+    """LinearFuncINT8FwdFP32Bwd (fms_mo/modules/linear.py:2127-2223): forward through the int8 chunk-
+    truncating GEMM with per-token / per-channel max scales (no lower clamp on the scales), backward
+    with plain matmuls in the activation dtype."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, lsb_trun_bits, chunk_size, max_acc_bits):
+        assert x.dtype in _FLOATS
+        org_dtype = x.dtype
+        tar_shape = x.shape[:-1] + (weight.shape[0],)
+        x2 = x.reshape(-1, x.shape[-1])
+        ctx.has_bias = bias is not None
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        ctx.save_for_backward(x2, weight)
+        native = 0 if org_dtype == torch.float32 else 3
+        xq, xs, _ = ops.act_quant(x2, mode=L.Q_I8_DYN, native_chain=native, dyn_eps=0.0)
+        wn = 0 if weight.dtype == torch.float32 else 3
+        wq, ws, _ = ops.act_quant(weight.detach(), mode=L.Q_I8_DYN, native_chain=wn, dyn_eps=0.0)
+        rnd = None if org_dtype == torch.float32 else org_dtype
+        out = ops.gemm(
+            xq, wq, chunk_k=_normalised_chunk(int(chunk_size)), trun_bits=int(lsb_trun_bits), max_acc_bits=int(max_acc_bits),
+            epilogue=L.EPI_SCALE_SEQ, row_scale=xs, col_scale=ws, bias=(bias.detach().to(org_dtype) if bias is not None else None),
+            mid_round=rnd, acc_round=rnd, out_dtype=org_dtype,
+        )  # fmt: skip
+        return out.reshape(tar_shape)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x2, weight = ctx.saved_tensors
+        dtype_grad = x2.dtype
+        g2 = grad_output.reshape(-1, weight.shape[0]).to(dtype_grad)
+        grad_weight = torch.matmul(g2.transpose(0, 1).contiguous(), x2.to(dtype_grad)).to(weight.dtype)
+        grad_input = torch.matmul(g2, weight.to(dtype_grad)).reshape(grad_output.shape[:-1] + (weight.shape[1],)).to(x2.dtype)
+        grad_bias = g2.sum(0).to(ctx.bias_dtype) if ctx.has_bias else None
+        return grad_input, grad_weight, grad_bias, None, None, None
+
+
+class QLinearINT8Train(nn.Linear):
+    """Linear that runs its forward on the int8 GEMM (with optional LSB truncation / narrow
+    accumulator) and its backward in floating point: QLinearINT8Train of the reference
+    (fms_mo/modules/linear.py:2227-2285)."""
+
+    @classmethod
+    def from_fms_mo(cls, nnlin, lsb_trun_bits=0, **kwargs):
+        target_device = kwargs.get("target_device", kwargs.get("device", next(nnlin.parameters()).device))
+        lin = cls(nnlin.in_features, nnlin.out_features, bias=nnlin.bias is not None, device="meta")
+        lin.weight = nnlin.weight
+        lin.lsb_trun_bits = lsb_trun_bits
+        lin.chunk_size = kwargs.get("chunk_size", 64)
+        lin.max_acc_bits = kwargs.get("max_acc_bits", 32)
+        if nnlin.bias is not None:
+            lin.bias = nnlin.bias
+        return lin.to(target_device)
+
+    def forward(self, inputs):
+        return _LinearINT8FwdFP32Bwd.apply(inputs, self.weight, self.bias, self.lsb_trun_bits, self.chunk_size, self.max_acc_bits)
+
+    def extra_repr(self) -> str:
+        s = f"{self.in_features},{self.out_features},bias={self.bias is not None},chunk_size={self.chunk_size}"
+        if self.lsb_trun_bits > 0:
+            s += f",lsb_trun={self.lsb_trun_bits}"
+        if self.max_acc_bits < 32:
+            s += f",max_acc_bits={self.max_acc_bits}"
+        return s
+
+
 class QLinear(nn.Linear):
     """Fake-quant Linear for QAT / DQ (fms_mo/modules/linear.py:51-393, forward :248-305):
     ``F.linear(Qa(x / s), Qw(W * s), bias)`` with the SmoothQuant scale ``s`` of :345-368.  The two

@@ -311,6 +311,7 @@ def act_quant(
     hi: float = 0.0,
     shift: float = 0.0,
     add2: float = 0.0,
+    dyn_eps: float = 1e-5,
 ) -> Tuple[Optional[torch.Tensor], torch.Tensor, Optional[torch.Tensor]]:
     """Row-wise 8-bit quantisation of a 2-D tensor; returns ``(codes, scale[rows], dq)``.
     See ``qlin_act_quant`` in include/qlin_b200.h for the modes."""
@@ -341,7 +342,7 @@ def act_quant(
         native_chain=int(native_chain), smooth_mul=int(bool(smooth_mul)), clamp_codes=int(bool(clamp_codes)),
         qmax_levels=int(levels), dl8_flush=int(bool(dl8_flush)),
         scale_in_stride=(0 if si is None or si.numel() == 1 else 1),
-        scale0=scale0, zp0=zp0, lo=lo, hi=hi, shift=shift, add2=add2,
+        scale0=scale0, zp0=zp0, lo=lo, hi=hi, shift=shift, add2=add2, dyn_eps=dyn_eps,
     )  # fmt: skip
     nbytes = rows * cols * (x.element_size() + (1 if want_codes else 0) + (x.element_size() if want_dq else 0)) + 4 * rows
     nbytes += 4 * cols if sm is not None else 0
@@ -408,15 +409,19 @@ def _clip_f32(t: torch.Tensor, dev: torch.device) -> torch.Tensor:
     return t.contiguous()
 
 
-def pact2_fwd(x: torch.Tensor, clip_val: torch.Tensor, clip_valn: torch.Tensor, num_bits: int, align_zero: bool) -> torch.Tensor:
-    """PACTplus2STE.forward with dequantize=True (fms_mo/quant/quantizers.py:1949-2055)."""
+def pact2_fwd(x: torch.Tensor, clip_val: torch.Tensor, clip_valn: Optional[torch.Tensor], num_bits: int, align_zero: bool,
+              variant: int = L.PACT_TWO_SIDED) -> torch.Tensor:
+    """PACTplus2STE.forward with dequantize=True (fms_mo/quant/quantizers.py:1949-2055); ``variant`` selects the
+    one-sided (PACTplusSTE, :1016) or symmetric (PACTplusSymSTE_rev1, :1073) member of the family."""
     dev = _require_cuda(x)
     xc = x.contiguous()
     out = torch.empty_like(xc)
-    cv, cvn = _clip_f32(clip_val, dev), _clip_f32(clip_valn, dev)
+    cv = _clip_f32(clip_val, dev)
+    cvn = _clip_f32(clip_valn, dev) if clip_valn is not None else None
     args = L.Pact2Args(
         x=_ptr(xc), grad_out=None, out=_ptr(out), clip_val=_ptr(cv), clip_valn=_ptr(cvn), grad_clip=None,
         workspace=None, numel=xc.numel(), dtype=_DT[xc.dtype], num_bits=int(num_bits), align_zero=int(bool(align_zero)),
+        variant=int(variant),
     )  # fmt: skip
     with torch.cuda.device(dev):
         rc = _timed("pact2_fwd", 2.0 * xc.numel() * xc.element_size(), dev, lambda: L.load().qlin_pact2_fwd(C.byref(args), _stream(dev)))
@@ -425,7 +430,8 @@ def pact2_fwd(x: torch.Tensor, clip_val: torch.Tensor, clip_valn: torch.Tensor, 
 
 
 def pact2_bwd(
-    x: torch.Tensor, grad_out: torch.Tensor, clip_val: torch.Tensor, clip_valn: torch.Tensor, num_bits: int, align_zero: bool
+    x: torch.Tensor, grad_out: torch.Tensor, clip_val: torch.Tensor, clip_valn: Optional[torch.Tensor], num_bits: int,
+    align_zero: bool, variant: int = L.PACT_TWO_SIDED,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """PACTplus2STE.backward (fms_mo/quant/quantizers.py:2058-2102): returns ``(grad_x, [grad_cv, grad_cvn])``."""
     dev = _require_cuda(x, grad_out)
@@ -434,14 +440,15 @@ def pact2_bwd(
     if gc.dtype != xc.dtype:
         gc = gc.to(xc.dtype)
     gx = torch.empty_like(xc)
-    cv, cvn = _clip_f32(clip_val, dev), _clip_f32(clip_valn, dev)
+    cv = _clip_f32(clip_val, dev)
+    cvn = _clip_f32(clip_valn, dev) if clip_valn is not None else None
     lib = L.load()
     ws = torch.empty((max(1, lib.qlin_pact2_bwd_workspace_bytes(xc.numel()) // 4),), dtype=torch.float32, device=dev)
     grads = torch.empty((2,), dtype=torch.float32, device=dev)
     args = L.Pact2Args(
         x=_ptr(xc), grad_out=_ptr(gc), out=_ptr(gx), clip_val=_ptr(cv), clip_valn=_ptr(cvn), grad_clip=_ptr(grads),
         workspace=_ptr(ws), numel=xc.numel(), dtype=_DT[xc.dtype], num_bits=int(num_bits),
-        align_zero=int(bool(align_zero)),
+        align_zero=int(bool(align_zero)), variant=int(variant),
     )  # fmt: skip
     with torch.cuda.device(dev):
         rc = _timed("pact2_bwd", 3.0 * xc.numel() * xc.element_size(), dev, lambda: lib.qlin_pact2_bwd(C.byref(args), _stream(dev)))

@@ -73,6 +73,64 @@ class PACT2(nn.Module):
                 f"neg-clip={self.clip_valn[0]:.4f},quantizer={self.quantizer})")  # fmt: skip
 
 
+class _PactOneClipSTE(torch.autograd.Function):
+    """One-sided PACT+ (PACTplusSTE, fms_mo/quant/quantizers.py:1016-1070) and symmetric PACT+
+    (PACTplusSymSTE_rev1, :1073-1154): a single learnable clip value."""
+
+    @staticmethod
+    def forward(ctx, input_tensor, clip_val, num_bits, variant, intg_zp):
+        ctx.save_for_backward(input_tensor, clip_val)
+        ctx.cfg = (num_bits, variant, bool(intg_zp))
+        return ops.pact2_fwd(input_tensor, clip_val, None, num_bits, bool(intg_zp), variant)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, clip_val = ctx.saved_tensors
+        num_bits, variant, intg_zp = ctx.cfg
+        gx, gclip = ops.pact2_bwd(x, grad_output, clip_val, None, num_bits, intg_zp, variant)
+        return gx.view_as(x), gclip[0].to(clip_val.dtype).expand_as(clip_val), None, None, None
+
+
+class PACT(nn.Module):
+    """One-sided PACT with the PACT+ gradient rule (fms_mo/quant/quantizers.py:791-844), for
+    non-negative activations."""
+
+    def __init__(self, num_bits, init_clip_val, init_clip_valn=0, dequantize=True, inplace=False, cggrad=False,
+                 grad_scale=False, pact_plus=False):  # fmt: skip
+        super().__init__()
+        if cggrad or grad_scale or not pact_plus or not dequantize or inplace:
+            raise NotImplementedError("PACT on B200 provides the pact_plus=True, dequantize=True quantizer")
+        self.num_bits = num_bits
+        self.clip_val = nn.Parameter(init_clip_val if isinstance(init_clip_val, torch.Tensor) else torch.Tensor([init_clip_val]))
+        self.dequantize = dequantize
+        self.inplace = inplace
+        self.quantizer = _PactOneClipSTE
+
+    def forward(self, input_tensor):
+        return self.quantizer.apply(input_tensor, self.clip_val, self.num_bits, L.PACT_ONE_SIDED, False)
+
+
+class PACTplusSym(nn.Module):
+    """Two-sided symmetric PACT+ (fms_mo/quant/quantizers.py:1247-1304)."""
+
+    def __init__(self, num_bits, init_clip_val, dequantize=True, inplace=False, intg_zp=False, OORgradnoclip=False,
+                 extend_act_range=False):  # fmt: skip
+        super().__init__()
+        if extend_act_range or OORgradnoclip or not dequantize or inplace:
+            raise NotImplementedError("PACTplusSym on B200: dequantize=True, out-of-range gradients clipped")
+        self.num_bits = num_bits
+        self.clip_val = nn.Parameter(init_clip_val if isinstance(init_clip_val, torch.Tensor) else torch.Tensor([init_clip_val]))
+        self.dequantize = dequantize
+        self.inplace = inplace
+        self.intg_zp = intg_zp
+        self.OORgradnoclip = OORgradnoclip
+        self.quantizer = _PactOneClipSTE
+        self.quantizer_name = "PACT+sym"
+
+    def forward(self, input_tensor):
+        return self.quantizer.apply(input_tensor, self.clip_val, self.num_bits, L.PACT_SYMMETRIC, self.intg_zp)
+
+
 class _PerChSTE(torch.autograd.Function):
     """Per-channel symmetric fake quantisation with identity gradient: the quantise step of
     SAWBPlusZeroPerChSTE (fms_mo/quant/quantizers.py:503-572) and QmaxPerChSTE (:3190-3224)."""
@@ -199,6 +257,10 @@ class PerTokenMax(QMaxDynamic):
 def get_activation_quantizer(qa_mode="pact+", nbits=8, clip_val=None, clip_valn=None, non_neg=False, align_zero=True, **_):
     """Subset of get_activation_quantizer (fms_mo/quant/quantizers.py:46-226) for the modes on the
     quantized Linear's path."""
+    if qa_mode == "pact+" and non_neg:
+        return PACT(nbits, init_clip_val=clip_val, init_clip_valn=clip_valn, dequantize=True, inplace=False, pact_plus=True)
+    if qa_mode == "pactsym+":
+        return PACTplusSym(nbits, init_clip_val=clip_val, dequantize=True, inplace=False, intg_zp=align_zero)
     if qa_mode == "pact+" and not non_neg:
         return PACT2(nbits, init_clip_valn=clip_valn, init_clip_val=clip_val, dequantize=True, inplace=False,
                      pact_plus=True, align_zero=align_zero)  # fmt: skip

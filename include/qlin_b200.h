@@ -192,6 +192,8 @@ typedef struct qlin_quant_args {
   int32_t dl8_flush;      /* QLIN_Q_F8_DYN: flush |code| < 0.0087890625 to 0 */
   int32_t scale_in_stride;/* QLIN_Q_I8_GIVEN_SCALE: 0 = one scalar, 1 = per row */
   float scale0, zp0, lo, hi, shift, add2; /* static modes */
+  float dyn_eps;          /* dynamic modes: lower clamp of the row absmax; the deploy modules use 1e-5,
+                             QLinearINT8Train uses 0 (fms_mo/modules/linear.py:2167-2171) */
 } qlin_quant_args;
 
 int qlin_act_quant(const qlin_quant_args* args, void* stream);
@@ -211,6 +213,15 @@ int qlin_act_quant(const qlin_quant_args* args, void* stream);
  *       The two sums are reduced in a fixed order (run-to-run deterministic) through a
  *       caller-provided workspace of qlin_pact2_bwd_workspace_bytes(numel) bytes.
  * ---------------------------------------------------------------------------------------------- */
+/* variant: which member of the PACT+ family.
+ *   QLIN_PACT_TWO_SIDED  PACT2 / PACTplus2STE (above).
+ *   QLIN_PACT_ONE_SIDED  PACT / PACTplusSTE (fms_mo/quant/quantizers.py:1016-1070): clamp to [0, cv],
+ *                        step = cv / (2^b - 1); grad_clip[0] only.
+ *   QLIN_PACT_SYMMETRIC  PACTplusSym / PACTplusSymSTE_rev1 (:1073-1154): clamp to [-cv, cv], levels
+ *                        2^b - 2 when align_zero (the reference's intg_zp) else 2^b - 1, out-of-range
+ *                        input gradients zeroed; grad_clip[0] only. */
+typedef enum qlin_pact_variant { QLIN_PACT_TWO_SIDED = 0, QLIN_PACT_ONE_SIDED = 1, QLIN_PACT_SYMMETRIC = 2 } qlin_pact_variant;
+
 typedef struct qlin_pact2_args {
   const void* x;
   const void* grad_out;   /* bwd only */
@@ -223,6 +234,7 @@ typedef struct qlin_pact2_args {
   int32_t dtype;          /* F32 / F16 / BF16 (x, out, grad_out) */
   int32_t num_bits;
   int32_t align_zero;
+  int32_t variant;        /* qlin_pact_variant */
 } qlin_pact2_args;
 
 int qlin_pact2_fwd(const qlin_pact2_args* args, void* stream);

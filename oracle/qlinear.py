@@ -132,3 +132,21 @@ def linear_fpx_forward(
     if return_parts:
         return out, xq, x_scale, wq, w_scale, acc
     return out
+
+
+def linear_int8_train_forward(x, weight, bias, lsb_trun_bits=0, chunk_size=64, max_acc_bits=32):
+    """LinearFuncINT8FwdFP32Bwd.forward (fms_mo/modules/linear.py:2142-2191): per-token and per-channel
+    ``amax / 127`` scales without a lower clamp, codes cast to int8 without clamp, chunk-truncating
+    int matmul, ``acc.float() * x_scale * w_scale.t()`` cast to the input dtype, ``+ bias``."""
+    org_dtype = x.dtype
+    tar_shape = x.shape[:-1] + (weight.shape[0],)
+    x2 = x.reshape(-1, x.shape[-1])
+    x_scale = x2.abs().amax(dim=-1, keepdim=True) / 127
+    w_scale = weight.abs().amax(dim=-1, keepdim=True) / 127
+    x_i8 = torch.round(x2 / x_scale).to(torch.int8)
+    w_i8 = torch.round(weight / w_scale).to(torch.int8)
+    acc = G.imatmul_chunk_truncate(x_i8, w_i8.t(), chunk_trun_bits=lsb_trun_bits, chunk_size=chunk_size, max_acc_bits=max_acc_bits)
+    out = (acc.to(torch.float) * x_scale * w_scale.t()).reshape(tar_shape).to(org_dtype)
+    if bias is not None:
+        out = out + bias.to(org_dtype)
+    return out

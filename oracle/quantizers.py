@@ -140,6 +140,55 @@ def pact2plus_bwd(
     return gx, ga.sum(), gan.sum()
 
 
+def pact_one_sided_fwd(x, clip_val, num_bits=8):
+    """PACTplusSTE.forward, dequantize=True (fms_mo/quant/quantizers.py:1018-1042)."""
+    cv = clip_val.to(x.dtype)
+    stepsize = 1.0 / ((2**num_bits - 1) / cv)
+    return torch.round(torch.clamp(x, torch.zeros_like(cv), cv) / stepsize) * stepsize
+
+
+def pact_one_sided_bwd(x, grad_out, clip_val, num_bits=8):
+    """PACTplusSTE.backward (fms_mo/quant/quantizers.py:1044-1070): ``(grad_x, grad_clip_val)``."""
+    cv = clip_val.to(x.dtype)
+    n_levels = 2**num_bits - 1
+    stepsize = 1.0 / (n_levels / cv)
+    z = x / stepsize
+    delz = (z - torch.round(z)) / n_levels
+    ga = -grad_out * delz
+    zeros = torch.zeros_like(grad_out)
+    gx = torch.where(x <= 0, zeros, grad_out)
+    gx = torch.where(x >= cv, zeros, gx)
+    ga = torch.where(x <= 0, zeros, ga)
+    ga = torch.where(x >= cv, grad_out, ga)
+    return gx, ga.sum()
+
+
+def pact_sym_fwd(x, clip_val, num_bits=8, intg_zp=True):
+    """PACTplusSymSTE_rev1.forward, dequantize=True (fms_mo/quant/quantizers.py:1077-1116)."""
+    cv = clip_val.to(x.dtype)
+    n_levels = 2**num_bits - 2 if intg_zp else 2**num_bits - 1
+    stepsize = 1.0 / (n_levels / (2 * cv))
+    out = torch.where(x > cv, torch.ones_like(x) * cv, x)
+    out = torch.where(out < -cv, torch.ones_like(x) * -cv, out)
+    return torch.round((out + cv) / stepsize) * stepsize - cv
+
+
+def pact_sym_bwd(x, grad_out, clip_val, num_bits=8, intg_zp=True):
+    """PACTplusSymSTE_rev1.backward with out-of-range gradients clipped (fms_mo/quant/quantizers.py:1118-1154)."""
+    cv = clip_val.to(x.dtype)
+    n_levels = 2**num_bits - 2 if intg_zp else 2**num_bits - 1
+    stepsize = 1.0 / (n_levels / (2 * cv))
+    z = (x + cv) / stepsize
+    delz = 2 * (torch.round(z) - z) / n_levels
+    zeros = torch.zeros_like(grad_out)
+    gx = torch.where(x <= -cv, zeros, grad_out)
+    gx = torch.where(x >= cv, zeros, gx)
+    ga = torch.ones_like(grad_out) * delz
+    ga = torch.where(x <= -cv, -torch.ones_like(gx), ga)
+    ga = torch.where(x >= cv, torch.ones_like(gx), ga)
+    return gx, (ga * grad_out).sum()
+
+
 # ---------------------------------------------------------------------------------------------
 # FP8 scaling of the FP8 linear
 # ---------------------------------------------------------------------------------------------

@@ -228,9 +228,50 @@ def gen_aiu_vectors():
     save("aiu_i8i8_vectors.pt", out)
 
 
+def gen_extra():
+    """One-sided and symmetric PACT+ (forward and backward) and QLinearINT8Train.forward (its tl_matmul
+    replaced by oracle.gemm.imatmul_chunk_truncate, everything else the reference's code)."""
+    torch.manual_seed(5)
+    out = {"pact1": [], "pactsym": [], "int8train": []}
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        for nbits in (8, 4):
+            x = (torch.randn(29, 96) * 3).to(dtype).requires_grad_(True)
+            g = torch.randn(29, 96).to(dtype)
+            q = ref_q.PACT(nbits, init_clip_val=3.3, dequantize=True, pact_plus=True)
+            y = q(x)
+            y.backward(g)
+            out["pact1"].append(dict(dtype=dtype, nbits=nbits, cv=3.3, x=x.detach().clone(), g=g, y=y.detach().clone(),
+                                     gx=x.grad.clone(), gcv=q.clip_val.grad.clone()))  # fmt: skip
+            for intg in (True, False):
+                x = (torch.randn(29, 96) * 3).to(dtype).requires_grad_(True)
+                q = ref_q.PACTplusSym(nbits, init_clip_val=2.7, dequantize=True, intg_zp=intg)
+                y = q(x)
+                y.backward(g)
+                out["pactsym"].append(dict(dtype=dtype, nbits=nbits, cv=2.7, intg=intg, x=x.detach().clone(), g=g,
+                                           y=y.detach().clone(), gx=x.grad.clone(), gcv=q.clip_val.grad.clone()))  # fmt: skip
+
+    def tl_matmul(a, b, chunk_trun_bits=0, chunk_size=16, max_acc_bits=32, **kw):
+        return OG.imatmul_chunk_truncate(a, b, chunk_trun_bits=chunk_trun_bits, chunk_size=chunk_size, max_acc_bits=max_acc_bits)
+
+    ref_linear.tl_matmul = tl_matmul
+    for dtype in (torch.float32, torch.bfloat16):
+        for trun, chunk, accb, bias in ((0, 64, 32, True), (8, 64, 32, False), (4, 32, 24, True)):
+            M, K, N = 20, 192, 72
+            x = torch.randn(M, K).to(dtype)
+            lin = torch.nn.Linear(K, N, bias=bias).to(dtype)
+            q = ref_linear.QLinearINT8Train.from_fms_mo(lin, lsb_trun_bits=trun, chunk_size=chunk, max_acc_bits=accb,
+                                                        target_device="cpu")  # fmt: skip
+            with torch.no_grad():
+                y = q(x.reshape(4, 5, K))
+            out["int8train"].append(dict(dtype=dtype, trun=trun, chunk=chunk, accb=accb, x=x, weight=lin.weight.detach().clone(),
+                                         bias=None if not bias else lin.bias.detach().clone(), y=y.clone()))  # fmt: skip
+    save("extra.pt", out)
+
+
 if __name__ == "__main__":
     gen_quantizers()
     gen_qlinear()
     gen_deploy()
     gen_fp8()
     gen_aiu_vectors()
+    gen_extra()

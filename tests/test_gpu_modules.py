@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from conftest import load_golden
-from fms_model_optimizer_b200.modules import LinearFPxAcc, QLinear, QLinearINT8Deploy
+from fms_model_optimizer_b200.modules import LinearFPxAcc, QLinear, QLinearINT8Deploy, QLinearINT8Train
 from fms_model_optimizer_b200.modules.linear import lower_qmodel_b200
 from oracle import qlinear as OL
 from test_host_logic import _RefLikeQLinear
@@ -168,3 +168,41 @@ def test_lowering_swaps_modules(cuda_dev):
     assert torch.norm(y - y_fake) / torch.norm(y_fake) < 2e-2
     with torch.no_grad():
         assert m(x).shape == (10, 32)
+
+
+def test_int8_train_linear_matches_reference_outputs(cuda_dev):
+    """QLinearINT8Train.forward against outputs of the reference class (bit-exact), and its
+    floating-point backward against autograd of a plain linear."""
+    for c in load_golden("extra.pt")["int8train"]:
+        K, N = c["x"].shape[1], c["weight"].shape[0]
+        lin = torch.nn.Linear(K, N, bias=c["bias"] is not None).to(c["dtype"])
+        with torch.no_grad():
+            lin.weight.copy_(c["weight"])
+            if c["bias"] is not None:
+                lin.bias.copy_(c["bias"])
+        q = QLinearINT8Train.from_fms_mo(lin.to(cuda_dev), lsb_trun_bits=c["trun"], chunk_size=c["chunk"], max_acc_bits=c["accb"])
+        x = c["x"].reshape(4, 5, K).to(cuda_dev).requires_grad_(True)
+        y = q(x)
+        assert y.dtype == c["dtype"] and torch.equal(y.detach().cpu(), c["y"]), (c["dtype"], c["trun"], c["chunk"], c["accb"])
+        g = torch.randn_like(y)
+        y.backward(g)
+        xr = c["x"].reshape(4, 5, K).to(cuda_dev).requires_grad_(True)
+        wr = c["weight"].to(cuda_dev).requires_grad_(True)
+        torch.nn.functional.linear(xr, wr).backward(g)
+        tol = 1e-4 if c["dtype"] == torch.float32 else 5e-2
+        assert torch.allclose(x.grad.float(), xr.grad.float(), rtol=tol, atol=tol)
+        assert torch.allclose(q.weight.grad.float(), wr.grad.float(), rtol=tol, atol=tol)
+        if c["bias"] is not None:
+            assert torch.allclose(q.bias.grad.float(), g.reshape(-1, N).sum(0).float(), rtol=tol, atol=tol)
+
+
+def test_int8_train_linear_larger_shape_vs_oracle(cuda_dev):
+    torch.manual_seed(3)
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        x = torch.randn(300, 1024).to(dtype)
+        lin = torch.nn.Linear(1024, 520, bias=True).to(dtype)
+        want = OL.linear_int8_train_forward(x, lin.weight.detach(), lin.bias.detach(), 8, 64, 32)
+        q = QLinearINT8Train.from_fms_mo(lin.to(cuda_dev), lsb_trun_bits=8, chunk_size=64, max_acc_bits=32)
+        with torch.no_grad():
+            got = q(x.to(cuda_dev))
+        assert torch.equal(got.cpu(), want), dtype

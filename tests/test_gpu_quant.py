@@ -7,7 +7,7 @@ import torch
 from conftest import load_golden
 from fms_model_optimizer_b200 import _lib as L
 from fms_model_optimizer_b200 import ops
-from fms_model_optimizer_b200.quant.quantizers import PACT2, SAWB, QMaxDynamic, Qmax
+from fms_model_optimizer_b200.quant.quantizers import PACT, PACT2, SAWB, PACTplusSym, QMaxDynamic, Qmax
 from oracle import quantizers as OQ
 
 pytestmark = pytest.mark.gpu
@@ -101,6 +101,25 @@ def test_pact2_forward_backward_vs_reference_golden(cuda_dev):
         for got, want in ((q.clip_val.grad, c["gcv"]), (q.clip_valn.grad, c["gcvn"])):
             scale = max(1.0, c["g"].float().abs().sum().item() * 0.05)
             assert abs(got.item() - want.float().item()) <= eps * scale, (c["dtype"], got.item(), want.item())
+
+
+def test_pact_one_sided_and_symmetric_vs_reference_golden(cuda_dev):
+    g = load_golden("extra.pt")
+    eps = {torch.float32: 2e-5, torch.bfloat16: 2e-2, torch.float16: 4e-3}
+    for kind in ("pact1", "pactsym"):
+        for c in g[kind]:
+            if kind == "pact1":
+                q = PACT(c["nbits"], init_clip_val=c["cv"], dequantize=True, pact_plus=True).to(cuda_dev)
+            else:
+                q = PACTplusSym(c["nbits"], init_clip_val=c["cv"], dequantize=True, intg_zp=c["intg"]).to(cuda_dev)
+            x = c["x"].to(cuda_dev).requires_grad_(True)
+            y = q(x)
+            assert torch.equal(y.detach().cpu(), c["y"]), (kind, c["dtype"], c["nbits"])
+            y.backward(c["g"].to(cuda_dev))
+            assert torch.equal(x.grad.cpu(), c["gx"])
+            scale = max(1.0, c["g"].float().abs().sum().item() * 0.05)
+            got, want = q.clip_val.grad.item(), c["gcv"].float().item()
+            assert abs(got - want) <= eps[c["dtype"]] * scale, (kind, c["dtype"], got, want)
 
 
 def test_pact2_backward_is_deterministic_and_matches_oracle_fp32(cuda_dev):

@@ -159,3 +159,26 @@ def test_chunk_gemm_properties():
     e128 = rel(OG.imatmul_chunk_truncate(a, b, chunk_trun_bits=8, chunk_size=128))
     assert e32 < 1e-2 and e128 < 1e-2
     assert rel(OG.imatmul_chunk_truncate(a, b, max_acc_bits=18, chunk_size=32)) < 1e-2
+
+
+def test_pact_one_sided_and_symmetric_match_reference():
+    g = load_golden("extra.pt")
+    for c in g["pact1"]:
+        cv = torch.tensor([c["cv"]])
+        assert torch.equal(OQ.pact_one_sided_fwd(c["x"], cv, c["nbits"]), c["y"]), (c["dtype"], c["nbits"])
+        gx, gcv = OQ.pact_one_sided_bwd(c["x"], c["g"], cv, c["nbits"])
+        assert torch.equal(gx, c["gx"])
+        assert torch.equal(gcv.reshape(1).float(), c["gcv"].float())
+    for c in g["pactsym"]:
+        cv = torch.tensor([c["cv"]])
+        assert torch.equal(OQ.pact_sym_fwd(c["x"], cv, c["nbits"], c["intg"]), c["y"]), (c["dtype"], c["nbits"], c["intg"])
+        gx, gcv = OQ.pact_sym_bwd(c["x"], c["g"], cv, c["nbits"], c["intg"])
+        assert torch.equal(gx, c["gx"])
+        assert torch.equal(gcv.reshape(1).float(), c["gcv"].float())
+
+
+def test_linear_int8_train_forward_matches_reference():
+    for c in load_golden("extra.pt")["int8train"]:
+        K = c["x"].shape[1]
+        y = OL.linear_int8_train_forward(c["x"].reshape(4, 5, K), c["weight"], c["bias"], c["trun"], c["chunk"], c["accb"])
+        assert y.dtype == c["y"].dtype and torch.equal(y, c["y"]), (c["dtype"], c["trun"], c["chunk"], c["accb"])
