@@ -24,13 +24,14 @@ DT_NONE, DT_I8, DT_U8, DT_I32, DT_F32, DT_F16, DT_BF16, DT_F8E4M3 = range(8)
 EPI_RAW, EPI_SCALE_PROD, EPI_SCALE_SEQ = 0, 1, 2
 
 # qlin_quant_mode
-Q_I8_DYN, Q_I8_STATIC, Q_I8_STATIC_CLAMP_FIRST, Q_F8_DYN, Q_I8_GIVEN_SCALE = range(5)
+Q_I8_DYN, Q_I8_STATIC, Q_I8_STATIC_CLAMP_FIRST, Q_F8_DYN, Q_I8_GIVEN_SCALE, Q_F8_FAKE_SCALED = range(6)
 
 # qlin_pact_variant
 PACT_TWO_SIDED, PACT_ONE_SIDED, PACT_SYMMETRIC = 0, 1, 2
 
 # qlin_wq_mode
 W_SAWB, W_MAX, W_GIVEN = 0, 1, 2
+PT_INT_SYM, PT_F8_SCALED, PT_F8_SAT = 0, 1, 2
 
 EXPORTED_SYMBOLS = (
     "qlin_version",
@@ -44,6 +45,8 @@ EXPORTED_SYMBOLS = (
     "qlin_pact2_bwd_noalloc",
     "qlin_pact2_bwd_noalloc_max_numel",
     "qlin_weight_fq_perch",
+    "qlin_tensor_fq",
+    "qlin_tensor_fq_workspace_bytes",
 )
 
 
@@ -153,6 +156,24 @@ class WfqArgs(C.Structure):
     ]
 
 
+class TensorFqArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p),
+        ("out", C.c_void_p),
+        ("clip_io", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("numel", C.c_int64),
+        ("dtype", C.c_int32),
+        ("num_bits", C.c_int32),
+        ("mode", C.c_int32),
+        ("kind", C.c_int32),
+        ("align_zero", C.c_int32),
+        ("dequantize", C.c_int32),
+        ("c0", C.c_float),
+        ("c1", C.c_float),
+    ]
+
+
 _lib = None
 
 
@@ -178,6 +199,7 @@ def load() -> C.CDLL:
         ("qlin_pact2_bwd", Pact2Args),
         ("qlin_pact2_bwd_noalloc", Pact2Args),
         ("qlin_weight_fq_perch", WfqArgs),
+        ("qlin_tensor_fq", TensorFqArgs),
     ):
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(struct), C.c_void_p]
@@ -185,6 +207,8 @@ def load() -> C.CDLL:
     lib.qlin_pact2_bwd_workspace_bytes.argtypes = [C.c_int64]
     lib.qlin_pact2_bwd_workspace_bytes.restype = C.c_size_t
     lib.qlin_pact2_bwd_noalloc_max_numel.restype = C.c_int64
+    lib.qlin_tensor_fq_workspace_bytes.argtypes = [C.c_int64]
+    lib.qlin_tensor_fq_workspace_bytes.restype = C.c_int64
     _lib = lib
     return lib
 

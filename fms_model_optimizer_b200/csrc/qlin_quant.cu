@@ -48,6 +48,13 @@ __device__ __forceinline__ float smooth_apply(const QuantParams& p, float x, flo
 template <typename XT>
 __device__ __forceinline__ float dyn_scale(const QuantParams& p, float amax) {
   const float eps = rnd_if<XT>(p.dyn_eps, p.native);
+  if (p.mode == QLIN_Q_F8_FAKE_SCALED) {
+    // max_to_scale: 448 / clamp(amax, eps) is reciprocal * 448 (scalar numerator), then the fp16 cap
+    const float r = rnd_if<XT>(__fdiv_rn(1.0f, fmaxf(amax, eps)), p.native);
+    float sc = rnd_if<XT>(__fmul_rn(r, 448.0f), p.native);
+    if (std::is_same<XT, __half>::value && p.native) sc = fminf(sc, 65504.0f);
+    return sc;
+  }
   if (p.mode == QLIN_Q_F8_DYN) {
     const float a = rnd_if<XT>(__fdiv_rn(amax, 448.0f), p.native);
     return fmaxf(a, eps);
@@ -98,6 +105,15 @@ __device__ __forceinline__ uint8_t quant_one(const QuantParams& p, float v, floa
       dq = r;
       return static_cast<uint8_t>(static_cast<int>(r) & 0xFF);
     }
+    case QLIN_Q_F8_FAKE_SCALED: {  // s multiplies: x * s, saturate, cast to e4m3 and back, / s
+      float t = rnd_if<XT>(__fmul_rn(v, s), nat);
+      const bool is_nan = t != t;  // torch.clamp keeps NaN, fminf / fmaxf would drop it
+      t = fminf(fmaxf(t, -448.0f), 448.0f);
+      if (is_nan) t = __int_as_float(0x7FC00000);
+      const uint8_t c = to_e4m3(t);
+      dq = rnd_if<XT>(__fdiv_rn(from_e4m3(c), s), nat);
+      return c;
+    }
     default: {  // QLIN_Q_F8_DYN
       const float t = rnd_if<XT>(div_exact(v, s, rs), nat);
       uint8_t c = to_e4m3(t);
@@ -112,7 +128,9 @@ __device__ __forceinline__ uint8_t quant_one(const QuantParams& p, float v, floa
   }
 }
 
-__device__ __forceinline__ bool is_dynamic(int mode) { return mode == QLIN_Q_I8_DYN || mode == QLIN_Q_F8_DYN; }
+__device__ __forceinline__ bool is_dynamic(int mode) {
+  return mode == QLIN_Q_I8_DYN || mode == QLIN_Q_F8_DYN || mode == QLIN_Q_F8_FAKE_SCALED;
+}
 
 template <typename XT>
 __device__ __forceinline__ float row_scale_of(const QuantParams& p, int row, float amax) {
@@ -955,7 +973,7 @@ extern "C" int qlin_act_quant(const qlin_quant_args* a, void* stream) {
   if (a->rows == 0 || a->cols == 0) return QLIN_OK;
   if (a->ldx < a->cols || (a->codes != nullptr && a->ldq < a->cols) || (a->dq_out != nullptr && a->lddq < a->cols))
     return fail(QLIN_ERR_BAD_SHAPE, "qlin_act_quant: leading dimension smaller than the row length");
-  if (a->mode < QLIN_Q_I8_DYN || a->mode > QLIN_Q_I8_GIVEN_SCALE)
+  if (a->mode < QLIN_Q_I8_DYN || a->mode > QLIN_Q_F8_FAKE_SCALED)
     return fail(QLIN_ERR_UNSUPPORTED, "qlin_act_quant: unknown mode %d", a->mode);
   if (a->smooth != nullptr && !a->smooth_mul && a->smooth_rcp == nullptr)
     return fail(QLIN_ERR_NULL, "qlin_act_quant: smooth_rcp is required when rows are divided by smooth");

@@ -399,6 +399,48 @@ def weight_fq_perch(
     return dq, codes, clip_io
 
 
+def tensor_fq(
+    x: torch.Tensor,
+    *,
+    kind: int = L.PT_INT_SYM,
+    mode: int = L.W_SAWB,
+    num_bits: int = 8,
+    clip: Optional[torch.Tensor] = None,
+    align_zero: bool = True,
+    dequantize: bool = True,
+    want_out: bool = True,
+    c0: float = 0.0,
+    c1: float = 0.0,
+) -> Tuple[Optional[torch.Tensor], torch.Tensor]:
+    """Per-tensor fake quantisation; returns ``(out, clip[1] fp32)``.  See ``qlin_tensor_fq`` in
+    include/qlin_b200.h."""
+    dev = _require_cuda(x, clip)
+    if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise RuntimeError(f"unsupported dtype {x.dtype}")
+    xc = x if x.is_contiguous() else x.contiguous()
+    if mode == L.W_GIVEN:
+        if kind != L.PT_F8_SAT and (clip is None or clip.numel() != 1):
+            raise RuntimeError("W_GIVEN needs one clip value")
+        clip_io = _clip_f32(clip, dev).clone() if clip is not None else torch.zeros(1, dtype=torch.float32, device=dev)
+        ws = None
+    else:
+        clip_io = torch.empty((1,), dtype=torch.float32, device=dev)
+        ws = torch.empty((L.load().qlin_tensor_fq_workspace_bytes(xc.numel()) // 4,), dtype=torch.float32, device=dev)
+    out = torch.empty_like(xc) if want_out else None
+    if xc.numel() == 0:
+        return out, clip_io
+    args = L.TensorFqArgs(
+        x=_ptr(xc), out=_ptr(out), clip_io=_ptr(clip_io), workspace=_ptr(ws), numel=xc.numel(), dtype=_DT[xc.dtype],
+        num_bits=int(num_bits), mode=int(mode), kind=int(kind), align_zero=int(bool(align_zero)),
+        dequantize=int(bool(dequantize)), c0=float(c0), c1=float(c1),
+    )  # fmt: skip
+    nbytes = xc.numel() * xc.element_size() * ((1 if mode != L.W_GIVEN else 0) + (2 if want_out else 0))
+    with torch.cuda.device(dev):
+        rc = _timed("tensor_fq", float(nbytes), dev, lambda: L.load().qlin_tensor_fq(C.byref(args), _stream(dev)))
+        L.check(rc, "qlin_tensor_fq")
+    return (out.view_as(x) if out is not None else None), clip_io
+
+
 # --------------------------------------------------------------------------------------------------
 # PACT+ two-sided fake quantisation
 # --------------------------------------------------------------------------------------------------

@@ -153,17 +153,39 @@ class _PerChSTE(torch.autograd.Function):
         return grad_output.clone(), None, None, None, None
 
 
+class _PerTensorSTE(torch.autograd.Function):
+    """Per-tensor symmetric fake quantisation with identity gradient: SAWBPlusZeroSTE
+    (fms_mo/quant/quantizers.py:455-500) and QmaxSTE (:3159-3187)."""
+
+    @staticmethod
+    def forward(ctx, x, num_bits, mode, clip_buf, dequantize, align_zero):
+        c0, c1 = SAWB_COEFFS.get(num_bits, (0.0, 0.0))
+        if mode == L.W_SAWB and num_bits not in SAWB_COEFFS:
+            mode = L.W_MAX
+        out, clip = ops.tensor_fq(
+            x, kind=L.PT_INT_SYM, mode=mode, num_bits=num_bits, clip=(clip_buf if mode == L.W_GIVEN else None),
+            align_zero=align_zero, dequantize=dequantize, c0=c0, c1=c1,
+        )  # fmt: skip
+        if mode != L.W_GIVEN:
+            clip_buf.copy_(clip.to(clip_buf.dtype))
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return grad_output, None, None, None, None, None
+
+
 class SAWB(nn.Module):
-    """SAWB+ with zero alignment, per output channel (fms_mo/quant/quantizers.py:377-452, :503-572):
-    in training mode the clip value of every channel is recomputed from mean|w| and sqrt(mean w^2),
-    in eval mode the stored ``clip_val`` is used."""
+    """SAWB+ with zero alignment (fms_mo/quant/quantizers.py:377-452), per output channel
+    (SAWBPlusZeroPerChSTE, :503-572) or per tensor (SAWBPlusZeroSTE, :455-500): in training mode the
+    clip value is recomputed from mean|w| and sqrt(mean w^2), in eval mode the stored ``clip_val`` is used."""
 
     def __init__(self, num_bits, dequantize=True, inplace=False, align_zero=False, clipSTE=True, perCh=False, interp=False):
         super().__init__()
         if num_bits not in [2, 4, 8]:
             raise ValueError("FMS: SAWB supports 2, 4, and 8-bit quantization only.")
-        if not (clipSTE and align_zero and perCh) or inplace:
-            raise NotImplementedError("SAWB on B200 provides the sawb+ per-channel quantizer (align_zero, perCh)")
+        if not (clipSTE and align_zero) or inplace:
+            raise NotImplementedError("SAWB on B200 provides the sawb+ quantizers (clipSTE, align_zero)")
         self.num_bits = num_bits
         self.dequantize = dequantize
         self.inplace = inplace
@@ -171,27 +193,29 @@ class SAWB(nn.Module):
         self.clipSTE = clipSTE
         self.perCh = perCh
         self.interp = interp
-        self.quantizer = _PerChSTE
-        self.register_buffer("clip_val", torch.zeros(perCh))
+        self.quantizer = _PerChSTE if perCh else _PerTensorSTE
+        self.register_buffer("clip_val", torch.zeros(perCh) if perCh else torch.Tensor([0.0]))
 
     def forward(self, input_tensor: torch.Tensor) -> torch.Tensor:
         mode = L.W_SAWB if self.training else L.W_GIVEN
-        return self.quantizer.apply(input_tensor, self.num_bits, mode, self.clip_val, self.dequantize)
+        if self.perCh:
+            return self.quantizer.apply(input_tensor, self.num_bits, mode, self.clip_val, self.dequantize)
+        return self.quantizer.apply(input_tensor, self.num_bits, mode, self.clip_val, self.dequantize, True)
 
     def __repr__(self):
         return f"{self.__class__.__name__}(num_bits={self.num_bits}, quantizer={self.quantizer})"
 
 
 class Qmax(nn.Module):
-    """Symmetric max quantizer per output channel (fms_mo/quant/quantizers.py:2990-3141, :3190-3224):
-    training uses the fresh per-row absmax and keeps a moving average (factor 0.1) in ``clip_val``;
-    eval uses the stored value."""
+    """Symmetric max quantizer (fms_mo/quant/quantizers.py:2990-3141), per output channel (QmaxPerChSTE,
+    :3190-3224) or per tensor (QmaxSTE, :3159-3187): training uses the fresh absmax and keeps a moving
+    average (factor 0.1) in ``clip_val``; eval uses the stored value."""
 
     def __init__(self, num_bits, dequantize=True, inplace=False, align_zero=False, clipSTE=True, minmax=False,
                  perCh=None, perGp=None, extend_act_range=False):  # fmt: skip
         super().__init__()
-        if minmax or perGp or extend_act_range or not perCh or inplace or not dequantize:
-            raise NotImplementedError("Qmax on B200 provides the symmetric per-channel quantizer")
+        if minmax or perGp or extend_act_range or inplace or (perCh and not dequantize):
+            raise NotImplementedError("Qmax on B200 provides the symmetric per-channel and per-tensor quantizers")
         self.num_bits = num_bits
         self.dequantize = dequantize
         self.align_zero = align_zero
@@ -199,13 +223,18 @@ class Qmax(nn.Module):
         self.movAvgFac = 0.1
         self.Niter = 0
         self.quantizer_name = "Qmax"
-        self.register_buffer("clip_val", torch.zeros(perCh))
-        self.register_buffer("clip_valn", torch.zeros(perCh))
+        self.register_buffer("clip_val", torch.zeros(perCh) if perCh else torch.Tensor([0.0]))
+        self.register_buffer("clip_valn", torch.zeros(perCh) if perCh else torch.Tensor([0.0]))
+
+    def _quantise(self, x, mode, clip):
+        if self.perCh:
+            return _PerChSTE.apply(x, self.num_bits, mode, clip, True)
+        return _PerTensorSTE.apply(x, self.num_bits, mode, clip, self.dequantize, self.align_zero)
 
     def forward(self, input_tensor):
         if self.training:
             fresh = torch.empty_like(self.clip_val, dtype=torch.float32)
-            out = _PerChSTE.apply(input_tensor, self.num_bits, L.W_MAX, fresh, True)
+            out = self._quantise(input_tensor, L.W_MAX, fresh)
             with torch.no_grad():
                 new = fresh.to(input_tensor.dtype)
                 if self.Niter == 0:
@@ -214,12 +243,12 @@ class Qmax(nn.Module):
                 self.clip_val.copy_(self.clip_val * (1.0 - self.movAvgFac) + new * self.movAvgFac)
                 self.clip_valn.copy_(self.clip_valn * (1.0 - self.movAvgFac) + (-new) * self.movAvgFac)
         else:
-            out = _PerChSTE.apply(input_tensor, self.num_bits, L.W_GIVEN, self.clip_val, True)
+            out = self._quantise(input_tensor, L.W_GIVEN, self.clip_val)
         self.Niter += 1
         return out
 
     def __repr__(self):
-        return f"Qmax(num_bits={self.num_bits}, per channel of {self.perCh})"
+        return f"Qmax(num_bits={self.num_bits}, " + (f"per channel of {self.perCh})" if self.perCh else "per tensor)")
 
 
 class QMaxDynamic(nn.Module):
@@ -254,6 +283,63 @@ class PerTokenMax(QMaxDynamic):
         self.register_buffer("clip_valn", torch.Tensor([0.0]))
 
 
+class _Fp8FakeSTE(torch.autograd.Function):
+    """e4m3 quantise-dequantise with identity gradient."""
+
+    @staticmethod
+    def forward(ctx, x, variant):
+        if variant == "row":
+            x2 = x.reshape(-1, x.shape[-1])
+            native = 0 if x2.dtype == torch.float32 else 3
+            _, _, dq = ops.act_quant(x2, mode=L.Q_F8_FAKE_SCALED, native_chain=native, want_codes=False, want_dq=True,
+                                     dyn_eps=1e-12)  # fmt: skip
+            return dq.view_as(x)
+        if variant == "tensor":
+            return ops.tensor_fq(x, kind=L.PT_F8_SCALED, mode=L.W_MAX)[0]
+        return ops.tensor_fq(x, kind=L.PT_F8_SAT, mode=L.W_GIVEN)[0]
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return grad_output, None
+
+
+class to_fp8(nn.Module):  # noqa: N801  (the reference's class name)
+    """FP8 e4m3 quantise-dequantise in the tensor dtype (fms_mo/quant/quantizers.py:5422-5488 with
+    to_fp8_saturated / to_fp8_scaled / to_fp8_scaled_perCh / to_fp8_scaled_perToken, :5316-5420):
+    ``emulate=True`` only.  The reference's e5m2 branch cannot be constructed (it names a dtype that
+    does not exist), so only e4m3 is provided."""
+
+    def __init__(self, n_bits: int = 8, q_mode: str = "fp8_e4m3_sat", perCh=None, perToken: bool = False, emulate: bool = True):
+        super().__init__()
+        assert n_bits == 8, "only for 8-bit floating point conversion"
+        if "e4m3" not in q_mode:
+            raise ValueError("FP8 on B200 provides e4m3 (the reference's e5m2 quantizer cannot be constructed)")
+        if not emulate:
+            raise NotImplementedError("to_fp8 on B200 provides emulate=True; real FP8 tensors come from LinearFPxAcc")
+        self.q_mode = q_mode
+        self.float8_dtype = torch.float8_e4m3fn
+        self.emulate = emulate
+        self.perCh = perCh
+        self.perToken = perToken
+        self.register_buffer("scale", torch.zeros(perCh) if perCh else torch.Tensor([0.0]))
+
+    def forward(self, x: torch.Tensor):
+        if self.perCh:
+            if x.dim() != 2:
+                raise RuntimeError("per-channel FP8 quantisation expects a [out, in] weight")
+            return _Fp8FakeSTE.apply(x, "row")
+        if self.perToken:
+            return _Fp8FakeSTE.apply(x, "row")
+        if "_sat" in self.q_mode:
+            return _Fp8FakeSTE.apply(x, "sat")
+        if "_scale" in self.q_mode:
+            return _Fp8FakeSTE.apply(x, "tensor")
+        return None
+
+    def __repr__(self):
+        return f"{self.__class__.__name__}(q_mode={self.q_mode}, emulate={self.emulate})"
+
+
 def get_activation_quantizer(qa_mode="pact+", nbits=8, clip_val=None, clip_valn=None, non_neg=False, align_zero=True, **_):
     """Subset of get_activation_quantizer (fms_mo/quant/quantizers.py:46-226) for the modes on the
     quantized Linear's path."""
@@ -266,14 +352,22 @@ def get_activation_quantizer(qa_mode="pact+", nbits=8, clip_val=None, clip_valn=
                      pact_plus=True, align_zero=align_zero)  # fmt: skip
     if "max" in qa_mode and ("pertoken" in qa_mode or "perToken" in qa_mode):
         return QMaxDynamic(nbits, dim=-1)
+    if "max" in qa_mode and "min" not in qa_mode and "per_channel" not in qa_mode and "perCh" not in qa_mode:
+        return Qmax(nbits, align_zero=True if "sym" in qa_mode else align_zero, minmax=False)
+    if "fp8" in qa_mode and "custom" not in qa_mode:
+        return to_fp8(nbits, q_mode=qa_mode, perToken="perToken" in qa_mode, emulate=True)
     raise NotImplementedError(f"activation quantizer {qa_mode!r} is not on the B200 quantized-Linear path")
 
 
-def get_weight_quantizer(qw_mode="sawb+", nbits=8, w_shape=None, align_zero=True, **_):
+def get_weight_quantizer(qw_mode="sawb+", nbits=8, w_shape=None, align_zero=True, clip_val=None, **_):
     """Subset of get_weight_quantizer (fms_mo/quant/quantizers.py:229-374)."""
     cout = w_shape[0] if w_shape is not None else None
-    if qw_mode in ("sawb+perCh", "sawb+_perCh") or (qw_mode.startswith("sawb") and "perCh" in qw_mode):
-        return SAWB(nbits, dequantize=True, inplace=False, align_zero=True, clipSTE=True, perCh=cout)
-    if qw_mode in ("maxperCh", "max_perCh"):
-        return Qmax(nbits, align_zero=align_zero, minmax=False, perCh=cout)
+    if "sawb" in qw_mode and "+" in qw_mode and "interp" not in qw_mode:
+        return SAWB(nbits, dequantize=True, inplace=False, align_zero=True, clipSTE=True, perCh=cout if "perCh" in qw_mode else False)
+    if "max" in qw_mode and "min" not in qw_mode and "perGp" not in qw_mode:
+        return Qmax(nbits, align_zero=align_zero, minmax=False, perCh=cout if "perCh" in qw_mode else None)
+    if qw_mode == "pact+":
+        return PACTplusSym(nbits, init_clip_val=clip_val, dequantize=True, inplace=False, intg_zp=align_zero)
+    if "fp8" in qw_mode and "custom" not in qw_mode:
+        return to_fp8(nbits, q_mode=qw_mode, emulate=True, perCh=cout if "perCh" in qw_mode else False)
     raise NotImplementedError(f"weight quantizer {qw_mode!r} is not on the B200 quantized-Linear path")

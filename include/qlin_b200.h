@@ -153,6 +153,11 @@ int qlin_gemm(const qlin_gemm_args* args, void* stream);
  *   QLIN_Q_I8_GIVEN_SCALE
  *                     scale = scale_in[row * scale_in_stride]; code = rint(v / scale) + zp0,
  *                     wrapped to int8 or clamped to +-qmax_levels
+ *   QLIN_Q_F8_FAKE_SCALED
+ *                     to_fp8_scaled_perToken / _perCh (fms_mo/quant/quantizers.py:5336-5420), e4m3:
+ *                     scale = 448 / max(amax, dyn_eps) (a multiplier, capped at 65504 on fp16 rows);
+ *                     code = e4m3(clamp(v * scale, +-448)); dq_out = e4m3 value / scale;
+ *                     scale_out receives the multiplier
  * native_chain is a bit mask: bit 0 rounds the smoothed value to the dtype of x, bit 1 rounds every
  * later intermediate to the dtype of x (what the reference computes when the tensors involved are
  * bf16 / fp16); 0 evaluates the same formulas in fp32 on the widened inputs.  Bit 2 is a promise by the
@@ -167,7 +172,8 @@ typedef enum qlin_quant_mode {
   QLIN_Q_I8_STATIC = 1,
   QLIN_Q_I8_STATIC_CLAMP_FIRST = 2,
   QLIN_Q_F8_DYN = 3,
-  QLIN_Q_I8_GIVEN_SCALE = 4
+  QLIN_Q_I8_GIVEN_SCALE = 4,
+  QLIN_Q_F8_FAKE_SCALED = 5
 } qlin_quant_mode;
 
 typedef struct qlin_quant_args {
@@ -294,6 +300,44 @@ typedef struct qlin_wfq_args {
 } qlin_wfq_args;
 
 int qlin_weight_fq_perch(const qlin_wfq_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * qlin_tensor_fq -- per-tensor fake quantisers: one clip value (or one FP8 scale) for all elements.
+ *
+ * Replaces: SAWB.forward -> SAWBPlusZeroSTE.forward + sawb_params_code(perCh=False)
+ *           (fms_mo/quant/quantizers.py:434-446, :455-500, :657-671), the recipe default "sawb+";
+ *           Qmax.forward -> QmaxSTE.forward (fms_mo/quant/quantizers.py:3048-3141, :3159-3187);
+ *           to_fp8_scaled / to_fp8_saturated (fms_mo/quant/quantizers.py:5316-5372), e4m3, emulate.
+ * mode (qlin_wq_mode): QLIN_W_SAWB  clip = c1 * mean|x| + c0 * sqrt(mean x^2), max|x| if that is <= 0
+ *                      QLIN_W_MAX   clip = max|x|
+ *                      QLIN_W_GIVEN clip read from clip_io[0]
+ * clip_io[0] is written for SAWB / MAX (out may then be NULL to get the statistic alone).
+ * kind: QLIN_PT_INT_SYM    t = clamp(x * (1/clip), -1, 1) * 0.5 + 0.5; q = rint(levels * t) with
+ *                          levels = 2^bits - 2 (align_zero) or 2^bits - 1;
+ *                          out = (2 * (q / levels) - 1) * clip, or q - levels / 2 when dequantize == 0
+ *       QLIN_PT_F8_SCALED  s = 448 / max(clip, 1e-12); out = e4m3(clamp(x * s, +-448)) / s
+ *       QLIN_PT_F8_SAT     out = e4m3(clamp(x, +-448))   (mode must be QLIN_W_GIVEN; clip unused)
+ * workspace: qlin_tensor_fq_workspace_bytes(numel) bytes of device memory (not needed for GIVEN).
+ * ---------------------------------------------------------------------------------------------- */
+typedef enum qlin_pt_kind { QLIN_PT_INT_SYM = 0, QLIN_PT_F8_SCALED = 1, QLIN_PT_F8_SAT = 2 } qlin_pt_kind;
+
+typedef struct qlin_tensor_fq_args {
+  const void* x;
+  void* out;         /* optional for SAWB / MAX */
+  float* clip_io;    /* [1] */
+  float* workspace;
+  int64_t numel;
+  int32_t dtype;     /* F32 / F16 / BF16 */
+  int32_t num_bits;
+  int32_t mode;      /* qlin_wq_mode */
+  int32_t kind;      /* qlin_pt_kind */
+  int32_t align_zero;
+  int32_t dequantize;
+  float c0, c1;
+} qlin_tensor_fq_args;
+
+int qlin_tensor_fq(const qlin_tensor_fq_args* args, void* stream);
+int64_t qlin_tensor_fq_workspace_bytes(int64_t numel);
 
 #ifdef __cplusplus
 }

@@ -95,6 +95,58 @@ def qmax_perch(w: torch.Tensor, num_bits: int = 8):
     return perch_fake_quant(w, clip, num_bits).to(w.dtype), clip
 
 
+def sawb_clip_pertensor(w: torch.Tensor, num_bits: int) -> torch.Tensor:
+    """sawb_params_code(perCh=False) (fms_mo/quant/quantizers.py:657-671) with the fallback of
+    SAWBPlusZeroSTE.forward (:482-487): a non-positive clip becomes max|w|; returned with shape [1]."""
+    c0, c1 = SAWB_COEFFS[SAWB_CODE[num_bits]]
+    x = w.flatten()
+    mu = x.abs().mean()
+    std = x.mul(x).mean().sqrt()
+    clip = c1 * mu + c0 * std
+    if clip <= 0:
+        clip = w.abs().max()
+    return clip.unsqueeze(0)
+
+
+def pertensor_sym_fake_quant(w: torch.Tensor, clip: torch.Tensor, num_bits: int, align_zero: bool = True, dequantize: bool = True):
+    """The quantise step shared by SAWBPlusZeroSTE.forward (fms_mo/quant/quantizers.py:488-495) and
+    QmaxSTE.forward (:3168-3183) with linear_quantize / linear_dequantize (:2561-2585, :2622-2633)."""
+    scale = (2**num_bits - 2) if align_zero else (2**num_bits - 1)
+    clip = clip.to(w.dtype)
+    out = w.mul(1 / clip).clamp(-1, 1).mul(0.5).add(0.5)
+    out = torch.round(scale * out - 0.0)
+    if dequantize:
+        out = (out + 0.0) / scale
+        return (2 * out - 1) * clip
+    return out - scale / 2
+
+
+def to_fp8_scaled_rows(x: torch.Tensor):
+    """to_fp8_scaled_perToken / to_fp8_scaled_perCh on a 2-D tensor with emulate=True, e4m3
+    (fms_mo/quant/quantizers.py:5336-5420): returns ``(fake-quantised x, scale multiplier)``."""
+    amax = torch.max(torch.abs(x), dim=-1, keepdim=True)[0]
+    return _fp8_scaled(x, amax)
+
+
+def to_fp8_scaled_tensor(x: torch.Tensor):
+    """to_fp8_scaled, emulate=True, e4m3 (fms_mo/quant/quantizers.py:5352-5372)."""
+    return _fp8_scaled(x, torch.max(torch.abs(x)))
+
+
+def _fp8_scaled(x, amax):
+    res = 448.0 / torch.clamp(amax, min=1e-12)
+    if x.dtype is torch.float16:
+        res = torch.clamp(res, max=torch.finfo(torch.float16).max)
+    scale = torch.empty_like(amax, dtype=x.dtype)
+    scale.copy_(res)
+    return (to_fp8_saturated(x * scale) / scale).to(x.dtype), scale
+
+
+def to_fp8_saturated(x: torch.Tensor) -> torch.Tensor:
+    """to_fp8_saturated, emulate=True, e4m3 (fms_mo/quant/quantizers.py:5316-5333)."""
+    return x.clamp(min=-448.0, max=448.0).to(torch.float8_e4m3fn).to(x.dtype)
+
+
 # ---------------------------------------------------------------------------------------------
 # PACT+ two-sided
 # ---------------------------------------------------------------------------------------------

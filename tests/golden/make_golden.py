@@ -265,6 +265,39 @@ def gen_extra():
                 y = q(x.reshape(4, 5, K))
             out["int8train"].append(dict(dtype=dtype, trun=trun, chunk=chunk, accb=accb, x=x, weight=lin.weight.detach().clone(),
                                          bias=None if not bias else lin.bias.detach().clone(), y=y.clone()))  # fmt: skip
+    # per-tensor SAWB+ (training and eval), per-tensor Qmax, FP8 e4m3 quantise-dequantise
+    out["sawb_tensor"], out["qmax_tensor"], out["fp8_fake"] = [], [], []
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        for nbits in (8, 4, 2):
+            w = (torch.randn(72, 100) * 0.05).to(dtype)
+            q = ref_q.SAWB(nbits, dequantize=True, align_zero=True, perCh=False).to(dtype)
+            q.train()
+            y = q(w)
+            clip = q.clip_val.clone()
+            q.eval()
+            y_eval = q(w * 1.5)
+            q2 = ref_q.SAWB(nbits, dequantize=False, align_zero=True, perCh=False).to(dtype)
+            q2.train()
+            out["sawb_tensor"].append(dict(dtype=dtype, nbits=nbits, w=w, y=y.clone(), clip=clip, y_eval=y_eval.clone(),
+                                           codes=q2(w).clone()))  # fmt: skip
+        for align in (True, False):
+            w = (torch.randn(72, 100) * 0.05).to(dtype)
+            q = ref_q.Qmax(8, align_zero=align, minmax=False).to(dtype)
+            q.train()
+            y1 = q(w)
+            y2 = q(w * 0.5)
+            clip = q.clip_val.clone()
+            q.eval()
+            out["qmax_tensor"].append(dict(dtype=dtype, align=align, w=w, y1=y1.clone(), y2=y2.clone(), clip=clip,
+                                           y_eval=q(w).clone()))  # fmt: skip
+        x = torch.randn(37, 96).to(dtype)
+        x[:, 5] *= 30
+        x[3] *= 1e-3
+        case = dict(dtype=dtype, x=x)
+        for mode, kw in (("fp8_e4m3_scale_perToken", dict(perToken=True)), ("fp8_e4m3_scale_perCh", dict(perCh=37)),
+                         ("fp8_e4m3_scale", {}), ("fp8_e4m3_sat", {})):  # fmt: skip
+            case[mode] = ref_q.to_fp8(8, q_mode=mode, **kw)(x * (300 if mode.endswith("sat") else 1)).clone()
+        out["fp8_fake"].append(case)
     save("extra.pt", out)
 
 

@@ -7,7 +7,7 @@ import torch
 from conftest import load_golden
 from fms_model_optimizer_b200 import _lib as L
 from fms_model_optimizer_b200 import ops
-from fms_model_optimizer_b200.quant.quantizers import PACT, PACT2, SAWB, PACTplusSym, QMaxDynamic, Qmax
+from fms_model_optimizer_b200.quant.quantizers import PACT, PACT2, SAWB, PACTplusSym, QMaxDynamic, Qmax, to_fp8
 from oracle import quantizers as OQ
 
 pytestmark = pytest.mark.gpu
@@ -185,3 +185,61 @@ def test_ragged_and_unaligned_rows_take_the_scalar_path(cuda_dev):
     want_codes, want_scale = OQ.qa_dynamic_max_qfunc(x)
     codes, scale, _ = ops.act_quant(xv, mode=L.Q_I8_DYN)
     assert torch.equal(codes.cpu(), want_codes) and torch.equal(scale.cpu(), want_scale.reshape(-1))
+
+
+def _bits(t):
+    return t.contiguous().view(torch.int16 if t.element_size() == 2 else torch.int32)
+
+
+def test_per_tensor_sawb_vs_reference_golden(cuda_dev):
+    for c in load_golden("extra.pt")["sawb_tensor"]:
+        q = SAWB(c["nbits"], dequantize=True, align_zero=True, perCh=False).to(c["dtype"]).to(cuda_dev)
+        q.train()
+        w = c["w"].to(cuda_dev)
+        y = q(w)
+        # the clip value is c1 * mean|w| + c0 * rms(w) over 7200 values summed in a different order:
+        # last-place differences are possible and cancel about one decimal digit
+        rtol = {torch.float32: 3e-5, torch.bfloat16: 2e-2, torch.float16: 4e-3}[c["dtype"]]
+        assert torch.allclose(q.clip_val.float().cpu(), c["clip"].float(), rtol=rtol), (c["dtype"], c["nbits"])
+        step = c["clip"].float() * 2 / (2 ** c["nbits"] - 2)
+        assert ((y.cpu().float() - c["y"].float()).abs() <= step * 1.01 + c["clip"].float().abs() * rtol).all()
+        # with the reference's clip value every elementwise step is bit exact
+        for x, key, deq in ((c["w"], "y", True), (c["w"] * 1.5, "y_eval", True), (c["w"], "codes", False)):
+            out, _ = ops.tensor_fq(x.to(cuda_dev), kind=L.PT_INT_SYM, mode=L.W_GIVEN, num_bits=c["nbits"], clip=c["clip"].to(cuda_dev),
+                                   align_zero=True, dequantize=deq)
+            assert torch.equal(_bits(out.cpu()), _bits(c[key])), (c["dtype"], c["nbits"], key)
+        q.eval()
+        q.clip_val.copy_(c["clip"].to(cuda_dev))
+        assert torch.equal(q(w * 1.5).cpu(), c["y_eval"])
+
+
+def test_per_tensor_qmax_vs_reference_golden(cuda_dev):
+    for c in load_golden("extra.pt")["qmax_tensor"]:
+        q = Qmax(8, align_zero=c["align"], minmax=False).to(c["dtype"]).to(cuda_dev)
+        q.train()
+        w = c["w"].to(cuda_dev)
+        assert torch.equal(q(w).cpu(), c["y1"]), (c["dtype"], c["align"])
+        assert torch.equal(q(w * 0.5).cpu(), c["y2"])
+        assert torch.equal(q.clip_val.cpu(), c["clip"])
+        q.eval()
+        assert torch.equal(q(w).cpu(), c["y_eval"])
+
+
+def test_fp8_fake_quantisers_vs_reference_golden(cuda_dev):
+    for c in load_golden("extra.pt")["fp8_fake"]:
+        x = c["x"].to(cuda_dev)
+        for mode, kw, scale in (("fp8_e4m3_scale_perToken", dict(perToken=True), 1), ("fp8_e4m3_scale_perCh", dict(perCh=37), 1),
+                                ("fp8_e4m3_scale", {}, 1), ("fp8_e4m3_sat", {}, 300)):  # fmt: skip
+            got = to_fp8(8, q_mode=mode, **kw).to(cuda_dev)(x * scale)
+            assert got.dtype == c[mode].dtype and torch.equal(_bits(got.cpu()), _bits(c[mode])), (mode, c["dtype"])
+
+
+def test_per_tensor_sawb_large_tensor_statistics(cuda_dev):
+    g = torch.Generator().manual_seed(9)
+    w = (torch.randn(3072, 768, generator=g) * 0.03)
+    want_clip = OQ.sawb_clip_pertensor(w.double(), 8).float()
+    out, clip = ops.tensor_fq(w.to(cuda_dev), kind=L.PT_INT_SYM, mode=L.W_SAWB, num_bits=8, c0=31.76, c1=-35.04)
+    assert torch.allclose(clip.cpu(), want_clip, rtol=2e-5)
+    assert torch.equal(out.cpu(), OQ.pertensor_sym_fake_quant(w, clip.cpu(), 8))
+    out2, clip2 = ops.tensor_fq(w.to(cuda_dev), kind=L.PT_INT_SYM, mode=L.W_SAWB, num_bits=8, c0=31.76, c1=-35.04)
+    assert torch.equal(clip, clip2) and torch.equal(out, out2)

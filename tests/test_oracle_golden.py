@@ -182,3 +182,34 @@ def test_linear_int8_train_forward_matches_reference():
         K = c["x"].shape[1]
         y = OL.linear_int8_train_forward(c["x"].reshape(4, 5, K), c["weight"], c["bias"], c["trun"], c["chunk"], c["accb"])
         assert y.dtype == c["y"].dtype and torch.equal(y, c["y"]), (c["dtype"], c["trun"], c["chunk"], c["accb"])
+
+
+def test_per_tensor_sawb_and_qmax_match_reference():
+    g = load_golden("extra.pt")
+    for c in g["sawb_tensor"]:
+        clip = OQ.sawb_clip_pertensor(c["w"], c["nbits"])
+        assert torch.equal(clip, c["clip"]), (c["dtype"], c["nbits"])
+        assert torch.equal(OQ.pertensor_sym_fake_quant(c["w"], clip, c["nbits"]), c["y"])
+        assert torch.equal(OQ.pertensor_sym_fake_quant(c["w"] * 1.5, clip, c["nbits"]), c["y_eval"])
+        assert torch.equal(OQ.pertensor_sym_fake_quant(c["w"], clip, c["nbits"], dequantize=False), c["codes"])
+    for c in g["qmax_tensor"]:
+        w = c["w"]
+        m1, m2 = w.abs().max().unsqueeze(0), (w * 0.5).abs().max().unsqueeze(0)
+        assert torch.equal(OQ.pertensor_sym_fake_quant(w, m1, 8, c["align"]), c["y1"])
+        assert torch.equal(OQ.pertensor_sym_fake_quant(w * 0.5, m2, 8, c["align"]), c["y2"])
+        clip = m1 * (1.0 - 0.1) + m1 * 0.1  # first call latches the fresh value, then the moving average
+        clip = clip * (1.0 - 0.1) + m2 * 0.1
+        assert torch.equal(clip, c["clip"])
+        assert torch.equal(OQ.pertensor_sym_fake_quant(w, clip, 8, c["align"]), c["y_eval"])
+
+
+def test_fp8_fake_quantisers_match_reference():
+    for c in load_golden("extra.pt")["fp8_fake"]:
+        x = c["x"]
+        for key, fn in (("fp8_e4m3_scale_perToken", OQ.to_fp8_scaled_rows), ("fp8_e4m3_scale_perCh", OQ.to_fp8_scaled_rows),
+                        ("fp8_e4m3_scale", OQ.to_fp8_scaled_tensor)):  # fmt: skip
+            got = fn(x)[0]
+            assert got.dtype == c[key].dtype and torch.equal(got.view(torch.int16 if x.element_size() == 2 else torch.int32),
+                                                             c[key].view(torch.int16 if x.element_size() == 2 else torch.int32)), (key, c["dtype"])
+        got = OQ.to_fp8_saturated(x * 300)
+        assert torch.equal(got, c["fp8_e4m3_sat"])
