@@ -24,7 +24,8 @@ DT_NONE, DT_I8, DT_U8, DT_I32, DT_F32, DT_F16, DT_BF16, DT_F8E4M3 = range(8)
 EPI_RAW, EPI_SCALE_PROD, EPI_SCALE_SEQ = 0, 1, 2
 
 # qlin_quant_mode
-Q_I8_DYN, Q_I8_STATIC, Q_I8_STATIC_CLAMP_FIRST, Q_F8_DYN, Q_I8_GIVEN_SCALE, Q_F8_FAKE_SCALED = range(6)
+(Q_I8_DYN, Q_I8_STATIC, Q_I8_STATIC_CLAMP_FIRST, Q_F8_DYN, Q_I8_GIVEN_SCALE, Q_F8_FAKE_SCALED, Q_I8_STATIC_ROUND_FIRST,
+ Q_I8_AFFINE_RCP) = range(8)
 
 # qlin_pact_variant
 PACT_TWO_SIDED, PACT_ONE_SIDED, PACT_SYMMETRIC = 0, 1, 2
@@ -150,7 +151,7 @@ class WfqArgs(C.Structure):
         ("num_bits", C.c_int32),
         ("mode", C.c_int32),
         ("native_mul", C.c_int32),
-        ("clip_f32", C.c_int32),
+        ("clip_dtype", C.c_int32),
         ("c0", C.c_float),
         ("c1", C.c_float),
     ]

@@ -105,6 +105,18 @@ __device__ __forceinline__ uint8_t quant_one(const QuantParams& p, float v, floa
       dq = r;
       return static_cast<uint8_t>(static_cast<int>(r) & 0xFF);
     }
+    case QLIN_Q_I8_STATIC_ROUND_FIRST: {  // clamp(rint(v / s + zp), lo, hi) - shift
+      float t = rnd_if<XT>(div_exact(v, s, rs), nat);
+      t = rnd_if<XT>(__fadd_rn(t, p.zp0), nat);
+      const float r = fminf(fmaxf(rintf(t), p.lo), p.hi) - p.shift;
+      dq = r;
+      return static_cast<uint8_t>(static_cast<int>(r) & 0xFF);
+    }
+    case QLIN_Q_I8_AFFINE_RCP: {  // torch.quantize_per_tensor: clamp(nearbyint(v * (1 / s)) + zp, -128, 127)
+      const float r = fminf(fmaxf(nearbyintf(__fmul_rn(v, __fdiv_rn(1.0f, s))) + p.zp0, -128.0f), 127.0f);
+      dq = r;
+      return static_cast<uint8_t>(static_cast<int>(r) & 0xFF);
+    }
     case QLIN_Q_F8_FAKE_SCALED: {  // s multiplies: x * s, saturate, cast to e4m3 and back, / s
       float t = rnd_if<XT>(__fmul_rn(v, s), nat);
       const bool is_nan = t != t;  // torch.clamp keeps NaN, fminf / fmaxf would drop it
@@ -773,7 +785,7 @@ struct WfqParams {
   int8_t* codes;
   float* clip_io;
   int64_t ldw, ldo, ldq;
-  int32_t rows, cols, num_bits, mode, native_mul, clip_f32;
+  int32_t rows, cols, num_bits, mode, native_mul, clip_dtype;
   float c0, c1;
 };
 
@@ -788,6 +800,22 @@ __device__ __forceinline__ float wfq_clip(const WfqParams& p, float sum_abs, flo
   const float a = Elem<XT>::rnd(__fmul_rn(p.c1, mu));
   const float b = Elem<XT>::rnd(__fmul_rn(p.c0, sd));
   return Elem<XT>::rnd(__fadd_rn(a, b));
+}
+
+// scale = clip * 2 / nspace, each step rounded to the dtype of the clip tensor (the weight dtype unless
+// the caller names another one).
+template <typename XT>
+__device__ __forceinline__ float wfq_scale(const WfqParams& p, float clip, float nspace) {
+  switch (p.clip_dtype) {
+    case QLIN_DT_F32:
+      return __fdiv_rn(__fmul_rn(clip, 2.0f), nspace);
+    case QLIN_DT_F16:
+      return Elem<__half>::rnd(__fdiv_rn(Elem<__half>::rnd(__fmul_rn(clip, 2.0f)), nspace));
+    case QLIN_DT_BF16:
+      return Elem<__nv_bfloat16>::rnd(__fdiv_rn(Elem<__nv_bfloat16>::rnd(__fmul_rn(clip, 2.0f)), nspace));
+    default:
+      return Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fmul_rn(clip, 2.0f)), nspace));
+  }
 }
 
 // torch.fake_quantize_per_channel_affine with zero_point 0:
@@ -855,8 +883,7 @@ __global__ void __launch_bounds__(1024) wfq_vec_kernel(const WfqParams p) {
     const float clip = wfq_clip<XT>(p, sa, sq, am, row);
     if (threadIdx.x == 0 && p.mode != QLIN_W_GIVEN) p.clip_io[row] = clip;
     // scale = clip * 2 / nspace in the weight dtype, then widened
-    const float scale = p.clip_f32 ? __fdiv_rn(__fmul_rn(clip, 2.0f), nspace)
-                                   : Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fmul_rn(clip, 2.0f)), nspace));
+    const float scale = wfq_scale<XT>(p, clip, nspace);
     const float inv_scale = __fdiv_rn(1.0f, scale);
     auto emit = [&](int ch, const float (&val)[16]) {
       float dq[16];
@@ -915,8 +942,7 @@ __global__ void __launch_bounds__(256) wfq_scalar_kernel(const WfqParams p) {
     }
     const float clip = wfq_clip<XT>(p, sa, sq, am, row);
     if (threadIdx.x == 0 && p.mode != QLIN_W_GIVEN) p.clip_io[row] = clip;
-    const float scale = p.clip_f32 ? __fdiv_rn(__fmul_rn(clip, 2.0f), nspace)
-                                   : Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fmul_rn(clip, 2.0f)), nspace));
+    const float scale = wfq_scale<XT>(p, clip, nspace);
     const float inv_scale = __fdiv_rn(1.0f, scale);
     for (int c = threadIdx.x; c < p.cols; c += blockDim.x) {
       float v = load1(wr + c);
@@ -973,7 +999,7 @@ extern "C" int qlin_act_quant(const qlin_quant_args* a, void* stream) {
   if (a->rows == 0 || a->cols == 0) return QLIN_OK;
   if (a->ldx < a->cols || (a->codes != nullptr && a->ldq < a->cols) || (a->dq_out != nullptr && a->lddq < a->cols))
     return fail(QLIN_ERR_BAD_SHAPE, "qlin_act_quant: leading dimension smaller than the row length");
-  if (a->mode < QLIN_Q_I8_DYN || a->mode > QLIN_Q_F8_FAKE_SCALED)
+  if (a->mode < QLIN_Q_I8_DYN || a->mode > QLIN_Q_I8_AFFINE_RCP)
     return fail(QLIN_ERR_UNSUPPORTED, "qlin_act_quant: unknown mode %d", a->mode);
   if (a->smooth != nullptr && !a->smooth_mul && a->smooth_rcp == nullptr)
     return fail(QLIN_ERR_NULL, "qlin_act_quant: smooth_rcp is required when rows are divided by smooth");
@@ -1049,7 +1075,7 @@ extern "C" int qlin_weight_fq_perch(const qlin_wfq_args* a, void* stream) {
   p.num_bits = a->num_bits;
   p.mode = a->mode;
   p.native_mul = a->native_mul != 0;
-  p.clip_f32 = a->clip_f32 != 0;
+  p.clip_dtype = a->clip_dtype;
   p.c0 = a->c0;
   p.c1 = a->c1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

@@ -361,6 +361,73 @@ class LinearFPxAcc(nn.Linear):
         return s + f",chunk_size={self.chunk_size}"
 
 
+class QLinearCublasI8I32NT(nn.Linear):
+    """Static per-tensor activation quantisation, int8 x int8 -> int32 GEMM, ``input_scale * w_scale * acc + bias``
+    (QLinearCublasI8I32NT of the reference, fms_mo/modules/linear.py:1341-1537; the GEMM replaces
+    ``mygemm::gemm_nt_i8i32`` / ``cutlass_gemm::i8i32nt``).  ``weight`` is int8 ``[out, in]``; with uint8
+    activations the zero-point correction ``w_scale * input_scale * (zp - 128) * sum_k W`` is folded into ``bias``."""
+
+    @classmethod
+    def from_fms_mo(cls, fms_mo_qlinear, **kwargs):
+        """fms_mo/modules/linear.py:1427-1490: activation scale / zero point from the PACT clip values, per-channel
+        weight scale ``clip * 2 / (2^b - 2)``, integer weights from the weight quantizer run without dequantisation."""
+        assert fms_mo_qlinear.num_bits_feature in [4, 8] and fms_mo_qlinear.num_bits_weight in [4, 8], "Please check nbits setting!"
+        target_device = kwargs.get("target_device", next(fms_mo_qlinear.parameters()).device)
+        q = cls(fms_mo_qlinear.in_features, fms_mo_qlinear.out_features, device="meta")
+        q.input_dtype = torch.quint8
+        q.forceSymA = False
+        with torch.no_grad():
+            # The handful of scalar / per-channel conversions run on the host: torch's CUDA kernels divide
+            # by a Python scalar through its reciprocal, the CPU kernels (and IEEE) divide.
+            Qa = fms_mo_qlinear.quantize_feature
+            a_cv, a_cvn = Qa.clip_val.detach().cpu(), Qa.clip_valn.detach().cpu()
+            input_scale = (a_cv - a_cvn) / (2**Qa.num_bits - 1)
+            input_zero_point = torch.round(-a_cvn / input_scale).to(torch.int)
+            q.register_buffer("input_scale", input_scale)
+            q.register_buffer("input_zp", input_zero_point)
+            Qw = fms_mo_qlinear.quantize_weight
+            w_scale = Qw.clip_val.detach().cpu() * 2 / (2**Qw.num_bits - 2)
+            q.register_buffer("w_scale", w_scale.float())
+            q.register_buffer("w_zp", torch.zeros_like(w_scale, dtype=torch.int))
+            Qw.dequantize = False
+            q.weight = nn.Parameter(Qw(fms_mo_qlinear.weight.float()).to(torch.int8), requires_grad=False)
+            corr_term = q.w_scale * input_scale * (input_zero_point - 128) * q.weight.sum(dim=1).cpu()
+            corr_term = corr_term.to(fms_mo_qlinear.bias.dtype)
+            q.bias = nn.Parameter(fms_mo_qlinear.bias.detach().cpu() - corr_term, requires_grad=False)
+        return q.to(target_device)
+
+    def _get_name(self):
+        return "QuantizedLinear_cublasi8i32"
+
+    def _quantise(self, x2):
+        native = 3 if (x2.dtype != torch.float32 and self.input_scale.dtype == x2.dtype) else 0
+        if not hasattr(self, "_host_scalars"):  # read once: the module's scale and zero point never change
+            self._host_scalars = (float(self.input_scale.reshape(-1)[0].item()), float(self.input_zp.reshape(-1)[0].item()))
+        s0, zp0 = self._host_scalars
+        lo, hi, shift = (0.0, 255.0, 128.0) if self.input_dtype == torch.quint8 else (-127.0, 127.0, 0.0)
+        codes, _, _ = ops.act_quant(x2, mode=L.Q_I8_STATIC_ROUND_FIRST, native_chain=native, scale0=s0, zp0=zp0, lo=lo, hi=hi, shift=shift)
+        return codes
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        with torch.no_grad():
+            in_dtype = x.dtype
+            if in_dtype not in _FLOATS:
+                raise RuntimeError(f"unsupported activation dtype {in_dtype}")
+            tar_shape = x.shape[:-1] + (self.weight.shape[0],)
+            codes = self._quantise(x.reshape(-1, x.shape[-1]))
+            out = ops.gemm(codes, self.weight, epilogue=L.EPI_SCALE_PROD, row_scale=self.input_scale.reshape(-1)[:1],
+                           col_scale=self.w_scale, bias=self.bias, out_dtype=in_dtype)  # fmt: skip
+        return out.reshape(tar_shape)
+
+
+class QLinearCutlassI8I32NT(QLinearCublasI8I32NT):
+    """fms_mo/modules/linear.py:1540-1583: the same module; both of the reference's library GEMMs are
+    replaced by the one tcgen05 GEMM here."""
+
+    def _get_name(self):
+        return "QuantizedLinear_cutlassi8i32"
+
+
 class _LinearINT8FwdFP32Bwd(torch.autograd.Function):
     """LinearFuncINT8FwdFP32Bwd (fms_mo/modules/linear.py:2127-2223): forward through the int8 chunk-
     truncating GEMM with per-token / per-channel max scales (no lower clamp on the scales), backward

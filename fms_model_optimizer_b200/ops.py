@@ -360,7 +360,7 @@ def weight_fq_perch(
     clip: Optional[torch.Tensor] = None,
     smooth: Optional[torch.Tensor] = None,
     native_mul: bool = True,
-    clip_f32: bool = False,
+    clip_dtype: Optional[torch.dtype] = None,
     want_dq: bool = True,
     want_codes: bool = False,
     c0: float = 0.0,
@@ -390,7 +390,7 @@ def weight_fq_perch(
     args = L.WfqArgs(
         w=_ptr(w), smooth=_ptr(sm), dq_out=_ptr(dq), codes=_ptr(codes), clip_io=_ptr(clip_io),
         ldw=w.stride(0), ldo=cols, ldq=cols, rows=rows, cols=cols, dtype=_DT[w.dtype], num_bits=int(num_bits),
-        mode=int(mode), native_mul=int(bool(native_mul)), clip_f32=int(bool(clip_f32)), c0=float(c0), c1=float(c1),
+        mode=int(mode), native_mul=int(bool(native_mul)), clip_dtype=(0 if clip_dtype is None or clip_dtype == w.dtype else _DT[clip_dtype]), c0=float(c0), c1=float(c1),
     )  # fmt: skip
     nbytes = rows * cols * (w.element_size() * (2 if want_dq else 1) + (1 if want_codes else 0)) + 4 * rows
     with torch.cuda.device(dev):
@@ -533,3 +533,40 @@ def _iaddmm_op(bias: torch.Tensor, m1: torch.Tensor, m2: torch.Tensor, scale_i: 
 @_iaddmm_op.register_fake
 def _(bias, m1, m2, scale_i, scale_w):
     return m1.new_empty((m1.shape[0], m2.shape[1]), dtype=torch.float32)
+
+
+def _scalar(t) -> float:
+    return float(t.reshape(-1)[0].item()) if isinstance(t, torch.Tensor) else float(t)
+
+
+@torch.library.custom_op("qlin_b200::q_iaddmm_dq", mutates_args=())
+def _q_iaddmm_dq_op(bias: torch.Tensor, m1: torch.Tensor, m2: torch.Tensor, scale_i: torch.Tensor, zp_i: torch.Tensor,
+                    scale_w: torch.Tensor) -> torch.Tensor:  # fmt: skip
+    """fms_mo::q_iaddmm_dq (fms_mo/custom_ext_kernels/utils.py:748-782): quantise the float ``m1 [m,k]`` with a
+    static per-tensor scale and zero point (uint8 codes shifted by 128), int8 GEMM with ``m2 [k,n]``, then
+    ``(scale_i.float() * acc * scale_w + bias).to(m1.dtype)``.  The scale and zero point are read on the host."""
+    assert m2.dtype == torch.int8, f"weight tensor is of incorrect dtype {m2.dtype}"
+    native = 3 if (m1.dtype != torch.float32 and scale_i.dtype == m1.dtype) else 0
+    codes, _, _ = act_quant(m1, mode=L.Q_I8_STATIC, native_chain=native, scale0=_scalar(scale_i), zp0=_scalar(zp_i), shift=128.0)
+    return gemm(codes, _as_nk(m2), epilogue=L.EPI_SCALE_SEQ, row_scale=scale_i.reshape(-1)[:1], col_scale=scale_w, bias=bias,
+                out_dtype=m1.dtype)  # fmt: skip
+
+
+@_q_iaddmm_dq_op.register_fake
+def _(bias, m1, m2, scale_i, zp_i, scale_w):
+    return m1.new_empty((m1.shape[0], m2.shape[1]))
+
+
+@torch.library.custom_op("qlin_b200::q_per_t_sym", mutates_args=())
+def _q_per_t_sym_op(x: torch.Tensor, s: torch.Tensor, zp: torch.Tensor) -> torch.Tensor:
+    """fms_mo::q_per_t_sym (fms_mo/custom_ext_kernels/utils.py:792-794):
+    ``torch.quantize_per_tensor(x, s, zp, torch.qint8).int_repr()`` for fp32 ``x``."""
+    if x.dtype != torch.float32:
+        raise RuntimeError("q_per_t_sym takes a float32 tensor, as torch.quantize_per_tensor does")
+    codes, _, _ = act_quant(x.reshape(-1, x.shape[-1]), mode=L.Q_I8_AFFINE_RCP, scale0=_scalar(s), zp0=_scalar(zp))
+    return codes.reshape(x.shape)
+
+
+@_q_per_t_sym_op.register_fake
+def _(x, s, zp):
+    return x.new_empty(x.shape, dtype=torch.int8)

@@ -142,7 +142,7 @@ class _PerChSTE(torch.autograd.Function):
         dq, codes, clip = ops.weight_fq_perch(
             w2, num_bits=num_bits, mode=mode, clip=(clip_buf if mode == L.W_GIVEN else None), want_dq=dequantize,
             want_codes=not dequantize, c0=c0, c1=c1,
-            clip_f32=(mode == L.W_GIVEN and clip_buf.dtype == torch.float32),
+            clip_dtype=(clip_buf.dtype if mode == L.W_GIVEN else None),
         )  # fmt: skip
         if mode != L.W_GIVEN:
             clip_buf.copy_(clip.to(clip_buf.dtype))

@@ -153,6 +153,14 @@ int qlin_gemm(const qlin_gemm_args* args, void* stream);
  *   QLIN_Q_I8_GIVEN_SCALE
  *                     scale = scale_in[row * scale_in_stride]; code = rint(v / scale) + zp0,
  *                     wrapped to int8 or clamped to +-qmax_levels
+ *   QLIN_Q_I8_STATIC_ROUND_FIRST
+ *                     code = clamp(rint(v / scale0 + zp0), lo, hi) - shift
+ *                     (QLinearCublasI8I32NT.forward, fms_mo/modules/linear.py:1505-1512: uint8 codes
+ *                     shifted by 128, or symmetric codes clamped to +-127)
+ *   QLIN_Q_I8_AFFINE_RCP
+ *                     code = clamp(nearbyint(v * (1 / scale0)) + zp0, -128, 127), fp32 rows:
+ *                     torch.quantize_per_tensor(...).int_repr() (fms_mo::q_per_t_sym,
+ *                     fms_mo/custom_ext_kernels/utils.py:792-794)
  *   QLIN_Q_F8_FAKE_SCALED
  *                     to_fp8_scaled_perToken / _perCh (fms_mo/quant/quantizers.py:5336-5420), e4m3:
  *                     scale = 448 / max(amax, dyn_eps) (a multiplier, capped at 65504 on fp16 rows);
@@ -173,7 +181,9 @@ typedef enum qlin_quant_mode {
   QLIN_Q_I8_STATIC_CLAMP_FIRST = 2,
   QLIN_Q_F8_DYN = 3,
   QLIN_Q_I8_GIVEN_SCALE = 4,
-  QLIN_Q_F8_FAKE_SCALED = 5
+  QLIN_Q_F8_FAKE_SCALED = 5,
+  QLIN_Q_I8_STATIC_ROUND_FIRST = 6,
+  QLIN_Q_I8_AFFINE_RCP = 7
 } qlin_quant_mode;
 
 typedef struct qlin_quant_args {
@@ -294,8 +304,8 @@ typedef struct qlin_wfq_args {
   int32_t num_bits;
   int32_t mode;         /* qlin_wq_mode */
   int32_t native_mul;   /* round w * smooth to dtype before use (reference multiplies in the weight dtype) */
-  int32_t clip_f32;     /* the clip values live in an fp32 tensor: form scale = clip * 2 / (2^bits - 2) in fp32
-                           instead of the weight dtype (QLIN_W_GIVEN with an fp32 clip_val buffer) */
+  int32_t clip_dtype;   /* 0: scale = clip * 2 / (2^bits - 2) is formed in the weight dtype; F32 / F16 / BF16: in that
+                           dtype (QLIN_W_GIVEN with a clip_val buffer whose dtype differs from the weights') */
   float c0, c1;
 } qlin_wfq_args;
 

@@ -150,3 +150,41 @@ def linear_int8_train_forward(x, weight, bias, lsb_trun_bits=0, chunk_size=64, m
     if bias is not None:
         out = out + bias.to(org_dtype)
     return out
+
+
+def static_int8_from_fms_mo(weight, bias, a_cv, a_cvn, w_cv, nbits_a=8, nbits_w=8):
+    """QLinearCublasI8I32NT.from_fms_mo (fms_mo/modules/linear.py:1427-1490) for a QLinear whose weight
+    quantizer is SAWB per channel in eval mode: returns ``dict(input_scale, input_zp, w_scale, weight, bias)``."""
+    input_scale = (a_cv - a_cvn) / (2**nbits_a - 1)
+    input_zp = torch.round(-a_cvn / input_scale).to(torch.int)
+    w_scale = (w_cv * 2 / (2**nbits_w - 2)).float()
+    w_int8 = Q.perch_fake_quant(weight.float(), w_cv, nbits_w, dequantize=False).to(torch.int8)
+    corr_term = (w_scale * input_scale * (input_zp - 128) * w_int8.sum(dim=1)).to(bias.dtype)
+    return dict(input_scale=input_scale, input_zp=input_zp, w_scale=w_scale, weight=w_int8, bias=bias - corr_term)
+
+
+def static_int8_forward(x, st, input_is_uint8=True):
+    """QLinearCublasI8I32NT.forward (fms_mo/modules/linear.py:1499-1537) with an exact integer matmul."""
+    in_dtype = x.dtype
+    if input_is_uint8:
+        q = torch.clamp((x / st["input_scale"] + st["input_zp"]).round(), 0, 255)
+        q = (q.to(torch.int16) - 128).to(torch.int8)
+    else:
+        q = torch.clamp((x / st["input_scale"] + st["input_zp"]).round(), -127, 127).to(torch.int8)
+    tar_shape = q.shape[:-1] + (st["weight"].shape[0],)
+    acc = G.imatmul_chunk_truncate(q.reshape(-1, q.shape[-1]), st["weight"].t()).reshape(tar_shape)
+    return (st["input_scale"] * st["w_scale"] * acc + st["bias"]).to(in_dtype)
+
+
+def q_iaddmm_dq(bias, m1, m2, scale_i, zp_i, scale_w):
+    """fms_mo::q_iaddmm_dq (fms_mo/custom_ext_kernels/utils.py:748-782)."""
+    q = torch.clamp((m1 / scale_i + zp_i - 128).round(), -128, 127).to(torch.int8)
+    acc = G.imatmul_chunk_truncate(q, m2)
+    return (scale_i.float() * acc * scale_w + bias).to(m1.dtype)
+
+
+def q_per_t_sym(x, s, zp):
+    """fms_mo::q_per_t_sym (fms_mo/custom_ext_kernels/utils.py:792-794): the arithmetic of
+    torch.quantize_per_tensor, ``clamp(nearbyint(x * (1 / s)) + zp, -128, 127)`` in fp32."""
+    inv = torch.tensor(1.0, dtype=torch.float32) / torch.as_tensor(s, dtype=torch.float32)
+    return torch.clamp(torch.round(x.float() * inv) + int(zp), -128, 127).to(torch.int8)

@@ -228,6 +228,56 @@ def gen_aiu_vectors():
     save("aiu_i8i8_vectors.pt", out)
 
 
+def gen_static_int8():
+    """QLinearCublasI8I32NT.from_fms_mo + forward (its library GEMM op replaced by an exact integer matmul),
+    fms_mo::q_iaddmm_dq and fms_mo::q_per_t_sym as registered by the reference's imatmul_ops_reg."""
+    torch.manual_seed(11)
+    lib = torch.library.Library("mygemm", "DEF")
+    lib.define("gemm_nt_i8i32(Tensor x, Tensor w) -> Tensor")
+    lib.impl("gemm_nt_i8i32", lambda x, w: (x.double() @ w.double().t()).to(torch.int32), "CompositeExplicitAutograd")
+    _keep.append(lib)
+    imatmul_ops_reg("triton", mm_func=_dispatch_mm)
+    _mm["fn"] = lambda m1, m2: (m1.double() @ m2.double()).to(torch.int32)
+    out = {"static_int8": [], "q_iaddmm_dq": [], "q_per_t_sym": []}
+    for dtype in (torch.float32, torch.float16, torch.bfloat16):
+        M, K, N = 24, 160, 88
+        x = (torch.randn(M, K) * 1.5).to(dtype)
+        lin = ref_linear.QLinear(K, N, bias=True, num_bits_feature=8, qa_mode="pact+", num_bits_weight=8, qw_mode="sawb+perCh",
+                                 qcfg={}, device="cpu")  # fmt: skip
+        with torch.no_grad():
+            lin.weight.copy_(torch.randn(N, K) * 0.05)
+            lin.bias.copy_(torch.randn(N) * 0.1)
+            lin.quantize_feature.clip_val.fill_(3.7)
+            lin.quantize_feature.clip_valn.fill_(-2.9)
+        lin = lin.to(dtype)
+        lin.train()
+        with torch.no_grad():
+            lin(x)
+        lin.eval()
+        dep = ref_linear.QLinearCublasI8I32NT.from_fms_mo(lin, target_device="cpu")
+        y = dep(x.reshape(4, 6, K))
+        out["static_int8"].append(dict(dtype=dtype, x=x, weight=lin.weight.detach().clone(), bias=lin.bias.detach().clone(),
+                                       a_cv=3.7, a_cvn=-2.9, w_cv=lin.quantize_weight.clip_val.clone(),
+                                       input_scale=dep.input_scale.clone(), input_zp=dep.input_zp.clone(),
+                                       w_scale=dep.w_scale.clone(), w_int8=dep.weight.detach().clone(),
+                                       new_bias=dep.bias.detach().clone(), y=y.clone()))  # fmt: skip
+        if dtype != torch.bfloat16:
+            w_i8 = torch.randint(-127, 128, (N, K), dtype=torch.int8)
+            s_i, zp_i = torch.tensor([0.031]).to(dtype), torch.tensor([117])
+            s_w = (torch.rand(N) * 0.01 + 0.001)
+            bias = (torch.randn(N) * 0.1).to(dtype)
+            y = torch.ops.fms_mo.q_iaddmm_dq(bias, x, w_i8.t(), s_i, zp_i, s_w)
+            out["q_iaddmm_dq"].append(dict(dtype=dtype, x=x, w_i8=w_i8, scale_i=s_i, zp_i=zp_i, scale_w=s_w, bias=bias, y=y.clone()))
+    xf = torch.randn(31, 77) * 2
+    for s_, zp_ in ((0.0173, 0), (0.0291, -5)):
+        st, zt = torch.tensor(s_), torch.tensor(zp_)
+        out["q_per_t_sym"].append(dict(x=xf, s=st, zp=zt, y=torch.ops.fms_mo.q_per_t_sym(xf, st, zt).clone()))
+    return out
+
+
+_keep = []
+
+
 def gen_extra():
     """One-sided and symmetric PACT+ (forward and backward) and QLinearINT8Train.forward (its tl_matmul
     replaced by oracle.gemm.imatmul_chunk_truncate, everything else the reference's code)."""
@@ -298,6 +348,7 @@ def gen_extra():
                          ("fp8_e4m3_scale", {}), ("fp8_e4m3_sat", {})):  # fmt: skip
             case[mode] = ref_q.to_fp8(8, q_mode=mode, **kw)(x * (300 if mode.endswith("sat") else 1)).clone()
         out["fp8_fake"].append(case)
+    out.update(gen_static_int8())
     save("extra.pt", out)
 
 

@@ -206,3 +206,61 @@ def test_int8_train_linear_larger_shape_vs_oracle(cuda_dev):
         with torch.no_grad():
             got = q(x.to(cuda_dev))
         assert torch.equal(got.cpu(), want), dtype
+
+
+class _QStub(torch.nn.Module):
+    """Carries what QLinearCublasI8I32NT.from_fms_mo reads from a QLinear's quantizers."""
+
+    def __init__(self, num_bits, clip_val, clip_valn=None, codes=None):
+        super().__init__()
+        self.num_bits = num_bits
+        self.clip_val = clip_val
+        self.clip_valn = clip_valn
+        self.dequantize = True
+        self._codes = codes
+
+    def forward(self, w):
+        assert not self.dequantize
+        return self._codes.to(w.device, torch.float32)
+
+
+def test_static_int8_linear_matches_reference_outputs(cuda_dev):
+    from fms_model_optimizer_b200.modules import QLinearCublasI8I32NT, QLinearCutlassI8I32NT
+    from fms_model_optimizer_b200.quant.quantizers import SAWB
+
+    for c in load_golden("extra.pt")["static_int8"]:
+        dt = c["dtype"]
+        K, N = c["x"].shape[1], c["weight"].shape[0]
+        src = torch.nn.Linear(K, N).to(dt)
+        with torch.no_grad():
+            src.weight.copy_(c["weight"])
+            src.bias.copy_(c["bias"])
+        src = src.to(cuda_dev)
+        src.num_bits_feature = src.num_bits_weight = 8
+        src.quantize_feature = _QStub(8, torch.tensor([c["a_cv"]]).to(dt).to(cuda_dev), torch.tensor([c["a_cvn"]]).to(dt).to(cuda_dev))
+        qw = SAWB(8, dequantize=True, align_zero=True, perCh=N).to(dt).to(cuda_dev)  # this package's GPU quantizer, eval mode
+        qw.clip_val.copy_(c["w_cv"].to(cuda_dev))
+        qw.eval()
+        src.quantize_weight = qw
+        for cls in (QLinearCublasI8I32NT, QLinearCutlassI8I32NT):
+            dep = cls.from_fms_mo(src)
+            assert torch.equal(dep.weight.cpu(), c["w_int8"]) and torch.equal(dep.bias.cpu(), c["new_bias"])
+            assert torch.equal(dep.input_scale.cpu(), c["input_scale"]) and torch.equal(dep.input_zp.cpu(), c["input_zp"])
+            y = dep(c["x"].reshape(4, 6, K).to(cuda_dev))
+            assert y.dtype == dt and torch.equal(y.cpu(), c["y"]), (dt, cls.__name__)
+
+
+def test_fused_quantise_gemm_ops_match_reference_outputs(cuda_dev):
+    g = load_golden("extra.pt")
+    for c in g["q_iaddmm_dq"]:
+        y = torch.ops.qlin_b200.q_iaddmm_dq(c["bias"].to(cuda_dev), c["x"].to(cuda_dev), c["w_i8"].to(cuda_dev).t(),
+                                            c["scale_i"].to(cuda_dev), c["zp_i"].to(cuda_dev), c["scale_w"].to(cuda_dev))
+        assert y.dtype == c["y"].dtype and torch.equal(y.cpu(), c["y"]), c["dtype"]
+    for c in g["q_per_t_sym"]:
+        y = torch.ops.qlin_b200.q_per_t_sym(c["x"].to(cuda_dev), c["s"], c["zp"])
+        assert torch.equal(y.cpu(), c["y"])
+    torch.manual_seed(2)
+    x = torch.randn(257, 1000) * 3
+    y = torch.ops.qlin_b200.q_per_t_sym(x.to(cuda_dev), torch.tensor(0.0213), torch.tensor(3))
+    assert torch.equal(y.cpu(), OL.q_per_t_sym(x, 0.0213, 3))
+    assert torch.equal(y.cpu(), torch.quantize_per_tensor(x, 0.0213, 3, torch.qint8).int_repr())

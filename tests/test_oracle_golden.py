@@ -213,3 +213,22 @@ def test_fp8_fake_quantisers_match_reference():
                                                              c[key].view(torch.int16 if x.element_size() == 2 else torch.int32)), (key, c["dtype"])
         got = OQ.to_fp8_saturated(x * 300)
         assert torch.equal(got, c["fp8_e4m3_sat"])
+
+
+def test_static_int8_linear_and_fused_ops_match_reference():
+    g = load_golden("extra.pt")
+    for c in g["static_int8"]:
+        dt = c["dtype"]
+        a_cv, a_cvn = torch.tensor([c["a_cv"]]).to(dt), torch.tensor([c["a_cvn"]]).to(dt)
+        st = OL.static_int8_from_fms_mo(c["weight"], c["bias"], a_cv, a_cvn, c["w_cv"])
+        assert torch.equal(st["input_scale"], c["input_scale"]) and torch.equal(st["input_zp"], c["input_zp"])
+        assert torch.equal(st["w_scale"], c["w_scale"]) and torch.equal(st["weight"], c["w_int8"])
+        assert torch.equal(st["bias"], c["new_bias"])
+        K = c["x"].shape[1]
+        y = OL.static_int8_forward(c["x"].reshape(4, 6, K), st)
+        assert y.dtype == c["y"].dtype and torch.equal(y, c["y"]), dt
+    for c in g["q_iaddmm_dq"]:
+        y = OL.q_iaddmm_dq(c["bias"], c["x"], c["w_i8"].t(), c["scale_i"], c["zp_i"], c["scale_w"])
+        assert y.dtype == c["y"].dtype and torch.equal(y, c["y"]), c["dtype"]
+    for c in g["q_per_t_sym"]:
+        assert torch.equal(OL.q_per_t_sym(c["x"], c["s"], c["zp"]), c["y"])
