@@ -136,8 +136,11 @@ class Decoder:
     """Llama-shaped decoder whose Linears are ``tp.W8A8Linear``; norms, RoPE, attention and SwiGLU
     are plain PyTorch ops on the device (they are not part of the quantized-Linear path)."""
 
-    def __init__(self, cfg, dev, world, rank, layers=None):
+    def __init__(self, cfg, dev, world, rank, layers=None, n_micro=1):
         from fms_model_optimizer_b200 import tp
+
+        self.n_micro = n_micro
+        self.streams = [torch.cuda.Stream(device=dev) for _ in range(n_micro)] if n_micro > 1 else []
 
         self.cfg = cfg
         self.dev = dev
@@ -167,35 +170,77 @@ class Decoder:
         S = cfg["seq"]
         inv = 1.0 / (cfg["rope_theta"] ** (torch.arange(0, hd, 2, device=dev).float() / hd))
         ang = torch.outer(torch.arange(S, device=dev).float(), inv)
-        # [1, S, 1, hd] tables for activations laid out [B, S, heads, hd]; rotate_half(x) is a roll by
-        # hd/2 with the sign folded into the sine table: x*cos + roll(x)*sin_signed (3 passes)
-        self.cos = torch.cat([ang.cos(), ang.cos()], -1).bfloat16()[None, :, None, :]
-        self.sin = torch.cat([-ang.sin(), ang.sin()], -1).bfloat16()[None, :, None, :]
-        self.half = hd // 2
+        self.cos, self.sin = ang.cos().contiguous(), ang.sin().contiguous()  # fp32 [S, hd / 2]
 
-    def _rope(self, x):
-        return torch.addcmul(x * self.cos, x.roll(self.half, -1), self.sin)
+    def _forward_steps(self, ids):
+        """The forward pass of one group of sequences as a generator: it yields after every row-parallel
+        Linear (whose all-reduce has just been queued), so that a driver can advance another group on another
+        stream while the collective runs.  Returns the next-token ids through StopIteration."""
+        from fms_model_optimizer_b200 import _lib as L
+        from fms_model_optimizer_b200 import ops
 
-    @torch.no_grad()
-    def forward(self, ids):
         cfg = self.cfg
         B, S = ids.shape
         hd = cfg["head_dim"]
+        bf = torch.bfloat16
         x = F.embedding(ids, self.embed).view(B * S, -1)
+        pending = None  # output of the last row-parallel Linear, added to the stream by the next fused kernel
         for lin in self.layers:
-            h = F.rms_norm(x, (x.shape[-1],), lin["ln1"], 1e-5)
-            q = self._rope(lin["q"](h).view(B, S, self.nq, hd)).transpose(1, 2)
-            k = self._rope(lin["k"](h).view(B, S, self.nkv, hd)).transpose(1, 2)
-            v = lin["v"](h).view(B, S, self.nkv, hd).transpose(1, 2)
-            a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+            # (x += pending) -> RMSNorm -> per-token int8 codes for q, k, v: one pass over the stream
+            cs, ss, xs, _ = ops.block_quant(x, prologue=L.BLOCK_NORM, r=pending, norm_w=lin["ln1"], store_sum=True,
+                                            smooth_rcps=[lin["q"].smooth_rcp, lin["k"].smooth_rcp, lin["v"].smooth_rcp])  # fmt: skip
+            x = xs if xs is not None else x
+            q = ops.rope_(lin["q"](None, (cs[0], ss[0]), bf).view(B * S, self.nq, hd), self.cos, self.sin, S)
+            k = ops.rope_(lin["k"](None, (cs[1], ss[1]), bf).view(B * S, self.nkv, hd), self.cos, self.sin, S)
+            v = lin["v"](None, (cs[2], ss[2]), bf)
+            del cs, ss
+            a = F.scaled_dot_product_attention(q.view(B, S, self.nq, hd).transpose(1, 2), k.view(B, S, self.nkv, hd).transpose(1, 2),
+                                               v.view(B, S, self.nkv, hd).transpose(1, 2), is_causal=True, enable_gqa=True)  # fmt: skip
             a = a.transpose(1, 2).reshape(B * S, self.nq * hd)
-            x = x + lin["o"](a)
-            h = F.rms_norm(x, (x.shape[-1],), lin["ln2"], 1e-5)
-            m = F.silu(lin["gate"](h)) * lin["up"](h)
-            x = x + lin["down"](m)
-        last = F.rms_norm(x.view(B, S, -1)[:, -1], (x.shape[-1],), self.norm, 1e-5)
+            pending = lin["o"](None, lin["o"].quantise_fused(a), bf)
+            yield
+            cs, ss, x, _ = ops.block_quant(x, prologue=L.BLOCK_NORM, r=pending, norm_w=lin["ln2"], store_sum=True,
+                                           smooth_rcps=[lin["gate"].smooth_rcp, lin["up"].smooth_rcp])  # fmt: skip
+            g = lin["gate"](None, (cs[0], ss[0]), bf)
+            u = lin["up"](None, (cs[1], ss[1]), bf)
+            del cs, ss
+            pending = lin["down"](None, lin["down"].quantise_fused(g, L.BLOCK_SILU_MUL, u), bf)
+            yield
+        last = x.view(B, S, -1)[:, -1] + pending.view(B, S, -1)[:, -1]
+        last = F.rms_norm(last, (last.shape[-1],), self.norm, 1e-5)
         logits = last @ self.lm_head.t()
         return logits.argmax(-1)
+
+    @torch.no_grad()
+    def forward(self, ids):
+        nm = self.n_micro
+        if nm <= 1:
+            gen = self._forward_steps(ids)
+            try:
+                while True:
+                    next(gen)
+            except StopIteration as stop:
+                return stop.value
+        # groups of sequences on their own streams, advanced round-robin: while the all-reduce of one group is
+        # in flight (its stream waits for it), the other groups' kernels keep the SMs busy
+        main = torch.cuda.current_stream()
+        gens, results = [], [None] * nm
+        for i, part in enumerate(ids.chunk(nm, 0)):
+            self.streams[i].wait_stream(main)
+            gens.append(self._forward_steps(part))
+        live = list(range(nm))
+        while live:
+            for i in list(live):
+                with torch.cuda.stream(self.streams[i]):
+                    try:
+                        next(gens[i])
+                    except StopIteration as stop:
+                        results[i] = stop.value
+                        live.remove(i)
+        for i in range(nm):
+            main.wait_stream(self.streams[i])
+            results[i].record_stream(main)
+        return torch.cat(results)
 
 
 def decoder_linear_ops(cfg, tokens, layers=None):
@@ -263,7 +308,10 @@ def run_c5(args, rank, world, dev):
     from fms_model_optimizer_b200 import ops
 
     cfg = dict(LLAMA)
-    model = Decoder(cfg, dev, world, rank, layers=args.layers)
+    n_micro = args.micro if args.micro > 0 else (2 if world > 1 else 1)
+    if n_micro > 1 and world > 1:
+        ops.GEMM_MAX_CTAS = args.gemm_ctas
+    model = Decoder(cfg, dev, world, rank, layers=args.layers, n_micro=n_micro)
     nl = len(model.layers)
     B, S = cfg["batch"], cfg["seq"]
     tokens = B * S
@@ -328,8 +376,8 @@ def run_c5(args, rank, world, dev):
     gemm_ms = sum(a.elapsed_time(b) for (name, a, b, work) in prof if name == "gemm")
     gemm_ops = sum(work for (name, a, b, work) in prof if name == "gemm")
     n_gemm = sum(1 for p in prof if p[0] == "gemm")
-    quant_ms = sum(a.elapsed_time(b) for (name, a, b, work) in prof if name == "act_quant")
-    quant_bytes = sum(work for (name, a, b, work) in prof if name == "act_quant")
+    quant_ms = sum(a.elapsed_time(b) for (name, a, b, work) in prof if name in ("act_quant", "block_quant"))
+    quant_bytes = sum(work for (name, a, b, work) in prof if name in ("act_quant", "block_quant"))
     achieved = gemm_ops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
     peak = 2.0 * pk["bf16_sustained"]
     line = {
@@ -338,7 +386,7 @@ def run_c5(args, rank, world, dev):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {
             "workload": "c5: Llama-3-8B-shaped decoder, all decoder Linears W8A8 SmoothQuant INT8, prefill 8x2048",
-            "layers": nl, "global_batch": B, "seq_len": S, "parallelism": f"tp{world}",
+            "layers": nl, "global_batch": B, "seq_len": S, "parallelism": f"tp{world}", "sequence_groups_in_flight": n_micro,
             "l2": "inputs larger than L2 (activations 134 MB per Linear, weights 7 GB)",
             "linear_tops": decoder_linear_ops(cfg, tokens, nl) * args.steps / (ms * 1e-3) / 1e12,
         },
@@ -442,6 +490,9 @@ def main():
     ap.add_argument("--workload", default="c5", choices=["c5", "c1", "c2", "c3", "c5lin"])
     ap.add_argument("--layers", type=int, default=None, help="development only: fewer decoder layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--micro", type=int, default=0, help="groups of sequences pipelined on separate streams (0: 2 when sharded, else 1)")
+    ap.add_argument("--gemm-ctas", type=int, default=132, help="CTAs per GEMM while a collective may run beside it (sharded runs)")
+    ap.add_argument("--nccl-ctas", type=int, default=16, help="upper bound on the CTAs of a collective (sharded runs)")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -456,6 +507,8 @@ def main():
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1:
+        if args.nccl_ctas > 0:
+            os.environ.setdefault("NCCL_MAX_CTAS", str(args.nccl_ctas))
         dist.init_process_group("nccl", device_id=dev)
     try:
         if args.workload == "c5":

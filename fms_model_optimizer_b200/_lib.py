@@ -33,6 +33,8 @@ PACT_TWO_SIDED, PACT_ONE_SIDED, PACT_SYMMETRIC = 0, 1, 2
 # qlin_wq_mode
 W_SAWB, W_MAX, W_GIVEN = 0, 1, 2
 PT_INT_SYM, PT_F8_SCALED, PT_F8_SAT = 0, 1, 2
+BLOCK_PLAIN, BLOCK_NORM, BLOCK_SILU_MUL = 0, 1, 2
+BLOCK_DYN, BLOCK_GIVEN_SCALE, BLOCK_SCALE_ONLY = 0, 1, 2
 
 EXPORTED_SYMBOLS = (
     "qlin_version",
@@ -48,6 +50,8 @@ EXPORTED_SYMBOLS = (
     "qlin_weight_fq_perch",
     "qlin_tensor_fq",
     "qlin_tensor_fq_workspace_bytes",
+    "qlin_block_quant",
+    "qlin_rope",
 )
 
 
@@ -82,6 +86,7 @@ class GemmArgs(C.Structure):
         ("mid_round", C.c_int32),
         ("acc_round", C.c_int32),
         ("out_dtype", C.c_int32),
+        ("max_ctas", C.c_int32),
     ]
 
 
@@ -175,6 +180,46 @@ class TensorFqArgs(C.Structure):
     ]
 
 
+class BlockQuantArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p),
+        ("r", C.c_void_p),
+        ("x_out", C.c_void_p),
+        ("h_out", C.c_void_p),
+        ("norm_w", C.c_void_p),
+        ("smooth_rcp", C.c_void_p * 3),
+        ("codes", C.c_void_p * 3),
+        ("scale_out", C.c_void_p * 3),
+        ("scale_in", C.c_void_p),
+        ("ldx", C.c_int64),
+        ("ldr", C.c_int64),
+        ("ldxo", C.c_int64),
+        ("ldh", C.c_int64),
+        ("ldq", C.c_int64 * 3),
+        ("rows", C.c_int32),
+        ("cols", C.c_int32),
+        ("nout", C.c_int32),
+        ("prologue", C.c_int32),
+        ("mode", C.c_int32),
+        ("qmax_levels", C.c_int32),
+        ("norm_eps", C.c_float),
+        ("dyn_eps", C.c_float),
+    ]
+
+
+class RopeArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p),
+        ("cos", C.c_void_p),
+        ("sin", C.c_void_p),
+        ("ld_token", C.c_int64),
+        ("tokens", C.c_int32),
+        ("heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("seq_len", C.c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -201,6 +246,8 @@ def load() -> C.CDLL:
         ("qlin_pact2_bwd_noalloc", Pact2Args),
         ("qlin_weight_fq_perch", WfqArgs),
         ("qlin_tensor_fq", TensorFqArgs),
+        ("qlin_block_quant", BlockQuantArgs),
+        ("qlin_rope", RopeArgs),
     ):
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(struct), C.c_void_p]

@@ -1,0 +1,286 @@
+// qlin_block_quant and qlin_rope: the per-token work that surrounds the W8A8 Linears of a decoder
+// block, fused so that every activation tensor is read once.
+//
+// qlin_block_quant builds the bf16 input row of up to three Linears that share it and quantises it
+// per token for each of them (each Linear has its own SmoothQuant scale), in one pass:
+//   prologue NORM  : t = x (+ r);  optionally store t;  h = bf16(t * rsqrt(mean t^2 + eps) * w)
+//   prologue SILU  : h = bf16(bf16(silu(x)) * r)
+//   prologue PLAIN : h = x
+//   for each output o: v = bf16(h / smooth_o); s = bf16(max(amax |v|, 1e-5) / 127) (or given);
+//                      codes_o = int8(rint(bf16(v / s)))   -- qa_dynamic_max_qfunc of the reference
+// A block owns a row at a time; each thread keeps its 16-element slice of h in registers across the
+// outputs, so the traffic per row is one read of the inputs plus the writes of the codes.
+//
+// The quantise step is the bf16 single-multiply path of qlin_quant.cu: with bf16 values and
+// bf16-valued smoothing / row scales, bf16(a * RN_f32(1 / b)) equals the reference's
+// bf16(RN_f32(a / b)) (a quotient of two 8-bit significands is never within 2^-18 of a bf16
+// rounding boundary).  Callers must pass correctly rounded reciprocals of bf16-valued scales.
+#include <cuda_bf16.h>
+
+#include "qlin_internal.h"
+#include "qlin_rows.cuh"
+
+namespace qlin {
+
+struct BlockQuantParams {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* r;
+  __nv_bfloat16* x_out;
+  __nv_bfloat16* h_out;
+  const __nv_bfloat16* norm_w;
+  const float* mul[3];
+  uint8_t* codes[3];
+  float* scale_out[3];
+  const float* scale_in;
+  int64_t ldx, ldr, ldxo, ldh, ldq[3];
+  int32_t rows, cols, nout, prologue, mode, levels;
+  float norm_eps, dyn_eps;
+};
+
+__device__ __forceinline__ uint32_t bq_pack(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ float bq_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bq_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+// SiLU rounded to bf16; the fast exponential and division are exact to well below half a bf16 place
+__device__ __forceinline__ float bq_silu(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
+
+__device__ __forceinline__ void bq_load8(const __nv_bfloat16* p, uint32_t (&w)[8]) {
+  const uint4 a = reinterpret_cast<const uint4*>(p)[0], b = reinterpret_cast<const uint4*>(p)[1];
+  w[0] = a.x, w[1] = a.y, w[2] = a.z, w[3] = a.w, w[4] = b.x, w[5] = b.y, w[6] = b.z, w[7] = b.w;
+}
+__device__ __forceinline__ void bq_store8(__nv_bfloat16* p, const uint32_t (&w)[8]) {
+  reinterpret_cast<uint4*>(p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  reinterpret_cast<uint4*>(p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+template <int TPB>
+__global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams p) {
+  __shared__ float red[2][32];
+  const int nchunks = p.cols >> 4;
+  const int ch = threadIdx.x;
+  const bool active = ch < nchunks;
+  const float eps = Elem<__nv_bfloat16>::rnd(p.dyn_eps);
+  const float inv_cols = 1.0f / static_cast<float>(p.cols);
+  int flip = 0;
+  for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    uint32_t h[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) h[j] = 0u;
+    if (p.prologue == QLIN_BLOCK_NORM) {
+      float ssq = 0.0f;
+      if (active) {
+        bq_load8(p.x + static_cast<int64_t>(row) * p.ldx + ch * 16, h);
+        if (p.r != nullptr) {
+          uint32_t a[8];
+          bq_load8(p.r + static_cast<int64_t>(row) * p.ldr + ch * 16, a);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) h[j] = bq_pack(__fadd_rn(bq_lo(h[j]), bq_lo(a[j])), __fadd_rn(bq_hi(h[j]), bq_hi(a[j])));
+          if (p.x_out != nullptr) bq_store8(p.x_out + static_cast<int64_t>(row) * p.ldxo + ch * 16, h);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ssq += bq_lo(h[j]) * bq_lo(h[j]) + bq_hi(h[j]) * bq_hi(h[j]);
+      }
+      ssq = block_reduce<OpSum>(ssq, red[flip], 0.0f);
+      flip ^= 1;
+      const float rstd = rsqrtf(ssq * inv_cols + p.norm_eps);
+      if (active) {
+        uint32_t w[8];
+        bq_load8(p.norm_w + ch * 16, w);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[j] = bq_pack(bq_lo(h[j]) * rstd * bq_lo(w[j]), bq_hi(h[j]) * rstd * bq_hi(w[j]));
+      }
+    } else if (active) {
+      bq_load8(p.x + static_cast<int64_t>(row) * p.ldx + ch * 16, h);
+      if (p.prologue == QLIN_BLOCK_SILU_MUL) {
+        uint32_t u[8];
+        bq_load8(p.r + static_cast<int64_t>(row) * p.ldr + ch * 16, u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t sl = bq_pack(bq_silu(bq_lo(h[j])), bq_silu(bq_hi(h[j])));
+          h[j] = bq_pack(__fmul_rn(bq_lo(sl), bq_lo(u[j])), __fmul_rn(bq_hi(sl), bq_hi(u[j])));
+        }
+      }
+    }
+    if (active && p.h_out != nullptr) bq_store8(p.h_out + static_cast<int64_t>(row) * p.ldh + ch * 16, h);
+
+    for (int o = 0; o < p.nout; ++o) {
+      uint32_t v[8];
+      __nv_bfloat162 amax2 = __floats2bfloat162_rn(0.0f, 0.0f);
+      if (active) {
+        if (p.mul[o] != nullptr) {
+          float m[16];
+          load16(p.mul[o] + ch * 16, m);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = bq_pack(__fmul_rn(bq_lo(h[j]), m[2 * j]), __fmul_rn(bq_hi(h[j]), m[2 * j + 1]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = h[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax2 = __hmax2(amax2, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&v[j])));
+      }
+      float s;
+      if (p.mode == QLIN_BLOCK_GIVEN_SCALE) {
+        s = p.scale_in[row];
+      } else {
+        float amax = fmaxf(__low2float(amax2), __high2float(amax2));
+        amax = block_reduce<OpMax>(amax, red[flip], 0.0f);
+        flip ^= 1;
+        s = Elem<__nv_bfloat16>::rnd(__fdiv_rn(fmaxf(amax, eps), static_cast<float>(p.levels)));
+        if (threadIdx.x == 0 && p.scale_out[o] != nullptr) p.scale_out[o][row] = s;
+      }
+      if (p.mode == QLIN_BLOCK_SCALE_ONLY || !active) continue;
+      const float rs = __frcp_rn(s);
+      uint32_t out[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        int q[4];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const uint32_t t2 = bq_pack(__fmul_rn(bq_lo(v[2 * g + k]), rs), __fmul_rn(bq_hi(v[2 * g + k]), rs));
+          (void)fast_rint(bq_lo(t2), q[2 * k]);
+          (void)fast_rint(bq_hi(t2), q[2 * k + 1]);
+        }
+        out[g] = __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
+      }
+      *reinterpret_cast<uint4*>(p.codes[o] + static_cast<int64_t>(row) * p.ldq[o] + ch * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+  }
+}
+
+// Rotary embedding in place on [tokens, heads, head_dim] bf16: position = token % seq_len;
+// out[..., i] = x[i] cos[i] - x[i + d/2] sin[i], out[..., i + d/2] = x[i + d/2] cos[i] + x[i] sin[i],
+// computed in fp32 and rounded once.  One thread rotates 8 pairs.
+struct RopeParams {
+  __nv_bfloat16* x;
+  const float* cos;
+  const float* sin;
+  int64_t ld_token;
+  int32_t tokens, heads, head_dim, seq_len;
+};
+
+__global__ void __launch_bounds__(256) rope_kernel(const RopeParams p) {
+  const int half = p.head_dim >> 1;
+  const int groups = half >> 3;  // 8 pairs per thread
+  const int64_t total = static_cast<int64_t>(p.tokens) * p.heads * groups;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int g = static_cast<int>(i % groups);
+    const int64_t th = i / groups;
+    const int head = static_cast<int>(th % p.heads);
+    const int64_t token = th / p.heads;
+    const int pos = static_cast<int>(token % p.seq_len);
+    __nv_bfloat16* base = p.x + token * p.ld_token + static_cast<int64_t>(head) * p.head_dim + g * 8;
+    const uint4 a = *reinterpret_cast<const uint4*>(base), b = *reinterpret_cast<const uint4*>(base + half);
+    const float4 c0 = *reinterpret_cast<const float4*>(p.cos + static_cast<int64_t>(pos) * half + g * 8);
+    const float4 c1 = *reinterpret_cast<const float4*>(p.cos + static_cast<int64_t>(pos) * half + g * 8 + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(p.sin + static_cast<int64_t>(pos) * half + g * 8);
+    const float4 s1 = *reinterpret_cast<const float4*>(p.sin + static_cast<int64_t>(pos) * half + g * 8 + 4);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+    const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    uint32_t ao[4], bo[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float x0 = bq_lo(aw[j]), x1 = bq_hi(aw[j]), y0 = bq_lo(bw[j]), y1 = bq_hi(bw[j]);
+      ao[j] = bq_pack(x0 * cs[2 * j] - y0 * sn[2 * j], x1 * cs[2 * j + 1] - y1 * sn[2 * j + 1]);
+      bo[j] = bq_pack(y0 * cs[2 * j] + x0 * sn[2 * j], y1 * cs[2 * j + 1] + x1 * sn[2 * j + 1]);
+    }
+    *reinterpret_cast<uint4*>(base) = make_uint4(ao[0], ao[1], ao[2], ao[3]);
+    *reinterpret_cast<uint4*>(base + half) = make_uint4(bo[0], bo[1], bo[2], bo[3]);
+  }
+}
+
+}  // namespace qlin
+
+using namespace qlin;
+
+extern "C" int qlin_block_quant(const qlin_block_quant_args* a, void* stream) {
+  if (a == nullptr) return fail(QLIN_ERR_NULL, "qlin_block_quant: args is NULL");
+  if (a->x == nullptr) return fail(QLIN_ERR_NULL, "qlin_block_quant: x is NULL");
+  if (a->rows < 0 || a->cols < 0) return fail(QLIN_ERR_BAD_SHAPE, "qlin_block_quant: negative dimension");
+  if (a->rows == 0 || a->cols == 0) return QLIN_OK;
+  if (a->cols % 16 != 0 || a->cols > 16384) return fail(QLIN_ERR_BAD_SHAPE, "qlin_block_quant: cols must be a multiple of 16, at most 16384");
+  if (a->prologue < QLIN_BLOCK_PLAIN || a->prologue > QLIN_BLOCK_SILU_MUL) return fail(QLIN_ERR_UNSUPPORTED, "qlin_block_quant: unknown prologue");
+  if (a->mode < QLIN_BLOCK_DYN || a->mode > QLIN_BLOCK_SCALE_ONLY) return fail(QLIN_ERR_UNSUPPORTED, "qlin_block_quant: unknown mode");
+  if (a->nout < 0 || a->nout > 3) return fail(QLIN_ERR_BAD_SHAPE, "qlin_block_quant: between 0 and 3 outputs");
+  if (a->prologue == QLIN_BLOCK_NORM && a->norm_w == nullptr) return fail(QLIN_ERR_NULL, "qlin_block_quant: norm_w is NULL");
+  if (a->prologue == QLIN_BLOCK_SILU_MUL && a->r == nullptr) return fail(QLIN_ERR_NULL, "qlin_block_quant: the second factor is NULL");
+  if (a->mode == QLIN_BLOCK_GIVEN_SCALE && (a->scale_in == nullptr || a->nout != 1))
+    return fail(QLIN_ERR_NULL, "qlin_block_quant: GIVEN_SCALE takes scale_in and exactly one output");
+  if (a->qmax_levels < 1 || a->qmax_levels > 127) return fail(QLIN_ERR_UNSUPPORTED, "qlin_block_quant: qmax_levels must be in [1, 127]");
+  BlockQuantParams p;
+  p.x = static_cast<const __nv_bfloat16*>(a->x);
+  p.r = static_cast<const __nv_bfloat16*>(a->r);
+  p.x_out = static_cast<__nv_bfloat16*>(a->x_out);
+  p.h_out = static_cast<__nv_bfloat16*>(a->h_out);
+  p.norm_w = static_cast<const __nv_bfloat16*>(a->norm_w);
+  bool ok = aligned16(p.x) && aligned16(p.r) && aligned16(p.x_out) && aligned16(p.h_out) && aligned16(p.norm_w) && a->ldx % 8 == 0 &&
+            a->ldr % 8 == 0 && a->ldxo % 8 == 0 && a->ldh % 8 == 0;
+  for (int o = 0; o < 3; ++o) {
+    const bool used = o < a->nout;
+    p.mul[o] = used ? a->smooth_rcp[o] : nullptr;
+    p.codes[o] = used ? static_cast<uint8_t*>(a->codes[o]) : nullptr;
+    p.scale_out[o] = used ? a->scale_out[o] : nullptr;
+    p.ldq[o] = a->ldq[o];
+    if (used) {
+      if (a->mode != QLIN_BLOCK_SCALE_ONLY && p.codes[o] == nullptr) return fail(QLIN_ERR_NULL, "qlin_block_quant: codes[%d] is NULL", o);
+      if (a->mode == QLIN_BLOCK_SCALE_ONLY && p.scale_out[o] == nullptr) return fail(QLIN_ERR_NULL, "qlin_block_quant: scale_out[%d] is NULL", o);
+      ok = ok && aligned16(p.codes[o]) && aligned16(p.mul[o]) && (p.codes[o] == nullptr || a->ldq[o] % 16 == 0);
+    }
+  }
+  if (!ok) return fail(QLIN_ERR_BAD_ALIGN, "qlin_block_quant: pointers must be 16-byte aligned and leading dimensions multiples of 16 bytes");
+  p.scale_in = a->scale_in;
+  p.ldx = a->ldx;
+  p.ldr = a->ldr;
+  p.ldxo = a->ldxo;
+  p.ldh = a->ldh;
+  p.rows = a->rows;
+  p.cols = a->cols;
+  p.nout = a->nout;
+  p.prologue = a->prologue;
+  p.mode = a->mode;
+  p.levels = a->qmax_levels;
+  p.norm_eps = a->norm_eps;
+  p.dyn_eps = a->dyn_eps;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int nchunks = p.cols / 16;
+  if (nchunks <= 256) {
+    int grid = sm_count() * 8;
+    if (grid > p.rows) grid = p.rows;
+    block_quant_kernel<256><<<grid, 256, 0, s>>>(p);
+  } else {
+    int grid = sm_count() * 2;
+    if (grid > p.rows) grid = p.rows;
+    block_quant_kernel<1024><<<grid, 1024, 0, s>>>(p);
+  }
+  QLIN_CHECK_LAUNCH("qlin_block_quant");
+  return QLIN_OK;
+}
+
+extern "C" int qlin_rope(const qlin_rope_args* a, void* stream) {
+  if (a == nullptr) return fail(QLIN_ERR_NULL, "qlin_rope: args is NULL");
+  if (a->x == nullptr || a->cos == nullptr || a->sin == nullptr) return fail(QLIN_ERR_NULL, "qlin_rope: x, cos or sin is NULL");
+  if (a->tokens < 0 || a->heads < 0 || a->seq_len < 1) return fail(QLIN_ERR_BAD_SHAPE, "qlin_rope: bad dimensions");
+  if (a->head_dim < 16 || a->head_dim % 16 != 0) return fail(QLIN_ERR_BAD_SHAPE, "qlin_rope: head_dim must be a multiple of 16");
+  if (a->tokens == 0 || a->heads == 0) return QLIN_OK;
+  if (!aligned16(a->x) || !aligned16(a->cos) || !aligned16(a->sin) || a->ld_token % 8 != 0)
+    return fail(QLIN_ERR_BAD_ALIGN, "qlin_rope: pointers must be 16-byte aligned and the token pitch a multiple of 8 elements");
+  RopeParams p;
+  p.x = static_cast<__nv_bfloat16*>(a->x);
+  p.cos = a->cos;
+  p.sin = a->sin;
+  p.ld_token = a->ld_token;
+  p.tokens = a->tokens;
+  p.heads = a->heads;
+  p.head_dim = a->head_dim;
+  p.seq_len = a->seq_len;
+  const int64_t total = static_cast<int64_t>(p.tokens) * p.heads * (p.head_dim / 16);
+  int64_t blocks = (total + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  rope_kernel<<<static_cast<int>(blocks), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  QLIN_CHECK_LAUNCH("qlin_rope");
+  return QLIN_OK;
+}

@@ -79,7 +79,7 @@ struct GemmParams {
   int32_t chunk_k32;   // 32-byte MMA steps per accumulation chunk
   int32_t trun_bits, max_acc_bits, trunc_then_acc, clamp_dl16;
   int32_t epilogue, rs_stride, cs_stride, prod_round, scale_round, mid_round, acc_round, out_dtype;
-  int32_t num_m, num_n;
+  int32_t num_m, num_n, max_ctas;
 };
 
 __device__ __forceinline__ float round_to(float y, int dt) {
@@ -666,7 +666,8 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
     configured[dev] = true;
   }
   const int tiles = p.num_m * p.num_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
   qlin_gemm_kernel<F8, CHUNKED><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
   QLIN_CHECK_LAUNCH("qlin_gemm");
   return QLIN_OK;
@@ -744,6 +745,7 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   p.mid_round = a->mid_round;
   p.acc_round = a->acc_round;
   p.out_dtype = a->out_dtype;
+  p.max_ctas = a->max_ctas;
   const int bn = chunked ? Cfg<true>::BN : Cfg<false>::BN;
   p.num_m = (a->M + kBM - 1) / kBM;
   p.num_n = (a->N + bn - 1) / bn;

@@ -12,7 +12,7 @@ of the file) so that modules call ``torch.ops.qlin_b200.*`` the way the referenc
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -36,6 +36,9 @@ _status_words: dict[int, torch.Tensor] = {}
 # (name, start, end, work) is appended (work = operations for the GEMM, bytes for the others).
 LAUNCHES = 0
 PROFILE = None
+# Upper bound on the CTAs of a GEMM launch (0 = one per SM).  A caller that overlaps GEMMs with a collective on another
+# stream lowers it so that the collective's CTAs find free SMs.
+GEMM_MAX_CTAS = 0
 
 
 def _timed(name: str, work: float, dev: torch.device, call):
@@ -187,7 +190,7 @@ def gemm(
         row_scale_stride=(0 if rs is None or rs.numel() == 1 else 1),
         col_scale_stride=(0 if cs is None or cs.numel() == 1 else 1),
         prod_round=_ROUND[prod_round], scale_round=_ROUND[scale_round], mid_round=_ROUND[mid_round], acc_round=_ROUND[acc_round],
-        out_dtype=_DT[out_dtype],
+        out_dtype=_DT[out_dtype], max_ctas=int(GEMM_MAX_CTAS),
     )  # fmt: skip
     with torch.cuda.device(dev):
         rc = _timed("gemm", 2.0 * M * N * K, dev, lambda: L.load().qlin_gemm(C.byref(args), _stream(dev)))
@@ -496,6 +499,74 @@ def pact2_bwd(
         rc = _timed("pact2_bwd", 3.0 * xc.numel() * xc.element_size(), dev, lambda: lib.qlin_pact2_bwd(C.byref(args), _stream(dev)))
         L.check(rc, "qlin_pact2_bwd")
     return gx, grads
+
+
+# --------------------------------------------------------------------------------------------------
+# Decoder-block fusions: (residual add +) RMSNorm / SiLU * up, then per-token quantisation for up to
+# three Linears that share the input; rotary embedding.
+# --------------------------------------------------------------------------------------------------
+def block_quant(
+    x: torch.Tensor,
+    *,
+    prologue: int = L.BLOCK_PLAIN,
+    r: Optional[torch.Tensor] = None,
+    norm_w: Optional[torch.Tensor] = None,
+    smooth_rcps: Sequence[Optional[torch.Tensor]] = (None,),
+    mode: int = L.BLOCK_DYN,
+    scale_in: Optional[torch.Tensor] = None,
+    store_sum: bool = False,
+    want_h: bool = False,
+    levels: int = 127,
+    norm_eps: float = 1e-5,
+    dyn_eps: float = 1e-5,
+):
+    """See ``qlin_block_quant`` in include/qlin_b200.h.  ``x`` (and ``r``) are 2-D bf16 with unit column
+    stride; ``smooth_rcps`` holds one fp32 reciprocal vector (or None) per Linear that consumes the row.
+    Returns ``(codes list, scales list, x_plus_r or None, h or None)``; with ``BLOCK_SCALE_ONLY`` the codes are None."""
+    dev = _require_cuda(x, r, norm_w, scale_in, *smooth_rcps)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
+        raise RuntimeError("block_quant takes a 2-D bf16 tensor with contiguous rows")
+    if r is not None and (r.dtype != torch.bfloat16 or r.shape != x.shape or r.stride(1) != 1):
+        raise RuntimeError("r must match x")
+    rows, cols = x.shape
+    nout = len(smooth_rcps)
+    codes = [None if mode == L.BLOCK_SCALE_ONLY else torch.empty((rows, cols), dtype=torch.int8, device=dev) for _ in range(nout)]
+    scales = [scale_in if mode == L.BLOCK_GIVEN_SCALE else torch.empty((rows,), dtype=torch.float32, device=dev) for _ in range(nout)]
+    x_out = torch.empty((rows, cols), dtype=torch.bfloat16, device=dev) if (store_sum and r is not None) else None
+    h_out = torch.empty((rows, cols), dtype=torch.bfloat16, device=dev) if want_h else None
+    if rows == 0 or cols == 0:
+        return codes, scales, x_out, h_out
+    p3 = C.c_void_p * 3
+    i3 = C.c_int64 * 3
+    pad = [None] * (3 - nout)
+    args = L.BlockQuantArgs(
+        x=_ptr(x), r=_ptr(r), x_out=_ptr(x_out), h_out=_ptr(h_out), norm_w=_ptr(norm_w),
+        smooth_rcp=p3(*[_ptr(t) for t in list(smooth_rcps) + pad]), codes=p3(*[_ptr(t) for t in codes + pad]),
+        scale_out=p3(*[(_ptr(t) if mode != L.BLOCK_GIVEN_SCALE else None) for t in scales + pad]), scale_in=_ptr(scale_in),
+        ldx=x.stride(0), ldr=(r.stride(0) if r is not None else 0), ldxo=cols, ldh=cols, ldq=i3(cols, cols, cols),
+        rows=rows, cols=cols, nout=nout, prologue=int(prologue), mode=int(mode), qmax_levels=int(levels),
+        norm_eps=float(norm_eps), dyn_eps=float(dyn_eps),
+    )  # fmt: skip
+    nbytes = rows * cols * (2 * (1 + (r is not None) + (x_out is not None) + (h_out is not None)) + (0 if mode == L.BLOCK_SCALE_ONLY else nout))
+    with torch.cuda.device(dev):
+        rc = _timed("block_quant", float(nbytes), dev, lambda: L.load().qlin_block_quant(C.byref(args), _stream(dev)))
+        L.check(rc, "qlin_block_quant")
+    return codes, scales, x_out, h_out
+
+
+def rope_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq_len: int) -> torch.Tensor:
+    """Rotary embedding in place on ``x [tokens, heads, head_dim]`` bf16 (``qlin_rope``)."""
+    dev = _require_cuda(x, cos, sin)
+    if x.dtype != torch.bfloat16 or x.dim() != 3 or x.stride(2) != 1 or x.stride(1) != x.shape[2]:
+        raise RuntimeError("rope_ takes [tokens, heads, head_dim] bf16 with contiguous heads")
+    if cos.dtype != torch.float32 or sin.dtype != torch.float32 or not cos.is_contiguous() or not sin.is_contiguous():
+        raise RuntimeError("cos / sin are contiguous fp32 [seq_len, head_dim / 2]")
+    args = L.RopeArgs(x=_ptr(x), cos=_ptr(cos), sin=_ptr(sin), ld_token=x.stride(0), tokens=x.shape[0], heads=x.shape[1],
+                      head_dim=x.shape[2], seq_len=int(seq_len))  # fmt: skip
+    with torch.cuda.device(dev):
+        rc = _timed("rope", 4.0 * x.numel(), dev, lambda: L.load().qlin_rope(C.byref(args), _stream(dev)))
+        L.check(rc, "qlin_rope")
+    return x
 
 
 # --------------------------------------------------------------------------------------------------

@@ -92,10 +92,25 @@ class W8A8Linear:
             return codes, scale
         return self._q(x2, None)
 
-    def __call__(self, x2: torch.Tensor, quantised=None) -> torch.Tensor:
+    def quantise_fused(self, x2: torch.Tensor, prologue: int = L.BLOCK_PLAIN, r: Optional[torch.Tensor] = None):
+        """Per-token codes and scales of ``prologue(x2, r) / smooth`` for bf16 rows through the fused kernel
+        (``ops.block_quant``); a row-parallel shard takes two passes around the MAX all-reduce of the scales."""
+        rcp = [self.smooth_rcp]
+        if self.mode == "row" and self.world > 1:
+            _, (scale,), _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_SCALE_ONLY)
+            dist.all_reduce(scale, op=dist.ReduceOp.MAX, group=self.group)
+            (codes,), _, _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_GIVEN_SCALE, scale_in=scale)
+            return codes, scale
+        (codes,), (scale,), _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp)
+        return codes, scale
+
+    def __call__(self, x2: Optional[torch.Tensor], quantised=None, act_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``quantised=(codes, scale)`` skips the quantiser (a fused kernel upstream produced them for the
+        activation dtype ``act_dtype``; for a row-parallel shard the scale must already be the maximum over ranks)."""
         codes, scale = quantised if quantised is not None else self.quantise(x2)
-        prod_dtype = torch.promote_types(x2.dtype, self.w_scale_dtype)
-        out = self.gemm_fn(codes, self.weight, scale, self.w_scale, self.bias, x2.dtype, prod_dtype)
+        act_dtype = act_dtype if x2 is None else x2.dtype
+        prod_dtype = torch.promote_types(act_dtype, self.w_scale_dtype)
+        out = self.gemm_fn(codes, self.weight, scale, self.w_scale, self.bias, act_dtype, prod_dtype)
         if self.mode == "row" and self.world > 1:
             dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
         return out

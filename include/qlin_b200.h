@@ -124,6 +124,9 @@ typedef struct qlin_gemm_args {
   int32_t mid_round;        /* qlin_dtype */
   int32_t acc_round;        /* qlin_dtype */
   int32_t out_dtype;        /* qlin_dtype */
+  int32_t max_ctas;         /* 0: one persistent CTA per SM; > 0: at most this many CTAs (each needs a whole SM),
+                               leaving SMs free for a kernel that runs concurrently on another stream, e.g. a
+                               collective.  Results do not depend on it. */
 } qlin_gemm_args;
 
 int qlin_gemm(const qlin_gemm_args* args, void* stream);
@@ -348,6 +351,64 @@ typedef struct qlin_tensor_fq_args {
 
 int qlin_tensor_fq(const qlin_tensor_fq_args* args, void* stream);
 int64_t qlin_tensor_fq_workspace_bytes(int64_t numel);
+
+/* ------------------------------------------------------------------------------------------------
+ * qlin_block_quant -- builds the bf16 input row of up to three W8A8 Linears that share it and
+ * quantises it per token for each of them, reading the activations once.
+ *
+ * The quantise step replaces QLinearINT8Deploy.qa_dynamic_max_qfunc after the SmoothQuant division
+ * (fms_mo/modules/linear.py:1085-1100, :1322-1324) for bf16 activations, bit for bit.  The prologues
+ * have no counterpart in the reference: a model runs them as separate PyTorch kernels around its
+ * Linears (RMSNorm, residual add, SiLU * up); they are fused here because at prefill sizes those
+ * kernels move more bytes than the quantiser itself.
+ *   QLIN_BLOCK_PLAIN     h = x
+ *   QLIN_BLOCK_NORM      t = x (+ r, stored to x_out when given); h = bf16(t * rsqrt(mean t^2 + norm_eps) * norm_w)
+ *   QLIN_BLOCK_SILU_MUL  h = bf16(bf16(x / (1 + exp(-x))) * r)
+ * For output o < nout: v = bf16(h * smooth_rcp[o]) (h when smooth_rcp[o] is NULL),
+ *   QLIN_BLOCK_DYN          s = bf16(max(amax|v|, dyn_eps) / qmax_levels) -> scale_out[o]; codes[o] = int8(rint(bf16(v / s)))
+ *   QLIN_BLOCK_GIVEN_SCALE  s = scale_in[row] (one output): the second pass of a row-parallel shard,
+ *                           after the scales of all shards were reduced with MAX
+ *   QLIN_BLOCK_SCALE_ONLY   only scale_out[o] is written: the first pass of a row-parallel shard
+ * smooth_rcp[o][c] must be the correctly rounded fp32 reciprocal of a bf16-valued SmoothQuant scale
+ * (the reference casts that scale to the activation dtype).  All tensors bf16, 16-byte aligned rows,
+ * cols a multiple of 16 and at most 16384.  h_out (optional) receives h.
+ * ---------------------------------------------------------------------------------------------- */
+typedef enum qlin_block_prologue { QLIN_BLOCK_PLAIN = 0, QLIN_BLOCK_NORM = 1, QLIN_BLOCK_SILU_MUL = 2 } qlin_block_prologue;
+typedef enum qlin_block_mode { QLIN_BLOCK_DYN = 0, QLIN_BLOCK_GIVEN_SCALE = 1, QLIN_BLOCK_SCALE_ONLY = 2 } qlin_block_mode;
+
+typedef struct qlin_block_quant_args {
+  const void* x;        /* [rows, cols] bf16 */
+  const void* r;        /* NORM: optional addend; SILU_MUL: the second factor */
+  void* x_out;          /* NORM with r: x + r (may alias x) */
+  void* h_out;          /* optional: the row the Linears see */
+  const void* norm_w;   /* NORM: [cols] bf16 */
+  const float* smooth_rcp[3];
+  void* codes[3];       /* [rows, cols] int8 */
+  float* scale_out[3];  /* [rows] */
+  const float* scale_in;/* GIVEN_SCALE: [rows] */
+  int64_t ldx, ldr, ldxo, ldh, ldq[3];
+  int32_t rows, cols, nout;
+  int32_t prologue;     /* qlin_block_prologue */
+  int32_t mode;         /* qlin_block_mode */
+  int32_t qmax_levels;
+  float norm_eps, dyn_eps;
+} qlin_block_quant_args;
+
+int qlin_block_quant(const qlin_block_quant_args* args, void* stream);
+
+/* qlin_rope -- rotary position embedding in place on x [tokens, heads, head_dim] bf16 (token pitch
+ * ld_token elements), position = token % seq_len, cos / sin [seq_len, head_dim / 2] fp32, halves
+ * rotated as (x[i], x[i + head_dim / 2]).  No counterpart in the reference (model plumbing between
+ * the q/k Linears and attention). */
+typedef struct qlin_rope_args {
+  void* x;
+  const float* cos;
+  const float* sin;
+  int64_t ld_token;
+  int32_t tokens, heads, head_dim, seq_len;
+} qlin_rope_args;
+
+int qlin_rope(const qlin_rope_args* args, void* stream);
 
 #ifdef __cplusplus
 }
