@@ -52,6 +52,10 @@ EXPORTED_SYMBOLS = (
     "qlin_tensor_fq_workspace_bytes",
     "qlin_block_quant",
     "qlin_rope",
+    "qlin_ipc_export",
+    "qlin_ipc_open",
+    "qlin_ipc_close",
+    "qlin_peer_barrier",
 )
 
 
@@ -86,6 +90,9 @@ class GemmArgs(C.Structure):
         ("mid_round", C.c_int32),
         ("acc_round", C.c_int32),
         ("out_dtype", C.c_int32),
+        ("scatter_d", C.c_void_p * 8),
+        ("scatter_rows", C.c_int32),
+        ("scatter_row0", C.c_int32),
         ("max_ctas", C.c_int32),
     ]
 
@@ -184,6 +191,8 @@ class BlockQuantArgs(C.Structure):
     _fields_ = [
         ("x", C.c_void_p),
         ("r", C.c_void_p),
+        ("r_parts", C.c_int32),
+        ("r_part_stride", C.c_int64),
         ("x_out", C.c_void_p),
         ("h_out", C.c_void_p),
         ("norm_w", C.c_void_p),
@@ -191,6 +200,11 @@ class BlockQuantArgs(C.Structure):
         ("codes", C.c_void_p * 3),
         ("scale_out", C.c_void_p * 3),
         ("scale_in", C.c_void_p),
+        ("dst_base", C.c_void_p * 8),
+        ("codes_off", C.c_int64 * 3),
+        ("scale_off", C.c_int64 * 3),
+        ("ndst", C.c_int32),
+        ("dst_row0", C.c_int32),
         ("ldx", C.c_int64),
         ("ldr", C.c_int64),
         ("ldxo", C.c_int64),
@@ -217,6 +231,17 @@ class RopeArgs(C.Structure):
         ("heads", C.c_int32),
         ("head_dim", C.c_int32),
         ("seq_len", C.c_int32),
+    ]
+
+
+class PeerBarrierArgs(C.Structure):
+    _fields_ = [
+        ("local_flags", C.c_void_p),
+        ("peer_flags", C.c_void_p * 8),
+        ("epoch", C.c_void_p),
+        ("status", C.c_void_p),
+        ("rank", C.c_int32),
+        ("world", C.c_int32),
     ]
 
 
@@ -248,6 +273,7 @@ def load() -> C.CDLL:
         ("qlin_tensor_fq", TensorFqArgs),
         ("qlin_block_quant", BlockQuantArgs),
         ("qlin_rope", RopeArgs),
+        ("qlin_peer_barrier", PeerBarrierArgs),
     ):
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(struct), C.c_void_p]
@@ -255,6 +281,12 @@ def load() -> C.CDLL:
     lib.qlin_pact2_bwd_workspace_bytes.argtypes = [C.c_int64]
     lib.qlin_pact2_bwd_workspace_bytes.restype = C.c_size_t
     lib.qlin_pact2_bwd_noalloc_max_numel.restype = C.c_int64
+    lib.qlin_ipc_export.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]
+    lib.qlin_ipc_export.restype = C.c_int
+    lib.qlin_ipc_open.argtypes = [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]
+    lib.qlin_ipc_open.restype = C.c_int
+    lib.qlin_ipc_close.argtypes = [C.c_void_p]
+    lib.qlin_ipc_close.restype = C.c_int
     lib.qlin_tensor_fq_workspace_bytes.argtypes = [C.c_int64]
     lib.qlin_tensor_fq_workspace_bytes.restype = C.c_int64
     _lib = lib

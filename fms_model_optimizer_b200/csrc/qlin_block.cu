@@ -33,8 +33,14 @@ struct BlockQuantParams {
   float* scale_out[3];
   const float* scale_in;
   int64_t ldx, ldr, ldxo, ldh, ldq[3];
+  int64_t r_part_stride;
+  int32_t r_parts;
   int32_t rows, cols, nout, prologue, mode, levels;
   float norm_eps, dyn_eps;
+  // replicated outputs
+  uint8_t* dst_base[8];
+  int64_t codes_off[3], scale_off[3];
+  int32_t ndst, dst_row0;
 };
 
 __device__ __forceinline__ uint32_t bq_pack(float lo, float hi) {
@@ -74,7 +80,20 @@ __global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams
         bq_load8(p.x + static_cast<int64_t>(row) * p.ldx + ch * 16, h);
         if (p.r != nullptr) {
           uint32_t a[8];
-          bq_load8(p.r + static_cast<int64_t>(row) * p.ldr + ch * 16, a);
+          const __nv_bfloat16* rp = p.r + static_cast<int64_t>(row) * p.ldr + ch * 16;
+          bq_load8(rp, a);
+          if (p.r_parts > 1) {  // sum of the shards' partial outputs: fp32 in index order, one rounding
+            float acc[16];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[2 * j] = bq_lo(a[j]), acc[2 * j + 1] = bq_hi(a[j]);
+            for (int s = 1; s < p.r_parts; ++s) {
+              bq_load8(rp + s * p.r_part_stride, a);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[2 * j] += bq_lo(a[j]), acc[2 * j + 1] += bq_hi(a[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) a[j] = bq_pack(acc[2 * j], acc[2 * j + 1]);
+          }
 #pragma unroll
           for (int j = 0; j < 8; ++j) h[j] = bq_pack(__fadd_rn(bq_lo(h[j]), bq_lo(a[j])), __fadd_rn(bq_hi(h[j]), bq_hi(a[j])));
           if (p.x_out != nullptr) bq_store8(p.x_out + static_cast<int64_t>(row) * p.ldxo + ch * 16, h);
@@ -129,7 +148,12 @@ __global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams
         amax = block_reduce<OpMax>(amax, red[flip], 0.0f);
         flip ^= 1;
         s = Elem<__nv_bfloat16>::rnd(__fdiv_rn(fmaxf(amax, eps), static_cast<float>(p.levels)));
-        if (threadIdx.x == 0 && p.scale_out[o] != nullptr) p.scale_out[o][row] = s;
+        if (p.ndst > 0) {
+          if (static_cast<int>(threadIdx.x) < p.ndst)
+            reinterpret_cast<float*>(p.dst_base[threadIdx.x] + p.scale_off[o])[p.dst_row0 + row] = s;
+        } else if (threadIdx.x == 0 && p.scale_out[o] != nullptr) {
+          p.scale_out[o][row] = s;
+        }
       }
       if (p.mode == QLIN_BLOCK_SCALE_ONLY || !active) continue;
       const float rs = __frcp_rn(s);
@@ -145,7 +169,13 @@ __global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams
         }
         out[g] = __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
       }
-      *reinterpret_cast<uint4*>(p.codes[o] + static_cast<int64_t>(row) * p.ldq[o] + ch * 16) = make_uint4(out[0], out[1], out[2], out[3]);
+      const uint4 packed = make_uint4(out[0], out[1], out[2], out[3]);
+      if (p.ndst > 0) {
+        const int64_t off = p.codes_off[o] + static_cast<int64_t>(p.dst_row0 + row) * p.ldq[o] + ch * 16;
+        for (int d = 0; d < p.ndst; ++d) *reinterpret_cast<uint4*>(p.dst_base[d] + off) = packed;
+      } else {
+        *reinterpret_cast<uint4*>(p.codes[o] + static_cast<int64_t>(row) * p.ldq[o] + ch * 16) = packed;
+      }
     }
   }
 }
@@ -224,12 +254,28 @@ extern "C" int qlin_block_quant(const qlin_block_quant_args* a, void* stream) {
     p.codes[o] = used ? static_cast<uint8_t*>(a->codes[o]) : nullptr;
     p.scale_out[o] = used ? a->scale_out[o] : nullptr;
     p.ldq[o] = a->ldq[o];
-    if (used) {
+    p.codes_off[o] = a->codes_off[o];
+    p.scale_off[o] = a->scale_off[o];
+    if (used && a->ndst > 0) {
+      ok = ok && aligned16(p.mul[o]) && a->ldq[o] % 16 == 0 && a->codes_off[o] % 16 == 0 && a->scale_off[o] % 4 == 0;
+    } else if (used) {
       if (a->mode != QLIN_BLOCK_SCALE_ONLY && p.codes[o] == nullptr) return fail(QLIN_ERR_NULL, "qlin_block_quant: codes[%d] is NULL", o);
       if (a->mode == QLIN_BLOCK_SCALE_ONLY && p.scale_out[o] == nullptr) return fail(QLIN_ERR_NULL, "qlin_block_quant: scale_out[%d] is NULL", o);
       ok = ok && aligned16(p.codes[o]) && aligned16(p.mul[o]) && (p.codes[o] == nullptr || a->ldq[o] % 16 == 0);
     }
   }
+  if (a->ndst < 0 || a->ndst > 8) return fail(QLIN_ERR_BAD_SHAPE, "qlin_block_quant: at most 8 destinations");
+  if (a->ndst > 0 && a->mode != QLIN_BLOCK_DYN) return fail(QLIN_ERR_UNSUPPORTED, "qlin_block_quant: replicated outputs take the dynamic mode");
+  for (int d = 0; d < 8; ++d) {
+    p.dst_base[d] = d < a->ndst ? static_cast<uint8_t*>(a->dst_base[d]) : nullptr;
+    if (d < a->ndst && (p.dst_base[d] == nullptr || !aligned16(p.dst_base[d]))) return fail(QLIN_ERR_NULL, "qlin_block_quant: dst_base[%d] is NULL or unaligned", d);
+  }
+  p.ndst = a->ndst;
+  p.dst_row0 = a->dst_row0;
+  if (a->r_parts < 0 || a->r_parts > 8 || (a->r_parts > 1 && a->r_part_stride % 8 != 0))
+    return fail(QLIN_ERR_BAD_SHAPE, "qlin_block_quant: r_parts must be in [0, 8] with a part stride that is a multiple of 8 elements");
+  p.r_parts = a->r_parts;
+  p.r_part_stride = a->r_part_stride;
   if (!ok) return fail(QLIN_ERR_BAD_ALIGN, "qlin_block_quant: pointers must be 16-byte aligned and leading dimensions multiples of 16 bytes");
   p.scale_in = a->scale_in;
   p.ldx = a->ldx;

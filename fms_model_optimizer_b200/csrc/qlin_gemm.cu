@@ -80,6 +80,8 @@ struct GemmParams {
   int32_t trun_bits, max_acc_bits, trunc_then_acc, clamp_dl16;
   int32_t epilogue, rs_stride, cs_stride, prod_round, scale_round, mid_round, acc_round, out_dtype;
   int32_t num_m, num_n, max_ctas;
+  int32_t scatter_rows, scatter_row0;
+  uint8_t* scatter_d[8];
 };
 
 __device__ __forceinline__ float round_to(float y, int dt) {
@@ -156,6 +158,16 @@ __device__ __forceinline__ uint32_t pack16(const GemmParams& p, float lo, float 
          (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(hi))) << 16);
 }
 
+// Byte address of output row `row`, column 0 (`elt` bytes per element).  With row-block scatter the block of
+// scatter_rows rows that contains `row` lives in its own buffer (possibly another GPU's).
+__device__ __forceinline__ uint8_t* out_row(const GemmParams& p, int row, int elt) {
+  if (p.scatter_rows > 0) {
+    const int owner = row / p.scatter_rows;
+    return p.scatter_d[owner] + static_cast<int64_t>(row - owner * p.scatter_rows + p.scatter_row0) * p.ldd * elt;
+  }
+  return reinterpret_cast<uint8_t*>(p.d) + static_cast<int64_t>(row) * p.ldd * elt;
+}
+
 // Direct (uncoalesced, bounds-checked) store of NC consecutive columns of one row held by this
 // thread: the path for ragged right edges and for outputs that rule out 16-byte vectors.
 template <bool F8, int NC>
@@ -166,18 +178,19 @@ __device__ __forceinline__ void store_row_direct(const GemmParams& p, const uint
   if (ncol <= 0) return;
   const bool prod = p.epilogue == QLIN_EPI_SCALE_PROD;
   const bool has_bias = p.bias != nullptr;
-  const int64_t off = static_cast<int64_t>(row) * p.ldd + col0;
+  const int elt = (p.epilogue == QLIN_EPI_RAW || p.out_dtype == QLIN_DT_F32) ? 4 : 2;
+  uint8_t* base = out_row(p, row, elt) + static_cast<int64_t>(col0) * elt;
 #pragma unroll
   for (int j = 0; j < NC; ++j) {
     if (j < ncol) {
       if (p.epilogue == QLIN_EPI_RAW) {
-        reinterpret_cast<uint32_t*>(p.d)[off + j] = v[j];
+        reinterpret_cast<uint32_t*>(base)[j] = v[j];
       } else {
         const float y = dequant_one<F8>(p, v[j], rs, s_cs[s_off + j], s_bias[s_off + j], prod, has_bias);
         if (p.out_dtype == QLIN_DT_F32) {
-          reinterpret_cast<float*>(p.d)[off + j] = y;
+          reinterpret_cast<float*>(base)[j] = y;
         } else {
-          reinterpret_cast<uint16_t*>(p.d)[off + j] = static_cast<uint16_t>(pack16(p, y, 0.0f) & 0xFFFFu);
+          reinterpret_cast<uint16_t*>(base)[j] = static_cast<uint16_t>(pack16(p, y, 0.0f) & 0xFFFFu);
         }
       }
     }
@@ -247,7 +260,7 @@ __device__ __forceinline__ void emit64(const GemmParams& p, const uint32_t (&v)[
           dequant_one<F8>(p, v[2 * j + 1], rs, s_cs[s_off + 2 * j + 1], s_bias[s_off + 2 * j + 1], prod, has_bias);
       w[j] = pack16(p, y0, y1);
     }
-    uint8_t* g = reinterpret_cast<uint8_t*>(p.d) + (static_cast<int64_t>(row0) * p.ldd + col0) * 2;
+    uint8_t* g = out_row(p, row0, 2) + static_cast<int64_t>(col0) * 2;
     store_tile_coalesced(stage, w, g, p.ldd * 2, rows_valid, lane);
   } else {
     // 4-byte outputs: two staging passes of 32 columns
@@ -261,7 +274,7 @@ __device__ __forceinline__ void emit64(const GemmParams& p, const uint32_t (&v)[
                    ? v[k]
                    : __float_as_uint(dequant_one<F8>(p, v[k], rs, s_cs[s_off + k], s_bias[s_off + k], prod, has_bias));
       }
-      uint8_t* g = reinterpret_cast<uint8_t*>(p.d) + (static_cast<int64_t>(row0) * p.ldd + col0 + h * 32) * 4;
+      uint8_t* g = out_row(p, row0, 4) + static_cast<int64_t>(col0 + h * 32) * 4;
       store_tile_coalesced(stage, w, g, p.ldd * 4, rows_valid, lane);
     }
   }
@@ -286,7 +299,7 @@ __device__ __forceinline__ void emit32(const GemmParams& p, const uint32_t (&v)[
     w[j] = p.epilogue == QLIN_EPI_RAW
                ? v[j]
                : __float_as_uint(dequant_one<F8>(p, v[j], rs, s_cs[s_off + j], s_bias[s_off + j], prod, has_bias));
-  uint8_t* g = reinterpret_cast<uint8_t*>(p.d) + (static_cast<int64_t>(row0) * p.ldd + col0) * 4;
+  uint8_t* g = out_row(p, row0, 4) + static_cast<int64_t>(col0) * 4;
   store_tile_coalesced(stage, w, g, p.ldd * 4, p.M - row0, lane);
 }
 
@@ -505,7 +518,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
     uint8_t* stage = smem + C::OUT_OFFSET + warp * kStageOutBytes;
     const int elt = (p.out_dtype == QLIN_DT_F16 || p.out_dtype == QLIN_DT_BF16) ? 2 : 4;
-    const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.d) & 15u) == 0) && ((p.ldd * elt) % 16 == 0);
+    const bool vec_ok = (p.scatter_rows > 0 || (reinterpret_cast<uintptr_t>(p.d) & 15u) == 0) && ((p.ldd * elt) % 16 == 0);
     const bool clamp = !F8 && p.max_acc_bits < 32;
     const int32_t lo = clamp ? -(1 << (p.max_acc_bits - 1)) : 0;
     const int32_t hi = clamp ? (1 << (p.max_acc_bits - 1)) - 1 : 0;
@@ -683,7 +696,19 @@ using namespace qlin;
 
 extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   if (a == nullptr) return fail(QLIN_ERR_NULL, "qlin_gemm: args is NULL");
-  if (a->a == nullptr || a->b == nullptr || a->d == nullptr) return fail(QLIN_ERR_NULL, "qlin_gemm: a, b or d is NULL");
+  if (a->a == nullptr || a->b == nullptr || (a->d == nullptr && a->scatter_rows <= 0))
+    return fail(QLIN_ERR_NULL, "qlin_gemm: a, b or d is NULL");
+  if (a->scatter_rows < 0 || (a->scatter_rows > 0 && a->scatter_rows % 128 != 0))
+    return fail(QLIN_ERR_BAD_SHAPE, "qlin_gemm: scatter_rows must be a multiple of 128");
+  if (a->scatter_rows > 0) {
+    const int64_t owners = (static_cast<int64_t>(a->M) + a->scatter_rows - 1) / a->scatter_rows;
+    if (owners > 8) return fail(QLIN_ERR_BAD_SHAPE, "qlin_gemm: more than 8 scatter destinations");
+    for (int i = 0; i < owners; ++i) {
+      if (a->scatter_d[i] == nullptr) return fail(QLIN_ERR_NULL, "qlin_gemm: scatter_d[%d] is NULL", i);
+      if (!aligned16(a->scatter_d[i])) return fail(QLIN_ERR_BAD_ALIGN, "qlin_gemm: scatter_d[%d] is not 16-byte aligned", i);
+    }
+    if (a->c != nullptr) return fail(QLIN_ERR_UNSUPPORTED, "qlin_gemm: scatter with an accumulator input is not provided");
+  }
   if (a->M < 0 || a->N < 0 || a->K < 0) return fail(QLIN_ERR_BAD_SHAPE, "qlin_gemm: negative dimension");
   if (a->kind != QLIN_DT_I8 && a->kind != QLIN_DT_F8E4M3)
     return fail(QLIN_ERR_BAD_DTYPE, "qlin_gemm: kind must be QLIN_DT_I8 or QLIN_DT_F8E4M3");
@@ -746,6 +771,9 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   p.acc_round = a->acc_round;
   p.out_dtype = a->out_dtype;
   p.max_ctas = a->max_ctas;
+  p.scatter_rows = a->scatter_rows;
+  p.scatter_row0 = a->scatter_row0;
+  for (int i = 0; i < 8; ++i) p.scatter_d[i] = static_cast<uint8_t*>(a->scatter_d[i]);
   const int bn = chunked ? Cfg<true>::BN : Cfg<false>::BN;
   p.num_m = (a->M + kBM - 1) / kBM;
   p.num_n = (a->N + bn - 1) / bn;

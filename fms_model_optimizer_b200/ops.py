@@ -140,6 +140,7 @@ def gemm(
     scale_round: Optional[torch.dtype] = None,
     mid_round: Optional[torch.dtype] = None,
     acc_round: Optional[torch.dtype] = None,
+    scatter: Optional[Tuple[Sequence[int], int, int]] = None,
     out_dtype: Optional[torch.dtype] = None,
 ) -> torch.Tensor:
     """``D[M,N] = epilogue(C + sum_chunks f(A_c @ B_c^T))`` with A ``[M,K]`` and B ``[N,K]`` (both
@@ -158,10 +159,19 @@ def gemm(
         out_dtype = raw_dtype
     elif out_dtype is None:
         out_dtype = torch.float32
-    if out is None:
+    ldd = N
+    if scatter is not None:
+        # (base addresses, rows per destination, first row in each destination[, leading dimension]): the epilogue
+        # stores row block m // rows to its own buffer, possibly another GPU's; nothing is returned
+        if out is not None or c is not None:
+            raise RuntimeError("scatter excludes out and c")
+        ldd = int(scatter[3]) if len(scatter) > 3 else N
+    elif out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=dev)
     elif out.dtype != out_dtype or out.shape != (M, N) or out.stride(1) != 1:
         raise RuntimeError("out has the wrong dtype, shape or layout")
+    else:
+        ldd = out.stride(0)
     if M == 0 or N == 0:
         return out
     if K == 0:
@@ -183,7 +193,7 @@ def gemm(
     args = L.GemmArgs(
         a=_ptr(a), b=_ptr(b_nk), c=_ptr(c), d=_ptr(out),
         row_scale=_ptr(rs), col_scale=_ptr(cs), bias=_ptr(bs), status=_ptr(status_word(dev)),
-        lda=a.stride(0), ldb=b_nk.stride(0), ldc=(c.stride(0) if c is not None else 0), ldd=out.stride(0),
+        lda=a.stride(0), ldb=b_nk.stride(0), ldc=(c.stride(0) if c is not None else 0), ldd=ldd,
         M=M, N=N, K=K, kind=_DT[a.dtype],
         chunk_k=int(chunk_k), trun_bits=int(trun_bits), max_acc_bits=int(max_acc_bits),
         trunc_then_acc=int(bool(trunc_then_acc)), clamp_dl16=int(bool(clamp_dl16)), epilogue=int(epilogue),
@@ -192,6 +202,10 @@ def gemm(
         prod_round=_ROUND[prod_round], scale_round=_ROUND[scale_round], mid_round=_ROUND[mid_round], acc_round=_ROUND[acc_round],
         out_dtype=_DT[out_dtype], max_ctas=int(GEMM_MAX_CTAS),
     )  # fmt: skip
+    if scatter is not None:
+        bases = list(scatter[0]) + [None] * (8 - len(scatter[0]))
+        args.scatter_d = (C.c_void_p * 8)(*bases)
+        args.scatter_rows, args.scatter_row0 = int(scatter[1]), int(scatter[2])
     with torch.cuda.device(dev):
         rc = _timed("gemm", 2.0 * M * N * K, dev, lambda: L.load().qlin_gemm(C.byref(args), _stream(dev)))
         L.check(rc, "qlin_gemm")
@@ -515,6 +529,10 @@ def block_quant(
     mode: int = L.BLOCK_DYN,
     scale_in: Optional[torch.Tensor] = None,
     store_sum: bool = False,
+    sum_into: Optional[torch.Tensor] = None,
+    r_parts: int = 0,
+    r_part_stride: int = 0,
+    dst: Optional[Tuple[Sequence[int], Sequence[int], Sequence[int], int]] = None,
     want_h: bool = False,
     levels: int = 127,
     norm_eps: float = 1e-5,
@@ -530,9 +548,18 @@ def block_quant(
         raise RuntimeError("r must match x")
     rows, cols = x.shape
     nout = len(smooth_rcps)
-    codes = [None if mode == L.BLOCK_SCALE_ONLY else torch.empty((rows, cols), dtype=torch.int8, device=dev) for _ in range(nout)]
-    scales = [scale_in if mode == L.BLOCK_GIVEN_SCALE else torch.empty((rows,), dtype=torch.float32, device=dev) for _ in range(nout)]
-    x_out = torch.empty((rows, cols), dtype=torch.bfloat16, device=dev) if (store_sum and r is not None) else None
+    if dst is not None:
+        # (base address per destination, byte offset of each output's codes, of each output's scales, first row):
+        # every destination (this GPU's buffer or a peer's) receives the codes and scales of these rows
+        codes, scales = [None] * nout, [None] * nout
+    else:
+        codes = [None if mode == L.BLOCK_SCALE_ONLY else torch.empty((rows, cols), dtype=torch.int8, device=dev) for _ in range(nout)]
+        scales = [scale_in if mode == L.BLOCK_GIVEN_SCALE else torch.empty((rows,), dtype=torch.float32, device=dev) for _ in range(nout)]
+    x_out = None
+    if r is not None and sum_into is not None:
+        x_out = sum_into
+    elif r is not None and store_sum:
+        x_out = torch.empty((rows, cols), dtype=torch.bfloat16, device=dev)
     h_out = torch.empty((rows, cols), dtype=torch.bfloat16, device=dev) if want_h else None
     if rows == 0 or cols == 0:
         return codes, scales, x_out, h_out
@@ -540,14 +567,24 @@ def block_quant(
     i3 = C.c_int64 * 3
     pad = [None] * (3 - nout)
     args = L.BlockQuantArgs(
-        x=_ptr(x), r=_ptr(r), x_out=_ptr(x_out), h_out=_ptr(h_out), norm_w=_ptr(norm_w),
+        x=_ptr(x), r=_ptr(r), r_parts=int(r_parts), r_part_stride=int(r_part_stride), x_out=_ptr(x_out), h_out=_ptr(h_out),
+        norm_w=_ptr(norm_w),
         smooth_rcp=p3(*[_ptr(t) for t in list(smooth_rcps) + pad]), codes=p3(*[_ptr(t) for t in codes + pad]),
         scale_out=p3(*[(_ptr(t) if mode != L.BLOCK_GIVEN_SCALE else None) for t in scales + pad]), scale_in=_ptr(scale_in),
-        ldx=x.stride(0), ldr=(r.stride(0) if r is not None else 0), ldxo=cols, ldh=cols, ldq=i3(cols, cols, cols),
+        ldx=x.stride(0), ldr=(r.stride(0) if r is not None else 0), ldxo=(x_out.stride(0) if x_out is not None else cols),
+        ldh=cols, ldq=i3(cols, cols, cols),
         rows=rows, cols=cols, nout=nout, prologue=int(prologue), mode=int(mode), qmax_levels=int(levels),
         norm_eps=float(norm_eps), dyn_eps=float(dyn_eps),
     )  # fmt: skip
-    nbytes = rows * cols * (2 * (1 + (r is not None) + (x_out is not None) + (h_out is not None)) + (0 if mode == L.BLOCK_SCALE_ONLY else nout))
+    ndst = 1
+    if dst is not None:
+        ndst = len(dst[0])
+        args.dst_base = (C.c_void_p * 8)(*(list(dst[0]) + [None] * (8 - ndst)))
+        args.codes_off = i3(*(list(dst[1]) + [0] * (3 - nout)))
+        args.scale_off = i3(*(list(dst[2]) + [0] * (3 - nout)))
+        args.ndst, args.dst_row0 = ndst, int(dst[3])
+    nbytes = rows * cols * (2 * (1 + (max(1, r_parts) if r is not None else 0) + (x_out is not None) + (h_out is not None))
+                            + (0 if mode == L.BLOCK_SCALE_ONLY else nout * ndst))
     with torch.cuda.device(dev):
         rc = _timed("block_quant", float(nbytes), dev, lambda: L.load().qlin_block_quant(C.byref(args), _stream(dev)))
         L.check(rc, "qlin_block_quant")

@@ -124,6 +124,13 @@ typedef struct qlin_gemm_args {
   int32_t mid_round;        /* qlin_dtype */
   int32_t acc_round;        /* qlin_dtype */
   int32_t out_dtype;        /* qlin_dtype */
+  /* Row-block scatter of the output (the reduce-scatter half of a row-parallel Linear, done by the epilogue's own
+     stores): when scatter_rows > 0, output row m goes to scatter_d[m / scatter_rows] at row
+     scatter_row0 + m % scatter_rows (leading dimension ldd, d unused).  The bases may be buffers of other GPUs
+     mapped into this process; scatter_rows must be a multiple of 128.  No counterpart in the reference. */
+  void* scatter_d[8];
+  int32_t scatter_rows;
+  int32_t scatter_row0;
   int32_t max_ctas;         /* 0: one persistent CTA per SM; > 0: at most this many CTAs (each needs a whole SM),
                                leaving SMs free for a kernel that runs concurrently on another stream, e.g. a
                                collective.  Results do not depend on it. */
@@ -379,6 +386,10 @@ typedef enum qlin_block_mode { QLIN_BLOCK_DYN = 0, QLIN_BLOCK_GIVEN_SCALE = 1, Q
 typedef struct qlin_block_quant_args {
   const void* x;        /* [rows, cols] bf16 */
   const void* r;        /* NORM: optional addend; SILU_MUL: the second factor */
+  int32_t r_parts;      /* NORM: number of addends (0 or 1: just r); part i starts r_part_stride elements after part i-1.
+                           The parts are summed in fp32 in index order and rounded to bf16 once, then added to x:
+                           the reduction of a row-parallel Linear whose shards wrote their partial outputs side by side */
+  int64_t r_part_stride;
   void* x_out;          /* NORM with r: x + r (may alias x) */
   void* h_out;          /* optional: the row the Linears see */
   const void* norm_w;   /* NORM: [cols] bf16 */
@@ -386,6 +397,15 @@ typedef struct qlin_block_quant_args {
   void* codes[3];       /* [rows, cols] int8 */
   float* scale_out[3];  /* [rows] */
   const float* scale_in;/* GIVEN_SCALE: [rows] */
+  /* Replicated outputs (the all-gather half of sequence parallelism, done by the kernel's own stores): when ndst > 0
+     codes[o] and scale_out[o] are ignored; for every d < ndst the codes of output o go to
+     (int8*)dst_base[d] + codes_off[o] at row dst_row0 + row (leading dimension ldq[o]) and the scales to
+     (float*)((char*)dst_base[d] + scale_off[o]) + dst_row0 + row.  Offsets in bytes; bases may be other GPUs' buffers. */
+  void* dst_base[8];
+  int64_t codes_off[3];
+  int64_t scale_off[3];
+  int32_t ndst;
+  int32_t dst_row0;
   int64_t ldx, ldr, ldxo, ldh, ldq[3];
   int32_t rows, cols, nout;
   int32_t prologue;     /* qlin_block_prologue */
@@ -409,6 +429,33 @@ typedef struct qlin_rope_args {
 } qlin_rope_args;
 
 int qlin_rope(const qlin_rope_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Peer-memory plumbing of the tensor-parallel path (one process per GPU).  No counterpart in the
+ * reference, which leaves sharding to the serving stack around it.
+ *   qlin_ipc_export   handle_out receives 64 bytes naming the allocation dev_ptr lies in, offset_out the
+ *                     pointer's offset in that allocation; send both to the peer processes.
+ *   qlin_ipc_open     maps a peer's allocation into this process (peer access is enabled on first use);
+ *                     base_out is what qlin_ipc_close takes, ptr_out = base + offset.
+ *   qlin_peer_barrier launches a one-warp kernel: rank stores the next epoch into slot `rank` of every
+ *                     peer's flag array and waits (at most 2 s, then QLIN_ERR_TIMEOUT in *status) until all
+ *                     `world` slots of its own array carry it.  Stores made to peer memory by earlier work of
+ *                     the stream are visible to the peers' work after their barrier.  `epoch` is a device
+ *                     counter owned by this barrier object; flag arrays and epoch start zeroed.
+ * ---------------------------------------------------------------------------------------------- */
+int qlin_ipc_export(const void* dev_ptr, void* handle_out, int64_t* offset_out);
+int qlin_ipc_open(const void* handle, int64_t offset, void** base_out, void** ptr_out);
+int qlin_ipc_close(void* base);
+
+typedef struct qlin_peer_barrier_args {
+  uint32_t* local_flags;
+  uint32_t* peer_flags[8];
+  uint32_t* epoch;
+  int32_t* status;
+  int32_t rank, world;
+} qlin_peer_barrier_args;
+
+int qlin_peer_barrier(const qlin_peer_barrier_args* args, void* stream);
 
 #ifdef __cplusplus
 }

@@ -32,7 +32,9 @@ def test_library_exports_every_declared_symbol():
 def test_struct_layouts_match_header_field_order():
     text = HEADER.read_text()
     for struct, cls in (("qlin_gemm_args", L.GemmArgs), ("qlin_quant_args", L.QuantArgs),
-                        ("qlin_pact2_args", L.Pact2Args), ("qlin_wfq_args", L.WfqArgs)):
+                        ("qlin_pact2_args", L.Pact2Args), ("qlin_wfq_args", L.WfqArgs),
+                        ("qlin_tensor_fq_args", L.TensorFqArgs), ("qlin_block_quant_args", L.BlockQuantArgs),
+                        ("qlin_rope_args", L.RopeArgs), ("qlin_peer_barrier_args", L.PeerBarrierArgs)):
         body = re.search(r"typedef struct " + struct + r" \{(.*?)\} " + struct, text, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []
@@ -46,6 +48,7 @@ def test_struct_layouts_match_header_field_order():
             first = head.replace("*", " ").split()[-1]
             fields.append(first)
             fields += [r.strip().lstrip("*") for r in rest.split(",") if r.strip()]
+        fields = [re.sub(r"\[\d+\]$", "", f) for f in fields]  # arrays: "ldq[3]" is the ctypes field "ldq"
         assert fields == [f[0] for f in cls._fields_], struct
 
 

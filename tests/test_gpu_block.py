@@ -95,3 +95,61 @@ def test_rope_matches_fp32_formula(cuda_dev):
     # one bf16 rounding of a sum whose terms may cancel: bound the error by the size of the terms
     mag = torch.cat([(x1 * c).abs() + (x2 * s).abs(), (x2 * c).abs() + (x1 * s).abs()], -1).view(B * S, H, D)
     assert ((got.float() - want).abs() <= mag * 2.0**-8 + 1e-30).all()
+
+
+def test_gemm_row_block_scatter_to_local_buffers(cuda_dev):
+    """The scatter epilogue with all destinations on this GPU: row block i of the output lands in buffer i at the
+    requested row offset, bit-identical to the plain launch."""
+    g = torch.Generator().manual_seed(11)
+    M, K, N, rows = 512, 256, 384, 128
+    a = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8).to(cuda_dev)
+    b = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8).to(cuda_dev)
+    rs = (torch.rand(M, generator=g) * 0.01).to(cuda_dev)
+    cs = (torch.rand(N, generator=g) * 0.01).to(cuda_dev)
+    kw = dict(epilogue=L.EPI_SCALE_PROD, row_scale=rs, col_scale=cs, scale_round=torch.float16, acc_round=torch.float16,
+              out_dtype=torch.bfloat16)
+    want = ops.gemm(a, b, **kw)
+    bufs = [torch.zeros(3 * rows, N, dtype=torch.bfloat16, device=cuda_dev) for _ in range(M // rows)]
+    ops.gemm(a, b, scatter=([t.data_ptr() for t in bufs], rows, rows), **kw)
+    for i, t in enumerate(bufs):
+        assert torch.equal(t[rows : 2 * rows], want[i * rows : (i + 1) * rows])
+        assert not t[:rows].any() and not t[2 * rows :].any()
+    raw = ops.gemm(a, b)
+    bufs = [torch.zeros(rows, N, dtype=torch.int32, device=cuda_dev) for _ in range(M // rows)]
+    ops.gemm(a, b, scatter=([t.data_ptr() for t in bufs], rows, 0))
+    assert torch.equal(torch.cat(bufs), raw)
+    assert torch.equal(raw.cpu(), (a.cpu().double() @ b.cpu().double().t()).to(torch.int32))
+
+
+def test_block_quant_partial_sums_and_replicated_outputs(cuda_dev):
+    T, K, parts, ndst = 24, 1024, 4, 3
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(T, K, generator=g).bfloat16()
+    part = torch.randn(parts, T, K, generator=g).bfloat16()
+    w = (1 + 0.1 * torch.randn(K, generator=g)).bfloat16()
+    sms = [_smooth(K, 8), _smooth(K, 9)]
+    rcps = [ops.smooth_reciprocal(s.float().to(cuda_dev)) for s in sms]
+    part_d = part.to(cuda_dev)
+    # destinations: byte buffers holding [codes0 | codes1 | scales0 | scales1] for 2 * T rows; these rows go to row T..2T
+    R = 2 * T
+    offs_c = [0, R * K]
+    offs_s = [2 * R * K, 2 * R * K + 4 * R]
+    dsts = [torch.zeros(2 * R * K + 8 * R, dtype=torch.uint8, device=cuda_dev) for _ in range(ndst)]
+    xin = x.to(cuda_dev).clone()
+    _, _, xo, h = ops.block_quant(xin, prologue=L.BLOCK_NORM, r=part_d[0], r_parts=parts, r_part_stride=T * K, norm_w=w.to(cuda_dev),
+                                  smooth_rcps=rcps, sum_into=xin, want_h=True, dst=([d.data_ptr() for d in dsts], offs_c, offs_s, T))
+    red = part.float().sum(0)  # four addends: the fp32 sum is exact enough to be order independent here? no -- emulate the order
+    acc = part[0].float()
+    for s in range(1, parts):
+        acc = acc + part[s].float()
+    want_x = x + acc.bfloat16()
+    assert xo is xin and torch.equal(xin.cpu(), want_x)
+    assert _ulp_close(h.cpu(), F.rms_norm(want_x.float(), (K,), w.float(), 1e-5).bfloat16())
+    del red
+    for d in dsts:
+        for o, sm in enumerate(sms):
+            want_c, want_s = OQ.qa_dynamic_max_qfunc(h.cpu() / sm)
+            codes = d[offs_c[o] : offs_c[o] + R * K].view(torch.int8).view(R, K)
+            scales = d[offs_s[o] : offs_s[o] + 4 * R].view(torch.float32)
+            assert torch.equal(codes[T:].cpu(), want_c) and not codes[:T].any()
+            assert torch.equal(scales[T:].cpu(), want_s.float().reshape(-1)) and not scales[:T].any()
