@@ -140,6 +140,10 @@ class Decoder:
         from fms_model_optimizer_b200 import tp
 
         self.n_micro = n_micro
+        self.rank = rank
+        self.sp = None
+        self.exchange = "stores"
+        self.chain = False
         self.streams = [torch.cuda.Stream(device=dev) for _ in range(n_micro)] if n_micro > 1 else []
 
         self.cfg = cfg
@@ -211,32 +215,165 @@ class Decoder:
         logits = last @ self.lm_head.t()
         return logits.argmax(-1)
 
+    def enable_sequence_parallel(self, tokens_per_group):
+        """Buffers for the sharded forward that keeps the residual stream split by tokens: per group of sequences,
+        a receive buffer for the row-parallel Linears' partial outputs ([world][tokens / world, hidden] bf16), the
+        int8 codes and scales of up to three Linear inputs for all tokens, and a barrier."""
+        from fms_model_optimizer_b200.peer import PeerArena, PeerBarrier
+
+        H, W, T = self.cfg["hidden"], self.world, tokens_per_group
+        assert T % W == 0 and (T // W) % 128 == 0, "tokens per rank must be a multiple of 128"
+        per_group = T * H * 2 + 3 * (T * H + 4 * T) + 4096
+        self.arena = PeerArena(max(1, self.n_micro) * per_group + 4096, self.dev)
+        self.sp = []
+        for _ in range(max(1, self.n_micro)):
+            g = {"bar": PeerBarrier(self.arena), "T": T, "Ts": T // W}
+            g["part_off"], part = self.arena.alloc(T * H * 2)
+            g["part"] = part.view(torch.bfloat16).view(W, T // W, H)
+            g["codes_off"], g["scale_off"], g["codes"], g["scales"] = [], [], [], []
+            for _ in range(3):
+                off, c = self.arena.alloc(T * H)
+                g["codes_off"].append(off)
+                g["codes"].append(c.view(torch.int8).view(T, H))
+            for _ in range(3):
+                off, sc = self.arena.alloc(4 * T)
+                g["scale_off"].append(off)
+                g["scales"].append(sc.view(torch.float32)[:T])
+            g["part_bases"] = [self.arena.addr(r, g["part_off"]) for r in range(W)]
+            g["bases"] = [self.arena.addr(r, 0) for r in range(W)]
+            if self.exchange == "copies":
+                # local staging for the copy engines: this rank's codes and scales of its own tokens, and the
+                # partial output of a row-parallel GEMM for all tokens
+                Ts = T // W
+                g["stage"] = torch.empty(3 * Ts * H + 12 * Ts, dtype=torch.uint8, device=self.dev)
+                g["stage_codes_off"] = [o * Ts * H for o in range(3)]
+                g["stage_scale_off"] = [3 * Ts * H + o * 4 * Ts for o in range(3)]
+                g["po"] = torch.empty(T, H, dtype=torch.bfloat16, device=self.dev)
+                assert all(g["codes_off"][o] == g["codes_off"][0] + o * T * H for o in range(3))
+                assert all(g["scale_off"][o] == g["scale_off"][0] + o * 4 * T for o in range(3))
+            self.sp.append(g)
+
+    def _forward_steps_sp(self, ids, g):
+        """Sharded forward with the residual stream split by tokens.  Each rank owns tokens [rank * Ts, (rank + 1) * Ts)
+        of the group: it sums the partial outputs the row-parallel GEMMs of all ranks stored into its receive buffer,
+        adds them to its slice of the stream, normalises, quantises for the following column-parallel Linears and
+        stores those codes into every rank's code buffer.  No collective carries activations; two barriers per
+        half layer order the remote stores."""
+        from fms_model_optimizer_b200 import _lib as L
+        from fms_model_optimizer_b200 import ops
+
+        cfg, W, rank = self.cfg, self.world, self.rank
+        B, S = ids.shape
+        hd, bf = cfg["head_dim"], torch.bfloat16
+        T, Ts, bar = g["T"], g["Ts"], g["bar"]
+        x = F.embedding(ids.reshape(-1)[rank * Ts : (rank + 1) * Ts], self.embed)
+        parts = None
+
+        H = x.shape[1]
+        copies = self.exchange == "copies"
+        arena = self.arena
+
+        def shared_quant(norm_w, lins):
+            yield "compute"
+            n = len(lins)
+            if copies:  # quantise into local staging, then the copy engines place my rows in every rank's buffers
+                dst = ([g["stage"].data_ptr()], g["stage_codes_off"][:n], g["stage_scale_off"][:n], 0)
+            else:  # the kernel stores to every rank's buffers itself
+                dst = (g["bases"], g["codes_off"][:n], g["scale_off"][:n], rank * Ts)
+            ops.block_quant(x, prologue=L.BLOCK_NORM, r=(parts[0] if parts is not None else None), r_parts=(W if parts is not None else 0),
+                            r_part_stride=Ts * H, norm_w=norm_w, smooth_rcps=[l.smooth_rcp for l in lins], sum_into=x, dst=dst)  # fmt: skip
+            if copies:
+                yield "comm"
+                src = g["stage"].data_ptr()
+                for p in range(W):
+                    arena.copy2d(arena.addr(p, g["codes_off"][0]) + rank * Ts * H, T * H, src, Ts * H, Ts * H, n)
+                    arena.copy2d(arena.addr(p, g["scale_off"][0]) + rank * Ts * 4, T * 4, src + 3 * Ts * H, Ts * 4, Ts * 4, n)
+            bar.wait()  # every rank's codes have landed here
+
+        def row_parallel(lin_, quantised):
+            if not copies:
+                yield "compute"
+            if copies:
+                lin_.gemm_fn(quantised[0], lin_.weight, quantised[1], lin_.w_scale, lin_.bias, bf,
+                             torch.promote_types(bf, lin_.w_scale_dtype), out=g["po"])
+                yield "comm"
+                for p in range(W):
+                    arena.copy2d(arena.addr(p, g["part_off"]) + rank * Ts * H * 2, 0, g["po"].data_ptr() + p * Ts * H * 2, 0, Ts * H * 2, 1)
+            else:
+                lin_.scatter(quantised, g["part_bases"], Ts, rank * Ts, bf)
+            bar.wait()  # every rank's partial rows for my tokens have landed
+
+        for lin in self.layers:
+            yield from shared_quant(lin["ln1"], [lin["q"], lin["k"], lin["v"]])
+            yield "compute"
+            q = ops.rope_(lin["q"](None, (g["codes"][0], g["scales"][0]), bf).view(T, self.nq, hd), self.cos, self.sin, S)
+            k = ops.rope_(lin["k"](None, (g["codes"][1], g["scales"][1]), bf).view(T, self.nkv, hd), self.cos, self.sin, S)
+            v = lin["v"](None, (g["codes"][2], g["scales"][2]), bf)
+            a = F.scaled_dot_product_attention(q.view(B, S, self.nq, hd).transpose(1, 2), k.view(B, S, self.nkv, hd).transpose(1, 2),
+                                               v.view(B, S, self.nkv, hd).transpose(1, 2), is_causal=True, enable_gqa=True)  # fmt: skip
+            a = a.transpose(1, 2).reshape(T, self.nq * hd)
+            yield from row_parallel(lin["o"], lin["o"].quantise_fused(a))
+            parts = g["part"]
+            yield from shared_quant(lin["ln2"], [lin["gate"], lin["up"]])
+            yield "compute"
+            gt = lin["gate"](None, (g["codes"][0], g["scales"][0]), bf)
+            u = lin["up"](None, (g["codes"][1], g["scales"][1]), bf)
+            yield from row_parallel(lin["down"], lin["down"].quantise_fused(gt, L.BLOCK_SILU_MUL, u))
+        yield "compute"
+        # final norm of my token slice; the last token of every sequence goes to all ranks through one small all-reduce
+        _, _, _, h = ops.block_quant(x, prologue=L.BLOCK_NORM, r=parts[0], r_parts=W, r_part_stride=Ts * x.shape[1], norm_w=self.norm,
+                                     smooth_rcps=[], sum_into=x, want_h=True)  # fmt: skip
+        last = torch.zeros(B, h.shape[1], dtype=bf, device=h.device)
+        for b in range(B):
+            idx = b * S + S - 1
+            if idx // Ts == rank:
+                last[b] = h[idx % Ts]
+        dist.all_reduce(last)
+        bar.wait()  # the receive buffers are free for the next forward pass
+        logits = last @ self.lm_head.t()
+        return logits.argmax(-1)
+
     @torch.no_grad()
     def forward(self, ids):
         nm = self.n_micro
+        if self.sp is not None:
+            return self._drive([self._forward_steps_sp(part, self.sp[i]) for i, part in enumerate(ids.chunk(max(1, nm), 0))])
+        return self._drive([self._forward_steps(part) for part in ids.chunk(max(1, nm), 0)])
+
+    def _drive(self, gens):
+        """Advances the groups round-robin, one segment at a time.  A generator announces the kind of its next segment
+        ("compute": kernels that fill the SMs; "comm": copy-engine transfers and the barrier that waits for the peers;
+        None: unclassified) and issues it when resumed.  Compute segments of all groups are chained through events, so
+        they run one after the other while the transfers of the other groups proceed beside them (``self.chain``;
+        without it the groups' streams are left to the hardware scheduler)."""
+        nm = len(gens)
         if nm <= 1:
-            gen = self._forward_steps(ids)
             try:
                 while True:
-                    next(gen)
+                    next(gens[0])
             except StopIteration as stop:
                 return stop.value
-        # groups of sequences on their own streams, advanced round-robin: while the all-reduce of one group is
-        # in flight (its stream waits for it), the other groups' kernels keep the SMs busy
         main = torch.cuda.current_stream()
-        gens, results = [], [None] * nm
-        for i, part in enumerate(ids.chunk(nm, 0)):
+        results, pending, token = [None] * nm, [None] * nm, None
+        for i in range(nm):
             self.streams[i].wait_stream(main)
-            gens.append(self._forward_steps(part))
         live = list(range(nm))
         while live:
             for i in list(live):
-                with torch.cuda.stream(self.streams[i]):
+                st = self.streams[i]
+                with torch.cuda.stream(st):
+                    if self.chain and pending[i] == "compute" and token is not None and token[0] != i:
+                        st.wait_event(token[1])
+                    issued = pending[i]
                     try:
-                        next(gens[i])
+                        pending[i] = next(gens[i])
                     except StopIteration as stop:
                         results[i] = stop.value
                         live.remove(i)
+                    if issued == "compute":
+                        ev = torch.cuda.Event()
+                        ev.record(st)
+                        token = (i, ev)
         for i in range(nm):
             main.wait_stream(self.streams[i])
             results[i].record_stream(main)
@@ -308,10 +445,14 @@ def run_c5(args, rank, world, dev):
     from fms_model_optimizer_b200 import ops
 
     cfg = dict(LLAMA)
-    n_micro = args.micro if args.micro > 0 else (2 if world > 1 else 1)
-    if n_micro > 1 and world > 1:
+    n_micro = args.micro if args.micro > 0 else (2 if world > 2 else 1)
+    if n_micro > 1 and world > 1 and args.allreduce:
         ops.GEMM_MAX_CTAS = args.gemm_ctas
     model = Decoder(cfg, dev, world, rank, layers=args.layers, n_micro=n_micro)
+    if world > 1 and not args.allreduce:
+        model.exchange = args.exchange
+        model.chain = args.chain
+        model.enable_sequence_parallel(cfg["batch"] * cfg["seq"] // n_micro)
     nl = len(model.layers)
     B, S = cfg["batch"], cfg["seq"]
     tokens = B * S
@@ -379,6 +520,15 @@ def run_c5(args, rank, world, dev):
     quant_ms = sum(a.elapsed_time(b) for (name, a, b, work) in prof if name in ("act_quant", "block_quant"))
     quant_bytes = sum(work for (name, a, b, work) in prof if name in ("act_quant", "block_quant"))
     achieved = gemm_ops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
+    if args.breakdown:
+        groups = {}
+        for name, a, b, work in prof:
+            t = groups.setdefault((name, work), [0, 0.0])
+            t[0] += 1
+            t[1] += a.elapsed_time(b)
+        for (name, work), (n, t) in sorted(groups.items(), key=lambda kv: -kv[1][1]):
+            print(f"# {name:12s} work {work:.3e} launches/step {n / args.steps:6.1f} avg {1e3 * t / n:8.1f} us  "
+                  f"total/step {t / args.steps:7.2f} ms", file=sys.stderr, flush=True)
     peak = 2.0 * pk["bf16_sustained"]
     line = {
         "metric": "w8a8_llama3_8b_prefill_tokens_per_s", "value": tokens * args.steps / (ms * 1e-3), "unit": "tokens/s",
@@ -387,6 +537,8 @@ def run_c5(args, rank, world, dev):
         "config": {
             "workload": "c5: Llama-3-8B-shaped decoder, all decoder Linears W8A8 SmoothQuant INT8, prefill 8x2048",
             "layers": nl, "global_batch": B, "seq_len": S, "parallelism": f"tp{world}", "sequence_groups_in_flight": n_micro,
+            "shard_exchange": ("none" if world == 1 else "nccl all-reduce" if args.allreduce else
+                               f"peer {args.exchange} over NVLink, residual stream split by tokens, flag barriers"),
             "l2": "inputs larger than L2 (activations 134 MB per Linear, weights 7 GB)",
             "linear_tops": decoder_linear_ops(cfg, tokens, nl) * args.steps / (ms * 1e-3) / 1e12,
         },
@@ -490,7 +642,15 @@ def main():
     ap.add_argument("--workload", default="c5", choices=["c5", "c1", "c2", "c3", "c5lin"])
     ap.add_argument("--layers", type=int, default=None, help="development only: fewer decoder layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--micro", type=int, default=0, help="groups of sequences pipelined on separate streams (0: 2 when sharded, else 1)")
+    ap.add_argument("--chain", action="store_true", help="sharded runs with several groups: run the groups' compute segments strictly "
+                    "one after the other (event chain) so that one group's transfers overlap the other's kernels")
+    ap.add_argument("--exchange", default="stores", choices=["stores", "copies"],
+                    help="sharded runs: how partial outputs and codes reach the other GPUs: stores from the GEMM epilogue / the "
+                    "quantiser, or copy-engine transfers from local staging")
+    ap.add_argument("--breakdown", action="store_true", help="development: per-kernel-shape times of the timed region on stderr")
+    ap.add_argument("--allreduce", action="store_true", help="sharded runs: NCCL all-reduce of the row-parallel outputs instead of "
+                    "remote stores from the GEMM epilogue with the residual stream split by tokens")
+    ap.add_argument("--micro", type=int, default=0, help="groups of sequences pipelined on separate streams (0: 2 on more than two GPUs, else 1)")
     ap.add_argument("--gemm-ctas", type=int, default=132, help="CTAs per GEMM while a collective may run beside it (sharded runs)")
     ap.add_argument("--nccl-ctas", type=int, default=16, help="upper bound on the CTAs of a collective (sharded runs)")
     args = ap.parse_args()

@@ -55,6 +55,7 @@ EXPORTED_SYMBOLS = (
     "qlin_ipc_export",
     "qlin_ipc_open",
     "qlin_ipc_close",
+    "qlin_peer_copy2d",
     "qlin_peer_barrier",
 )
 
@@ -285,6 +286,8 @@ def load() -> C.CDLL:
     lib.qlin_ipc_export.restype = C.c_int
     lib.qlin_ipc_open.argtypes = [C.c_void_p, C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]
     lib.qlin_ipc_open.restype = C.c_int
+    lib.qlin_peer_copy2d.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]
+    lib.qlin_peer_copy2d.restype = C.c_int
     lib.qlin_ipc_close.argtypes = [C.c_void_p]
     lib.qlin_ipc_close.restype = C.c_int
     lib.qlin_tensor_fq_workspace_bytes.argtypes = [C.c_int64]

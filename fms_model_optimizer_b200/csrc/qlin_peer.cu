@@ -6,6 +6,9 @@
 //       An allocation made by this process (any pointer inside a cudaMalloc block) becomes a 64-byte
 //       handle plus the pointer's offset in its block; another process on the same node maps it and
 //       gets an address its own kernels can store to (over NVLink when the GPUs are peers).
+//   qlin_peer_copy2d
+//       A (pitched) device-to-device copy queued on a stream; with a mapped peer address on one side the
+//       copy engines move the bytes over NVLink while the SMs run other kernels.
 //   qlin_peer_barrier
 //       Every rank stores the next epoch number into its slot of every peer's flag array
 //       (st.release.sys) and waits until all of its own slots show that epoch (ld.acquire.sys).
@@ -126,6 +129,22 @@ extern "C" int qlin_ipc_close(void* base) {
   if (e != cudaSuccess) {
     cudaGetLastError();
     return fail(QLIN_ERR_DEVICE, "qlin_ipc_close: %s", cudaGetErrorString(e));
+  }
+  return QLIN_OK;
+}
+
+extern "C" int qlin_peer_copy2d(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width, int64_t height,
+                                void* stream) {
+  if (dst == nullptr || src == nullptr) return fail(QLIN_ERR_NULL, "qlin_peer_copy2d: NULL pointer");
+  if (width < 0 || height < 0 || (height > 1 && (dpitch < width || spitch < width))) return fail(QLIN_ERR_BAD_SHAPE, "qlin_peer_copy2d: bad extent or pitch");
+  if (width == 0 || height == 0) return QLIN_OK;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = height == 1 ? cudaMemcpyAsync(dst, src, static_cast<size_t>(width), cudaMemcpyDeviceToDevice, s)
+                              : cudaMemcpy2DAsync(dst, static_cast<size_t>(dpitch), src, static_cast<size_t>(spitch),
+                                                  static_cast<size_t>(width), static_cast<size_t>(height), cudaMemcpyDeviceToDevice, s);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(QLIN_ERR_LAUNCH, "qlin_peer_copy2d: %s", cudaGetErrorString(e));
   }
   return QLIN_OK;
 }

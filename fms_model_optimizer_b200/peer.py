@@ -67,6 +67,13 @@ class PeerArena:
     def addr(self, rank: int, offset: int) -> int:
         return self.base[rank] + offset
 
+    def copy2d(self, dst_addr: int, dpitch: int, src_addr: int, spitch: int, width: int, height: int = 1) -> None:
+        """Queues a copy-engine transfer on the current stream (``qlin_peer_copy2d``); addresses are raw device
+        addresses, typically ``self.addr(peer, offset)`` on one side."""
+        with torch.cuda.device(self.dev):
+            L.check(L.load().qlin_peer_copy2d(C.c_void_p(dst_addr), dpitch, C.c_void_p(src_addr), spitch, width, height,
+                                              ops._stream(self.dev)), "qlin_peer_copy2d")  # fmt: skip
+
     def close(self):
         lib = L.load()
         torch.cuda.synchronize(self.dev)

@@ -104,14 +104,24 @@ class W8A8Linear:
         (codes,), (scale,), _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp)
         return codes, scale
 
-    def __call__(self, x2: Optional[torch.Tensor], quantised=None, act_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def scatter(self, quantised, bases, rows_per_rank: int, row0: int, act_dtype: torch.dtype) -> None:
+        """Row-parallel shard without a collective: the GEMM epilogue stores the partial output rows of token block
+        ``i`` into ``bases[i]`` (rank i's receive buffer, mapped through ``peer.PeerArena``) at row ``row0`` onwards.
+        The owner of a token block later sums the ``world`` partials (``ops.block_quant`` with ``r_parts``)."""
+        codes, scale = quantised
+        prod_dtype = torch.promote_types(act_dtype, self.w_scale_dtype)
+        self.gemm_fn(codes, self.weight, scale, self.w_scale, self.bias, act_dtype, prod_dtype, scatter=(bases, rows_per_rank, row0))
+
+    def __call__(self, x2: Optional[torch.Tensor], quantised=None, act_dtype: Optional[torch.dtype] = None,
+                 reduce: bool = True) -> torch.Tensor:
         """``quantised=(codes, scale)`` skips the quantiser (a fused kernel upstream produced them for the
-        activation dtype ``act_dtype``; for a row-parallel shard the scale must already be the maximum over ranks)."""
+        activation dtype ``act_dtype``; for a row-parallel shard the scale must already be the maximum over ranks).
+        ``reduce=False`` returns a row-parallel shard's partial output (the caller exchanges it)."""
         codes, scale = quantised if quantised is not None else self.quantise(x2)
         act_dtype = act_dtype if x2 is None else x2.dtype
         prod_dtype = torch.promote_types(act_dtype, self.w_scale_dtype)
         out = self.gemm_fn(codes, self.weight, scale, self.w_scale, self.bias, act_dtype, prod_dtype)
-        if self.mode == "row" and self.world > 1:
+        if reduce and self.mode == "row" and self.world > 1:
             dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
         return out
 
@@ -129,8 +139,8 @@ def _cuda_quant(x2, smooth, given_scale, smooth_rcp=None, smooth_is_bf16=False):
     return codes, scale
 
 
-def _cuda_gemm(codes, weight, scale, w_scale, bias, out_dtype, prod_dtype):
+def _cuda_gemm(codes, weight, scale, w_scale, bias, out_dtype, prod_dtype, scatter=None, out=None):
     # (acc.float() * (input_scale * w_scale).to(fp16) + bias).to(fp16).to(out_dtype), linear.py:1185-1188, :1338
     return ops.gemm(codes, weight, epilogue=L.EPI_SCALE_PROD, row_scale=scale, col_scale=w_scale, bias=bias,
                     prod_round=(None if prod_dtype == torch.float32 else prod_dtype), scale_round=torch.float16,
-                    acc_round=torch.float16, out_dtype=out_dtype)  # fmt: skip
+                    acc_round=torch.float16, out_dtype=out_dtype, scatter=scatter, out=out)  # fmt: skip

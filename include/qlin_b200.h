@@ -446,6 +446,9 @@ int qlin_rope(const qlin_rope_args* args, void* stream);
 int qlin_ipc_export(const void* dev_ptr, void* handle_out, int64_t* offset_out);
 int qlin_ipc_open(const void* handle, int64_t offset, void** base_out, void** ptr_out);
 int qlin_ipc_close(void* base);
+/* Queues a device-to-device copy of `height` rows of `width` bytes (pitches in bytes) on `stream`; either side may be
+ * a mapped peer address.  The copy engines carry it, so it overlaps kernels of other streams without taking SMs. */
+int qlin_peer_copy2d(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width, int64_t height, void* stream);
 
 typedef struct qlin_peer_barrier_args {
   uint32_t* local_flags;
