@@ -17,6 +17,8 @@
 //
 // All mbarrier waits are bounded; a wait that runs out raises an abort flag, the CTA drains its
 // copies and MMAs, frees TMEM, writes QLIN_ERR_TIMEOUT to the status word and returns.
+#include <cstdlib>
+
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -631,6 +633,263 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// CTA-pair variant of the unchunked kernel (cta_group::2).  A cluster of two CTAs computes a
+// 256 x 256 tile: CTA r of the pair loads rows [128 r, 128 r + 128) of the A tile and of the B tile
+// into its own shared memory (32 KB per stage instead of 48 KB for the same MMA work per SM, so six
+// stages fit and the L2 -> SM traffic per operation drops by a third), the even CTA issues the MMAs
+// for both, and each CTA drains its own 128 accumulator rows.  Barriers:
+//   full[s]   leader's copy: 1 arrival (the leader's expect_tx) + the bytes of both CTAs' loads
+//   empty[s]  every CTA's own copy, arrived on by the leader's commit (two-CTA mask)
+//   tfull[b]  every CTA's own copy, arrived on by the leader's commit (two-CTA mask)
+//   tempty[b] leader's copy: one arrival per epilogue warp of both CTAs
+// ------------------------------------------------------------------------------------------------
+struct PairCfg {
+  static constexpr int BN = 256;
+  static constexpr int NBUF = 2;
+  static constexpr int STAGES = 6;
+  static constexpr int EPI_WARPS = 8;
+  static constexpr int PRODUCER_WARP = EPI_WARPS;
+  static constexpr int MMA_WARP = EPI_WARPS + 1;
+  static constexpr int THREADS = (EPI_WARPS + 2) * 32;
+  static constexpr int A_BYTES = kBM * kBK;        // this CTA's 128 rows of A
+  static constexpr int B_BYTES = (BN / 2) * kBK;   // this CTA's 128 rows of B
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int COLS_PER_WARP = BN / (EPI_WARPS / 4);
+  static constexpr int OUT_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int AUX_OFFSET = OUT_OFFSET + EPI_WARPS * kStageOutBytes;
+  static constexpr int SMEM_BYTES = AUX_OFFSET + static_cast<int>(sizeof(Aux));
+};
+static_assert(PairCfg::SMEM_BYTES <= 232448, "shared memory budget");
+constexpr int kGroupM2 = 8;  // 256-row blocks per raster group
+
+__device__ __forceinline__ void tile_coords2(int t, int num_m, int num_n, int& mb, int& nb) {
+  const int per_group = kGroupM2 * num_n;
+  const int g = t / per_group;
+  const int first_m = g * kGroupM2;
+  const int gsz = min(num_m - first_m, kGroupM2);
+  const int r = t - g * per_group;
+  mb = first_m + r % gsz;
+  nb = r / gsz;
+}
+
+template <bool F8>
+__global__ void __launch_bounds__(PairCfg::THREADS, 1)
+qlin_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  using C = PairCfg;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  Aux* aux = reinterpret_cast<Aux*>(smem + C::AUX_OFFSET);
+  volatile int* abort_flag = &aux->abort_flag;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const bool aligned = (smem_u32(smem) & 1023u) == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&aux->full[s], 1);
+      mbar_init(&aux->empty[s], 1);
+    }
+    for (int b = 0; b < C::NBUF; ++b) {
+      mbar_init(&aux->tfull[b], 1);
+      mbar_init(&aux->tempty[b], 2 * C::EPI_WARPS);
+    }
+    mbar_init(&aux->drain, 1);
+    aux->abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async();
+  }
+  if (warp == C::MMA_WARP) {
+    tmem_alloc_pair(&aux->tmem_base, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  if (warp == C::PRODUCER_WARP && lane == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive_wait();  // both CTAs' barriers exist before either touches the other's
+  tc_fence_after();
+  const uint32_t tmem_base = aux->tmem_base;
+
+  const int num_m2 = (p.M + 2 * kBM - 1) / (2 * kBM);
+  const int num_tiles = num_m2 * p.num_n;
+  const int num_kb = (p.kbytes + kBK - 1) / kBK;
+  const int total_k32 = (p.kbytes + 31) / 32;
+  bool timed_out = false;
+
+  if (!aligned) {
+    if (threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, static_cast<int32_t>(QLIN_ERR_BAD_ALIGN));
+  } else if (warp == C::PRODUCER_WARP) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    uint32_t s = 0, ph = 0;
+    bool ok = true, ready = false;
+    for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      int mb, nb;
+      tile_coords2(t, num_m2, p.num_n, mb, nb);
+      const int ya = mb * 2 * kBM + static_cast<int>(rank) * kBM;
+      const int yb = nb * C::BN + static_cast<int>(rank) * (C::BN / 2);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!ready) {
+          ok = warp_mbar_wait(&aux->empty[s], ph ^ 1u, abort_flag);
+          if (!ok) break;
+        }
+        const uint32_t ns = (s + 1 == C::STAGES) ? 0u : s + 1;
+        const uint32_t nph = (ns == 0u) ? (ph ^ 1u) : ph;
+        const uint32_t peek = warp_mbar_test_begin(&aux->empty[ns], nph ^ 1u);
+        uint8_t* sa = smem + s * C::STAGE_BYTES;
+        tma_issue_stage_pair(map_to_cta(&aux->full[s], 0), leader, 2 * C::STAGE_BYTES, sa, &tmap_a, ya, sa + C::A_BYTES, &tmap_b, yb,
+                             kb * kBK);
+        ready = warp_mbar_test_end(peek);
+        s = ns;
+        ph = nph;
+      }
+    }
+    if (!ok && lane == 0) {
+      timed_out = !*abort_flag;
+      *abort_flag = 1;
+    }
+    __syncwarp();
+  } else if (warp == C::MMA_WARP) {
+    if (leader) {
+      // ---------------------------------------------------------------- MMA issuer (leader only)
+      constexpr uint32_t idesc = F8 ? make_idesc(1u, 0u, 2 * kBM, C::BN) : make_idesc(2u, 1u, 2 * kBM, C::BN);
+      const uint64_t adesc0 = make_smem_desc_sw128(smem_u32(smem));
+      const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(smem) + C::A_BYTES);
+      uint32_t s = 0, ph = 0, buf = 0, bph = 0;
+      bool ok = true, ready = false;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        uint32_t accumulate = 0, cur = 0;
+        int k32_left = total_k32;
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          if (!ready) {
+            ok = warp_mbar_wait(&aux->full[s], ph, abort_flag);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          const uint32_t ns = (s + 1 == C::STAGES) ? 0u : s + 1;
+          const uint32_t nph = (ns == 0u) ? (ph ^ 1u) : ph;
+          const uint32_t peek = warp_mbar_test_begin(&aux->full[ns], nph);
+          const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
+          const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
+          if (kb == 0) {
+            ok = warp_mbar_wait(&aux->tempty[buf], bph ^ 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            cur = buf;
+            if (++buf == C::NBUF) {
+              buf = 0;
+              bph ^= 1u;
+            }
+          }
+          if (k32_left >= 4) {
+            tc_mma4_release_pair<F8 ? 1 : 0>(tmem_base + cur * C::BN, adesc, bdesc, idesc, accumulate, &aux->empty[s]);
+            accumulate = 1;
+            k32_left -= 4;
+          } else {
+            for (int j = 0; j < k32_left; ++j) {
+              tc_mma1_pair<F8 ? 1 : 0>(tmem_base + cur * C::BN, adesc + static_cast<uint64_t>(j * 2), bdesc + static_cast<uint64_t>(j * 2),
+                                       idesc, accumulate);
+              accumulate = 1;
+            }
+            k32_left = 0;
+            tc_commit_pair_elect(&aux->empty[s]);
+          }
+          if (k32_left == 0) tc_commit_pair_elect(&aux->tfull[cur]);
+          ready = warp_mbar_test_end(peek);
+          s = ns;
+          ph = nph;
+        }
+      }
+      if (!ok && lane == 0) {
+        timed_out = !*abort_flag;
+        *abort_flag = 1;
+      }
+      // Nothing of the pair may still be reading shared memory or writing TMEM when the CTAs retire.
+      tc_commit_pair_elect(&aux->drain);
+      mbar_wait_drain(&aux->drain, 0);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue warps (both CTAs)
+    const int q = warp & 3;
+    const int half = warp >> 2;
+    const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+    uint8_t* stage = smem + C::OUT_OFFSET + warp * kStageOutBytes;
+    const int elt = (p.out_dtype == QLIN_DT_F16 || p.out_dtype == QLIN_DT_BF16) ? 2 : 4;
+    const bool vec_ok = (p.scatter_rows > 0 || (reinterpret_cast<uintptr_t>(p.d) & 15u) == 0) && ((p.ldd * elt) % 16 == 0);
+    const bool scaled = p.epilogue != QLIN_EPI_RAW;
+    uint32_t ebuf = 0, ebph = 0;
+    bool ok = true;
+    for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+      int mb, nb;
+      tile_coords2(t, num_m2, p.num_n, mb, nb);
+      const int row0 = mb * 2 * kBM + static_cast<int>(rank) * kBM + q * 32;
+      const int row = row0 + lane;
+      const int col_w = nb * C::BN + half * C::COLS_PER_WARP;
+      float rs = 1.0f;
+      if (scaled) {
+        asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
+        for (int i = threadIdx.x; i < C::BN; i += C::EPI_WARPS * 32) {
+          const int n = nb * C::BN + i;
+          aux->cs[i] = (p.cs != nullptr && n < p.N) ? p.cs[static_cast<int64_t>(n) * p.cs_stride] : 1.0f;
+          aux->bias[i] = (p.bias != nullptr && n < p.N) ? p.bias[n] : 0.0f;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
+        if (p.rs != nullptr && row < p.M) rs = p.rs[static_cast<int64_t>(row) * p.rs_stride];
+      }
+      const uint32_t buf = ebuf, bph = ebph;
+      if (++ebuf == C::NBUF) {
+        ebuf = 0;
+        ebph ^= 1u;
+      }
+      if (!warp_mbar_wait(&aux->tfull[buf], bph, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+#pragma unroll 1
+      for (int j = 0; j < C::COLS_PER_WARP; j += 64) {
+        uint32_t v[64];
+        tmem_ld64(tmem_base + lane_base + buf * C::BN + half * C::COLS_PER_WARP + j, v);
+        if (p.c != nullptr) {
+          uint32_t cv[64];
+          load_c_row<64>(p, cv, row, col_w + j);
+#pragma unroll
+          for (int i = 0; i < 64; ++i) v[i] = acc_add<F8>(cv[i], v[i]);
+        }
+        emit64<F8>(p, v, row0, lane, col_w + j, aux->cs, aux->bias, half * C::COLS_PER_WARP + j, rs, vec_ok, stage);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(&aux->tempty[buf], 0));
+    }
+    if (!ok && lane == 0) {
+      timed_out = !*abort_flag;
+      *abort_flag = 1;
+    }
+  }
+
+  if (timed_out && p.status != nullptr) atomicExch(p.status, static_cast<int32_t>(QLIN_ERR_TIMEOUT));
+  if (*abort_flag) {
+    // a wait gave up: copies of this CTA may still be in flight; give them time to land before the
+    // shared memory is handed back
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 2000000ull) __nanosleep(256);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_arrive_wait();
+  if (warp == C::MMA_WARP) {
+    __syncwarp();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
 // ---------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -684,6 +943,76 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   qlin_gemm_kernel<F8, CHUNKED><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
   QLIN_CHECK_LAUNCH("qlin_gemm");
   return QLIN_OK;
+}
+
+// Largest number of two-CTA clusters of the pair kernel that can be resident at once (cached per device).
+template <bool F8>
+static int pair_max_clusters() {
+  static int cached[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 0;
+  if (cached[dev] != 0) return cached[dev] > 0 ? cached[dev] : 0;
+  cached[dev] = -1;
+  if (cudaFuncSetAttribute(qlin_gemm_pair_kernel<F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg::SMEM_BYTES) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(sm_count() & ~1), 1, 1);
+  cfg.blockDim = dim3(PairCfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, qlin_gemm_pair_kernel<F8>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  cached[dev] = n > 0 ? n : -1;
+  return n > 0 ? n : 0;
+}
+
+template <bool F8>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+  int clusters = pair_max_clusters<F8>();
+  if (clusters <= 0) return 1;  // not available: the caller takes the single-CTA kernel
+  const int tiles = ((p.M + 2 * kBM - 1) / (2 * kBM)) * p.num_n;
+  if (clusters > tiles) clusters = tiles;
+  if (p.max_ctas > 0 && clusters > p.max_ctas / 2) clusters = p.max_ctas / 2 > 0 ? p.max_ctas / 2 : 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * clusters), 1, 1);
+  cfg.blockDim = dim3(PairCfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, qlin_gemm_pair_kernel<F8>, ta, tb, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(QLIN_ERR_LAUNCH, "qlin_gemm (CTA-pair kernel): %s", cudaGetErrorString(e));
+  }
+  return QLIN_OK;
+}
+
+// The CTA-pair kernel is used for unchunked problems of at least 256 rows unless QLIN_GEMM_PAIR=0.
+static bool pair_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("QLIN_GEMM_PAIR");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
 }
 
 static bool is_round_dtype(int dt) {
@@ -785,6 +1114,13 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   if (rc != QLIN_OK) return rc;
 
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (!chunked && a->M >= 2 * kBM && pair_enabled()) {
+    CUtensorMap tb_half;  // each CTA of a pair loads 128 of the tile's 256 B rows
+    rc = make_operand_map(&tb_half, a->b, a->N, a->K, a->ldb, PairCfg::BN / 2);
+    if (rc != QLIN_OK) return rc;
+    rc = f8 ? launch_pair<true>(ta, tb_half, p, s) : launch_pair<false>(ta, tb_half, p, s);
+    if (rc <= 0) return rc;
+  }
   if (f8) return chunked ? launch<true, true>(ta, tb, p, s) : launch<true, false>(ta, tb, p, s);
   return chunked ? launch<false, true>(ta, tb, p, s) : launch<false, false>(ta, tb, p, s);
 }

@@ -339,6 +339,125 @@ __device__ __forceinline__ void tc_commit_elect(uint64_t* bar) {
       : "memory");
 }
 
+// ---------------------------------------------------------------- CTA pairs (cta_group::2)
+// Two CTAs of a cluster of two share one MMA: the even CTA (the leader) issues tcgen05.mma for a
+// 256-row tile, each CTA holds its 128 rows of A, its half of B's rows and its 128 accumulator rows.
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_arrive_wait() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `p` (an address in this CTA's shared memory) as seen in CTA `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
+  uint32_t a;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(p)), "r"(rank));
+  return a;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// One stage of a CTA pair: both CTAs load their own two boxes into their own shared memory; the
+// bytes are counted on the leader's barrier (`leader_bar`, a shared::cluster address), on which only
+// the leader posts the expected total.  No multicast: each CTA fetches what it needs itself.
+__device__ __forceinline__ void tma_issue_stage_pair(uint32_t leader_bar, bool is_leader, uint32_t total_bytes, void* dst_a,
+                                                     const void* tmap_a, int32_t ya, void* dst_b, const void* tmap_b,
+                                                     int32_t yb, int32_t x) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pe, pl;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "setp.ne.b32 pl, %9, 0;\n\t"
+      "and.pred pl, pl, pe;\n\t"
+      "@pl mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;\n\t"
+      "@pe cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%2], [%3, {%4, %5}], [%0];\n\t"
+      "@pe cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%6], [%7, {%4, %8}], [%0];\n\t"
+      "}" ::"r"(leader_bar),
+      "r"(total_bytes), "r"(smem_u32(dst_a)), "l"(reinterpret_cast<uint64_t>(tmap_a)), "r"(x), "r"(ya), "r"(smem_u32(dst_b)),
+      "l"(reinterpret_cast<uint64_t>(tmap_b)), "r"(yb), "r"(is_leader ? 1u : 0u)
+      : "memory");
+}
+// Leader only.  Four K=32-byte MMAs of the pair into one accumulator, then the stage is released in
+// both CTAs (commit with a two-CTA mask on the barrier at this offset in each of them).
+template <int KIND_F8>
+__device__ __forceinline__ void tc_mma4_release_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                     uint32_t accumulate, uint64_t* empty_bar) {
+#define QLIN_MMA4P(KIND)                                                                                              \
+  asm volatile(                                                                                                       \
+      "{\n\t"                                                                                                         \
+      ".reg .pred pe, pa, pt;\n\t"                                                                                    \
+      ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"                                                                         \
+      ".reg .b16 mask;\n\t"                                                                                           \
+      "elect.sync _|pe, 0xffffffff;\n\t"                                                                              \
+      "setp.ne.b32 pa, %4, 0;\n\t"                                                                                    \
+      "setp.ne.b32 pt, %3, 0;\n\t"                                                                                    \
+      "mov.b16 mask, 3;\n\t"                                                                                          \
+      "add.s64 a1, %1, 2;\n\t"                                                                                        \
+      "add.s64 b1, %2, 2;\n\t"                                                                                        \
+      "add.s64 a2, %1, 4;\n\t"                                                                                        \
+      "add.s64 b2, %2, 4;\n\t"                                                                                        \
+      "add.s64 a3, %1, 6;\n\t"                                                                                        \
+      "add.s64 b3, %2, 6;\n\t"                                                                                        \
+      "@pe tcgen05.mma.cta_group::2.kind::" KIND " [%0], %1, %2, %3, pa;\n\t"                                         \
+      "@pe tcgen05.mma.cta_group::2.kind::" KIND " [%0], a1, b1, %3, pt;\n\t"                                         \
+      "@pe tcgen05.mma.cta_group::2.kind::" KIND " [%0], a2, b2, %3, pt;\n\t"                                         \
+      "@pe tcgen05.mma.cta_group::2.kind::" KIND " [%0], a3, b3, %3, pt;\n\t"                                         \
+      "@pe tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%5], mask;\n\t"  \
+      "}" ::"r"(d_tmem),                                                                                              \
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(smem_u32(empty_bar))                                   \
+      : "memory")
+  if (KIND_F8) {
+    QLIN_MMA4P("f8f6f4");
+  } else {
+    QLIN_MMA4P("i8");
+  }
+#undef QLIN_MMA4P
+}
+// Leader only.  One K=32-byte MMA of the pair (ragged K tail).
+template <int KIND_F8>
+__device__ __forceinline__ void tc_mma1_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+#define QLIN_MMA1P(KIND)                                                       \
+  asm volatile(                                                                \
+      "{\n\t"                                                                  \
+      ".reg .pred pe, pa;\n\t"                                                 \
+      "elect.sync _|pe, 0xffffffff;\n\t"                                       \
+      "setp.ne.b32 pa, %4, 0;\n\t"                                             \
+      "@pe tcgen05.mma.cta_group::2.kind::" KIND " [%0], %1, %2, %3, pa;\n\t"  \
+      "}" ::"r"(d_tmem),                                                       \
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)                      \
+      : "memory")
+  if (KIND_F8) {
+    QLIN_MMA1P("f8f6f4");
+  } else {
+    QLIN_MMA1P("i8");
+  }
+#undef QLIN_MMA1P
+}
+// Leader only.  Arrive on the barrier at this offset in both CTAs once the pair's MMAs so far are done.
+__device__ __forceinline__ void tc_commit_pair_elect(uint64_t* bar) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred pe;\n\t"
+      ".reg .b16 mask;\n\t"
+      "elect.sync _|pe, 0xffffffff;\n\t"
+      "mov.b16 mask, 3;\n\t"
+      "@pe tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], mask;\n\t"
+      "}" ::"r"(smem_u32(bar))
+      : "memory");
+}
+
 // Reads 32 consecutive 32-bit columns of this warp's 32 TMEM lanes (lane i of the warp gets TMEM
 // lane base+i) and waits for the data; the registers are valid when the call returns.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
