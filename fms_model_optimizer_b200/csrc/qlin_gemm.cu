@@ -255,12 +255,42 @@ __device__ __forceinline__ void emit64(const GemmParams& p, const uint32_t (&v)[
   if (p.epilogue != QLIN_EPI_RAW && p.out_dtype != QLIN_DT_F32) {
     // 2-byte outputs: 64 columns = one 128-byte staging row
     uint32_t w[32];
+    if (prod && p.scale_round == QLIN_DT_F16 && p.acc_round == QLIN_DT_F16 && p.out_dtype == QLIN_DT_BF16 &&
+        (p.prod_round == QLIN_DT_BF16 || p.prod_round == QLIN_DT_NONE || p.prod_round == QLIN_DT_F32)) {
+      // The deploy Linear's chain, two columns per instruction: s = fp16(bf16?(rs * cs)); y = fp16(acc * s (+ bias));
+      // the same roundings as dequant_one, done with packed fp32 arithmetic and packed conversions.
+      const bool prod_bf16 = p.prod_round == QLIN_DT_BF16;
+      const float2 rs2 = make_float2(rs, rs);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float2 c2 = *reinterpret_cast<const float2*>(s_cs + s_off + 2 * j);
+        float2 sc = __fmul2_rn(rs2, c2);
+        if (prod_bf16) {
+          const __nv_bfloat162 b2 = __float22bfloat162_rn(sc);
+          const uint32_t bw = *reinterpret_cast<const uint32_t*>(&b2);
+          sc = make_float2(__uint_as_float(bw << 16), __uint_as_float(bw & 0xFFFF0000u));
+        }
+        sc = __half22float2(__float22half2_rn(sc));
+        float2 a2;
+        if (F8) {
+          a2 = make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+        } else {
+          a2 = make_float2(__int2float_rn(static_cast<int32_t>(v[2 * j])), __int2float_rn(static_cast<int32_t>(v[2 * j + 1])));
+        }
+        float2 t = __fmul2_rn(a2, sc);
+        if (has_bias) t = __fadd2_rn(t, *reinterpret_cast<const float2*>(s_bias + s_off + 2 * j));
+        t = __half22float2(__float22half2_rn(t));
+        const __nv_bfloat162 o2 = __float22bfloat162_rn(t);
+        w[j] = *reinterpret_cast<const uint32_t*>(&o2);
+      }
+    } else {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       const float y0 = dequant_one<F8>(p, v[2 * j], rs, s_cs[s_off + 2 * j], s_bias[s_off + 2 * j], prod, has_bias);
       const float y1 =
           dequant_one<F8>(p, v[2 * j + 1], rs, s_cs[s_off + 2 * j + 1], s_bias[s_off + 2 * j + 1], prod, has_bias);
       w[j] = pack16(p, y0, y1);
+    }
     }
     uint8_t* g = out_row(p, row0, 2) + static_cast<int64_t>(col0) * 2;
     store_tile_coalesced(stage, w, g, p.ldd * 2, rows_valid, lane);
