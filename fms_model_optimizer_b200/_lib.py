@@ -18,14 +18,14 @@ ERR_BAD_SHAPE, ERR_BAD_ALIGN, ERR_BAD_DTYPE, ERR_UNSUPPORTED = -1, -2, -3, -4
 ERR_LAUNCH, ERR_TIMEOUT, ERR_NULL, ERR_DEVICE, ERR_TOO_LARGE = -5, -6, -7, -8, -9
 
 # qlin_dtype
-DT_NONE, DT_I8, DT_U8, DT_I32, DT_F32, DT_F16, DT_BF16, DT_F8E4M3 = range(8)
+DT_NONE, DT_I8, DT_U8, DT_I32, DT_F32, DT_F16, DT_BF16, DT_F8E4M3, DT_F8E5M2 = range(9)
 
 # qlin_epilogue
 EPI_RAW, EPI_SCALE_PROD, EPI_SCALE_SEQ = 0, 1, 2
 
 # qlin_quant_mode
 (Q_I8_DYN, Q_I8_STATIC, Q_I8_STATIC_CLAMP_FIRST, Q_F8_DYN, Q_I8_GIVEN_SCALE, Q_F8_FAKE_SCALED, Q_I8_STATIC_ROUND_FIRST,
- Q_I8_AFFINE_RCP) = range(8)
+ Q_I8_AFFINE_RCP, Q_F8_TENSOR) = range(9)
 
 # qlin_pact_variant
 PACT_TWO_SIDED, PACT_ONE_SIDED, PACT_SYMMETRIC = 0, 1, 2
@@ -128,6 +128,7 @@ class QuantArgs(C.Structure):
         ("shift", C.c_float),
         ("add2", C.c_float),
         ("dyn_eps", C.c_float),
+        ("f8_format", C.c_int32),
     ]
 
 

@@ -84,6 +84,7 @@ struct GemmParams {
   int32_t num_m, num_n, max_ctas;
   int32_t scatter_rows, scatter_row0;
   uint8_t* scatter_d[8];
+  int32_t f8_ab_format;  // float kinds: operand format of the instruction descriptor, 0 = e4m3, 1 = e5m2
 };
 
 __device__ __forceinline__ float round_to(float y, int dt) {
@@ -432,7 +433,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // One instruction stream feeds the tensor pipe, so this loop is latency-critical: no
     // divisions, positions carried as counters, a whole 128-byte K block issued by one fused
     // statement, and the next stage's barrier polled before the current block is issued.
-    constexpr uint32_t idesc = F8 ? make_idesc(1u, 0u, kBM, C::BN) : make_idesc(2u, 1u, kBM, C::BN);
+    const uint32_t idesc = F8 ? make_idesc(1u, static_cast<uint32_t>(p.f8_ab_format), kBM, C::BN) : make_idesc(2u, 1u, kBM, C::BN);
     const uint64_t adesc0 = make_smem_desc_sw128(smem_u32(smem));
     const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(smem) + C::A_BYTES);
     uint32_t s = 0, ph = 0;          // smem stage and its phase
@@ -787,7 +788,7 @@ qlin_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   } else if (warp == C::MMA_WARP) {
     if (leader) {
       // ---------------------------------------------------------------- MMA issuer (leader only)
-      constexpr uint32_t idesc = F8 ? make_idesc(1u, 0u, 2 * kBM, C::BN) : make_idesc(2u, 1u, 2 * kBM, C::BN);
+      const uint32_t idesc = F8 ? make_idesc(1u, static_cast<uint32_t>(p.f8_ab_format), 2 * kBM, C::BN) : make_idesc(2u, 1u, 2 * kBM, C::BN);
       const uint64_t adesc0 = make_smem_desc_sw128(smem_u32(smem));
       const uint64_t bdesc0 = make_smem_desc_sw128(smem_u32(smem) + C::A_BYTES);
       uint32_t s = 0, ph = 0, buf = 0, bph = 0;
@@ -1069,9 +1070,9 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
     if (a->c != nullptr) return fail(QLIN_ERR_UNSUPPORTED, "qlin_gemm: scatter with an accumulator input is not provided");
   }
   if (a->M < 0 || a->N < 0 || a->K < 0) return fail(QLIN_ERR_BAD_SHAPE, "qlin_gemm: negative dimension");
-  if (a->kind != QLIN_DT_I8 && a->kind != QLIN_DT_F8E4M3)
-    return fail(QLIN_ERR_BAD_DTYPE, "qlin_gemm: kind must be QLIN_DT_I8 or QLIN_DT_F8E4M3");
-  const bool f8 = a->kind == QLIN_DT_F8E4M3;
+  if (a->kind != QLIN_DT_I8 && a->kind != QLIN_DT_F8E4M3 && a->kind != QLIN_DT_F8E5M2)
+    return fail(QLIN_ERR_BAD_DTYPE, "qlin_gemm: kind must be QLIN_DT_I8, QLIN_DT_F8E4M3 or QLIN_DT_F8E5M2");
+  const bool f8 = a->kind != QLIN_DT_I8;
   if (a->M == 0 || a->N == 0) return QLIN_OK;
   if (a->K == 0) return fail(QLIN_ERR_BAD_SHAPE, "qlin_gemm: K must be positive");
   if (a->lda < a->K || a->ldb < a->K || a->ldd < a->N || (a->c != nullptr && a->ldc < a->N))
@@ -1132,6 +1133,7 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   p.max_ctas = a->max_ctas;
   p.scatter_rows = a->scatter_rows;
   p.scatter_row0 = a->scatter_row0;
+  p.f8_ab_format = a->kind == QLIN_DT_F8E5M2 ? 1 : 0;
   for (int i = 0; i < 8; ++i) p.scatter_d[i] = static_cast<uint8_t*>(a->scatter_d[i]);
   const int bn = chunked ? Cfg<true>::BN : Cfg<false>::BN;
   p.num_m = (a->M + kBM - 1) / kBM;

@@ -36,6 +36,7 @@ struct QuantParams {
   int32_t smooth_exact;  // smoothing scales are exactly representable in the dtype of x
   int32_t mode, native, native_smooth, smooth_mul, clamp_codes, levels, dl8_flush, scale_in_stride;
   float scale0, zp0, lo, hi, shift, add2, dyn_eps;
+  int32_t f8_e5m2;
 };
 
 template <typename XT>
@@ -67,6 +68,15 @@ __device__ __forceinline__ float dyn_scale(const QuantParams& p, float amax) {
 __device__ __forceinline__ uint8_t to_e4m3(float v) {
   if (!(fabsf(v) <= 464.0f)) return static_cast<uint8_t>(0x7F | (signbit(v) ? 0x80 : 0));
   return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+// torch's float -> float8_e5m2 conversion: round to nearest even, infinity from 61440 upwards.
+__device__ __forceinline__ uint8_t to_e5m2(float v) {
+  if (v != v) return 0x7F;
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_NOSAT, __NV_E5M2));
+}
+__device__ __forceinline__ float from_e5m2(uint8_t c) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(c), __NV_E5M2);
+  return __half2float(*reinterpret_cast<const __half*>(&h));
 }
 __device__ __forceinline__ float from_e4m3(uint8_t c) {
   const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(c), __NV_E4M3);
@@ -117,6 +127,17 @@ __device__ __forceinline__ uint8_t quant_one(const QuantParams& p, float v, floa
       dq = r;
       return static_cast<uint8_t>(static_cast<int>(r) & 0xFF);
     }
+    case QLIN_Q_F8_TENSOR: {  // one scale for the whole tensor, e4m3 or e5m2 codes
+      const float t = rnd_if<XT>(div_exact(v, s, rs), nat);
+      uint8_t c = p.f8_e5m2 ? to_e5m2(t) : to_e4m3(t);
+      float f = p.f8_e5m2 ? from_e5m2(c) : from_e4m3(c);
+      if (p.dl8_flush && fabsf(f) < 0.0087890625f) {
+        c = 0;
+        f = 0.0f;
+      }
+      dq = f;
+      return c;
+    }
     case QLIN_Q_F8_FAKE_SCALED: {  // s multiplies: x * s, saturate, cast to e4m3 and back, / s
       float t = rnd_if<XT>(__fmul_rn(v, s), nat);
       const bool is_nan = t != t;  // torch.clamp keeps NaN, fminf / fmaxf would drop it
@@ -148,6 +169,10 @@ template <typename XT>
 __device__ __forceinline__ float row_scale_of(const QuantParams& p, int row, float amax) {
   if (is_dynamic(p.mode)) return dyn_scale<XT>(p, amax);
   if (p.mode == QLIN_Q_I8_GIVEN_SCALE) return p.scale_in[static_cast<int64_t>(row) * p.scale_in_stride];
+  if (p.mode == QLIN_Q_F8_TENSOR) {
+    const float a = rnd_if<XT>(__fdiv_rn(p.scale_in[0], p.scale0), p.native);
+    return fmaxf(a, rnd_if<XT>(p.dyn_eps, p.native));
+  }
   return p.scale0;
 }
 
@@ -999,10 +1024,12 @@ extern "C" int qlin_act_quant(const qlin_quant_args* a, void* stream) {
   if (a->rows == 0 || a->cols == 0) return QLIN_OK;
   if (a->ldx < a->cols || (a->codes != nullptr && a->ldq < a->cols) || (a->dq_out != nullptr && a->lddq < a->cols))
     return fail(QLIN_ERR_BAD_SHAPE, "qlin_act_quant: leading dimension smaller than the row length");
-  if (a->mode < QLIN_Q_I8_DYN || a->mode > QLIN_Q_I8_AFFINE_RCP)
+  if (a->mode < QLIN_Q_I8_DYN || a->mode > QLIN_Q_F8_TENSOR)
     return fail(QLIN_ERR_UNSUPPORTED, "qlin_act_quant: unknown mode %d", a->mode);
   if (a->smooth != nullptr && !a->smooth_mul && a->smooth_rcp == nullptr)
     return fail(QLIN_ERR_NULL, "qlin_act_quant: smooth_rcp is required when rows are divided by smooth");
+  if (a->mode == QLIN_Q_F8_TENSOR && (a->scale_in == nullptr || !(a->scale0 > 0.0f)))
+    return fail(QLIN_ERR_NULL, "qlin_act_quant: QLIN_Q_F8_TENSOR needs the tensor absmax in scale_in and a positive scale0");
   if (a->mode == QLIN_Q_I8_GIVEN_SCALE && a->scale_in == nullptr)
     return fail(QLIN_ERR_NULL, "qlin_act_quant: scale_in is required by QLIN_Q_I8_GIVEN_SCALE");
   if ((a->mode == QLIN_Q_I8_DYN || a->mode == QLIN_Q_I8_GIVEN_SCALE) && (a->qmax_levels < 1 || a->qmax_levels > 127))
@@ -1037,6 +1064,7 @@ extern "C" int qlin_act_quant(const qlin_quant_args* a, void* stream) {
   p.shift = a->shift;
   p.add2 = a->add2;
   p.dyn_eps = a->dyn_eps;
+  p.f8_e5m2 = a->f8_format == 1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (a->x_dtype) {
     case QLIN_DT_F32:

@@ -293,11 +293,71 @@ def _normalised_chunk(chunk_size: int) -> int:
     return max(chunk_size, 32) if pow2 else 32
 
 
+def _fp8_chunk(chunk_size):
+    chunk = _normalised_chunk(int(chunk_size)) if int(chunk_size) != 8 else 8
+    if chunk == 8:
+        raise NotImplementedError("chunk_size=8 is provided by ops.tl_matmul_chunk_truncate only")
+    return chunk
+
+
+class _LinearFPxFwdBwd(torch.autograd.Function):
+    """LinearFuncFPxFwdBwd (fms_mo/modules/linear.py:1892-2058).  Forward: e4m3 codes of x and W with per-token /
+    per-channel or per-tensor scales, fp32-accumulating tcgen05 GEMM with optional chunk truncation, ``* x_scale * w_scale``
+    and bias in the epilogue.  Backward (per-tensor scaling only, as in the reference, whose per-token branch cannot
+    broadcast its scales): e5m2 codes of x, W and grad_output with one scale each, two e5m2 GEMMs; the bias gradient is the
+    column sum of the scaled e5m2 gradient codes, which is what the reference returns."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, trun_bits, chunk_size, fp8_dyn, clamp_acc_to_dl16, wq_ws):
+        org_dtype = x.dtype
+        tar_shape = x.shape[:-1] + (weight.shape[0],)
+        x2 = x.reshape(-1, x.shape[-1])
+        ctx.save_for_backward(x2, weight)
+        ctx.cfg = (trun_bits, chunk_size, fp8_dyn, bool(clamp_acc_to_dl16), bias.dtype if bias is not None else None)
+        native = 0 if org_dtype == torch.float32 else 3
+        if fp8_dyn == "per_token":
+            xq, xs, _ = ops.act_quant(x2, mode=L.Q_F8_DYN, native_chain=native, dl8_flush=clamp_acc_to_dl16)
+            wq, ws = wq_ws
+        else:
+            xq, xs = ops.fp8_quant_per_tensor(x2, dl8_flush=clamp_acc_to_dl16)
+            wq, ws = ops.fp8_quant_per_tensor(weight.detach(), dl8_flush=clamp_acc_to_dl16)
+        rnd = None if org_dtype == torch.float32 else org_dtype
+        out = ops.gemm(
+            xq, wq, chunk_k=_fp8_chunk(chunk_size), trun_bits=(14 if clamp_acc_to_dl16 else int(trun_bits)),
+            clamp_dl16=bool(clamp_acc_to_dl16), epilogue=L.EPI_SCALE_SEQ, row_scale=xs, col_scale=ws,
+            bias=(bias.detach().to(org_dtype) if bias is not None else None), mid_round=rnd, acc_round=rnd, out_dtype=org_dtype,
+        )  # fmt: skip
+        return out.reshape(tar_shape)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x2, weight = ctx.saved_tensors
+        trun_bits, chunk_size, fp8_dyn, dl16, bias_dtype = ctx.cfg
+        if fp8_dyn != "per_tensor":
+            raise NotImplementedError("the backward of the FP8 Linear runs with dynamic_fp8='per_tensor' only (so does the reference's)")
+        dtype_input = x2.dtype
+        out_dim, in_dim = weight.shape
+        g2 = grad_output.reshape(-1, out_dim).to(dtype_input)
+        xq, xs = ops.fp8_quant_per_tensor(x2, e5m2=True, eps=0.0, dl8_flush=dl16)
+        wq, ws = ops.fp8_quant_per_tensor(weight.detach(), e5m2=True, eps=0.0, dl8_flush=dl16)
+        gq, gs = ops.fp8_quant_per_tensor(g2, e5m2=True, eps=0.0, dl8_flush=dl16)
+        kw = dict(chunk_k=_fp8_chunk(chunk_size), trun_bits=(14 if dl16 else int(trun_bits)), clamp_dl16=dl16, epilogue=L.EPI_SCALE_SEQ)
+
+        def t8(c):  # both GEMM operands are K-major: transpose the one-byte codes
+            return c.view(torch.uint8).t().contiguous().view(torch.float8_e5m2)
+
+        # grad_weight[n, k] = sum_m g[m, n] x[m, k];  grad_input[m, k] = sum_n g[m, n] w[n, k]
+        grad_weight = ops.gemm(t8(gq), t8(xq), row_scale=gs, col_scale=xs, out_dtype=weight.dtype, **kw)
+        grad_input = ops.gemm(gq, t8(wq), row_scale=gs, col_scale=ws, out_dtype=dtype_input, **kw)
+        grad_input = grad_input.reshape(grad_output.shape[:-1] + (in_dim,))
+        grad_bias = gq.float().sum(0).to(bias_dtype) if bias_dtype is not None else None
+        return grad_input, grad_weight, grad_bias, None, None, None, None, None
+
+
 class LinearFPxAcc(nn.Linear):
-    """FP8 (e4m3) Linear with dynamic per-token / per-channel scales and optional reduced-precision
-    accumulation, mirroring LinearFPxAcc / LinearFuncFPxFwdBwd.forward of the reference
-    (fms_mo/modules/linear.py:1892-1975, :2048-2124).  Forward only: quantise x, quantise W (cached
-    until the weight changes), e4m3 tcgen05 GEMM with ``* x_scale * w_scale`` and bias in the epilogue."""
+    """FP8 Linear with dynamic scales and optional reduced-precision accumulation, mirroring LinearFPxAcc /
+    LinearFuncFPxFwdBwd of the reference (fms_mo/modules/linear.py:1892-2124): e4m3 forward with per-token / per-channel
+    scales (W's codes cached until the weight changes) or per-tensor scales, e5m2 backward with per-tensor scales."""
 
     @classmethod
     def from_nn(cls, nnlin, trun_bits=0, **kwargs):
@@ -325,28 +385,12 @@ class LinearFPxAcc(nn.Linear):
     def forward(self, inputs: torch.Tensor) -> torch.Tensor:
         if not inputs.is_cuda:
             raise RuntimeError("LinearFPxAcc(b200) runs on CUDA tensors only")
-        if self.fp8_dyn != "per_token":
-            raise NotImplementedError("the B200 FP8 Linear provides dynamic_fp8='per_token'")
-        if torch.is_grad_enabled() and (inputs.requires_grad or self.weight.requires_grad):
-            raise NotImplementedError("LinearFPxAcc(b200) is forward-only; wrap the call in torch.no_grad()")
+        if self.fp8_dyn not in ("per_token", "per_tensor"):
+            raise NotImplementedError("the B200 FP8 Linear provides dynamic_fp8='per_token' or 'per_tensor'")
         assert inputs.dtype in _FLOATS
-        org_dtype = inputs.dtype
-        tar_shape = inputs.shape[:-1] + (self.weight.shape[0],)
-        x2 = inputs.reshape(-1, inputs.shape[-1])
-        native = 0 if org_dtype == torch.float32 else 3
-        xq, xs, _ = ops.act_quant(x2, mode=L.Q_F8_DYN, native_chain=native, dl8_flush=self.clamp_acc_to_dl16)
-        wq, ws = self._quantised_weight()
-        chunk = _normalised_chunk(int(self.chunk_size)) if int(self.chunk_size) != 8 else 8
-        if chunk == 8:
-            raise NotImplementedError("chunk_size=8 is provided by ops.tl_matmul_chunk_truncate only")
-        rnd = None if org_dtype == torch.float32 else org_dtype
-        out = ops.gemm(
-            xq, wq, chunk_k=chunk, trun_bits=(14 if self.clamp_acc_to_dl16 else int(self.trun_bits)),
-            clamp_dl16=bool(self.clamp_acc_to_dl16), epilogue=L.EPI_SCALE_SEQ, row_scale=xs, col_scale=ws,
-            bias=(self.bias.detach().to(org_dtype) if self.bias is not None else None), mid_round=rnd, acc_round=rnd,
-            out_dtype=org_dtype,
-        )  # fmt: skip
-        return out.reshape(tar_shape)
+        wq_ws = self._quantised_weight() if self.fp8_dyn == "per_token" else None
+        return _LinearFPxFwdBwd.apply(inputs, self.weight, self.bias, self.trun_bits, self.chunk_size, self.fp8_dyn,
+                                      self.clamp_acc_to_dl16, wq_ws)  # fmt: skip
 
     def extra_repr(self) -> str:
         s = f"{self.in_features},{self.out_features}"

@@ -26,6 +26,7 @@ _DT = {
     torch.float16: L.DT_F16,
     torch.bfloat16: L.DT_BF16,
     torch.float8_e4m3fn: L.DT_F8E4M3,
+    torch.float8_e5m2: L.DT_F8E5M2,
 }
 _ROUND = {None: L.DT_NONE, torch.float32: L.DT_F32, torch.float16: L.DT_F16, torch.bfloat16: L.DT_BF16}
 
@@ -149,9 +150,9 @@ def gemm(
     dev = _require_cuda(a, b_nk, c, out, row_scale, col_scale, bias)
     if a.dim() != 2 or b_nk.dim() != 2 or a.shape[1] != b_nk.shape[1]:
         raise RuntimeError(f"incompatible shapes {tuple(a.shape)} x {tuple(b_nk.shape)}^T")
-    if a.dtype != b_nk.dtype or a.dtype not in (torch.int8, torch.float8_e4m3fn):
-        raise RuntimeError(f"operands must both be int8 or float8_e4m3fn, got {a.dtype} and {b_nk.dtype}")
-    f8 = a.dtype == torch.float8_e4m3fn
+    if a.dtype != b_nk.dtype or a.dtype not in (torch.int8, torch.float8_e4m3fn, torch.float8_e5m2):
+        raise RuntimeError(f"operands must both be int8, float8_e4m3fn or float8_e5m2, got {a.dtype} and {b_nk.dtype}")
+    f8 = a.dtype != torch.int8
     M, K = a.shape
     N = b_nk.shape[0]
     raw_dtype = torch.float32 if f8 else torch.int32
@@ -329,6 +330,7 @@ def act_quant(
     shift: float = 0.0,
     add2: float = 0.0,
     dyn_eps: float = 1e-5,
+    f8_e5m2: bool = False,
 ) -> Tuple[Optional[torch.Tensor], torch.Tensor, Optional[torch.Tensor]]:
     """Row-wise 8-bit quantisation of a 2-D tensor; returns ``(codes, scale[rows], dq)``.
     See ``qlin_act_quant`` in include/qlin_b200.h for the modes."""
@@ -340,7 +342,11 @@ def act_quant(
     if x.stride(1) != 1:
         x = x.contiguous()
     rows, cols = x.shape
-    code_dtype = torch.float8_e4m3fn if mode == L.Q_F8_DYN else torch.int8
+    code_dtype = torch.int8
+    if mode == L.Q_F8_DYN or (mode == L.Q_F8_TENSOR and not f8_e5m2):
+        code_dtype = torch.float8_e4m3fn
+    elif mode == L.Q_F8_TENSOR:
+        code_dtype = torch.float8_e5m2
     codes = torch.empty((rows, cols), dtype=code_dtype, device=dev) if want_codes else None
     dq = torch.empty((rows, cols), dtype=x.dtype, device=dev) if want_dq else None
     scale = torch.empty((rows,), dtype=torch.float32, device=dev)
@@ -359,7 +365,7 @@ def act_quant(
         native_chain=int(native_chain), smooth_mul=int(bool(smooth_mul)), clamp_codes=int(bool(clamp_codes)),
         qmax_levels=int(levels), dl8_flush=int(bool(dl8_flush)),
         scale_in_stride=(0 if si is None or si.numel() == 1 else 1),
-        scale0=scale0, zp0=zp0, lo=lo, hi=hi, shift=shift, add2=add2, dyn_eps=dyn_eps,
+        scale0=scale0, zp0=zp0, lo=lo, hi=hi, shift=shift, add2=add2, dyn_eps=dyn_eps, f8_format=int(bool(f8_e5m2)),
     )  # fmt: skip
     nbytes = rows * cols * (x.element_size() + (1 if want_codes else 0) + (x.element_size() if want_dq else 0)) + 4 * rows
     nbytes += 4 * cols if sm is not None else 0
@@ -641,6 +647,22 @@ def _iaddmm_op(bias: torch.Tensor, m1: torch.Tensor, m2: torch.Tensor, scale_i: 
 @_iaddmm_op.register_fake
 def _(bias, m1, m2, scale_i, scale_w):
     return m1.new_empty((m1.shape[0], m2.shape[1]), dtype=torch.float32)
+
+
+def tensor_absmax(x: torch.Tensor) -> torch.Tensor:
+    """max|x| over the whole tensor as a 1-element fp32 device tensor (``qlin_tensor_fq`` statistics only)."""
+    return tensor_fq(x, kind=L.PT_INT_SYM, mode=L.W_MAX, want_out=False)[1]
+
+
+def fp8_quant_per_tensor(x2: torch.Tensor, *, e5m2: bool = False, eps: float = 1e-5, dl8_flush: bool = False):
+    """The per-tensor FP8 scaling of LinearFuncFPxFwdBwd (fms_mo/modules/linear.py:1939-1953 forward, e4m3, scale clamped at
+    1e-5; :2003-2017 backward, e5m2, no clamp): ``scale = max(amax / fp8_max, eps)``, ``codes = fp8(x / scale)``.
+    Returns ``(codes [rows, cols], scale [1] fp32)``; nothing is read back to the host."""
+    amax = tensor_absmax(x2)
+    native = 0 if x2.dtype == torch.float32 else 3
+    codes, scale, _ = act_quant(x2, mode=L.Q_F8_TENSOR, native_chain=native, scale_in=amax, scale0=(57344.0 if e5m2 else 448.0),
+                                dyn_eps=eps, f8_e5m2=e5m2, dl8_flush=dl8_flush)  # fmt: skip
+    return codes, scale[:1]
 
 
 def _scalar(t) -> float:

@@ -48,7 +48,8 @@ typedef enum qlin_dtype {
   QLIN_DT_F32 = 4,
   QLIN_DT_F16 = 5,
   QLIN_DT_BF16 = 6,
-  QLIN_DT_F8E4M3 = 7
+  QLIN_DT_F8E4M3 = 7,
+  QLIN_DT_F8E5M2 = 8
 } qlin_dtype;
 
 /* ------------------------------------------------------------------------------------------------
@@ -73,7 +74,8 @@ int qlin_device_supported(int device);
  *
  * Operands: A is [M,K], B is [N,K], both with K contiguous ("NT"; B is the `.t()` view the
  * reference passes as its [k,n] operand).  kind = QLIN_DT_I8 (int32 accumulation) or
- * QLIN_DT_F8E4M3 (fp32 accumulation).  a, b must be 16-byte aligned, lda/ldb multiples of 16.
+ * QLIN_DT_F8E4M3 / QLIN_DT_F8E5M2 (fp32 accumulation; e5m2 operands are what the backward of the FP8 Linear
+ * multiplies, fms_mo/modules/linear.py:2003-2046).  a, b must be 16-byte aligned, lda/ldb multiples of 16.
  *
  * Chunked accumulation (K1/K2 semantics): K is cut into chunks of `chunk_k` elements (a multiple
  * of 32; <=0 means one chunk).  Per chunk p = A_c . B_c^T; integer kinds: clamp p to
@@ -171,6 +173,10 @@ int qlin_gemm(const qlin_gemm_args* args, void* stream);
  *                     code = clamp(nearbyint(v * (1 / scale0)) + zp0, -128, 127), fp32 rows:
  *                     torch.quantize_per_tensor(...).int_repr() (fms_mo::q_per_t_sym,
  *                     fms_mo/custom_ext_kernels/utils.py:792-794)
+ *   QLIN_Q_F8_TENSOR  one scale for the whole tensor from its absmax: scale = max(scale_in[0] / scale0, dyn_eps);
+ *                     code = fp8(v / scale) in e4m3 (f8_format 0) or e5m2 (f8_format 1), optional DL8 flush; the per-tensor
+ *                     branch of LinearFuncFPxFwdBwd (fms_mo/modules/linear.py:1939-1953 with scale0 = 448, dyn_eps = 1e-5;
+ *                     :2003-2017 with scale0 = 57344, dyn_eps = 0, e5m2).  scale_out receives the scale in every row.
  *   QLIN_Q_F8_FAKE_SCALED
  *                     to_fp8_scaled_perToken / _perCh (fms_mo/quant/quantizers.py:5336-5420), e4m3:
  *                     scale = 448 / max(amax, dyn_eps) (a multiplier, capped at 65504 on fp16 rows);
@@ -193,7 +199,8 @@ typedef enum qlin_quant_mode {
   QLIN_Q_I8_GIVEN_SCALE = 4,
   QLIN_Q_F8_FAKE_SCALED = 5,
   QLIN_Q_I8_STATIC_ROUND_FIRST = 6,
-  QLIN_Q_I8_AFFINE_RCP = 7
+  QLIN_Q_I8_AFFINE_RCP = 7,
+  QLIN_Q_F8_TENSOR = 8
 } qlin_quant_mode;
 
 typedef struct qlin_quant_args {
@@ -220,6 +227,7 @@ typedef struct qlin_quant_args {
   float scale0, zp0, lo, hi, shift, add2; /* static modes */
   float dyn_eps;          /* dynamic modes: lower clamp of the row absmax; the deploy modules use 1e-5,
                              QLinearINT8Train uses 0 (fms_mo/modules/linear.py:2167-2171) */
+  int32_t f8_format;      /* QLIN_Q_F8_TENSOR: 0 = e4m3, 1 = e5m2 */
 } qlin_quant_args;
 
 int qlin_act_quant(const qlin_quant_args* args, void* stream);

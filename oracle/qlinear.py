@@ -188,3 +188,32 @@ def q_per_t_sym(x, s, zp):
     torch.quantize_per_tensor, ``clamp(nearbyint(x * (1 / s)) + zp, -128, 127)`` in fp32."""
     inv = torch.tensor(1.0, dtype=torch.float32) / torch.as_tensor(s, dtype=torch.float32)
     return torch.clamp(torch.round(x.float() * inv) + int(zp), -128, 127).to(torch.int8)
+
+
+def linear_fpx_backward(x, weight, grad_output, bias_dtype=None, trun_bits=0, chunk_size=16, clamp_acc_to_dl16=False):
+    """LinearFuncFPxFwdBwd.backward with ``fp8_dyn="per_tensor"`` (fms_mo/modules/linear.py:1977-2058): e5m2 codes of
+    x, W and grad_output with one unclamped ``amax / 57344`` scale each, two fp32-accumulated matmuls with optional chunk
+    truncation, ``* grad_out_scale * scale`` and a cast; the bias gradient is the column sum of the (scaled) e5m2 gradient
+    codes.  Returns ``(grad_input, grad_weight, grad_bias)``."""
+    e5m2_max = torch.finfo(torch.float8_e5m2).max
+    dl8_min = 0.0087890625
+    out_dim, in_dim = weight.shape
+    x2 = x.reshape(-1, x.shape[-1])
+    dtype_input = x2.dtype
+    g2 = grad_output.reshape(-1, out_dim).to(dtype_input)
+    x_scale = x2.abs().amax(dim=None) / e5m2_max
+    w_scale = weight.abs().amax(dim=None) / e5m2_max
+    g_scale = g2.abs().amax(dim=None) / e5m2_max
+    xq = (x2 / x_scale).to(torch.float8_e5m2).to(torch.float)
+    wq = (weight / w_scale).to(torch.float8_e5m2).to(torch.float)
+    gq = (g2 / g_scale).to(torch.float8_e5m2).to(torch.float)
+    if clamp_acc_to_dl16:
+        xq.masked_fill_(xq.abs() < dl8_min, 0)
+        wq.masked_fill_(wq.abs() < dl8_min, 0)
+        gq.masked_fill_(gq.abs() < dl8_min, 0)
+    kw = dict(chunk_trun_bits=trun_bits, chunk_size=chunk_size, clamp_acc_to_dl16=clamp_acc_to_dl16)
+    grad_weight = (G.fmatmul_chunk_truncate(gq.transpose(0, 1).contiguous(), xq, **kw) * g_scale.t() * x_scale).to(weight.dtype)
+    grad_input = (G.fmatmul_chunk_truncate(gq, wq, **kw) * g_scale * w_scale).to(dtype_input)
+    grad_input = grad_input.reshape(grad_output.shape[:-1] + (in_dim,))
+    grad_bias = gq.sum(0).to(bias_dtype) if bias_dtype is not None else None
+    return grad_input, grad_weight, grad_bias

@@ -275,6 +275,36 @@ def gen_static_int8():
     return out
 
 
+def gen_fp8_per_tensor():
+    """LinearFPxAcc with dynamic_fp8="per_tensor": forward and backward of the reference's autograd function, its
+    ``tl_matmul`` callable replaced by oracle.gemm.fmatmul_chunk_truncate."""
+    torch.manual_seed(13)
+
+    def tl_matmul(a, b, chunk_trun_bits=0, chunk_size=16, clamp_acc_to_dl16=False, **kw):
+        return OG.fmatmul_chunk_truncate(a, b, chunk_trun_bits=chunk_trun_bits, chunk_size=chunk_size,
+                                         clamp_acc_to_dl16=clamp_acc_to_dl16)  # fmt: skip
+
+    ref_linear.tl_matmul = tl_matmul
+    cases = []
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        for trun, chunk, dl16, bias in ((0, 64, False, True), (8, 32, False, False), (0, 64, True, True)):
+            M, K, N = 24, 192, 80
+            x = torch.randn(M, K).to(dtype).requires_grad_(True)
+            nn_lin = torch.nn.Linear(K, N, bias=bias).to(dtype)
+            with torch.no_grad():
+                nn_lin.weight.copy_(torch.randn(N, K).to(dtype) * 0.3)
+            lin = ref_linear.LinearFPxAcc.from_nn(nn_lin, trun_bits=trun, chunk_size=chunk, dynamic_fp8="per_tensor",
+                                                  clamp_acc_to_dl16=dl16, target_device="cpu")  # fmt: skip
+            y = lin(x.reshape(2, 12, K))
+            g = torch.randn(2, 12, N).to(dtype)
+            y.backward(g)
+            cases.append(dict(dtype=dtype, trun=trun, chunk=chunk, dl16=dl16, x=x.detach().clone(), g=g,
+                              weight=nn_lin.weight.detach().clone(), bias=None if not bias else nn_lin.bias.detach().clone(),
+                              y=y.detach().clone(), gx=x.grad.clone(), gw=lin.weight.grad.clone(),
+                              gb=None if not bias else lin.bias.grad.clone()))  # fmt: skip
+    return cases
+
+
 _keep = []
 
 
@@ -349,6 +379,7 @@ def gen_extra():
             case[mode] = ref_q.to_fp8(8, q_mode=mode, **kw)(x * (300 if mode.endswith("sat") else 1)).clone()
         out["fp8_fake"].append(case)
     out.update(gen_static_int8())
+    out["fp8_train"] = gen_fp8_per_tensor()
     save("extra.pt", out)
 
 

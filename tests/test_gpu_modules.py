@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from conftest import load_golden
+from fms_model_optimizer_b200 import ops
 from fms_model_optimizer_b200.modules import LinearFPxAcc, QLinear, QLinearINT8Deploy, QLinearINT8Train
 from fms_model_optimizer_b200.modules.linear import lower_qmodel_b200
 from oracle import qlinear as OL
@@ -264,3 +265,49 @@ def test_fused_quantise_gemm_ops_match_reference_outputs(cuda_dev):
     y = torch.ops.qlin_b200.q_per_t_sym(x.to(cuda_dev), torch.tensor(0.0213), torch.tensor(3))
     assert torch.equal(y.cpu(), OL.q_per_t_sym(x, 0.0213, 3))
     assert torch.equal(y.cpu(), torch.quantize_per_tensor(x, 0.0213, 3, torch.qint8).int_repr())
+
+
+def test_linear_fp8_per_tensor_forward_backward_matches_reference_outputs(cuda_dev):
+    """dynamic_fp8="per_tensor": e4m3 forward and e5m2 backward against outputs and gradients of the reference's autograd
+    function.  Codes and scales are bit exact; the fp32 accumulation order is the kernel's own, so results agree to the
+    rounding of the output dtype (or of the truncated accumulator where truncation is on)."""
+    for c in load_golden("extra.pt")["fp8_train"]:
+        K, N = c["weight"].shape[1], c["weight"].shape[0]
+        lin = torch.nn.Linear(K, N, bias=c["bias"] is not None).to(c["dtype"])
+        with torch.no_grad():
+            lin.weight.copy_(c["weight"])
+            if c["bias"] is not None:
+                lin.bias.copy_(c["bias"])
+        q = LinearFPxAcc.from_nn(lin.to(cuda_dev), trun_bits=c["trun"], chunk_size=c["chunk"], dynamic_fp8="per_tensor",
+                                 clamp_acc_to_dl16=c["dl16"])
+        x = c["x"].reshape(2, 12, K).to(cuda_dev).requires_grad_(True)
+        y = q(x)
+        y.backward(c["g"].to(cuda_dev))
+        ulp = {torch.bfloat16: 2**-7, torch.float16: 2**-10, torch.float32: 2**-18}[c["dtype"]]
+        tol = (ulp * 2 if c["trun"] == 0 and not c["dl16"] else 2.0 ** (-(23 - max(c["trun"], 14 if c["dl16"] else 0)) + 3))
+        for name, got, want in (("y", y.detach(), c["y"]), ("gx", x.grad, c["gx"].reshape(2, 12, K)), ("gw", q.weight.grad, c["gw"])):
+            got = got.cpu()
+            assert got.dtype == want.dtype and got.shape == want.shape, name
+            err = (got.float() - want.float()).abs()
+            scale = want.float().abs().clamp(min=want.float().abs().mean().item())
+            assert (err <= tol * scale).all(), (name, c["dtype"], c["trun"], c["dl16"], err.max().item())
+        if c["bias"] is not None:
+            gb, want = q.bias.grad.cpu(), c["gb"]
+            assert gb.dtype == want.dtype
+            assert torch.allclose(gb.float(), want.float(), rtol=4 * ulp, atol=4 * ulp * want.float().abs().max().item())
+
+
+def test_e5m2_codes_bit_exact_and_gemm_exact_on_small_sums(cuda_dev):
+    g = torch.Generator().manual_seed(21)
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        x = (torch.randn(40, 96, generator=g) * 3).to(dtype)
+        want_scale = x.abs().amax(dim=None) / torch.finfo(torch.float8_e5m2).max
+        want = (x / want_scale).to(torch.float8_e5m2)
+        codes, scale = ops.fp8_quant_per_tensor(x.to(cuda_dev), e5m2=True, eps=0.0)
+        assert torch.equal(codes.cpu().view(torch.uint8), want.view(torch.uint8)), dtype
+        assert scale.cpu().item() == want_scale.float().item()
+    # e5m2 x e5m2 products of small integers sum exactly in fp32: the GEMM must be exact
+    a = torch.randint(-4, 5, (256, 128), generator=g).float().to(torch.float8_e5m2)
+    b = torch.randint(-4, 5, (384, 128), generator=g).float().to(torch.float8_e5m2)
+    out = ops.gemm(a.to(cuda_dev), b.to(cuda_dev))
+    assert torch.equal(out.cpu(), a.float() @ b.float().t())

@@ -232,3 +232,15 @@ def test_static_int8_linear_and_fused_ops_match_reference():
         assert y.dtype == c["y"].dtype and torch.equal(y, c["y"]), c["dtype"]
     for c in g["q_per_t_sym"]:
         assert torch.equal(OL.q_per_t_sym(c["x"], c["s"], c["zp"]), c["y"])
+
+
+def test_fp8_linear_per_tensor_forward_backward_matches_reference():
+    for c in load_golden("extra.pt")["fp8_train"]:
+        K = c["x"].shape[1]
+        x3 = c["x"].reshape(2, 12, K)
+        y = OL.linear_fpx_forward(x3, c["weight"], c["bias"], c["trun"], c["chunk"], "per_tensor", c["dl16"])
+        assert torch.equal(y, c["y"]), (c["dtype"], c["trun"], c["dl16"])
+        gx, gw, gb = OL.linear_fpx_backward(x3, c["weight"], c["g"], None if c["bias"] is None else c["bias"].dtype, c["trun"],
+                                            c["chunk"], c["dl16"])
+        assert torch.equal(gx, c["gx"].reshape(gx.shape)) and torch.equal(gw, c["gw"])
+        assert (gb is None and c["gb"] is None) or torch.equal(gb, c["gb"])
