@@ -597,6 +597,106 @@ def run_c5(args, rank, world, dev):
     print(json.dumps(line), flush=True)
 
 
+class BertQAT(torch.nn.Module):
+    """BERT-base-shaped encoder (12 layers, hidden 768, 12 heads, FFN 3072) whose 72 Linears are this package's QLinear with
+    PACT+ activations (clip values +-6) and SAWB+ per-channel weights: BASELINE config 4.  Embeddings, LayerNorm, GELU and
+    attention are PyTorch."""
+
+    def __init__(self, dev, layers=12, hidden=768, heads=12, ffn=3072, vocab=30522, seq=128, dtype=torch.bfloat16):
+        super().__init__()
+        from fms_model_optimizer_b200.modules import QLinear
+
+        def qlin(i, o):
+            return QLinear(i, o, bias=True, num_bits_feature=8, qa_mode="pact+", num_bits_weight=8, qw_mode="sawb+perCh",
+                           act_clip_init_val=6.0, act_clip_init_valn=-6.0, device=dev)  # fmt: skip
+
+        self.heads = heads
+        self.word = torch.nn.Embedding(vocab, hidden, device=dev)
+        self.pos = torch.nn.Embedding(seq, hidden, device=dev)
+        self.ln0 = torch.nn.LayerNorm(hidden, device=dev)
+        self.blocks = torch.nn.ModuleList()
+        for _ in range(layers):
+            self.blocks.append(torch.nn.ModuleDict(dict(
+                q=qlin(hidden, hidden), k=qlin(hidden, hidden), v=qlin(hidden, hidden), o=qlin(hidden, hidden),
+                ln1=torch.nn.LayerNorm(hidden, device=dev), up=qlin(hidden, ffn), down=qlin(ffn, hidden),
+                ln2=torch.nn.LayerNorm(hidden, device=dev),
+            )))  # fmt: skip
+        self.to(dtype)
+
+    def forward(self, ids):
+        B, S = ids.shape
+        x = self.ln0(self.word(ids) + self.pos(torch.arange(S, device=ids.device))[None])
+        for blk in self.blocks:
+            def heads(t):
+                return t.view(B, S, self.heads, -1).transpose(1, 2)
+            a = F.scaled_dot_product_attention(heads(blk["q"](x)), heads(blk["k"](x)), heads(blk["v"](x)))
+            x = blk["ln1"](x + blk["o"](a.transpose(1, 2).reshape(B, S, -1)))
+            x = blk["ln2"](x + blk["down"](F.gelu(blk["up"](x))))
+        return x
+
+
+def run_c4(args, dev):
+    """BASELINE config 4: QAT forward + backward of the BERT-base-shaped encoder on a 32 x 128 batch of random token ids
+    (seed 3), random-init weights.  One step = forward, a scalar loss, backward (no optimizer step, as the config says)."""
+    from fms_model_optimizer_b200 import ops
+
+    torch.manual_seed(3)
+    model = BertQAT(dev, layers=args.layers or 12)
+    model.train()
+    B, S = 32, 128
+    ids = torch.randint(0, 30522, (B, S), device=dev)
+    params = [p for p in model.parameters() if p.requires_grad]
+
+    def step():
+        for p in params:
+            p.grad = None
+        loss = model(ids).float().pow(2).mean()
+        loss.backward()
+        return loss
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    ops.check_status(dev)
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    ops.PROFILE, ops.LAUNCHES = [], 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    prof, ops.PROFILE = ops.PROFILE, None
+    clocks = sampler.stop()
+    by = {}
+    for name, a, b, work in prof:
+        t = by.setdefault(name, [0, 0.0, 0.0])
+        t[0] += 1
+        t[1] += a.elapsed_time(b)
+        t[2] += work
+    mine_ms = sum(t[1] for t in by.values()) / args.steps
+    pact = [by.get(k) for k in ("pact2_fwd", "pact2_bwd") if by.get(k)]
+    pact_gbs = sum(t[2] for t in pact) / (sum(t[1] for t in pact) * 1e-3) / 1e9 if pact else None
+    pk = peaks()
+    print(json.dumps({
+        "metric": "qat_bert_base_fwd_bwd_tokens_per_s", "value": B * S / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "c4: BERT-base-shaped encoder, 72 QLinear (PACT+ 8-bit activations, SAWB+ per-channel 8-bit weights), "
+                               "QAT forward + backward, batch 32 x 128", "layers": len(model.blocks),
+                   "l2": "activations 6-25 MB per tensor: L2 resident between kernels, as in the real step",
+                   "library_kernels_ms_per_step": mine_ms,
+                   "launches_per_step": {k: v[0] / args.steps for k, v in by.items()}},
+        "roofline": {"bound": "hbm", "kernel": "pact2_fwd / pact2_bwd", "achieved": pact_gbs, "peak": pk["hbm"], "unit": "GB/s",
+                     "frac": (pact_gbs / pk["hbm"]) if pact_gbs else None, "traffic": None,
+                     "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({pk['src']}); tensors of this workload fit in L2, so the "
+                                    "fraction can exceed what HBM alone would allow"},
+        "gpu_launches": ops.LAUNCHES, "clocks": clocks,
+    }), flush=True)  # fmt: skip
+
+
 def run_kernel_workload(args, dev):
     """Single-kernel workloads: c1 (W8A8 Linear 2048x4096x4096), c2 (chunk-truncated int8 GEMM
     4096x8192x4096, chunk 64, 8 bits), c3 (FP8 Linear sweep).  Prints one JSON line per shape."""
@@ -669,7 +769,7 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="c5", choices=["c5", "c1", "c2", "c3", "c5lin"])
+    ap.add_argument("--workload", default="c5", choices=["c5", "c1", "c2", "c3", "c4", "c5lin"])
     ap.add_argument("--layers", type=int, default=None, help="development only: fewer decoder layers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
@@ -703,7 +803,9 @@ def main():
             os.environ.setdefault("NCCL_MAX_CTAS", str(args.nccl_ctas))
         dist.init_process_group("nccl", device_id=dev)
     try:
-        if args.workload == "c5":
+        if args.workload == "c4":
+            run_c4(args, dev)
+        elif args.workload == "c5":
             run_c5(args, rank, world, dev)
         else:
             run_kernel_workload(args, dev)

@@ -597,10 +597,11 @@ class QLinear(nn.Linear):
     def forward(self, x):
         if self.smoothq:
             scale = self.get_smoothq_scale(x)
-        else:
-            scale = torch.tensor([1.0]).to(x.dtype).to(x.device)
-        qinput = self.quantize_feature(x / scale).to(x.dtype)
-        qweight = self.quantize_weight(self.weight * scale).to(self.weight.dtype)
+            qinput = self.quantize_feature(x / scale).to(x.dtype)
+            qweight = self.quantize_weight(self.weight * scale).to(self.weight.dtype)
+        else:  # the reference divides and multiplies by a tensor holding 1.0 here: the identity, bit for bit
+            qinput = self.quantize_feature(x).to(x.dtype)
+            qweight = self.quantize_weight(self.weight).to(self.weight.dtype)
         output = nn.functional.linear(qinput, qweight, self.bias)
         self.num_module_called += 1
         return output
