@@ -144,6 +144,7 @@ class Decoder:
         self.sp = None
         self.exchange = "stores"
         self.chain = False
+        self.scale_exchange = True
         self.streams = [torch.cuda.Stream(device=dev) for _ in range(n_micro)] if n_micro > 1 else []
 
         self.cfg = cfg
@@ -223,7 +224,7 @@ class Decoder:
 
         H, W, T = self.cfg["hidden"], self.world, tokens_per_group
         assert T % W == 0 and (T // W) % 128 == 0, "tokens per rank must be a multiple of 128"
-        per_group = T * H * 2 + 3 * (T * H + 4 * T) + 4096
+        per_group = T * H * 2 + 3 * (T * H + 4 * T) + 4 * W * T + 4096
         self.arena = PeerArena(max(1, self.n_micro) * per_group + 4096, self.dev)
         self.sp = []
         for _ in range(max(1, self.n_micro)):
@@ -239,6 +240,8 @@ class Decoder:
                 off, sc = self.arena.alloc(4 * T)
                 g["scale_off"].append(off)
                 g["scales"].append(sc.view(torch.float32)[:T])
+            g["sslot_off"], sl = self.arena.alloc(4 * W * T)  # per-token scales of a row-parallel layer, one slot per shard
+            g["sslots"] = sl.view(torch.float32)[: W * T]
             g["part_bases"] = [self.arena.addr(r, g["part_off"]) for r in range(W)]
             g["bases"] = [self.arena.addr(r, 0) for r in range(W)]
             if self.exchange == "copies":
@@ -270,6 +273,8 @@ class Decoder:
         parts = None
 
         H = x.shape[1]
+        # per-token scales of the row-parallel layers travel the same way as the activations (peer stores + barrier)
+        sx = (bar, g["bases"], g["sslot_off"], rank, g["sslots"]) if self.scale_exchange else None
         copies = self.exchange == "copies"
         arena = self.arena
 
@@ -312,13 +317,13 @@ class Decoder:
             a = F.scaled_dot_product_attention(q.view(B, S, self.nq, hd).transpose(1, 2), k.view(B, S, self.nkv, hd).transpose(1, 2),
                                                v.view(B, S, self.nkv, hd).transpose(1, 2), is_causal=True, enable_gqa=True)  # fmt: skip
             a = a.transpose(1, 2).reshape(T, self.nq * hd)
-            yield from row_parallel(lin["o"], lin["o"].quantise_fused(a))
+            yield from row_parallel(lin["o"], lin["o"].quantise_fused(a, exchange=sx))
             parts = g["part"]
             yield from shared_quant(lin["ln2"], [lin["gate"], lin["up"]])
             yield "compute"
             gt = lin["gate"](None, (g["codes"][0], g["scales"][0]), bf)
             u = lin["up"](None, (g["codes"][1], g["scales"][1]), bf)
-            yield from row_parallel(lin["down"], lin["down"].quantise_fused(gt, L.BLOCK_SILU_MUL, u))
+            yield from row_parallel(lin["down"], lin["down"].quantise_fused(gt, L.BLOCK_SILU_MUL, u, exchange=sx))
         yield "compute"
         # final norm of my token slice; the last token of every sequence goes to all ranks through one small all-reduce
         _, _, _, h = ops.block_quant(x, prologue=L.BLOCK_NORM, r=parts[0], r_parts=W, r_part_stride=Ts * x.shape[1], norm_w=self.norm,
@@ -573,7 +578,7 @@ def run_c5(args, rank, world, dev):
             "linear_tops": decoder_linear_ops(cfg, tokens, nl) * args.steps / (ms * 1e-3) / 1e12,
         },
         "roofline": {
-            "bound": "tensor", "kernel": "qlin_gemm_kernel<int8>", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "bound": "tensor", "kernel": "qlin_gemm_pair_kernel<int8> (all decoder GEMMs have at least 256 rows)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
             "frac": achieved / peak if peak else None, "traffic": None, "launches": n_gemm,
             "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({pk['src']}); no 8-bit peak was measured; "
                            f"datasheet dense int8 4500 TOPS -> frac {achieved / 4500.0:.3f}",

@@ -202,6 +202,8 @@ class BlockQuantArgs(C.Structure):
         ("codes", C.c_void_p * 3),
         ("scale_out", C.c_void_p * 3),
         ("scale_in", C.c_void_p),
+        ("scale_in_stride", C.c_int64),
+        ("scale_in_parts", C.c_int32),
         ("dst_base", C.c_void_p * 8),
         ("codes_off", C.c_int64 * 3),
         ("scale_off", C.c_int64 * 3),

@@ -32,6 +32,8 @@ struct BlockQuantParams {
   uint8_t* codes[3];
   float* scale_out[3];
   const float* scale_in;
+  int64_t scale_in_stride;
+  int32_t scale_in_parts;
   int64_t ldx, ldr, ldxo, ldh, ldq[3];
   int64_t r_part_stride;
   int32_t r_parts;
@@ -45,6 +47,13 @@ struct BlockQuantParams {
 
 __device__ __forceinline__ uint32_t bq_pack(float lo, float hi) {
   const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+// Packed pair arithmetic: two bf16 values of one word as float2, multiplied by two fp32 factors with one packed
+// instruction and rounded back to a bf16 pair with one packed conversion (the same roundings as the scalar forms).
+__device__ __forceinline__ float2 bq_unpack(uint32_t w) { return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xFFFF0000u)); }
+__device__ __forceinline__ uint32_t bq_mul_pack(uint32_t w, float2 f) {
+  const __nv_bfloat162 h = __float22bfloat162_rn(__fmul2_rn(bq_unpack(w), f));
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 __device__ __forceinline__ float bq_lo(uint32_t w) { return __uint_as_float(w << 16); }
@@ -132,7 +141,7 @@ __global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams
           float m[16];
           load16(p.mul[o] + ch * 16, m);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = bq_pack(__fmul_rn(bq_lo(h[j]), m[2 * j]), __fmul_rn(bq_hi(h[j]), m[2 * j + 1]));
+          for (int j = 0; j < 8; ++j) v[j] = bq_mul_pack(h[j], make_float2(m[2 * j], m[2 * j + 1]));
         } else {
 #pragma unroll
           for (int j = 0; j < 8; ++j) v[j] = h[j];
@@ -143,6 +152,9 @@ __global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams
       float s;
       if (p.mode == QLIN_BLOCK_GIVEN_SCALE) {
         s = p.scale_in[row];
+        // the shards of a row-parallel Linear each reported the scale of their slice: the row's scale is the largest
+        for (int k = 1; k < p.scale_in_parts; ++k) s = fmaxf(s, p.scale_in[k * p.scale_in_stride + row]);
+        if (threadIdx.x == 0 && p.scale_out[o] != nullptr) p.scale_out[o][row] = s;
       } else {
         float amax = fmaxf(__low2float(amax2), __high2float(amax2));
         amax = block_reduce<OpMax>(amax, red[flip], 0.0f);
@@ -157,17 +169,15 @@ __global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams
       }
       if (p.mode == QLIN_BLOCK_SCALE_ONLY || !active) continue;
       const float rs = __frcp_rn(s);
+      const float2 rs2 = make_float2(rs, rs);
+      const float2 magic = make_float2(12582912.0f, 12582912.0f);  // 1.5 * 2^23: the sum's low mantissa byte is rint's code
       uint32_t out[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
-        int q[4];
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const uint32_t t2 = bq_pack(__fmul_rn(bq_lo(v[2 * g + k]), rs), __fmul_rn(bq_hi(v[2 * g + k]), rs));
-          (void)fast_rint(bq_lo(t2), q[2 * k]);
-          (void)fast_rint(bq_hi(t2), q[2 * k + 1]);
-        }
-        out[g] = __byte_perm(__byte_perm(q[0], q[1], 0x0040), __byte_perm(q[2], q[3], 0x0040), 0x5410);
+        const float2 qa = __fadd2_rn(bq_unpack(bq_mul_pack(v[2 * g], rs2)), magic);
+        const float2 qb = __fadd2_rn(bq_unpack(bq_mul_pack(v[2 * g + 1], rs2)), magic);
+        out[g] = __byte_perm(__byte_perm(__float_as_uint(qa.x), __float_as_uint(qa.y), 0x0040),
+                             __byte_perm(__float_as_uint(qb.x), __float_as_uint(qb.y), 0x0040), 0x5410);
       }
       const uint4 packed = make_uint4(out[0], out[1], out[2], out[3]);
       if (p.ndst > 0) {
@@ -265,7 +275,9 @@ extern "C" int qlin_block_quant(const qlin_block_quant_args* a, void* stream) {
     }
   }
   if (a->ndst < 0 || a->ndst > 8) return fail(QLIN_ERR_BAD_SHAPE, "qlin_block_quant: at most 8 destinations");
-  if (a->ndst > 0 && a->mode != QLIN_BLOCK_DYN) return fail(QLIN_ERR_UNSUPPORTED, "qlin_block_quant: replicated outputs take the dynamic mode");
+  if (a->ndst > 0 && a->mode == QLIN_BLOCK_GIVEN_SCALE)
+    return fail(QLIN_ERR_UNSUPPORTED, "qlin_block_quant: replicated outputs take the dynamic or the scale-only mode");
+  if (a->scale_in_parts < 0 || a->scale_in_parts > 8) return fail(QLIN_ERR_BAD_SHAPE, "qlin_block_quant: scale_in_parts must be in [0, 8]");
   for (int d = 0; d < 8; ++d) {
     p.dst_base[d] = d < a->ndst ? static_cast<uint8_t*>(a->dst_base[d]) : nullptr;
     if (d < a->ndst && (p.dst_base[d] == nullptr || !aligned16(p.dst_base[d]))) return fail(QLIN_ERR_NULL, "qlin_block_quant: dst_base[%d] is NULL or unaligned", d);
@@ -278,6 +290,8 @@ extern "C" int qlin_block_quant(const qlin_block_quant_args* a, void* stream) {
   p.r_part_stride = a->r_part_stride;
   if (!ok) return fail(QLIN_ERR_BAD_ALIGN, "qlin_block_quant: pointers must be 16-byte aligned and leading dimensions multiples of 16 bytes");
   p.scale_in = a->scale_in;
+  p.scale_in_parts = a->scale_in_parts;
+  p.scale_in_stride = a->scale_in_stride;
   p.ldx = a->ldx;
   p.ldr = a->ldr;
   p.ldxo = a->ldxo;

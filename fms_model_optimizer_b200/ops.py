@@ -534,6 +534,8 @@ def block_quant(
     smooth_rcps: Sequence[Optional[torch.Tensor]] = (None,),
     mode: int = L.BLOCK_DYN,
     scale_in: Optional[torch.Tensor] = None,
+    scale_in_parts: int = 0,
+    scale_in_stride: int = 0,
     store_sum: bool = False,
     sum_into: Optional[torch.Tensor] = None,
     r_parts: int = 0,
@@ -560,7 +562,8 @@ def block_quant(
         codes, scales = [None] * nout, [None] * nout
     else:
         codes = [None if mode == L.BLOCK_SCALE_ONLY else torch.empty((rows, cols), dtype=torch.int8, device=dev) for _ in range(nout)]
-        scales = [scale_in if mode == L.BLOCK_GIVEN_SCALE else torch.empty((rows,), dtype=torch.float32, device=dev) for _ in range(nout)]
+        given_as_is = mode == L.BLOCK_GIVEN_SCALE and scale_in_parts <= 1
+        scales = [scale_in if given_as_is else torch.empty((rows,), dtype=torch.float32, device=dev) for _ in range(nout)]
     x_out = None
     if r is not None and sum_into is not None:
         x_out = sum_into
@@ -576,7 +579,7 @@ def block_quant(
         x=_ptr(x), r=_ptr(r), r_parts=int(r_parts), r_part_stride=int(r_part_stride), x_out=_ptr(x_out), h_out=_ptr(h_out),
         norm_w=_ptr(norm_w),
         smooth_rcp=p3(*[_ptr(t) for t in list(smooth_rcps) + pad]), codes=p3(*[_ptr(t) for t in codes + pad]),
-        scale_out=p3(*[(_ptr(t) if mode != L.BLOCK_GIVEN_SCALE else None) for t in scales + pad]), scale_in=_ptr(scale_in),
+        scale_out=p3(*[(_ptr(t) if (mode != L.BLOCK_GIVEN_SCALE or scale_in_parts > 1) else None) for t in scales + pad]), scale_in=_ptr(scale_in), scale_in_parts=int(scale_in_parts), scale_in_stride=int(scale_in_stride),
         ldx=x.stride(0), ldr=(r.stride(0) if r is not None else 0), ldxo=(x_out.stride(0) if x_out is not None else cols),
         ldh=cols, ldq=i3(cols, cols, cols),
         rows=rows, cols=cols, nout=nout, prologue=int(prologue), mode=int(mode), qmax_levels=int(levels),

@@ -92,10 +92,22 @@ class W8A8Linear:
             return codes, scale
         return self._q(x2, None)
 
-    def quantise_fused(self, x2: torch.Tensor, prologue: int = L.BLOCK_PLAIN, r: Optional[torch.Tensor] = None):
+    def quantise_fused(self, x2: torch.Tensor, prologue: int = L.BLOCK_PLAIN, r: Optional[torch.Tensor] = None, exchange=None):
         """Per-token codes and scales of ``prologue(x2, r) / smooth`` for bf16 rows through the fused kernel
-        (``ops.block_quant``); a row-parallel shard takes two passes around the MAX all-reduce of the scales."""
+        (``ops.block_quant``); a row-parallel shard takes two passes around the MAX all-reduce of the scales.
+        ``exchange = (barrier, peer base addresses, byte offset of the [world][tokens] fp32 slots, rank, local slots)``
+        replaces that all-reduce: the first pass stores this shard's scales into slot ``rank`` on every GPU, and after
+        the barrier the second pass takes the maximum over the slots itself."""
         rcp = [self.smooth_rcp]
+        if self.mode == "row" and self.world > 1 and exchange is not None:
+            bar, bases, slots_off, rank, slots = exchange
+            T = x2.shape[0]
+            ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_SCALE_ONLY,
+                            dst=(bases, [0], [slots_off + rank * T * 4], 0))
+            bar.wait()
+            (codes,), (scale,), _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_GIVEN_SCALE,
+                                                       scale_in=slots, scale_in_parts=self.world, scale_in_stride=T)
+            return codes, scale
         if self.mode == "row" and self.world > 1:
             _, (scale,), _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_SCALE_ONLY)
             dist.all_reduce(scale, op=dist.ReduceOp.MAX, group=self.group)

@@ -383,7 +383,8 @@ int64_t qlin_tensor_fq_workspace_bytes(int64_t numel);
  *   QLIN_BLOCK_DYN          s = bf16(max(amax|v|, dyn_eps) / qmax_levels) -> scale_out[o]; codes[o] = int8(rint(bf16(v / s)))
  *   QLIN_BLOCK_GIVEN_SCALE  s = scale_in[row] (one output): the second pass of a row-parallel shard,
  *                           after the scales of all shards were reduced with MAX
- *   QLIN_BLOCK_SCALE_ONLY   only scale_out[o] is written: the first pass of a row-parallel shard
+ *   QLIN_BLOCK_SCALE_ONLY   only scale_out[o] is written (or, with ndst > 0, stored to every destination): the first pass
+ *                           of a row-parallel shard
  * smooth_rcp[o][c] must be the correctly rounded fp32 reciprocal of a bf16-valued SmoothQuant scale
  * (the reference casts that scale to the activation dtype).  All tensors bf16, 16-byte aligned rows,
  * cols a multiple of 16 and at most 16384.  h_out (optional) receives h.
@@ -405,6 +406,9 @@ typedef struct qlin_block_quant_args {
   void* codes[3];       /* [rows, cols] int8 */
   float* scale_out[3];  /* [rows] */
   const float* scale_in;/* GIVEN_SCALE: [rows] */
+  int64_t scale_in_stride; /* GIVEN_SCALE with scale_in_parts > 1: elements between the parts */
+  int32_t scale_in_parts;  /* GIVEN_SCALE: 0 or 1 = scale_in as is; n > 1 = the row's scale is the maximum of n arrays
+                              (the scales the shards of a row-parallel Linear stored side by side) */
   /* Replicated outputs (the all-gather half of sequence parallelism, done by the kernel's own stores): when ndst > 0
      codes[o] and scale_out[o] are ignored; for every d < ndst the codes of output o go to
      (int8*)dst_base[d] + codes_off[o] at row dst_row0 + row (leading dimension ldq[o]) and the scales to
