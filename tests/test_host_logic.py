@@ -69,3 +69,38 @@ def test_qlinear_constructs_on_cpu_and_refuses_to_run():
     assert float(lin.quantize_feature.clip_val) == 6.0 and float(lin.quantize_feature.clip_valn) == -6.0
     with pytest.raises(RuntimeError):
         lin(torch.randn(4, 64))
+
+
+def test_quantizer_factories_map_mode_strings_like_the_reference():
+    """get_activation_quantizer / get_weight_quantizer (fms_mo/quant/quantizers.py:46-374): which class and which
+    arguments every mode string on the quantized-Linear path resolves to.  Construction needs no GPU."""
+    from fms_model_optimizer_b200.quant import quantizers as Q
+
+    a = Q.get_activation_quantizer("pact+", nbits=8, clip_val=6.0, clip_valn=-6.0)
+    assert isinstance(a, Q.PACT2) and a.clip_val.item() == 6.0 and a.clip_valn.item() == -6.0
+    a = Q.get_activation_quantizer("pact+", nbits=4, clip_val=5.0, clip_valn=0.0, non_neg=True)
+    assert isinstance(a, Q.PACT) and a.num_bits == 4 and a.clip_val.item() == 5.0
+    a = Q.get_activation_quantizer("pactsym+", nbits=8, clip_val=3.0, align_zero=True)
+    assert isinstance(a, Q.PACTplusSym) and a.intg_zp is True
+    assert isinstance(Q.get_activation_quantizer("pertokenmax", nbits=8), Q.QMaxDynamic)
+    a = Q.get_activation_quantizer("max", nbits=8, align_zero=False)
+    assert isinstance(a, Q.Qmax) and not a.perCh and a.align_zero is False
+    assert Q.get_activation_quantizer("maxsym", nbits=8, align_zero=False).align_zero is True
+    a = Q.get_activation_quantizer("fp8_e4m3_scale_perToken", nbits=8)
+    assert isinstance(a, Q.to_fp8) and a.perToken and not a.perCh
+    w = Q.get_weight_quantizer("sawb+", nbits=8, w_shape=(48, 80))
+    assert isinstance(w, Q.SAWB) and not w.perCh and w.clip_val.shape == (1,)
+    w = Q.get_weight_quantizer("sawb+perCh", nbits=4, w_shape=(48, 80))
+    assert isinstance(w, Q.SAWB) and w.perCh == 48 and w.clip_val.shape == (48,)
+    w = Q.get_weight_quantizer("maxperCh", nbits=8, w_shape=(48, 80))
+    assert isinstance(w, Q.Qmax) and w.perCh == 48
+    assert not Q.get_weight_quantizer("max", nbits=8, w_shape=(48, 80)).perCh
+    w = Q.get_weight_quantizer("pact+", nbits=8, w_shape=(48, 80), clip_val=2.5)
+    assert isinstance(w, Q.PACTplusSym) and w.clip_val.item() == 2.5
+    w = Q.get_weight_quantizer("fp8_e4m3_scale_perCh", nbits=8, w_shape=(48, 80))
+    assert isinstance(w, Q.to_fp8) and w.perCh == 48
+    for bad in ("lsq+", "dorefa"):
+        with pytest.raises(NotImplementedError):
+            Q.get_activation_quantizer(bad, nbits=8)
+    with pytest.raises(ValueError):
+        Q.to_fp8(8, q_mode="fp8_e5m2_sat")
