@@ -23,7 +23,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+if len(sys.argv) < 2:
+    raise SystemExit("usage: python tests/golden/make_golden.py /path/to/fms-model-optimizer")
+REF = Path(sys.argv[1])
 sys.path.insert(0, str(REF))
 sys.path.insert(0, str(ROOT))
 
