@@ -284,6 +284,32 @@ __device__ __forceinline__ void emit64(const GemmParams& p, const uint32_t (&v)[
         const __nv_bfloat162 o2 = __float22bfloat162_rn(t);
         w[j] = *reinterpret_cast<const uint32_t*>(&o2);
       }
+    } else if (!prod && p.out_dtype == QLIN_DT_BF16 && (p.mid_round == QLIN_DT_BF16 || p.mid_round == QLIN_DT_NONE) &&
+               (p.acc_round == QLIN_DT_BF16 || p.acc_round == QLIN_DT_NONE)) {
+      // (acc * rs) * cs, optional bf16 rounding, + bias, bf16: the chain of the FP8 Linear and of the fused ops, two columns
+      // per instruction; the final packed conversion is the last rounding
+      const bool mid_bf16 = p.mid_round == QLIN_DT_BF16;
+      const float2 rs2 = make_float2(rs, rs);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float2 a2;
+        if (F8) {
+          a2 = make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+        } else {
+          a2 = make_float2(__int2float_rn(static_cast<int32_t>(v[2 * j])), __int2float_rn(static_cast<int32_t>(v[2 * j + 1])));
+        }
+        float2 t = __fmul2_rn(__fmul2_rn(a2, rs2), *reinterpret_cast<const float2*>(s_cs + s_off + 2 * j));
+        if (has_bias) {
+          if (mid_bf16) {
+            const __nv_bfloat162 b2 = __float22bfloat162_rn(t);
+            const uint32_t bw = *reinterpret_cast<const uint32_t*>(&b2);
+            t = make_float2(__uint_as_float(bw << 16), __uint_as_float(bw & 0xFFFF0000u));
+          }
+          t = __fadd2_rn(t, *reinterpret_cast<const float2*>(s_bias + s_off + 2 * j));
+        }
+        const __nv_bfloat162 o2 = __float22bfloat162_rn(t);
+        w[j] = *reinterpret_cast<const uint32_t*>(&o2);
+      }
     } else {
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
