@@ -481,11 +481,16 @@ def run_c5(args, rank, world, dev):
     use_graph = args.graph == "on" or (args.graph == "auto" and world > 1)
     static_ids, static_out, graph = ids_dev.clone(), None, None
     if use_graph:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            static_out = model.forward(static_ids)
-        for _ in range(2):
-            graph.replay()
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                static_out = model.forward(static_ids)
+            for _ in range(2):
+                graph.replay()
+        except Exception as e:  # noqa: BLE001 -- every rank runs the same code, so all of them land here together
+            print(f"# CUDA graph capture failed ({type(e).__name__}: {e}); timing eager launches instead", file=sys.stderr, flush=True)
+            graph = None
+            torch.cuda.synchronize()
         barrier()
         ops.check_status(dev)
 
