@@ -224,6 +224,12 @@ class Decoder:
 
         H, W, T = self.cfg["hidden"], self.world, tokens_per_group
         assert T % W == 0 and (T // W) % 128 == 0, "tokens per rank must be a multiple of 128"
+        # load the attention library on every rank before the first flag barrier can start counting: a rank that is
+        # still reading shared objects from a cold disk must not make its peers' bounded waits run out
+        t = torch.zeros(1, 2, 128, self.cfg["head_dim"], dtype=torch.bfloat16, device=self.dev)
+        F.scaled_dot_product_attention(t, t, t, is_causal=True)
+        torch.cuda.synchronize(self.dev)
+        dist.barrier()
         per_group = T * H * 2 + 3 * (T * H + 4 * T) + 4 * W * T + 4096
         self.arena = PeerArena(max(1, self.n_micro) * per_group + 4096, self.dev)
         self.sp = []
@@ -820,7 +826,10 @@ def main():
     if world > 1:
         if args.nccl_ctas > 0:
             os.environ.setdefault("NCCL_MAX_CTAS", str(args.nccl_ctas))
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+
+        # a rank that fails must not leave the others waiting for NCCL's default ten minutes
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     try:
         if args.workload == "c4":
             run_c4(args, dev)

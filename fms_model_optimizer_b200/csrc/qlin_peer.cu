@@ -13,8 +13,8 @@
 //       Every rank stores the next epoch number into its slot of every peer's flag array
 //       (st.release.sys) and waits until all of its own slots show that epoch (ld.acquire.sys).
 //       Plain peer stores written by earlier kernels of the stream are visible to the peers' later
-//       kernels once the barrier has passed.  The wait is bounded by wall-clock time: when a peer
-//       never arrives the kernel records QLIN_ERR_TIMEOUT in `status` and returns.
+//       kernels once the barrier has passed.  The wait is bounded by wall-clock time (10 s): when a
+//       peer never arrives the kernel records QLIN_ERR_TIMEOUT in `status` and returns.
 #include <cstring>
 
 #include <cuda.h>
@@ -23,7 +23,7 @@
 
 namespace qlin {
 
-constexpr unsigned long long kBarrierTimeoutNs = 2000000000ull;  // 2 s
+constexpr unsigned long long kBarrierTimeoutNs = 10000000000ull;  // 10 s: peers may still be loading libraries on their first step
 
 __device__ __forceinline__ unsigned long long peer_now_ns() {
   unsigned long long t;

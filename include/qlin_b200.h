@@ -450,7 +450,7 @@ int qlin_rope(const qlin_rope_args* args, void* stream);
  *   qlin_ipc_open     maps a peer's allocation into this process (peer access is enabled on first use);
  *                     base_out is what qlin_ipc_close takes, ptr_out = base + offset.
  *   qlin_peer_barrier launches a one-warp kernel: rank stores the next epoch into slot `rank` of every
- *                     peer's flag array and waits (at most 2 s, then QLIN_ERR_TIMEOUT in *status) until all
+ *                     peer's flag array and waits (at most 10 s, then QLIN_ERR_TIMEOUT in *status) until all
  *                     `world` slots of its own array carry it.  Stores made to peer memory by earlier work of
  *                     the stream are visible to the peers' work after their barrier.  `epoch` is a device
  *                     counter owned by this barrier object; flag arrays and epoch start zeroed.
