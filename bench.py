@@ -145,6 +145,7 @@ class Decoder:
         self.exchange = "stores"
         self.chain = False
         self.scale_exchange = True
+        self.reserve_sms = 0
         self.streams = [torch.cuda.Stream(device=dev) for _ in range(n_micro)] if n_micro > 1 else []
 
         self.cfg = cfg
@@ -292,7 +293,8 @@ class Decoder:
             else:  # the kernel stores to every rank's buffers itself
                 dst = (g["bases"], g["codes_off"][:n], g["scale_off"][:n], rank * Ts)
             ops.block_quant(x, prologue=L.BLOCK_NORM, r=(parts[0] if parts is not None else None), r_parts=(W if parts is not None else 0),
-                            r_part_stride=Ts * H, norm_w=norm_w, smooth_rcps=[l.smooth_rcp for l in lins], sum_into=x, dst=dst)  # fmt: skip
+                            r_part_stride=Ts * H, norm_w=norm_w, smooth_rcps=[l.smooth_rcp for l in lins], sum_into=x, dst=dst,
+                            max_ctas=(4 * self.reserve_sms if not copies else 0))  # fmt: skip
             if copies:
                 yield "comm"
                 src = g["stage"].data_ptr()
@@ -463,6 +465,16 @@ def run_c5(args, rank, world, dev):
     if world > 1 and not args.allreduce:
         model.exchange = args.exchange
         model.chain = args.chain
+        if n_micro > 1 and args.reserve_sms > 0 and args.exchange == "stores":
+            # SM partition between the groups' streams: kernels bound by the links (row-parallel GEMMs storing to the
+            # peers, the quantiser replicating its codes) run on `reserve` SMs, the compute-bound GEMMs on the rest, so a
+            # kernel of each kind fits on the GPU at the same time
+            sms = torch.cuda.get_device_properties(dev).multi_processor_count
+            model.reserve_sms = args.reserve_sms
+            for lin in model.layers:
+                for name, l_ in lin.items():
+                    if hasattr(l_, "max_ctas"):
+                        l_.max_ctas = args.reserve_sms if name in ("o", "down") else sms - args.reserve_sms
         model.enable_sequence_parallel(cfg["batch"] * cfg["seq"] // n_micro)
     nl = len(model.layers)
     B, S = cfg["batch"], cfg["seq"]
@@ -783,7 +795,9 @@ def run_kernel_workload(args, dev):
             "dtype": dt, "data": "synthetic",
             "config": {"workload": name, "l2": "256 MB flush between timed launches", "launch": "CUDA graph replay of the call"},
             "roofline": {"bound": "tensor", "achieved": tops, "peak": 2.0 * pk["bf16"], "unit": "TFLOP/s",
-                         "frac": tops / (2.0 * pk["bf16"]), "traffic": None,
+                         "frac": tops / (2.0 * pk["bf16"]),
+                         # DRAM bytes of the GEMM launch from the ncu capture of this very shape (profiles/qlin_gemm_pair_*)
+                         "traffic": (86.8e6 + 97.6e6) if args.workload == "c5lin" else None,
                          "peak_source": f"2 x bf16_tflops (burst) of MEASURED_PEAKS.json ({pk['src']})"},
         }), flush=True)  # fmt: skip
 
@@ -799,6 +813,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the forward pass as one CUDA graph in the timed region (auto: sharded runs only)")
+    ap.add_argument("--reserve-sms", type=int, default=0, help="sharded runs with several groups: SMs set aside for the kernels that "
+                    "are bound by the links (even; 0: no partition)")
     ap.add_argument("--chain", action="store_true", help="sharded runs with several groups: run the groups' compute segments strictly "
                     "one after the other (event chain) so that one group's transfers overlap the other's kernels")
     ap.add_argument("--exchange", default="stores", choices=["stores", "copies"],

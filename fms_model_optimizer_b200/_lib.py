@@ -222,6 +222,7 @@ class BlockQuantArgs(C.Structure):
         ("qmax_levels", C.c_int32),
         ("norm_eps", C.c_float),
         ("dyn_eps", C.c_float),
+        ("max_ctas", C.c_int32),
     ]
 
 

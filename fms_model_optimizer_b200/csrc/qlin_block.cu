@@ -43,6 +43,7 @@ struct BlockQuantParams {
   uint8_t* dst_base[8];
   int64_t codes_off[3], scale_off[3];
   int32_t ndst, dst_row0;
+  int32_t max_ctas;
 };
 
 __device__ __forceinline__ uint32_t bq_pack(float lo, float hi) {
@@ -284,6 +285,7 @@ extern "C" int qlin_block_quant(const qlin_block_quant_args* a, void* stream) {
   }
   p.ndst = a->ndst;
   p.dst_row0 = a->dst_row0;
+  p.max_ctas = a->max_ctas;
   if (a->r_parts < 0 || a->r_parts > 8 || (a->r_parts > 1 && a->r_part_stride % 8 != 0))
     return fail(QLIN_ERR_BAD_SHAPE, "qlin_block_quant: r_parts must be in [0, 8] with a part stride that is a multiple of 8 elements");
   p.r_parts = a->r_parts;
@@ -309,10 +311,12 @@ extern "C" int qlin_block_quant(const qlin_block_quant_args* a, void* stream) {
   if (nchunks <= 256) {
     int grid = sm_count() * 8;
     if (grid > p.rows) grid = p.rows;
+    if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
     block_quant_kernel<256><<<grid, 256, 0, s>>>(p);
   } else {
     int grid = sm_count() * 2;
     if (grid > p.rows) grid = p.rows;
+    if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
     block_quant_kernel<1024><<<grid, 1024, 0, s>>>(p);
   }
   QLIN_CHECK_LAUNCH("qlin_block_quant");

@@ -142,6 +142,7 @@ def gemm(
     mid_round: Optional[torch.dtype] = None,
     acc_round: Optional[torch.dtype] = None,
     scatter: Optional[Tuple[Sequence[int], int, int]] = None,
+    max_ctas: Optional[int] = None,
     out_dtype: Optional[torch.dtype] = None,
 ) -> torch.Tensor:
     """``D[M,N] = epilogue(C + sum_chunks f(A_c @ B_c^T))`` with A ``[M,K]`` and B ``[N,K]`` (both
@@ -201,7 +202,7 @@ def gemm(
         row_scale_stride=(0 if rs is None or rs.numel() == 1 else 1),
         col_scale_stride=(0 if cs is None or cs.numel() == 1 else 1),
         prod_round=_ROUND[prod_round], scale_round=_ROUND[scale_round], mid_round=_ROUND[mid_round], acc_round=_ROUND[acc_round],
-        out_dtype=_DT[out_dtype], max_ctas=int(GEMM_MAX_CTAS),
+        out_dtype=_DT[out_dtype], max_ctas=int(GEMM_MAX_CTAS if max_ctas is None else max_ctas),
     )  # fmt: skip
     if scatter is not None:
         bases = list(scatter[0]) + [None] * (8 - len(scatter[0]))
@@ -542,6 +543,7 @@ def block_quant(
     r_part_stride: int = 0,
     dst: Optional[Tuple[Sequence[int], Sequence[int], Sequence[int], int]] = None,
     want_h: bool = False,
+    max_ctas: int = 0,
     levels: int = 127,
     norm_eps: float = 1e-5,
     dyn_eps: float = 1e-5,
@@ -583,7 +585,7 @@ def block_quant(
         ldx=x.stride(0), ldr=(r.stride(0) if r is not None else 0), ldxo=(x_out.stride(0) if x_out is not None else cols),
         ldh=cols, ldq=i3(cols, cols, cols),
         rows=rows, cols=cols, nout=nout, prologue=int(prologue), mode=int(mode), qmax_levels=int(levels),
-        norm_eps=float(norm_eps), dyn_eps=float(dyn_eps),
+        norm_eps=float(norm_eps), dyn_eps=float(dyn_eps), max_ctas=int(max_ctas),
     )  # fmt: skip
     ndst = 1
     if dst is not None:

@@ -76,6 +76,7 @@ class W8A8Linear:
         self.world = dist.get_world_size(group) if (group is not None or (dist.is_available() and dist.is_initialized())) else 1
         self.quant_fn = quant_fn or _cuda_quant
         self.gemm_fn = gemm_fn or _cuda_gemm
+        self.max_ctas = None  # cap on the GEMM's grid (None: ops.GEMM_MAX_CTAS), set by a caller that overlaps streams
 
     def _q(self, x2, given_scale):
         if self.quant_fn is _cuda_quant:
@@ -122,7 +123,8 @@ class W8A8Linear:
         The owner of a token block later sums the ``world`` partials (``ops.block_quant`` with ``r_parts``)."""
         codes, scale = quantised
         prod_dtype = torch.promote_types(act_dtype, self.w_scale_dtype)
-        self.gemm_fn(codes, self.weight, scale, self.w_scale, self.bias, act_dtype, prod_dtype, scatter=(bases, rows_per_rank, row0))
+        kw = {} if self.gemm_fn is not _cuda_gemm else {"max_ctas": self.max_ctas}
+        self.gemm_fn(codes, self.weight, scale, self.w_scale, self.bias, act_dtype, prod_dtype, scatter=(bases, rows_per_rank, row0), **kw)
 
     def __call__(self, x2: Optional[torch.Tensor], quantised=None, act_dtype: Optional[torch.dtype] = None,
                  reduce: bool = True) -> torch.Tensor:
@@ -132,7 +134,8 @@ class W8A8Linear:
         codes, scale = quantised if quantised is not None else self.quantise(x2)
         act_dtype = act_dtype if x2 is None else x2.dtype
         prod_dtype = torch.promote_types(act_dtype, self.w_scale_dtype)
-        out = self.gemm_fn(codes, self.weight, scale, self.w_scale, self.bias, act_dtype, prod_dtype)
+        kw = {} if self.gemm_fn is not _cuda_gemm else {"max_ctas": self.max_ctas}
+        out = self.gemm_fn(codes, self.weight, scale, self.w_scale, self.bias, act_dtype, prod_dtype, **kw)
         if reduce and self.mode == "row" and self.world > 1:
             dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
         return out
@@ -151,8 +154,8 @@ def _cuda_quant(x2, smooth, given_scale, smooth_rcp=None, smooth_is_bf16=False):
     return codes, scale
 
 
-def _cuda_gemm(codes, weight, scale, w_scale, bias, out_dtype, prod_dtype, scatter=None, out=None):
+def _cuda_gemm(codes, weight, scale, w_scale, bias, out_dtype, prod_dtype, scatter=None, out=None, max_ctas=None):
     # (acc.float() * (input_scale * w_scale).to(fp16) + bias).to(fp16).to(out_dtype), linear.py:1185-1188, :1338
     return ops.gemm(codes, weight, epilogue=L.EPI_SCALE_PROD, row_scale=scale, col_scale=w_scale, bias=bias,
                     prod_round=(None if prod_dtype == torch.float32 else prod_dtype), scale_round=torch.float16,
-                    acc_round=torch.float16, out_dtype=out_dtype, scatter=scatter, out=out)  # fmt: skip
+                    acc_round=torch.float16, out_dtype=out_dtype, scatter=scatter, out=out, max_ctas=max_ctas)  # fmt: skip

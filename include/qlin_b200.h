@@ -424,6 +424,8 @@ typedef struct qlin_block_quant_args {
   int32_t mode;         /* qlin_block_mode */
   int32_t qmax_levels;
   float norm_eps, dyn_eps;
+  int32_t max_ctas;     /* 0: fill the GPU; > 0: at most this many blocks, leaving SMs to kernels of other streams (a launch
+                           whose replicated outputs are bound by the links anyway) */
 } qlin_block_quant_args;
 
 int qlin_block_quant(const qlin_block_quant_args* args, void* stream);
