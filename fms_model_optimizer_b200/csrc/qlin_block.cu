@@ -72,11 +72,25 @@ __device__ __forceinline__ void bq_store8(__nv_bfloat16* p, const uint32_t (&w)[
 }
 
 template <int TPB>
-__global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams p) {
+__global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams p, int mul_in_smem) {
+  // The reciprocal SmoothQuant vectors are the same for every row: with `mul_in_smem` the block copies them into shared
+  // memory once, quarter-transposed ([output][quarter][slice] of four floats) so that the four 16-byte reads of a
+  // thread's slice are conflict free, instead of re-reading them through L1 for every row and output.
+  extern __shared__ __align__(16) float mul_s[];
   __shared__ float red[2][32];
   const int nchunks = p.cols >> 4;
   const int ch = threadIdx.x;
   const bool active = ch < nchunks;
+  if (mul_in_smem) {
+    for (int o = 0; o < p.nout; ++o) {
+      if (p.mul[o] == nullptr) continue;
+      for (int i = threadIdx.x; i < nchunks * 4; i += TPB) {
+        const int c = i >> 2, q = i & 3;
+        reinterpret_cast<float4*>(mul_s)[(o * 4 + q) * nchunks + c] = reinterpret_cast<const float4*>(p.mul[o])[i];
+      }
+    }
+    __syncthreads();
+  }
   const float eps = Elem<__nv_bfloat16>::rnd(p.dyn_eps);
   const float inv_cols = 1.0f / static_cast<float>(p.cols);
   int flip = 0;
@@ -140,7 +154,15 @@ __global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams
       if (active) {
         if (p.mul[o] != nullptr) {
           float m[16];
-          load16(p.mul[o] + ch * 16, m);
+          if (mul_in_smem) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 f = reinterpret_cast<const float4*>(mul_s)[(o * 4 + q) * nchunks + ch];
+              m[4 * q] = f.x, m[4 * q + 1] = f.y, m[4 * q + 2] = f.z, m[4 * q + 3] = f.w;
+            }
+          } else {
+            load16(p.mul[o] + ch * 16, m);
+          }
 #pragma unroll
           for (int j = 0; j < 8; ++j) v[j] = bq_mul_pack(h[j], make_float2(m[2 * j], m[2 * j + 1]));
         } else {
@@ -308,16 +330,30 @@ extern "C" int qlin_block_quant(const qlin_block_quant_args* a, void* stream) {
   p.dyn_eps = a->dyn_eps;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int nchunks = p.cols / 16;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(block_quant_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 49152) != cudaSuccess ||
+        cudaFuncSetAttribute(block_quant_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 98304) != cudaSuccess)
+      return fail(QLIN_ERR_LAUNCH, "cudaFuncSetAttribute failed for qlin_block_quant");
+    configured[dev] = true;
+  }
   if (nchunks <= 256) {
     int grid = sm_count() * 8;
     if (grid > p.rows) grid = p.rows;
     if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
-    block_quant_kernel<256><<<grid, 256, 0, s>>>(p);
+    // the vectors fit beside four resident blocks per SM: 3 outputs x 16 KB
+    const int smem = p.nout * p.cols * 4;
+    const bool in_smem = smem > 0 && smem <= 49152 && p.rows >= 4 * grid;
+    block_quant_kernel<256><<<grid, 256, in_smem ? smem : 0, s>>>(p, in_smem ? 1 : 0);
   } else {
     int grid = sm_count() * 2;
     if (grid > p.rows) grid = p.rows;
     if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
-    block_quant_kernel<1024><<<grid, 1024, 0, s>>>(p);
+    const int smem = p.nout * p.cols * 4;
+    const bool in_smem = smem > 0 && smem <= 98304 && p.rows >= 4 * grid;
+    block_quant_kernel<1024><<<grid, 1024, in_smem ? smem : 0, s>>>(p, in_smem ? 1 : 0);
   }
   QLIN_CHECK_LAUNCH("qlin_block_quant");
   return QLIN_OK;
