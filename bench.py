@@ -4,29 +4,30 @@ Default workload ("c5"): prefill of a Llama-3-8B-shaped decoder (32 layers, hidd
 heads of 128, SwiGLU FFN 14336, RMSNorm, RoPE theta 5e5, vocab 128256) whose every Linear inside the
 decoder layers is W8A8 SmoothQuant INT8 (alpha 0.5, per-channel weights, per-token activations), on a
 batch of 8 x 2048 random token ids.  With N > 1 GPUs the Linears are sharded column / row parallel
-(tensor parallel), one process per GPU, NCCL all-reduce at the row-parallel boundaries; the total
-work is fixed, so scaling is "strong".
+(tensor parallel), one process per GPU; the total work is fixed, so scaling is "strong".
 
     python bench.py --gpus N --steps K --warmup W                  # this implementation
     python bench.py --impl reference --gpus N --steps K --warmup W # reference CPU fake-quant path
 
-One JSON line is printed by rank 0.  `value` is tokens/s of the whole job with the token ids
-already on the device; `e2e` is the same with the ids copied from pinned host memory and the
-next-token ids copied back inside the timed region.  `roofline` is the int8 GEMM kernel (all its
-launches in the timed region, timed with CUDA events on the launching stream); `cpu_baseline` is
-the reference's CPU fake-quant arithmetic (QLinear.forward: per-token / per-channel fake quantise +
-F.linear) for one decoder layer on a bounded token sample, extrapolated to the 32 layers.
+One JSON line is printed by rank 0.  `value` is tokens/s of the whole job with the token ids already on
+the device; `e2e` is the same with the ids copied from pinned host memory and the next-token ids copied
+back inside the timed region.  `roofline` is the int8 GEMM kernel (all its launches in one step, timed
+with CUDA events on the launching stream in extra steps right after the timed region).  On one GPU the
+line also carries `surfaces` (the same decoder built from QLinear -> lower_qmodel_b200 ->
+QLinearINT8Deploy modules), `kernels` (every kernel family on the shapes the metric names, INT8 and FP8,
+with its bound and fraction of peak), `comparators` (cuBLASLt int8 and fp8 GEMMs through torch, same run)
+and `cpu_baseline` (the reference's CPU fake-quant QLinear.forward for one decoder layer on a bounded
+token sample).
 
-Other workloads, for single kernels: --workload c1 | c2 | c3 | c5lin (TOPS of one quantized Linear / GEMM;
-c5lin is one 16384 x 4096 x 4096 Linear of the c5 decoder).
-Weights and activations are synthetic (seeded); nothing is read from disk.
+Other workloads print single lines: --workload c1 | c2 | c3 | c5lin (one quantized Linear / GEMM), c4
+(BERT-base-shaped QAT forward + backward).  Weights and activations are synthetic (seeded); nothing is
+read from disk.
 """
 
 from __future__ import annotations
 
 import argparse
 import json
-import math
 import os
 import subprocess
 import sys
@@ -41,8 +42,12 @@ import torch.nn.functional as F
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-LLAMA = dict(layers=32, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, ffn=14336, vocab=128256, rope_theta=500000.0,
-             batch=8, seq=2048)  # fmt: skip
+DATASHEET_8BIT_TOPS = 4500.0  # NVIDIA's dense int8 / fp8 figure for one B200
+# DRAM bytes per launch of the CTA-pair int8 GEMM on 16384 x 4096 x 4096 with bf16 output from its ncu capture
+# (dram__bytes_read.sum + dram__bytes_write.sum, profiles/qlin_gemm_pair_int8_c5lin_16384x4096x4096.md), and the
+# algorithmic bytes of that launch (A + B + D)
+C5LIN_DRAM_BYTES = 86.8e6 + 97.6e6
+C5LIN_ALGO_BYTES = 16384 * 4096 + 4096 * 4096 + 16384 * 4096 * 2
 
 
 def peaks():
@@ -76,6 +81,7 @@ class ClockSampler:
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
             self.proc = None
+        return self
 
     def _pump(self):
         for line in self.proc.stdout:
@@ -110,373 +116,348 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------
-# synthetic W8A8 decoder
+# CPU arm: the reference's fake-quant QLinear on the host cores
 # ------------------------------------------------------------------------------------------------
-def synth_w8a8(n, k, seed, dev, dtype=torch.bfloat16):
-    """Random-init Linear [n, k] (N(0, 0.02)) turned into W8A8 SmoothQuant buffers the way
-    QLinearINT8Deploy.from_fms_mo does it (fms_mo/modules/linear.py:799-871): synthetic activation
-    scales (1% outlier channels x20), smoothing scale with alpha 0.5, per-channel max weight scale,
-    int8 codes."""
-    g = torch.Generator(device=dev).manual_seed(seed)
-    w = (torch.randn(n, k, generator=g, device=dev) * 0.02).to(dtype)
-    act = torch.full((k,), 4.0, device=dev)
-    idx = torch.randperm(k, generator=g, device=dev)[: max(1, k // 100)]
-    act[idx] *= 20
-    act = act.to(dtype)
-    w_sq = w.abs().max(dim=0, keepdim=True)[0].clamp(min=1e-5)
-    smooth = (act**0.5 / w_sq**0.5).clamp(min=1e-5).to(dtype)
-    ws = w * smooth
-    w_cv = ws.abs().max(dim=1).values
-    w_scale = w_cv * 2 / 254
-    codes = torch.round(ws.t() / w_scale).clamp(-127, 127).t().to(torch.int8).contiguous()
-    return codes, w_scale.float(), smooth.reshape(-1).float()
+def _reference_qlinear_class():
+    """fms-model-optimizer's own QLinear when the reference was installed under baseline/_ref (it is not part of this
+    repository's history), else None."""
+    ref = ROOT / "baseline" / "_ref"
+    if not (ref / "fms_mo").is_dir():
+        return None
+    sys.path.insert(0, str(ref))
+    try:
+        import warnings
+
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            from fms_mo.modules.linear import QLinear  # noqa: PLC0415
+        return QLinear
+    except Exception as e:  # noqa: BLE001
+        print(f"# reference import failed ({type(e).__name__}: {e}); timing the port instead", file=sys.stderr, flush=True)
+        return None
+    finally:
+        sys.path.remove(str(ref))
 
 
-class Decoder:
-    """Llama-shaped decoder whose Linears are ``tp.W8A8Linear``; norms, RoPE, attention and SwiGLU
-    are plain PyTorch ops on the device (they are not part of the quantized-Linear path)."""
-
-    def __init__(self, cfg, dev, world, rank, layers=None, n_micro=1):
-        from fms_model_optimizer_b200 import tp
-
-        self.n_micro = n_micro
-        self.rank = rank
-        self.sp = None
-        self.exchange = "stores"
-        self.chain = False
-        self.scale_exchange = True
-        self.reserve_sms = 0
-        self.streams = [torch.cuda.Stream(device=dev) for _ in range(n_micro)] if n_micro > 1 else []
-
-        self.cfg = cfg
-        self.dev = dev
-        self.world = world
-        H, hd = cfg["hidden"], cfg["head_dim"]
-        self.nq, self.nkv = cfg["q_heads"] // world, cfg["kv_heads"] // world
-        nl = layers if layers is not None else cfg["layers"]
-        self.layers = []
-        for li in range(nl):
-            lin = {}
-            for ni, (name, (n, k, mode)) in enumerate(dict(
-                q=(cfg["q_heads"] * hd, H, "column"), k=(cfg["kv_heads"] * hd, H, "column"), v=(cfg["kv_heads"] * hd, H, "column"),
-                o=(H, cfg["q_heads"] * hd, "row"), gate=(cfg["ffn"], H, "column"), up=(cfg["ffn"], H, "column"),
-                down=(H, cfg["ffn"], "row"),
-            ).items()):  # fmt: skip
-                codes, w_scale, smooth = synth_w8a8(n, k, 1000 * li + ni, dev)
-                wt, sc, sm, _ = tp.shard_w8a8(codes, w_scale, smooth, None, mode, world, rank)
-                lin[name] = tp.W8A8Linear(wt, sc, sm, None, mode=mode if world > 1 else "replicate")
-                del codes
-            lin["ln1"] = torch.ones(H, device=dev, dtype=torch.bfloat16)
-            lin["ln2"] = torch.ones(H, device=dev, dtype=torch.bfloat16)
-            self.layers.append(lin)
-        g = torch.Generator(device=dev).manual_seed(4)
-        self.embed = (torch.randn(cfg["vocab"], H, generator=g, device=dev) * 0.02).bfloat16()
-        self.lm_head = (torch.randn(cfg["vocab"], H, generator=g, device=dev) * 0.02).bfloat16()
-        self.norm = torch.ones(H, device=dev, dtype=torch.bfloat16)
-        S = cfg["seq"]
-        inv = 1.0 / (cfg["rope_theta"] ** (torch.arange(0, hd, 2, device=dev).float() / hd))
-        ang = torch.outer(torch.arange(S, device=dev).float(), inv)
-        self.cos, self.sin = ang.cos().contiguous(), ang.sin().contiguous()  # fp32 [S, hd / 2]
-
-    def _forward_steps(self, ids):
-        """The forward pass of one group of sequences as a generator: it yields after every row-parallel
-        Linear (whose all-reduce has just been queued), so that a driver can advance another group on another
-        stream while the collective runs.  Returns the next-token ids through StopIteration."""
-        from fms_model_optimizer_b200 import _lib as L
-        from fms_model_optimizer_b200 import ops
-
-        cfg = self.cfg
-        B, S = ids.shape
-        hd = cfg["head_dim"]
-        bf = torch.bfloat16
-        x = F.embedding(ids, self.embed).view(B * S, -1)
-        pending = None  # output of the last row-parallel Linear, added to the stream by the next fused kernel
-        for lin in self.layers:
-            # (x += pending) -> RMSNorm -> per-token int8 codes for q, k, v: one pass over the stream
-            cs, ss, xs, _ = ops.block_quant(x, prologue=L.BLOCK_NORM, r=pending, norm_w=lin["ln1"], store_sum=True,
-                                            smooth_rcps=[lin["q"].smooth_rcp, lin["k"].smooth_rcp, lin["v"].smooth_rcp])  # fmt: skip
-            x = xs if xs is not None else x
-            q = ops.rope_(lin["q"](None, (cs[0], ss[0]), bf).view(B * S, self.nq, hd), self.cos, self.sin, S)
-            k = ops.rope_(lin["k"](None, (cs[1], ss[1]), bf).view(B * S, self.nkv, hd), self.cos, self.sin, S)
-            v = lin["v"](None, (cs[2], ss[2]), bf)
-            del cs, ss
-            a = F.scaled_dot_product_attention(q.view(B, S, self.nq, hd).transpose(1, 2), k.view(B, S, self.nkv, hd).transpose(1, 2),
-                                               v.view(B, S, self.nkv, hd).transpose(1, 2), is_causal=True, enable_gqa=True)  # fmt: skip
-            a = a.transpose(1, 2).reshape(B * S, self.nq * hd)
-            pending = lin["o"](None, lin["o"].quantise_fused(a), bf)
-            yield
-            cs, ss, x, _ = ops.block_quant(x, prologue=L.BLOCK_NORM, r=pending, norm_w=lin["ln2"], store_sum=True,
-                                           smooth_rcps=[lin["gate"].smooth_rcp, lin["up"].smooth_rcp])  # fmt: skip
-            g = lin["gate"](None, (cs[0], ss[0]), bf)
-            u = lin["up"](None, (cs[1], ss[1]), bf)
-            del cs, ss
-            pending = lin["down"](None, lin["down"].quantise_fused(g, L.BLOCK_SILU_MUL, u), bf)
-            yield
-        last = x.view(B, S, -1)[:, -1] + pending.view(B, S, -1)[:, -1]
-        last = F.rms_norm(last, (last.shape[-1],), self.norm, 1e-5)
-        logits = last @ self.lm_head.t()
-        return logits.argmax(-1)
-
-    def enable_sequence_parallel(self, tokens_per_group):
-        """Buffers for the sharded forward that keeps the residual stream split by tokens: per group of sequences,
-        a receive buffer for the row-parallel Linears' partial outputs ([world][tokens / world, hidden] bf16), the
-        int8 codes and scales of up to three Linear inputs for all tokens, and a barrier."""
-        from fms_model_optimizer_b200.peer import PeerArena, PeerBarrier
-
-        H, W, T = self.cfg["hidden"], self.world, tokens_per_group
-        assert T % W == 0 and (T // W) % 128 == 0, "tokens per rank must be a multiple of 128"
-        # load the attention library on every rank before the first flag barrier can start counting: a rank that is
-        # still reading shared objects from a cold disk must not make its peers' bounded waits run out
-        t = torch.zeros(1, 2, 128, self.cfg["head_dim"], dtype=torch.bfloat16, device=self.dev)
-        F.scaled_dot_product_attention(t, t, t, is_causal=True)
-        torch.cuda.synchronize(self.dev)
-        dist.barrier()
-        per_group = T * H * 2 + 3 * (T * H + 4 * T) + 4 * W * T + 4096
-        self.arena = PeerArena(max(1, self.n_micro) * per_group + 4096, self.dev)
-        self.sp = []
-        for _ in range(max(1, self.n_micro)):
-            g = {"bar": PeerBarrier(self.arena), "T": T, "Ts": T // W}
-            g["part_off"], part = self.arena.alloc(T * H * 2)
-            g["part"] = part.view(torch.bfloat16).view(W, T // W, H)
-            g["codes_off"], g["scale_off"], g["codes"], g["scales"] = [], [], [], []
-            for _ in range(3):
-                off, c = self.arena.alloc(T * H)
-                g["codes_off"].append(off)
-                g["codes"].append(c.view(torch.int8).view(T, H))
-            for _ in range(3):
-                off, sc = self.arena.alloc(4 * T)
-                g["scale_off"].append(off)
-                g["scales"].append(sc.view(torch.float32)[:T])
-            g["sslot_off"], sl = self.arena.alloc(4 * W * T)  # per-token scales of a row-parallel layer, one slot per shard
-            g["sslots"] = sl.view(torch.float32)[: W * T]
-            g["part_bases"] = [self.arena.addr(r, g["part_off"]) for r in range(W)]
-            g["bases"] = [self.arena.addr(r, 0) for r in range(W)]
-            if self.exchange == "copies":
-                # local staging for the copy engines: this rank's codes and scales of its own tokens, and the
-                # partial output of a row-parallel GEMM for all tokens
-                Ts = T // W
-                g["stage"] = torch.empty(3 * Ts * H + 12 * Ts, dtype=torch.uint8, device=self.dev)
-                g["stage_codes_off"] = [o * Ts * H for o in range(3)]
-                g["stage_scale_off"] = [3 * Ts * H + o * 4 * Ts for o in range(3)]
-                g["po"] = torch.empty(T, H, dtype=torch.bfloat16, device=self.dev)
-                assert all(g["codes_off"][o] == g["codes_off"][0] + o * T * H for o in range(3))
-                assert all(g["scale_off"][o] == g["scale_off"][0] + o * 4 * T for o in range(3))
-            self.sp.append(g)
-
-    def _forward_steps_sp(self, ids, g):
-        """Sharded forward with the residual stream split by tokens.  Each rank owns tokens [rank * Ts, (rank + 1) * Ts)
-        of the group: it sums the partial outputs the row-parallel GEMMs of all ranks stored into its receive buffer,
-        adds them to its slice of the stream, normalises, quantises for the following column-parallel Linears and
-        stores those codes into every rank's code buffer.  No collective carries activations; two barriers per
-        half layer order the remote stores."""
-        from fms_model_optimizer_b200 import _lib as L
-        from fms_model_optimizer_b200 import ops
-
-        cfg, W, rank = self.cfg, self.world, self.rank
-        B, S = ids.shape
-        hd, bf = cfg["head_dim"], torch.bfloat16
-        T, Ts, bar = g["T"], g["Ts"], g["bar"]
-        x = F.embedding(ids.reshape(-1)[rank * Ts : (rank + 1) * Ts], self.embed)
-        parts = None
-
-        H = x.shape[1]
-        # per-token scales of the row-parallel layers travel the same way as the activations (peer stores + barrier)
-        sx = (bar, g["bases"], g["sslot_off"], rank, g["sslots"]) if self.scale_exchange else None
-        copies = self.exchange == "copies"
-        arena = self.arena
-
-        def shared_quant(norm_w, lins):
-            yield "compute"
-            n = len(lins)
-            if copies:  # quantise into local staging, then the copy engines place my rows in every rank's buffers
-                dst = ([g["stage"].data_ptr()], g["stage_codes_off"][:n], g["stage_scale_off"][:n], 0)
-            else:  # the kernel stores to every rank's buffers itself
-                dst = (g["bases"], g["codes_off"][:n], g["scale_off"][:n], rank * Ts)
-            ops.block_quant(x, prologue=L.BLOCK_NORM, r=(parts[0] if parts is not None else None), r_parts=(W if parts is not None else 0),
-                            r_part_stride=Ts * H, norm_w=norm_w, smooth_rcps=[l.smooth_rcp for l in lins], sum_into=x, dst=dst,
-                            max_ctas=(4 * self.reserve_sms if not copies else 0))  # fmt: skip
-            if copies:
-                yield "comm"
-                src = g["stage"].data_ptr()
-                for p in range(W):
-                    arena.copy2d(arena.addr(p, g["codes_off"][0]) + rank * Ts * H, T * H, src, Ts * H, Ts * H, n)
-                    arena.copy2d(arena.addr(p, g["scale_off"][0]) + rank * Ts * 4, T * 4, src + 3 * Ts * H, Ts * 4, Ts * 4, n)
-            bar.wait()  # every rank's codes have landed here
-
-        def row_parallel(lin_, quantised):
-            if not copies:
-                yield "compute"
-            if copies:
-                lin_.gemm_fn(quantised[0], lin_.weight, quantised[1], lin_.w_scale, lin_.bias, bf,
-                             torch.promote_types(bf, lin_.w_scale_dtype), out=g["po"])
-                yield "comm"
-                for p in range(W):
-                    arena.copy2d(arena.addr(p, g["part_off"]) + rank * Ts * H * 2, 0, g["po"].data_ptr() + p * Ts * H * 2, 0, Ts * H * 2, 1)
-            else:
-                lin_.scatter(quantised, g["part_bases"], Ts, rank * Ts, bf)
-            bar.wait()  # every rank's partial rows for my tokens have landed
-
-        for lin in self.layers:
-            yield from shared_quant(lin["ln1"], [lin["q"], lin["k"], lin["v"]])
-            yield "compute"
-            q = ops.rope_(lin["q"](None, (g["codes"][0], g["scales"][0]), bf).view(T, self.nq, hd), self.cos, self.sin, S)
-            k = ops.rope_(lin["k"](None, (g["codes"][1], g["scales"][1]), bf).view(T, self.nkv, hd), self.cos, self.sin, S)
-            v = lin["v"](None, (g["codes"][2], g["scales"][2]), bf)
-            a = F.scaled_dot_product_attention(q.view(B, S, self.nq, hd).transpose(1, 2), k.view(B, S, self.nkv, hd).transpose(1, 2),
-                                               v.view(B, S, self.nkv, hd).transpose(1, 2), is_causal=True, enable_gqa=True)  # fmt: skip
-            a = a.transpose(1, 2).reshape(T, self.nq * hd)
-            yield from row_parallel(lin["o"], lin["o"].quantise_fused(a, exchange=sx))
-            parts = g["part"]
-            yield from shared_quant(lin["ln2"], [lin["gate"], lin["up"]])
-            yield "compute"
-            gt = lin["gate"](None, (g["codes"][0], g["scales"][0]), bf)
-            u = lin["up"](None, (g["codes"][1], g["scales"][1]), bf)
-            yield from row_parallel(lin["down"], lin["down"].quantise_fused(gt, L.BLOCK_SILU_MUL, u, exchange=sx))
-        yield "compute"
-        # final norm of my token slice; the last token of every sequence goes to all ranks through one small all-reduce
-        _, _, _, h = ops.block_quant(x, prologue=L.BLOCK_NORM, r=parts[0], r_parts=W, r_part_stride=Ts * x.shape[1], norm_w=self.norm,
-                                     smooth_rcps=[], sum_into=x, want_h=True)  # fmt: skip
-        last = torch.zeros(B, h.shape[1], dtype=bf, device=h.device)
-        for b in range(B):
-            idx = b * S + S - 1
-            if idx // Ts == rank:
-                last[b] = h[idx % Ts]
-        dist.all_reduce(last)
-        bar.wait()  # the receive buffers are free for the next forward pass
-        logits = last @ self.lm_head.t()
-        return logits.argmax(-1)
-
-    @torch.no_grad()
-    def forward(self, ids):
-        nm = self.n_micro
-        if self.sp is not None:
-            return self._drive([self._forward_steps_sp(part, self.sp[i]) for i, part in enumerate(ids.chunk(max(1, nm), 0))])
-        return self._drive([self._forward_steps(part) for part in ids.chunk(max(1, nm), 0)])
-
-    def _drive(self, gens):
-        """Advances the groups round-robin, one segment at a time.  A generator announces the kind of its next segment
-        ("compute": kernels that fill the SMs; "comm": copy-engine transfers and the barrier that waits for the peers;
-        None: unclassified) and issues it when resumed.  Compute segments of all groups are chained through events, so
-        they run one after the other while the transfers of the other groups proceed beside them (``self.chain``;
-        without it the groups' streams are left to the hardware scheduler)."""
-        nm = len(gens)
-        if nm <= 1:
-            try:
-                while True:
-                    next(gens[0])
-            except StopIteration as stop:
-                return stop.value
-        main = torch.cuda.current_stream()
-        results, pending, token = [None] * nm, [None] * nm, None
-        for i in range(nm):
-            self.streams[i].wait_stream(main)
-        live = list(range(nm))
-        while live:
-            for i in list(live):
-                st = self.streams[i]
-                with torch.cuda.stream(st):
-                    if self.chain and pending[i] == "compute" and token is not None and token[0] != i:
-                        st.wait_event(token[1])
-                    issued = pending[i]
-                    try:
-                        pending[i] = next(gens[i])
-                    except StopIteration as stop:
-                        results[i] = stop.value
-                        live.remove(i)
-                    if issued == "compute":
-                        ev = torch.cuda.Event()
-                        ev.record(st)
-                        token = (i, ev)
-        for i in range(nm):
-            main.wait_stream(self.streams[i])
-            results[i].record_stream(main)
-        return torch.cat(results)
-
-
-def decoder_linear_ops(cfg, tokens, layers=None):
-    hd, H = cfg["head_dim"], cfg["hidden"]
-    per_layer = H * (cfg["q_heads"] * hd) * 2 + 2 * H * (cfg["kv_heads"] * hd) + 3 * H * cfg["ffn"]
-    return 2.0 * per_layer * tokens * (layers if layers is not None else cfg["layers"])
-
-
-# ------------------------------------------------------------------------------------------------
-# CPU baseline: the reference's fake-quant QLinear arithmetic (oracle port)
-# ------------------------------------------------------------------------------------------------
-def cpu_reference_layer_tokens_per_s(tokens: int, steps: int, warmup: int, cfg=LLAMA):
-    """Times the seven QLinear fake-quant forwards of one decoder layer (QLinear.forward,
-    fms_mo/modules/linear.py:248-305, with qa_mode pertokenmax / qw_mode maxperCh / SmoothQuant) on
-    `tokens` tokens with all host threads and returns (tokens/s of a 32-layer prefill, seconds per
-    step, threads).  Only the quantized Linears are timed, as they are the path being replaced."""
-    from oracle import qlinear as OL
+def cpu_layer_tokens_per_s(tokens: int, steps: int, warmup: int):
+    """Times the seven fake-quant QLinear forwards of one decoder layer (QLinear.forward, fms_mo/modules/linear.py:248-305,
+    qa_mode pertokenmax / qw_mode maxperCh / SmoothQuant, bf16) on `tokens` tokens with all host threads.  Runs the
+    reference's own class when it is installed under baseline/_ref (kind "reference"), else the oracle's restatement of
+    it (kind "port").  Returns (tokens/s of a 32-layer prefill, seconds per step, threads, kind).  Only the quantized
+    Linears are timed, as they are the path being replaced."""
+    from fms_model_optimizer_b200.decoder import LLAMA3_8B, linear_shapes
 
     torch.set_num_threads(os.cpu_count() or 1)
-    hd, H = cfg["head_dim"], cfg["hidden"]
-    shapes = [(cfg["q_heads"] * hd, H), (cfg["kv_heads"] * hd, H), (cfg["kv_heads"] * hd, H), (H, cfg["q_heads"] * hd),
-              (cfg["ffn"], H), (cfg["ffn"], H), (H, cfg["ffn"])]  # fmt: skip
     g = torch.Generator().manual_seed(4)
-    mods = []
-    for n, k in shapes:
+    QLinear = _reference_qlinear_class()
+    kind = "reference" if QLinear is not None else "port"
+    calls = []
+    for n, k, _ in linear_shapes(LLAMA3_8B).values():
         w = (torch.randn(n, k, generator=g) * 0.02).bfloat16()
         act = torch.full((k,), 4.0).bfloat16()
-        sq = OL.smoothq_scale(act, w, 0.5, torch.bfloat16)
-        clip = OL.qmax_clip_after_first_train_forward(w * sq)
         x = torch.randn(tokens, k, generator=g).bfloat16()
-        mods.append((x, w, sq, clip))
+        if QLinear is not None:
+            lin = QLinear(k, n, bias=False, num_bits_feature=8, qa_mode="pertokenmax", num_bits_weight=8, qw_mode="maxperCh",
+                          qcfg={"smoothq": True, "smoothq_alpha": 0.5}, device="cpu")  # fmt: skip
+            with torch.no_grad():
+                lin.weight.copy_(w)
+            lin = lin.to(torch.bfloat16)
+            lin.set_act_scale(act.float())
+            lin.train()
+            with torch.no_grad():
+                lin(x[:1])  # latches the weight clip values (fms_mo/quant/quantizers.py:3098-3104)
+            lin.eval()
+            calls.append((lin, x))
+        else:
+            from oracle import qlinear as OL
+
+            sq = OL.smoothq_scale(act, w, 0.5, torch.bfloat16)
+            clip = OL.qmax_clip_after_first_train_forward(w * sq)
+            calls.append(((lambda x_, w=w, sq=sq, clip=clip: OL.qlinear_fakequant_forward(x_, w, None, sq, clip)), x))
     times = []
-    for it in range(warmup + steps):
-        t0 = time.perf_counter()
-        for x, w, sq, clip in mods:
-            OL.qlinear_fakequant_forward(x, w, None, sq, clip)
-        dt = time.perf_counter() - t0
-        if it >= warmup:
-            times.append(dt)
+    with torch.no_grad():
+        for it in range(warmup + steps):
+            t0 = time.perf_counter()
+            for fn, x in calls:
+                fn(x)
+            if it >= warmup:
+                times.append(time.perf_counter() - t0)
     per_step = sum(times) / len(times)
-    return tokens / (per_step * cfg["layers"]), per_step, torch.get_num_threads()
+    return tokens / (per_step * LLAMA3_8B["layers"]), per_step, torch.get_num_threads(), kind
 
 
-# ------------------------------------------------------------------------------------------------
+CPU_SAMPLE_TOKENS = 2048
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
-    tokens = 256
-    tps, per_step, threads = cpu_reference_layer_tokens_per_s(tokens, args.steps, max(1, min(args.warmup, 1)))
+    tokens = CPU_SAMPLE_TOKENS
+    tps, per_step, threads, kind = cpu_layer_tokens_per_s(tokens, max(1, args.steps), 1)
     sample = (f"one decoder layer (7 QLinear fake-quant forwards, bf16) on {tokens} tokens per step, "
               f"tokens/s = {tokens} / (step time x 32 layers)")  # fmt: skip
     line = {
         "impl": "reference", "metric": "w8a8_llama3_8b_prefill_tokens_per_s", "value": tps, "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": 1, "ms_per_step": per_step * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "c5: Llama-3-8B-shaped W8A8 prefill 8x2048", "hardware": "host CPU"},
-        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": {"workload": "c5: Llama-3-8B-shaped decoder, all decoder Linears W8A8 SmoothQuant INT8, prefill 8x2048",
+                   "hardware": "host CPU", "sample": sample},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }  # fmt: skip
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------------------
+# single kernels
+# ------------------------------------------------------------------------------------------------
+class KernelTimer:
+    """Times one call as a CUDA graph replay (the way a serving loop issues it: for small shapes the launches of a
+    Linear take less GPU time than the host needs to queue them), with a 256 MB write between replays so that nothing
+    is served from L2."""
+
+    def __init__(self, dev):
+        self.dev = dev
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def __call__(self, fn, steps=5, warmup=3, graph=True):
+        with torch.no_grad():
+            for _ in range(max(warmup, 3)):
+                fn()
+            torch.cuda.synchronize()
+            run = fn
+            if graph:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    fn()
+                run = g.replay
+                run()
+                torch.cuda.synchronize()
+            tot = 0.0
+            for _ in range(steps):
+                self.flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                run()
+                e1.record()
+                torch.cuda.synchronize()
+                tot += e0.elapsed_time(e1)
+        return tot / steps
+
+
+def kernel_cases(dev, which):
+    """(name, dtype, bound, work, unit_scale, fn) for the single-kernel workloads: work is operations for tensor-bound
+    entries and algorithmic bytes for HBM-bound ones."""
+    from fms_model_optimizer_b200 import _lib as L, ops, tp
+    from fms_model_optimizer_b200.decoder import synth_w8a8
+    from fms_model_optimizer_b200.modules import LinearFPxAcc
+
+    cases = []
+
+    def add(name, dtype, bound, work, fn, graph=True):
+        cases.append(dict(name=name, dtype=dtype, bound=bound, work=float(work), fn=fn, graph=graph))
+
+    if which in ("c1", "c5lin", "all"):
+        for tag, (M, K, N) in (("c1", (2048, 4096, 4096)), ("c5lin", (16384, 4096, 4096))):
+            if which not in (tag, "all"):
+                continue
+            torch.manual_seed(0)
+            x = torch.randn(M, K, device=dev).bfloat16()
+            codes, w_scale, smooth = synth_w8a8(N, K, 0, dev)
+            lin = tp.W8A8Linear(codes, w_scale, smooth, torch.zeros(N, device=dev))
+            add(f"{tag} W8A8 INT8 Linear {M}x{K}x{N} (quantise + GEMM + dequantise)", "int8", "tensor", 2.0 * M * N * K, lambda lin=lin, x=x: lin(x))
+    if which in ("c2", "all"):
+        torch.manual_seed(1)
+        M, K, N = 4096, 8192, 4096
+        a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
+        b = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev)
+        out = torch.empty((M, N), dtype=torch.int32, device=dev)
+        add(f"c2 int8 chunk-truncated GEMM {M}x{K}x{N}, chunk 64, 8 bits", "int8", "tensor", 2.0 * M * N * K,
+            lambda: ops.gemm(a, b, out=out, chunk_k=64, trun_bits=8))  # fmt: skip
+    if which in ("c3", "all"):
+        torch.manual_seed(2)
+        for M, K, N in ((1, 4096, 14336), (128, 4096, 4096), (8192, 4096, 14336), (8192, 14336, 4096)):
+            x = torch.randn(M, K, device=dev).bfloat16()
+            lin = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
+            with torch.no_grad():
+                lin.weight.copy_(torch.randn(N, K, device=dev))
+            q = LinearFPxAcc.from_nn(lin, trun_bits=0, chunk_size=64, dynamic_fp8="per_token")
+            with torch.no_grad():
+                q(x)
+            small = M <= 128
+            work = (N * K + M * K * 3 + M * N * 2) if small else 2.0 * M * N * K
+            add(f"c3 FP8 e4m3 Linear {M}x{K}x{N} (quantise + GEMM + dequantise)", "fp8", "hbm" if small else "tensor", work,
+                (lambda q=q, x=x: q(x)))  # fmt: skip
+            cases[-1]["ops"] = 2.0 * M * N * K
+    if which == "all":
+        for M, K, N in ((16384, 4096, 4096), (8192, 8192, 8192)):
+            for kind, dt in (("int8", torch.int8), ("fp8", torch.float8_e4m3fn)):
+                a = torch.randint(-100, 100, (M, K), dtype=torch.int8, device=dev)
+                b = torch.randint(-100, 100, (N, K), dtype=torch.int8, device=dev)
+                if kind == "fp8":
+                    a, b = (a.float() / 64).to(dt), (b.float() / 64).to(dt)
+                rs, cs = torch.rand(M, device=dev) + 0.5, torch.rand(N, device=dev) + 0.5
+                out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+                add(f"GEMM {kind} {M}x{K}x{N}, bf16 output, scale epilogue", kind, "tensor", 2.0 * M * N * K,
+                    lambda a=a, b=b, rs=rs, cs=cs, out=out: ops.gemm(a, b, out=out, epilogue=L.EPI_SCALE_SEQ, row_scale=rs, col_scale=cs,
+                                                                      out_dtype=torch.bfloat16))  # fmt: skip
+        # HBM-bound kernels on c5 / c4 shaped tensors (larger than L2)
+        M, K = 16384, 4096
+        x = torch.randn(M, K, device=dev).bfloat16()
+        r = torch.randn(M, K, device=dev).bfloat16()
+        nw = torch.ones(K, device=dev, dtype=torch.bfloat16)
+        rc = [ops.smooth_reciprocal((torch.rand(K, device=dev) + 0.5).bfloat16().float()) for _ in range(3)]
+        sm = (torch.rand(K, device=dev) + 0.5).bfloat16().float()
+        add(f"act_quant bf16 per-token int8 with SmoothQuant {M}x{K}", "bf16", "hbm", M * K * 3 + 4 * M + 4 * K,
+            lambda: ops.act_quant(x, mode=L.Q_I8_DYN, smooth=sm, native_chain=7))  # fmt: skip
+        add(f"block_quant add+RMSNorm+3 outputs {M}x{K}", "bf16", "hbm", M * K * (2 + 2 + 2 + 3) + 12 * M,
+            lambda: ops.block_quant(x, prologue=L.BLOCK_NORM, r=r, norm_w=nw, smooth_rcps=rc, store_sum=True))  # fmt: skip
+        add(f"block_quant add+RMSNorm+2 outputs {M}x{K}", "bf16", "hbm", M * K * (2 + 2 + 2 + 2) + 8 * M,
+            lambda: ops.block_quant(x, prologue=L.BLOCK_NORM, r=r, norm_w=nw, smooth_rcps=rc[:2], store_sum=True))  # fmt: skip
+        add(f"block_quant SiLU*up+1 output {M}x{K}", "bf16", "hbm", M * K * (2 + 2 + 1) + 4 * M,
+            lambda: ops.block_quant(x, prologue=L.BLOCK_SILU_MUL, r=r, smooth_rcps=rc[:1]))  # fmt: skip
+        add(f"block_quant plain 1 output {M}x{K}", "bf16", "hbm", M * K * (2 + 1) + 4 * M,
+            lambda: ops.block_quant(x, prologue=L.BLOCK_PLAIN, smooth_rcps=rc[:1]))  # fmt: skip
+        for dt, name in ((torch.float32, "fp32"), (torch.bfloat16, "bf16")):
+            xx = (torch.randn(M, K, device=dev) * 3).to(dt)
+            gg = torch.randn(M, K, device=dev).to(dt)
+            cv, cvn = torch.tensor([6.0], device=dev), torch.tensor([-6.0], device=dev)
+            es = xx.element_size()
+            add(f"PACT+ forward {name} {M}x{K}", name, "hbm", 2 * es * M * K, lambda xx=xx: ops.pact2_fwd(xx, cv, cvn, 8, True))
+            add(f"PACT+ backward {name} {M}x{K}", name, "hbm", 3 * es * M * K, lambda xx=xx, gg=gg: ops.pact2_bwd(xx, gg, cv, cvn, 8, True))
+            w = (torch.randn(14336, 4096, device=dev) * 0.02).to(dt)
+            add(f"SAWB+ per-channel weight fake-quant {name} 14336x4096", name, "hbm", 2 * es * w.numel(),
+                lambda w=w: ops.weight_fq_perch(w, num_bits=8, mode=L.W_SAWB, c0=SAWB_C[0], c1=SAWB_C[1]))  # fmt: skip
+    return cases
+
+
+SAWB_C = (-12.80, 12.035)  # sawb_params_code coefficients for 8 bits (values only matter for timing here)
+
+
+def comparator_cases(dev):
+    """Library GEMMs on the same shapes, same run: cuBLASLt int8 through torch._int_mm (the call the reference's
+    ext_kernel_cublas.cpp:172-187 makes) and cuBLASLt fp8 through torch._scaled_mm, both as plain GEMMs."""
+    out = []
+    for M, K, N in ((16384, 4096, 4096), (8192, 8192, 8192)):
+        a = torch.randint(-100, 100, (M, K), dtype=torch.int8, device=dev)
+        b = torch.randint(-100, 100, (N, K), dtype=torch.int8, device=dev)
+        out.append(dict(name=f"torch._int_mm (cuBLASLt int8 -> int32) {M}x{K}x{N}", dtype="int8", work=2.0 * M * N * K,
+                        fn=lambda a=a, b=b: torch._int_mm(a, b.t())))  # fmt: skip
+        a8, b8 = (a.float() / 64).to(torch.float8_e4m3fn), (b.float() / 64).to(torch.float8_e4m3fn)
+        one = torch.ones((), device=dev)
+        out.append(dict(name=f"torch._scaled_mm (cuBLASLt e4m3 -> bf16) {M}x{K}x{N}", dtype="fp8", work=2.0 * M * N * K,
+                        fn=lambda a8=a8, b8=b8: torch._scaled_mm(a8, b8.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)))  # fmt: skip
+    return out
+
+
+def measure_kernels(dev, which="all", steps=5, warmup=3, with_comparators=True):
+    """Runs the single-kernel cases and returns (kernels, comparators): lists of dicts with TOPS or GB/s, the bound and
+    the fraction of the stated peak."""
+    pk = peaks()
+    timer = KernelTimer(dev)
+    kernels, comps = [], []
+    for c in kernel_cases(dev, which):
+        ms = timer(c["fn"], steps, warmup, c["graph"])
+        e = {"name": c["name"], "dtype": c["dtype"], "bound": c["bound"], "us": ms * 1e3}
+        if c["bound"] == "tensor":
+            tops = c["work"] / (ms * 1e-3) / 1e12
+            e.update(tops=tops, frac_of_2x_bf16_measured=tops / (2 * pk["bf16"]), frac_of_datasheet_8bit=tops / DATASHEET_8BIT_TOPS)
+        else:
+            gbs = c["work"] / (ms * 1e-3) / 1e9
+            e.update(gbs=gbs, frac_of_hbm_measured=gbs / pk["hbm"], algorithmic_bytes=c["work"])
+            if "ops" in c:
+                e["tops"] = c["ops"] / (ms * 1e-3) / 1e12
+        kernels.append(e)
+        c["fn"] = None
+    if with_comparators:
+        for c in comparator_cases(dev):
+            try:
+                ms = timer(c["fn"], steps, warmup, True)
+                tops = c["work"] / (ms * 1e-3) / 1e12
+                comps.append({"name": c["name"], "dtype": c["dtype"], "us": ms * 1e3, "tops": tops,
+                              "frac_of_datasheet_8bit": tops / DATASHEET_8BIT_TOPS})  # fmt: skip
+            except Exception as e:  # noqa: BLE001 -- a library call this torch build does not offer
+                comps.append({"name": c["name"], "unavailable": f"{type(e).__name__}: {e}"[:200]})
+            c["fn"] = None
+    torch.cuda.empty_cache()
+    return kernels, comps
+
+
+def run_kernel_workload(args, dev):
+    """--workload c1 | c2 | c3 | c5lin: one JSON line per shape."""
+    pk = peaks()
+    sampler = ClockSampler(dev.index).start()
+    kernels, _ = measure_kernels(dev, args.workload, args.steps, args.warmup, with_comparators=False)
+    clocks = sampler.stop()
+    for e in kernels:
+        tensor = e["bound"] == "tensor"
+        val = e["tops"] if tensor else e["gbs"]
+        peak = 2.0 * pk["bf16"] if tensor else pk["hbm"]
+        print(json.dumps({
+            "metric": "quantized_linear_tops" if tensor else "quantized_linear_weight_stream_gbs", "value": val,
+            "unit": "TOPS" if tensor else "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": e["us"] * 1e-3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": e["dtype"],
+            "data": "synthetic",
+            "config": {"workload": e["name"], "l2": "256 MB flush between timed launches", "launch": "CUDA graph replay of the call"},
+            "roofline": {"bound": e["bound"], "achieved": val, "peak": peak, "unit": "TFLOP/s" if tensor else "GB/s", "frac": val / peak,
+                         "traffic": C5LIN_DRAM_BYTES if args.workload == "c5lin" else None,
+                         "peak_source": (f"2 x bf16_tflops (burst) of MEASURED_PEAKS.json ({pk['src']}); datasheet dense 8-bit "
+                                         f"{DATASHEET_8BIT_TOPS:.0f} -> frac {val / DATASHEET_8BIT_TOPS:.3f}") if tensor else
+                                        f"hbm_gbs of MEASURED_PEAKS.json ({pk['src']})"},
+            "clocks": clocks,
+        }), flush=True)  # fmt: skip
+
+
+# ------------------------------------------------------------------------------------------------
+# c5: decoder prefill
+# ------------------------------------------------------------------------------------------------
+def _check_sharded_against_single(args, cfg, rank, world, dev, ids_dev, groups):
+    """Before timing a sharded run: a 2-layer decoder through the sharded path (eager and as a CUDA graph replay) and
+    through the one-GPU path (every rank holds the full 2-layer weights), same ids.  Returns the relative Frobenius
+    error of the final hidden states of the last tokens and whether the next-token ids agree; raises when the error is
+    beyond what rounding the shards' partial sums to bf16 explains (2e-2)."""
+    from fms_model_optimizer_b200 import ops
+    from fms_model_optimizer_b200.decoder import W8A8Decoder
+
+    single = W8A8Decoder(cfg, dev, 1, 0, layers=2)
+    want_ids = single.forward(ids_dev)
+    want_h = single.last_hidden.float().clone()
+    del single
+    sharded = W8A8Decoder(cfg, dev, world, rank, layers=2, groups=groups, exchange=args.exchange, reserve_sms=args.reserve_sms)
+    if sharded.exchange != "allreduce":
+        sharded.enable_token_split(cfg["batch"] * cfg["seq"] // groups)
+    res = {"exchange": sharded.exchange}
+    for mode in ("eager", "graph"):
+        if mode == "graph":
+            static_ids = ids_dev.clone()
+            sharded.forward(static_ids)
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                got_ids = sharded.forward(static_ids)
+            gr.replay()
+        else:
+            got_ids = sharded.forward(ids_dev)
+        torch.cuda.synchronize()
+        ops.check_status(dev)
+        got_h = sharded.last_hidden.float()
+        err = ((got_h - want_h).norm() / want_h.norm()).item()
+        res[mode] = {"hidden_rel_err": err, "next_tokens_equal": bool(torch.equal(got_ids, want_ids))}
+        if not err < 2e-2:
+            raise RuntimeError(f"sharded forward ({mode}) differs from the one-GPU forward: relative error {err}")
+    dist.barrier()
+    sharded.close()
+    del sharded
+    torch.cuda.empty_cache()
+    return res
+
+
 def run_c5(args, rank, world, dev):
     from fms_model_optimizer_b200 import ops
+    from fms_model_optimizer_b200.decoder import LLAMA3_8B, W8A8Decoder, decoder_linear_ops, linear_shapes
 
-    cfg = dict(LLAMA)
-    n_micro = args.micro if args.micro > 0 else (2 if world > 2 else 1)
-    if n_micro > 1 and world > 1 and args.allreduce:
-        ops.GEMM_MAX_CTAS = args.gemm_ctas
-    model = Decoder(cfg, dev, world, rank, layers=args.layers, n_micro=n_micro)
-    if world > 1 and not args.allreduce:
-        model.exchange = args.exchange
-        model.chain = args.chain
-        if n_micro > 1 and args.reserve_sms > 0 and args.exchange == "stores":
-            # SM partition between the groups' streams: kernels bound by the links (row-parallel GEMMs storing to the
-            # peers, the quantiser replicating its codes) run on `reserve` SMs, the compute-bound GEMMs on the rest, so a
-            # kernel of each kind fits on the GPU at the same time
-            sms = torch.cuda.get_device_properties(dev).multi_processor_count
-            model.reserve_sms = args.reserve_sms
-            for lin in model.layers:
-                for name, l_ in lin.items():
-                    if hasattr(l_, "max_ctas"):
-                        l_.max_ctas = args.reserve_sms if name in ("o", "down") else sms - args.reserve_sms
-        model.enable_sequence_parallel(cfg["batch"] * cfg["seq"] // n_micro)
-    nl = len(model.layers)
+    cfg = dict(LLAMA3_8B)
+    groups = args.groups if args.groups > 0 else (2 if world > 1 else 1)
     B, S = cfg["batch"], cfg["seq"]
     tokens = B * S
     g = torch.Generator().manual_seed(4)
@@ -484,10 +465,35 @@ def run_c5(args, rank, world, dev):
     ids_dev = ids_host.to(dev)
     out_host = torch.empty(B, dtype=torch.int64).pin_memory()
 
+    check = None
+    if world > 1 and not args.no_check:
+        check = _check_sharded_against_single(args, cfg, rank, world, dev, ids_dev, groups)
+
+    model = W8A8Decoder(cfg, dev, world, rank, layers=args.layers, groups=groups, exchange=args.exchange, reserve_sms=args.reserve_sms,
+                        surface=("fused" if args.surface == "both" else args.surface))  # fmt: skip
+    if world > 1 and model.exchange != "allreduce":
+        model.enable_token_split(tokens // groups)
+    nl = len(model.layers)
+
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        """`steps` calls of fn between two CUDA events on the current stream, bracketed by barrier + synchronize; the
+        maximum over the ranks, in ms."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
 
     for _ in range(max(args.warmup, 3)):
         model.forward(ids_dev)
@@ -512,60 +518,66 @@ def run_c5(args, rank, world, dev):
         barrier()
         ops.check_status(dev)
 
-    def step(ids):
+    def step(ids=None):
         if graph is None:
-            return model.forward(ids)
-        if ids is not static_ids:
+            return model.forward(static_ids if ids is None else ids)
+        if ids is not None and ids is not static_ids:
             static_ids.copy_(ids, non_blocking=True)
         graph.replay()
         return static_out
 
-    # ---- timed region: device-resident inputs.  Eager runs bracket every kernel launch of this library with CUDA
-    # events inside the region; graph runs take those per-launch times from eager steps right after it.
+    # ---- timed region: device-resident inputs, no instrumentation inside
     sampler = ClockSampler(dev.index)
     if rank == 0:
         sampler.start()
-    ops.PROFILE = [] if graph is None else None
-    ops.LAUNCHES = 0
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ops.PROFILE, ops.LAUNCHES = None, 0
     torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` capture exactly the timed region
-    e0.record()
-    for _ in range(args.steps):
-        step(static_ids)
-    e1.record()
-    barrier()
+    ms = timed(step, args.steps)
     torch.cuda.profiler.stop()
-    ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
-    if graph is not None:
-        ops.PROFILE = []
-        ops.LAUNCHES = 0
-        for _ in range(args.steps):
-            model.forward(ids_dev)
-        barrier()
-    prof, ops.PROFILE = ops.PROFILE, None
-    launches = ops.LAUNCHES
-    t = torch.tensor([ms], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = t.item()
 
     # ---- end to end: ids from pinned host memory, next-token ids back to the host, every step
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
+    def e2e_step():
         ids_d = ids_host.to(dev, non_blocking=True) if graph is None else static_ids.copy_(ids_host, non_blocking=True)
         out = step(ids_d)
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-    e1.record()
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_e2e = t.item()
+
+    ms_e2e = timed(e2e_step, args.steps)
     ops.check_status(dev)
+
+    # ---- per-launch times: the same number of eager steps with every launch of this library bracketed by CUDA events on
+    # its stream (the event pairs cost time, so these steps are not part of `value`)
+    ops.PROFILE, ops.LAUNCHES = [], 0
+    barrier()
+    for _ in range(args.steps):
+        model.forward(ids_dev)
+    barrier()
+    prof, ops.PROFILE = ops.PROFILE, None
+    launches = ops.LAUNCHES // args.steps
+    ops.check_status(dev)
+
+    surfaces = None
+    if world == 1 and args.surface == "both":
+        # the same decoder by the drop-in route: QLinear -> lower_qmodel_b200 -> QLinearINT8Deploy, unfused norms
+        del graph
+        model.layers.clear()
+        torch.cuda.empty_cache()
+        mod = W8A8Decoder(cfg, dev, 1, 0, layers=args.layers, surface="modules")
+        for _ in range(3):
+            mod.forward(ids_dev)
+        ops.LAUNCHES = 0
+        ms_mod = timed(lambda: mod.forward(ids_dev), max(2, args.steps // 2)) / max(2, args.steps // 2)
+        surfaces = {
+            "fused": {"tokens_per_s": tokens * args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps,
+                      "what": "tp.W8A8Linear fed by the fused block kernels (the headline)"},
+            "modules": {"tokens_per_s": tokens / (ms_mod * 1e-3), "ms_per_step": ms_mod,
+                        "what": "QLinear -> lower_qmodel_b200 -> QLinearINT8Deploy per Linear; RMSNorm, SiLU*up, residual adds as PyTorch ops"},
+        }  # fmt: skip
+        del mod
+        torch.cuda.empty_cache()
+    if world > 1:
+        model.close()
     if rank != 0:
         return
 
@@ -575,16 +587,24 @@ def run_c5(args, rank, world, dev):
     n_gemm = sum(1 for p in prof if p[0] == "gemm")
     quant_ms = sum(a.elapsed_time(b) for (name, a, b, work) in prof if name in ("act_quant", "block_quant"))
     quant_bytes = sum(work for (name, a, b, work) in prof if name in ("act_quant", "block_quant"))
+    bar_ms = sum(a.elapsed_time(b) for (name, a, b, work) in prof if name == "barrier")
+    prof_ms = sum(a.elapsed_time(b) for (name, a, b, work) in prof)
     achieved = gemm_ops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
     if args.breakdown:
-        groups = {}
+        by = {}
         for name, a, b, work in prof:
-            t = groups.setdefault((name, work), [0, 0.0])
+            t = by.setdefault((name, work), [0, 0.0])
             t[0] += 1
             t[1] += a.elapsed_time(b)
-        for (name, work), (n, t) in sorted(groups.items(), key=lambda kv: -kv[1][1]):
+        for (name, work), (n, t) in sorted(by.items(), key=lambda kv: -kv[1][1]):
             print(f"# {name:12s} work {work:.3e} launches/step {n / args.steps:6.1f} avg {1e3 * t / n:8.1f} us  "
                   f"total/step {t / args.steps:7.2f} ms", file=sys.stderr, flush=True)
+    # algorithmic bytes of the GEMM launches of one step on this rank (A codes + B codes + bf16 output)
+    algo = 0.0
+    for n, k, mode in linear_shapes(cfg).values():
+        n_r, k_r = (n // world, k) if mode == "column" else (n, k // world)
+        algo += tokens * k_r + n_r * k_r + tokens * n_r * 2
+    traffic = algo / 7 * (C5LIN_DRAM_BYTES / C5LIN_ALGO_BYTES)  # seven GEMM launches per layer
     peak = 2.0 * pk["bf16_sustained"]
     line = {
         "metric": "w8a8_llama3_8b_prefill_tokens_per_s", "value": tokens * args.steps / (ms * 1e-3), "unit": "tokens/s",
@@ -592,45 +612,71 @@ def run_c5(args, rank, world, dev):
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": {
             "workload": "c5: Llama-3-8B-shaped decoder, all decoder Linears W8A8 SmoothQuant INT8, prefill 8x2048",
-            "layers": nl, "global_batch": B, "seq_len": S, "parallelism": f"tp{world}", "sequence_groups_in_flight": n_micro,
-            "timed_region": ("eager launches, per-launch CUDA events inside the region" if graph is None else
-                             "CUDA graph replays; per-launch CUDA events from the same number of eager steps right after"),
-            "shard_exchange": ("none" if world == 1 else "nccl all-reduce" if args.allreduce else
-                               f"peer {args.exchange} over NVLink, residual stream split by tokens, flag barriers"),
+            "layers": nl, "global_batch": B, "seq_len": S, "parallelism": f"tp{world}", "sequence_groups_in_flight": groups,
+            "surface": model.surface,
+            "timed_region": ("eager launches" if graph is None else "CUDA graph replays") +
+                            ", no instrumentation; per-launch CUDA events (roofline, shares) from the same number of eager steps right after",
+            "shard_exchange": {"none": "none", "allreduce": "nccl all-reduce",
+                               "multimem": "token-split residual stream; partial sums reduced in the NVLink switch (multimem.ld_reduce), "
+                                           "codes replicated with multimem.st, flag barriers",
+                               "stores": "token-split residual stream; plain peer stores over NVLink, flag barriers"}[model.exchange],
+            "reserve_sms": args.reserve_sms,
             "l2": "inputs larger than L2 (activations 134 MB per Linear, weights 7 GB)",
             "linear_tops": decoder_linear_ops(cfg, tokens, nl) * args.steps / (ms * 1e-3) / 1e12,
         },
         "roofline": {
-            "bound": "tensor", "kernel": "qlin_gemm_pair_kernel<int8> (all decoder GEMMs have at least 256 rows)", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-            "frac": achieved / peak if peak else None, "traffic": None, "launches": n_gemm,
-            "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({pk['src']}); no 8-bit peak was measured; "
-                           f"datasheet dense int8 4500 TOPS -> frac {achieved / 4500.0:.3f}",
-            "gemm_share_of_step": gemm_ms / ms if ms else None,
+            "bound": "tensor", "kernel": "qlin_gemm_pair_kernel<int8> (all decoder GEMMs have at least 256 rows)", "achieved": achieved,
+            "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if peak else None, "traffic": traffic, "launches": n_gemm // args.steps,
+            "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({pk['src']}): a proxy, no 8-bit peak was measured by the "
+                           "driver; see frac_of_datasheet_int8 and, on one GPU, comparators for cuBLASLt int8 in the same run",
+            "frac_of_datasheet_int8": achieved / DATASHEET_8BIT_TOPS,
+            "traffic_source": "average DRAM bytes per GEMM launch, scaled from the ncu capture of the 16384x4096x4096 launch "
+                              "(184.4 MB measured for 218.1 MB algorithmic: part of the output is still in L2 when the kernel ends) "
+                              "by each shape's algorithmic bytes",
+            "gemm_ms_per_step": gemm_ms / args.steps,
             "act_quant_gbs": quant_bytes / (quant_ms * 1e-3) / 1e9 if quant_ms > 0 else None,
-            "act_quant_share_of_step": quant_ms / ms if ms else None,
+            "act_quant_ms_per_step": quant_ms / args.steps,
+            "shares_of_instrumented_kernel_time": {"gemm": gemm_ms / prof_ms, "quantise": quant_ms / prof_ms, "barrier": bar_ms / prof_ms} if prof_ms else None,
         },
         "e2e": {"value": tokens * args.steps / (ms_e2e * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": ids_host.numel() * ids_host.element_size(), "d2h_bytes_per_step": out_host.numel() * 8},
-        "gpu_launches": launches,
+        "gpu_launches": launches * args.steps,
         "clocks": clocks,
     }  # fmt: skip
+    if world > 1 and model.exchange in ("multimem", "stores"):
+        out_b, in_b = model.nvlink_bytes_per_forward
+        line["nvlink"] = {
+            "bytes_out_per_step": out_b, "bytes_in_per_step": in_b,
+            "achieved_gbs_in": in_b / (ms / args.steps * 1e-3) / 1e9, "achieved_gbs_out": out_b / (ms / args.steps * 1e-3) / 1e9,
+            "link_bound_ms_per_step_at_770_gbs": max(out_b, in_b) / 770e9 * 1e3,
+            "barrier_ms_per_step_eager": bar_ms / args.steps,
+            "barriers_per_step": sum(1 for p in prof if p[0] == "barrier") // args.steps,
+        }  # fmt: skip
+    if check is not None:
+        line["sharded_vs_single_gpu"] = check
+    if surfaces is not None:
+        line["surfaces"] = surfaces
+    if world == 1 and not args.no_kernels:
+        k, c = measure_kernels(dev, "all", 5, 3)
+        line["kernels"], line["comparators"] = k, c
     if world == 1 and not args.no_cpu_baseline:
-        tok = 256
-        tps, per_step, threads = cpu_reference_layer_tokens_per_s(tok, 2, 1)
+        tps, per_step, threads, kind = cpu_layer_tokens_per_s(CPU_SAMPLE_TOKENS, 2, 1)
         line["cpu_baseline"] = {
-            "value": tps, "unit": "tokens/s", "cores": threads, "kind": "port",
-            "sample": f"one decoder layer (7 QLinear fake-quant forwards, bf16) on {tok} tokens, {per_step:.2f} s per step, "
+            "value": tps, "unit": "tokens/s", "cores": threads, "kind": kind,
+            "sample": f"one decoder layer (7 QLinear fake-quant forwards, bf16) on {CPU_SAMPLE_TOKENS} tokens, {per_step:.2f} s per step, "
                       f"extrapolated to 32 layers",
         }  # fmt: skip
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------------------
+# c4: QAT encoder
+# ------------------------------------------------------------------------------------------------
 class BertQAT(torch.nn.Module):
     """BERT-base-shaped encoder (12 layers, hidden 768, 12 heads, FFN 3072) whose 72 Linears are this package's QLinear with
-    PACT+ activations (clip values +-6) and SAWB+ per-channel weights: BASELINE config 4.  Embeddings, LayerNorm, GELU and
-    attention are PyTorch."""
+    PACT+ activations (clip values +-6) and SAWB+ per-channel weights.  Embeddings, LayerNorm, GELU and attention are PyTorch."""
 
-    def __init__(self, dev, layers=12, hidden=768, heads=12, ffn=3072, vocab=30522, seq=128, dtype=torch.bfloat16):
+    def __init__(self, dev, layers=12, hidden=768, heads=12, ffn=3072, vocab=30522, seq=128, dtype=torch.float32):
         super().__init__()
         from fms_model_optimizer_b200.modules import QLinear
 
@@ -664,21 +710,24 @@ class BertQAT(torch.nn.Module):
 
 
 def run_c4(args, dev):
-    """BASELINE config 4: QAT forward + backward of the BERT-base-shaped encoder on a 32 x 128 batch of random token ids
-    (seed 3), random-init weights.  One step = forward, a scalar loss, backward (no optimizer step, as the config says)."""
+    """QAT forward + backward of the BERT-base-shaped encoder on a 32 x 128 batch of random token ids (seed 3), random-init
+    weights, fp32.  One step = forward, the scalar loss (out * G).sum() with a seeded G, backward (no optimizer step: the
+    workload is stated as forward + backward)."""
     from fms_model_optimizer_b200 import ops
 
     torch.manual_seed(3)
-    model = BertQAT(dev, layers=args.layers or 12)
+    dtype = torch.bfloat16 if args.c4_dtype == "bf16" else torch.float32
+    model = BertQAT(dev, layers=args.layers or 12, dtype=dtype)
     model.train()
     B, S = 32, 128
     ids = torch.randint(0, 30522, (B, S), device=dev)
+    G = torch.randn(B, S, 768, device=dev).to(dtype)
     params = [p for p in model.parameters() if p.requires_grad]
 
     def step():
         for p in params:
             p.grad = None
-        loss = model(ids).float().pow(2).mean()
+        loss = (model(ids) * G).sum()
         loss.backward()
         return loss
 
@@ -686,9 +735,8 @@ def run_c4(args, dev):
         step()
     torch.cuda.synchronize()
     ops.check_status(dev)
-    sampler = ClockSampler(dev.index)
-    sampler.start()
-    ops.PROFILE, ops.LAUNCHES = [], 0
+    sampler = ClockSampler(dev.index).start()
+    ops.PROFILE, ops.LAUNCHES = None, 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
@@ -696,8 +744,13 @@ def run_c4(args, dev):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
-    prof, ops.PROFILE = ops.PROFILE, None
     clocks = sampler.stop()
+    launches = ops.LAUNCHES
+    ops.PROFILE = []
+    for _ in range(args.steps):
+        step()
+    torch.cuda.synchronize()
+    prof, ops.PROFILE = ops.PROFILE, None
     by = {}
     for name, a, b, work in prof:
         t = by.setdefault(name, [0, 0.0, 0.0])
@@ -711,9 +764,9 @@ def run_c4(args, dev):
     print(json.dumps({
         "metric": "qat_bert_base_fwd_bwd_tokens_per_s", "value": B * S / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "vs_baseline": None, "dtype": args.c4_dtype, "data": "synthetic",
         "config": {"workload": "c4: BERT-base-shaped encoder, 72 QLinear (PACT+ 8-bit activations, SAWB+ per-channel 8-bit weights), "
-                               "QAT forward + backward, batch 32 x 128", "layers": len(model.blocks),
+                               "QAT forward + backward, batch 32 x 128, loss (out * G).sum()", "layers": len(model.blocks),
                    "l2": "activations 6-25 MB per tensor: L2 resident between kernels, as in the real step",
                    "library_kernels_ms_per_step": mine_ms,
                    "launches_per_step": {k: v[0] / args.steps for k, v in by.items()}},
@@ -721,85 +774,8 @@ def run_c4(args, dev):
                      "frac": (pact_gbs / pk["hbm"]) if pact_gbs else None, "traffic": None,
                      "peak_source": f"hbm_gbs of MEASURED_PEAKS.json ({pk['src']}); tensors of this workload fit in L2, so the "
                                     "fraction can exceed what HBM alone would allow"},
-        "gpu_launches": ops.LAUNCHES, "clocks": clocks,
+        "gpu_launches": launches, "clocks": clocks,
     }), flush=True)  # fmt: skip
-
-
-def run_kernel_workload(args, dev):
-    """Single-kernel workloads: c1 (W8A8 Linear 2048x4096x4096), c2 (chunk-truncated int8 GEMM
-    4096x8192x4096, chunk 64, 8 bits), c3 (FP8 Linear sweep).  Prints one JSON line per shape."""
-    from fms_model_optimizer_b200 import _lib as L, ops
-
-    pk = peaks()
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-
-    def timeit(fn, steps, warmup):
-        for _ in range(max(warmup, 3)):
-            fn()
-        torch.cuda.synchronize()
-        # the call is replayed as a CUDA graph, as a serving loop would run it: for the small shapes the two or three
-        # launches of a Linear take less time on the GPU than the host needs to issue them
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            fn()
-        fn = graph.replay
-        fn()
-        torch.cuda.synchronize()
-        tot = 0.0
-        for _ in range(steps):
-            flush.zero_()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            fn()
-            e1.record()
-            torch.cuda.synchronize()
-            tot += e0.elapsed_time(e1)
-        return tot / steps
-
-    cases = []
-    if args.workload in ("c1", "c5lin"):
-        torch.manual_seed(0)
-        M, K, N = (2048, 4096, 4096) if args.workload == "c1" else (16384, 4096, 4096)
-        x = torch.randn(M, K, device=dev).bfloat16()
-        codes, w_scale, smooth = synth_w8a8(N, K, 0, dev)
-        from fms_model_optimizer_b200 import tp
-
-        lin = tp.W8A8Linear(codes, w_scale, smooth, torch.zeros(N, device=dev))
-        cases.append((f"{args.workload} W8A8 INT8 Linear {M}x{K}x{N} (quantise + GEMM + dequantise)", 2.0 * M * N * K, lambda: lin(x), "int8"))
-    elif args.workload == "c2":
-        torch.manual_seed(1)
-        M, K, N = 4096, 8192, 4096
-        a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
-        b = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev)
-        out = torch.empty((M, N), dtype=torch.int32, device=dev)
-        cases.append((f"c2 int8 chunk-truncated GEMM {M}x{K}x{N}, chunk 64, 8 bits", 2.0 * M * N * K,
-                      lambda: ops.gemm(a, b, out=out, chunk_k=64, trun_bits=8), "int8"))  # fmt: skip
-    else:
-        torch.manual_seed(2)
-        from fms_model_optimizer_b200.modules import LinearFPxAcc
-
-        for M, K, N in ((1, 4096, 14336), (128, 4096, 4096), (8192, 4096, 14336), (8192, 14336, 4096)):
-            x = torch.randn(M, K, device=dev).bfloat16()
-            lin = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
-            q = LinearFPxAcc.from_nn(lin, trun_bits=0, chunk_size=64, dynamic_fp8="per_token")
-            with torch.no_grad():
-                q(x)
-            cases.append((f"c3 FP8 e4m3 Linear {M}x{K}x{N}", 2.0 * M * N * K, (lambda q=q, x=x: q(x)), "fp8"))
-    for name, work, fn, dt in cases:
-        with torch.no_grad():
-            ms = timeit(fn, args.steps, args.warmup)
-        tops = work / (ms * 1e-3) / 1e12
-        print(json.dumps({
-            "metric": "quantized_linear_tops", "value": tops, "unit": "TOPS", "n_gpus": 1, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": dt, "data": "synthetic",
-            "config": {"workload": name, "l2": "256 MB flush between timed launches", "launch": "CUDA graph replay of the call"},
-            "roofline": {"bound": "tensor", "achieved": tops, "peak": 2.0 * pk["bf16"], "unit": "TFLOP/s",
-                         "frac": tops / (2.0 * pk["bf16"]),
-                         # DRAM bytes of the GEMM launch from the ncu capture of this very shape (profiles/qlin_gemm_pair_*)
-                         "traffic": (86.8e6 + 97.6e6) if args.workload == "c5lin" else None,
-                         "peak_source": f"2 x bf16_tflops (burst) of MEASURED_PEAKS.json ({pk['src']})"},
-        }), flush=True)  # fmt: skip
 
 
 def main():
@@ -809,28 +785,30 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c5", choices=["c5", "c1", "c2", "c3", "c4", "c5lin"])
-    ap.add_argument("--layers", type=int, default=None, help="development only: fewer decoder layers")
+    ap.add_argument("--layers", type=int, default=None, help="development only: fewer layers")
+    ap.add_argument("--surface", default="both", choices=["fused", "modules", "both"],
+                    help="c5 on one GPU: the fused decoder (headline), the QLinearINT8Deploy module route, or the first timed and "
+                         "the second reported beside it")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-kernels", action="store_true", help="c5 on one GPU: skip the single-kernel block")
+    ap.add_argument("--no-check", action="store_true", help="sharded runs: skip the 2-layer comparison with the one-GPU forward")
     ap.add_argument("--graph", default="auto", choices=["auto", "on", "off"],
                     help="replay the forward pass as one CUDA graph in the timed region (auto: sharded runs only)")
-    ap.add_argument("--reserve-sms", type=int, default=0, help="sharded runs with several groups: SMs set aside for the kernels that "
-                    "are bound by the links (even; 0: no partition)")
-    ap.add_argument("--chain", action="store_true", help="sharded runs with several groups: run the groups' compute segments strictly "
-                    "one after the other (event chain) so that one group's transfers overlap the other's kernels")
-    ap.add_argument("--exchange", default="stores", choices=["stores", "copies"],
-                    help="sharded runs: how partial outputs and codes reach the other GPUs: stores from the GEMM epilogue / the "
-                    "quantiser, or copy-engine transfers from local staging")
-    ap.add_argument("--breakdown", action="store_true", help="development: per-kernel-shape times of the timed region on stderr")
-    ap.add_argument("--allreduce", action="store_true", help="sharded runs: NCCL all-reduce of the row-parallel outputs instead of "
-                    "remote stores from the GEMM epilogue with the residual stream split by tokens")
-    ap.add_argument("--micro", type=int, default=0, help="groups of sequences pipelined on separate streams (0: 2 on more than two GPUs, else 1)")
-    ap.add_argument("--gemm-ctas", type=int, default=132, help="CTAs per GEMM while a collective may run beside it (sharded runs)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "multimem", "stores", "allreduce"],
+                    help="sharded runs: how the shard boundary is crossed (auto: multimem where the node has NVLink multicast, else stores)")
+    ap.add_argument("--groups", type=int, default=0, help="groups of sequences pipelined on separate streams (0: 2 on sharded runs, else 1)")
+    ap.add_argument("--reserve-sms", type=int, default=-1, help="sharded runs with several groups: SMs left to the link-bound exchange "
+                    "kernels, GEMMs capped at the rest (-1: 16 on more than two GPUs, else 0)")
     ap.add_argument("--nccl-ctas", type=int, default=16, help="upper bound on the CTAs of a collective (sharded runs)")
+    ap.add_argument("--c4-dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--breakdown", action="store_true", help="development: per-kernel-shape times on stderr")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.reserve_sms < 0:
+        args.reserve_sms = 16 if world > 2 else 0
 
     if args.impl == "reference":
         run_reference(args, rank)
@@ -846,6 +824,7 @@ def main():
 
         # a rank that fails must not leave the others waiting for NCCL's default ten minutes
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+    failed = None
     try:
         if args.workload == "c4":
             run_c4(args, dev)
@@ -853,9 +832,22 @@ def main():
             run_c5(args, rank, world, dev)
         else:
             run_kernel_workload(args, dev)
+    except BaseException as e:  # noqa: BLE001
+        failed = e
+        import traceback
+
+        traceback.print_exc()
     finally:
         if world > 1:
+            # leave together: no rank may exit while another still sends traffic to memory it had bound to the multicast object
+            try:
+                torch.cuda.synchronize()
+                dist.barrier()
+            except Exception:  # noqa: BLE001
+                pass
             dist.destroy_process_group()
+    if failed is not None:
+        raise SystemExit(1)
 
 
 if __name__ == "__main__":

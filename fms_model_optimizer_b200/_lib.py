@@ -223,6 +223,8 @@ class BlockQuantArgs(C.Structure):
         ("norm_eps", C.c_float),
         ("dyn_eps", C.c_float),
         ("max_ctas", C.c_int32),
+        ("r_multimem", C.c_int32),
+        ("dst_multimem", C.c_int32),
     ]
 
 
@@ -247,6 +249,7 @@ class PeerBarrierArgs(C.Structure):
         ("status", C.c_void_p),
         ("rank", C.c_int32),
         ("world", C.c_int32),
+        ("timeout_ns", C.c_int64),
     ]
 
 

@@ -7,6 +7,7 @@ The library is compiled for sm_100a only with plain ``nvcc``; nothing is JIT-com
 
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
 import subprocess
@@ -43,14 +44,27 @@ def _sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
-def _deps_mtime() -> float:
-    files = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
+STAMP_PATH = LIB_DIR / "libqlin_b200.stamp"
+
+
+def source_digest(extra_flags: tuple = ()) -> str:
+    """SHA-256 over the compiler flags and the name and content of every file the library is built from.  File times
+    say nothing after a checkout or a copy to another machine, so staleness is decided by content."""
+    files = sorted(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")))
     files.append(PKG_DIR.parent / "include" / "qlin_b200.h")
-    return max(f.stat().st_mtime for f in files)
+    h = hashlib.sha256()
+    h.update("\0".join([*NVCC_FLAGS, *extra_flags]).encode())
+    for f in files:
+        h.update(f.name.encode() + b"\0")
+        h.update(f.read_bytes())
+    return h.hexdigest()
 
 
 def is_stale() -> bool:
-    return (not LIB_PATH.exists()) or LIB_PATH.stat().st_mtime < _deps_mtime()
+    """True unless the library exists and the digest stored beside it at build time equals the digest of the sources."""
+    if not LIB_PATH.exists() or not STAMP_PATH.exists():
+        return True
+    return STAMP_PATH.read_text().strip() != source_digest()
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
@@ -79,6 +93,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
     os.replace(tmp, LIB_PATH)
+    STAMP_PATH.write_text(source_digest() + "\n")
     return LIB_PATH
 
 

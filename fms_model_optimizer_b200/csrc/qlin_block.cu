@@ -44,6 +44,7 @@ struct BlockQuantParams {
   int64_t codes_off[3], scale_off[3];
   int32_t ndst, dst_row0;
   int32_t max_ctas;
+  int32_t r_multimem, dst_multimem;
 };
 
 __device__ __forceinline__ uint32_t bq_pack(float lo, float hi) {
@@ -69,6 +70,28 @@ __device__ __forceinline__ void bq_load8(const __nv_bfloat16* p, uint32_t (&w)[8
 __device__ __forceinline__ void bq_store8(__nv_bfloat16* p, const uint32_t (&w)[8]) {
   reinterpret_cast<uint4*>(p)[0] = make_uint4(w[0], w[1], w[2], w[3]);
   reinterpret_cast<uint4*>(p)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+// NVLink-switch forms for buffers that every GPU of the node has bound to one multicast object: a load that returns the
+// sum of all GPUs' copies (bf16 pairs, accumulated in fp32 by the switch, rounded once), and a store that lands in
+// every GPU's copy.  The address is the multicast mapping of the buffer, not a peer pointer.
+__device__ __forceinline__ void bq_load8_reduce(const __nv_bfloat16* mc, uint32_t (&w)[8]) {
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3])
+               : "l"(mc)
+               : "memory");
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+               : "l"(mc + 8)
+               : "memory");
+}
+__device__ __forceinline__ void bq_store16_all(uint8_t* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+__device__ __forceinline__ void bq_store_f32_all(float* mc, float v) {
+  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc), "f"(v) : "memory");
 }
 
 template <int TPB>
@@ -105,8 +128,12 @@ __global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams
         if (p.r != nullptr) {
           uint32_t a[8];
           const __nv_bfloat16* rp = p.r + static_cast<int64_t>(row) * p.ldr + ch * 16;
-          bq_load8(rp, a);
-          if (p.r_parts > 1) {  // sum of the shards' partial outputs: fp32 in index order, one rounding
+          if (p.r_multimem) {
+            bq_load8_reduce(rp, a);  // the switch adds the row-parallel shards' partial outputs
+          } else {
+            bq_load8(rp, a);
+          }
+          if (p.r_parts > 1 && !p.r_multimem) {  // sum of the shards' partial outputs: fp32 in index order, one rounding
             float acc[16];
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[2 * j] = bq_lo(a[j]), acc[2 * j + 1] = bq_hi(a[j]);
@@ -183,7 +210,9 @@ __global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams
         amax = block_reduce<OpMax>(amax, red[flip], 0.0f);
         flip ^= 1;
         s = Elem<__nv_bfloat16>::rnd(__fdiv_rn(fmaxf(amax, eps), static_cast<float>(p.levels)));
-        if (p.ndst > 0) {
+        if (p.dst_multimem) {
+          if (threadIdx.x == 0) bq_store_f32_all(reinterpret_cast<float*>(p.dst_base[0] + p.scale_off[o]) + p.dst_row0 + row, s);
+        } else if (p.ndst > 0) {
           if (static_cast<int>(threadIdx.x) < p.ndst)
             reinterpret_cast<float*>(p.dst_base[threadIdx.x] + p.scale_off[o])[p.dst_row0 + row] = s;
         } else if (threadIdx.x == 0 && p.scale_out[o] != nullptr) {
@@ -203,7 +232,9 @@ __global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams
                              __byte_perm(__float_as_uint(qb.x), __float_as_uint(qb.y), 0x0040), 0x5410);
       }
       const uint4 packed = make_uint4(out[0], out[1], out[2], out[3]);
-      if (p.ndst > 0) {
+      if (p.dst_multimem) {
+        bq_store16_all(p.dst_base[0] + p.codes_off[o] + static_cast<int64_t>(p.dst_row0 + row) * p.ldq[o] + ch * 16, packed);
+      } else if (p.ndst > 0) {
         const int64_t off = p.codes_off[o] + static_cast<int64_t>(p.dst_row0 + row) * p.ldq[o] + ch * 16;
         for (int d = 0; d < p.ndst; ++d) *reinterpret_cast<uint4*>(p.dst_base[d] + off) = packed;
       } else {
@@ -308,6 +339,11 @@ extern "C" int qlin_block_quant(const qlin_block_quant_args* a, void* stream) {
   p.ndst = a->ndst;
   p.dst_row0 = a->dst_row0;
   p.max_ctas = a->max_ctas;
+  p.r_multimem = a->r_multimem != 0;
+  p.dst_multimem = a->dst_multimem != 0;
+  if (p.dst_multimem && a->ndst != 1) return fail(QLIN_ERR_BAD_SHAPE, "qlin_block_quant: dst_multimem takes exactly one destination, the multicast address");
+  if (p.r_multimem && (a->prologue != QLIN_BLOCK_NORM || a->r == nullptr))
+    return fail(QLIN_ERR_UNSUPPORTED, "qlin_block_quant: r_multimem is the addend of the NORM prologue");
   if (a->r_parts < 0 || a->r_parts > 8 || (a->r_parts > 1 && a->r_part_stride % 8 != 0))
     return fail(QLIN_ERR_BAD_SHAPE, "qlin_block_quant: r_parts must be in [0, 8] with a part stride that is a multiple of 8 elements");
   p.r_parts = a->r_parts;

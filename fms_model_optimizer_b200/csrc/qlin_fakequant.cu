@@ -179,24 +179,31 @@ __global__ void __launch_bounds__(kFqThreads) pact2_bwd_finish_kernel(const floa
   }
 }
 
-// Grid of the elementwise kernels: a function of numel only, so the reduction order is fixed.
+// Fixed upper bound on the grid of the elementwise kernels; qlin_pact2_bwd_noalloc sizes its built-in scratch by it.
+constexpr int kFqMaxBlocks = 148 * 8;
+
+// Grid of the elementwise kernels: a function of numel and of the device's SM count only, so the reduction order is
+// fixed on a given GPU model (eight blocks per SM, never more than kFqMaxBlocks).
 static int fq_grid(int64_t numel) {
   const int64_t per_block = static_cast<int64_t>(kFqThreads) * 16;
   int64_t blocks = (numel + per_block - 1) / per_block;
-  const int64_t cap = 148 * 8;
+  int64_t cap = static_cast<int64_t>(sm_count()) * 8;
+  if (cap < 1 || cap > kFqMaxBlocks) cap = kFqMaxBlocks;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return static_cast<int>(blocks);
 }
 
-static int check_pact(const qlin_pact2_args* a, bool bwd, const char* name) {
+// Argument checks shared by every PACT+ entry point.  `needs_workspace` is false for the entry point that brings its
+// own scratch memory.
+static int check_pact(const qlin_pact2_args* a, bool bwd, const char* name, bool needs_workspace = true) {
   if (a == nullptr) return fail(QLIN_ERR_NULL, "%s: args is NULL", name);
   if (a->x == nullptr || a->out == nullptr || a->clip_val == nullptr ||
       (a->variant == QLIN_PACT_TWO_SIDED && a->clip_valn == nullptr))
     return fail(QLIN_ERR_NULL, "%s: x, out, clip_val or clip_valn is NULL", name);
   if (a->variant < QLIN_PACT_TWO_SIDED || a->variant > QLIN_PACT_SYMMETRIC)
     return fail(QLIN_ERR_UNSUPPORTED, "%s: unknown variant %d", name, a->variant);
-  if (bwd && (a->grad_out == nullptr || a->grad_clip == nullptr || a->workspace == nullptr))
+  if (bwd && (a->grad_out == nullptr || a->grad_clip == nullptr || (needs_workspace && a->workspace == nullptr)))
     return fail(QLIN_ERR_NULL, "%s: grad_out, grad_clip or workspace is NULL", name);
   if (a->numel < 0) return fail(QLIN_ERR_BAD_SHAPE, "%s: negative numel", name);
   if (a->num_bits < 2 || a->num_bits > 16) return fail(QLIN_ERR_UNSUPPORTED, "%s: num_bits must be in [2, 16]", name);
@@ -296,7 +303,7 @@ extern "C" int qlin_pact2_bwd(const qlin_pact2_args* a, void* stream) {
 // ------------------------------------------------------------------------------------------------
 namespace qlin {
 
-constexpr int kNoAllocMaxBlocks = 148 * 8;                 // the grid cap of the elementwise kernels
+constexpr int kNoAllocMaxBlocks = kFqMaxBlocks;            // the grid cap of the elementwise kernels
 constexpr int kNoAllocScratchFloats = 2 * kNoAllocMaxBlocks;  // 9472 bytes
 constexpr int64_t kNoAllocMaxNumel = int64_t(1) << 31;     // elements per call
 
@@ -326,21 +333,15 @@ extern "C" int64_t qlin_pact2_bwd_noalloc_max_numel(void) { return qlin::kNoAllo
 
 extern "C" int qlin_pact2_bwd_noalloc(const qlin_pact2_args* a, void* stream) {
   const char* name = "qlin_pact2_bwd_noalloc";
-  if (a == nullptr) return fail(QLIN_ERR_NULL, "%s: args is NULL", name);
-  if (a->x == nullptr || a->out == nullptr || a->clip_val == nullptr ||
-      (a->variant == QLIN_PACT_TWO_SIDED && a->clip_valn == nullptr) || a->grad_out == nullptr || a->grad_clip == nullptr)
-    return fail(QLIN_ERR_NULL, "%s: x, grad_out, out, clip_val, clip_valn or grad_clip is NULL", name);
-  if (a->numel < 0) return fail(QLIN_ERR_BAD_SHAPE, "%s: negative numel", name);
+  int rc = check_pact(a, true, name, /*needs_workspace=*/false);
+  if (rc != QLIN_OK) return rc;
   if (a->numel > kNoAllocMaxNumel)
     return fail(QLIN_ERR_TOO_LARGE, "%s: numel %lld exceeds the built-in scratch limit of %lld elements per call", name,
                 static_cast<long long>(a->numel), static_cast<long long>(kNoAllocMaxNumel));
-  if (a->num_bits < 2 || a->num_bits > 16) return fail(QLIN_ERR_UNSUPPORTED, "%s: num_bits must be in [2, 16]", name);
-  if (a->dtype != QLIN_DT_F32 && a->dtype != QLIN_DT_F16 && a->dtype != QLIN_DT_BF16)
-    return fail(QLIN_ERR_BAD_DTYPE, "%s: dtype must be F32, F16 or BF16", name);
   const int grid = fq_grid(a->numel);
   if (grid > kNoAllocMaxBlocks) return fail(QLIN_ERR_TOO_LARGE, "%s: grid %d exceeds the built-in scratch", name, grid);
   float* scratch = nullptr;
-  int rc = noalloc_scratch_ptr(&scratch);
+  rc = noalloc_scratch_ptr(&scratch);
   if (rc != QLIN_OK) return rc;
   PactParams p = to_params(a);
   p.ws = scratch;  // the looked-up device address, never the host-side symbol

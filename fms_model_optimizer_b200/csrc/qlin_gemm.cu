@@ -484,7 +484,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint32_t peek = warp_mbar_test_begin(&aux->full[ns], nph);
         const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
         const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
-        if (!CHUNKED && k32_left >= 4 && (kb > 0 || true)) {
+        if (!CHUNKED && k32_left >= 4) {
           if (kb == 0) {
             ok = warp_mbar_wait(&aux->tempty[buf], bph ^ 1u, abort_flag);
             if (!ok) break;

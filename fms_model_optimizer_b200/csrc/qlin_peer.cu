@@ -13,8 +13,9 @@
 //       Every rank stores the next epoch number into its slot of every peer's flag array
 //       (st.release.sys) and waits until all of its own slots show that epoch (ld.acquire.sys).
 //       Plain peer stores written by earlier kernels of the stream are visible to the peers' later
-//       kernels once the barrier has passed.  The wait is bounded by wall-clock time (10 s): when a
-//       peer never arrives the kernel records QLIN_ERR_TIMEOUT in `status` and returns.
+//       kernels once the barrier has passed.  The wait is bounded by wall-clock time (timeout_ns of the
+//       argument block, 10 s when that is 0): when a peer never arrives the kernel records
+//       QLIN_ERR_TIMEOUT in `status` and returns; the context stays usable.
 #include <cstring>
 
 #include <cuda.h>
@@ -23,7 +24,7 @@
 
 namespace qlin {
 
-constexpr unsigned long long kBarrierTimeoutNs = 10000000000ull;  // 10 s: peers may still be loading libraries on their first step
+constexpr unsigned long long kBarrierTimeoutNs = 10000000000ull;  // default, 10 s: peers may still be loading libraries on their first step
 
 __device__ __forceinline__ unsigned long long peer_now_ns() {
   unsigned long long t;
@@ -37,6 +38,7 @@ struct BarrierParams {
   uint32_t* epoch;         // local counter, one per barrier object
   int32_t* status;
   int32_t rank, world;
+  unsigned long long timeout_ns;
 };
 
 __global__ void __launch_bounds__(32) peer_barrier_kernel(const BarrierParams p) {
@@ -57,7 +59,7 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(const BarrierParams p)
       uint32_t v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(src) : "memory");
       seen = static_cast<int32_t>(v - e) >= 0;
-      if (!seen && peer_now_ns() - t0 > kBarrierTimeoutNs) {
+      if (!seen && peer_now_ns() - t0 > p.timeout_ns) {
         if (p.status != nullptr) atomicExch(p.status, static_cast<int32_t>(QLIN_ERR_TIMEOUT));
         break;
       }
@@ -159,6 +161,8 @@ extern "C" int qlin_peer_barrier(const qlin_peer_barrier_args* a, void* stream) 
   p.status = a->status;
   p.rank = a->rank;
   p.world = a->world;
+  if (a->timeout_ns < 0) return fail(QLIN_ERR_BAD_SHAPE, "qlin_peer_barrier: negative timeout_ns");
+  p.timeout_ns = a->timeout_ns > 0 ? static_cast<unsigned long long>(a->timeout_ns) : kBarrierTimeoutNs;
   for (int i = 0; i < 8; ++i) {
     p.peer_flags[i] = i < a->world ? a->peer_flags[i] : nullptr;
     if (i < a->world && p.peer_flags[i] == nullptr) return fail(QLIN_ERR_NULL, "qlin_peer_barrier: peer_flags[%d] is NULL", i);

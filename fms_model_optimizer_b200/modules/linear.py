@@ -84,7 +84,9 @@ class QLinearINT8Deploy(nn.Linear):
             if q.useDynMaxQfunc in [-1, -2]:
                 input_zero_point = torch.tensor(128 - q.useSymAct, device=tar_dev)
             elif 0 < q.useDynMaxQfunc < 65:
-                raise NotImplementedError("fake zero-shift dynamic quantisation is not provided on B200")
+                # per-tensor dynamic scale with a fake zero shift; the scale is computed at run time
+                q.use_fake_zero_shift = True
+                input_zero_point = torch.tensor(q.useDynMaxQfunc, device=tar_dev)
             elif q.usePTnativeQfunc:
                 input_scale = torch.tensor([(a_cv - a_cvn) / a_levels], device=tar_dev)
                 input_zero_point = torch.round(-a_cvn / input_scale)
@@ -120,6 +122,8 @@ class QLinearINT8Deploy(nn.Linear):
 
             if q.useSymAct:
                 corr_term_int = 0
+                if q.use_fake_zero_shift:
+                    corr_term_int = input_zero_point * (w_int8.sum(dim=1))
             else:
                 corr_term_int = (input_zero_point - 128) * (w_int8.sum(dim=1))
             q.register_buffer("corr_term", corr_term_int * w_scale.float() * input_scale.float())
@@ -128,6 +132,8 @@ class QLinearINT8Deploy(nn.Linear):
                 new_bias = fms_mo_qlinear.bias.float() - q.corr_term
             else:
                 new_bias = -q.corr_term
+            if q.use_fake_zero_shift:
+                new_bias += q.corr_term  # applied in forward, times the run-time input scale
             delattr(q, "bias")
             q.register_buffer("bias", new_bias.to(w_dtype))
 
@@ -197,7 +203,9 @@ class QLinearINT8Deploy(nn.Linear):
 
     def _prepared(self, dev: torch.device):
         """fp32 views of the per-channel vectors the kernels take, rebuilt when buffers move."""
-        key = (self.w_scale.data_ptr(), self.bias.data_ptr(), self.smoothq_scale.data_ptr(), str(dev))
+        bufs = (self.w_scale, self.bias, self.smoothq_scale)
+        # in-place updates (load_state_dict, buffer.copy_) keep the address and bump the version counter
+        key = tuple((b.data_ptr(), b._version, b.dtype) for b in bufs) + (str(dev),)
         if self._cache is None or self._cache[0] != key:
             sq = self.smoothq_scale
             use_sq = bool(torch.all(sq != 1).item())
@@ -245,14 +253,15 @@ class QLinearINT8Deploy(nn.Linear):
             smooth = prep["smooth"]
             chain = x2.dtype if smooth is None else _promote(x2.dtype, self.smoothq_scale.dtype)
             kw = {}
+            # `x / smoothq_scale` is rounded to the dtype of x when the scale has that dtype (or promotes to it); the
+            # static quantisers then divide by their fp32 scale buffers in fp32 (fms_mo/modules/linear.py:1330, :1061-1083)
+            smooth_native = 1 if (smooth is not None and chain == x2.dtype and chain != torch.float32) else 0
             if self.useDynMaxQfunc in [-1, -2]:
                 if self.useDynMaxQfunc == -2:
                     raise NotImplementedError("per-channel (dim=-2) dynamic activation quantisation")
                 # qa_dynamic_max_qfunc runs in `chain`; bit 0: the division by smoothq_scale rounds to
                 # the dtype of x, bit 1: the quantise chain does
-                native = (1 if (smooth is not None and chain == x2.dtype and chain != torch.float32) else 0) | (
-                    2 if (chain == x2.dtype and chain != torch.float32) else 0
-                )
+                native = smooth_native | (2 if (chain == x2.dtype and chain != torch.float32) else 0)
                 if smooth is None or self.smoothq_scale.dtype == x2.dtype:
                     native |= 4  # the smoothing scales are values of the activation dtype
                 codes, in_scale, _ = ops.act_quant(
@@ -260,17 +269,31 @@ class QLinearINT8Deploy(nn.Linear):
                     levels=2 ** (self.nbits_a - 1) - 1
                 )
                 scale_dtype = chain
+            elif self.use_fake_zero_shift:
+                # qa_dyn_max_fake_zero_shift (fms_mo/modules/linear.py:1102-1113): one scale for the whole tensor,
+                # amax / (127 - zp), codes shifted by zp; the largest per-row scale is that scale (rounding is monotonic)
+                zp = int(self.input_zp)
+                native = smooth_native | (2 if (chain == x2.dtype and chain != torch.float32) else 0)
+                if smooth is None or self.smoothq_scale.dtype == x2.dtype:
+                    native |= 4
+                kq = dict(smooth=smooth, smooth_rcp=prep["smooth_rcp"], native_chain=native)
+                _, row_scale, _ = ops.act_quant(x2, mode=L.Q_I8_DYN, levels=2 ** (self.nbits_a - 1) - 1 - zp, want_codes=False, **kq)
+                in_scale = row_scale.max().reshape(1)
+                codes, _, _ = ops.act_quant(x2, mode=L.Q_I8_GIVEN_SCALE, scale_in=in_scale, zp0=float(zp), **kq)
+                # iaddmm_int (:1179-1182): bias - input_scale * corr_term, formed in fp32
+                kw["bias"] = prep["bias"] - in_scale * self.corr_term.detach().float().reshape(-1)
+                scale_dtype = self.w_scale.dtype if self.w_scale.dim() > 0 else chain  # a 0-dim scale takes the other operand's dtype
             elif self.usePTnativeQfunc:
                 codes, in_scale, _ = ops.act_quant(
-                    x2, mode=L.Q_I8_STATIC, smooth=smooth, smooth_rcp=prep["smooth_rcp"], scale0=float(self.input_scale), zp0=float(self.input_zp),
-                    shift=128.0, add2=float(self.useSymAct),
+                    x2, mode=L.Q_I8_STATIC, smooth=smooth, smooth_rcp=prep["smooth_rcp"], native_chain=smooth_native,
+                    scale0=float(self.input_scale), zp0=float(self.input_zp), shift=128.0, add2=float(self.useSymAct),
                 )  # fmt: skip
                 in_scale = self.input_scale.detach().float().reshape(-1)
                 scale_dtype = self.input_scale.dtype
             else:
                 codes, in_scale, _ = ops.act_quant(
-                    x2, mode=L.Q_I8_STATIC_CLAMP_FIRST, smooth=smooth, smooth_rcp=prep["smooth_rcp"], scale0=float(self.quant_stepsize),
-                    zp0=float(self.quant_zero_point), lo=float(self.cvs[1]), hi=float(self.cvs[0]),
+                    x2, mode=L.Q_I8_STATIC_CLAMP_FIRST, smooth=smooth, smooth_rcp=prep["smooth_rcp"], native_chain=smooth_native,
+                    scale0=float(self.quant_stepsize), zp0=float(self.quant_zero_point), lo=float(self.cvs[1]), hi=float(self.cvs[0]),
                     shift=float(128 - self.useSymAct),
                 )  # fmt: skip
                 in_scale = self.input_scale.detach().float().reshape(-1)
@@ -279,7 +302,7 @@ class QLinearINT8Deploy(nn.Linear):
             out = ops.gemm(
                 codes, self.weight,
                 chunk_k=_normalised_chunk(self.chunk_size), trun_bits=int(self.truncate_lsb), max_acc_bits=self.max_acc_bits,
-                epilogue=L.EPI_SCALE_PROD, row_scale=in_scale, col_scale=prep["w_scale"], bias=prep["bias"],
+                epilogue=L.EPI_SCALE_PROD, row_scale=in_scale, col_scale=prep["w_scale"], bias=kw.pop("bias", prep["bias"]),
                 prod_round=(None if prod_dtype == torch.float32 else prod_dtype), scale_round=torch.float16,
                 acc_round=(None if self.acc_dtype == torch.float32 else self.acc_dtype), out_dtype=org_dtype, **kw,
             )  # fmt: skip
@@ -410,6 +433,36 @@ class QLinearCublasI8I32NT(nn.Linear):
     (QLinearCublasI8I32NT of the reference, fms_mo/modules/linear.py:1341-1537; the GEMM replaces
     ``mygemm::gemm_nt_i8i32`` / ``cutlass_gemm::i8i32nt``).  ``weight`` is int8 ``[out, in]``; with uint8
     activations the zero-point correction ``w_scale * input_scale * (zp - 128) * sum_k W`` is folded into ``bias``."""
+
+    @classmethod
+    def from_reference(cls, ref_qlinear, input_scale, input_zero_point, input_dtype, forceSymA=False):
+        """fms_mo/modules/linear.py:1349-1426: from a ``torch.ao.nn.quantized.reference.Linear`` with per-channel weight
+        quantisation.  uint8 activations are either made symmetric (``forceSymA``: a new scale ``2 max|range| / 253``, zero
+        point 0) or kept, with the zero-point correction folded into the bias."""
+        q = cls(ref_qlinear.in_features, ref_qlinear.out_features)
+        q.forceSymA = forceSymA
+        q.input_dtype = input_dtype
+        q.register_buffer("input_scale", input_scale)
+        q.register_buffer("input_zp", input_zero_point)
+        qweight = ref_qlinear.float().get_quantized_weight()
+        if ref_qlinear.weight_qscheme not in [torch.per_channel_symmetric, torch.per_channel_affine]:
+            raise RuntimeError("QLinear_cublas only supports perCh for now. ")
+        q.register_buffer("w_scale", qweight.q_per_channel_scales().float())
+        q.register_buffer("w_zp", qweight.q_per_channel_zero_points())
+        q.weight = nn.Parameter(qweight.int_repr(), requires_grad=False)
+        q.bias = nn.Parameter(ref_qlinear.bias, requires_grad=False)
+        if input_dtype == torch.quint8:
+            if forceSymA:
+                a_min = -input_zero_point * input_scale
+                a_max = (255 - input_zero_point) * input_scale
+                a_max_new = max(abs(a_min), abs(a_max))
+                q.input_scale.copy_((2 * a_max_new) / (255 - 2))
+                q.input_zp.copy_(0)
+                q.input_dtype = torch.qint8
+            else:
+                corr_term = q.w_scale * input_scale * (input_zero_point - 128) * q.weight.sum(dim=1)
+                q.bias = nn.Parameter(ref_qlinear.bias - corr_term.to(ref_qlinear.bias.dtype), requires_grad=False)
+        return q
 
     @classmethod
     def from_fms_mo(cls, fms_mo_qlinear, **kwargs):
@@ -612,7 +665,9 @@ def lower_qmodel_b200(model: nn.Module, use_dyn_max_act=False, max_acc_bits=32, 
     """In-place lowering with the signature of lower_qmodel_triton
     (fms_mo/custom_ext_kernels/utils.py:869-959): every QLinear (this package's, or the reference's --
     matched by class name so the reference need not be importable) becomes a QLinearINT8Deploy, every
-    plain ``nn.Linear`` a LinearFPxAcc."""
+    plain ``nn.Linear`` a LinearFPxAcc with per-token (``use_dyn_max_act`` -1 / -2) or per-tensor FP8 scaling.
+    With ``use_dyn_max_act=False`` the reference would run plain Linears through its 16-bit truncating matmul; the
+    B200 FP8 Linear has no unscaled mode, so those layers are left as they are (they stay ``nn.Linear``)."""
     fp_dyn = "per_token" if use_dyn_max_act in [-1, -2] else "per_tensor" if use_dyn_max_act else False
     if layer_to_exclude is None:
         layer_to_exclude = []
@@ -623,6 +678,8 @@ def lower_qmodel_b200(model: nn.Module, use_dyn_max_act=False, max_acc_bits=32, 
     for name, m in list(model.named_modules()):
         is_q = type(m).__name__ == "QLinear"
         if not (is_q or type(m) is nn.Linear) or name in layer_to_exclude:
+            continue
+        if not is_q and not fp_dyn:
             continue
         parent_name, _, module_name = name.rpartition(".")
         parent = model.get_submodule(parent_name) if parent_name else model

@@ -544,13 +544,18 @@ def block_quant(
     dst: Optional[Tuple[Sequence[int], Sequence[int], Sequence[int], int]] = None,
     want_h: bool = False,
     max_ctas: int = 0,
+    r_multimem: bool = False,
+    dst_multimem: bool = False,
+    r_ptr: Optional[int] = None,
     levels: int = 127,
     norm_eps: float = 1e-5,
     dyn_eps: float = 1e-5,
 ):
     """See ``qlin_block_quant`` in include/qlin_b200.h.  ``x`` (and ``r``) are 2-D bf16 with unit column
     stride; ``smooth_rcps`` holds one fp32 reciprocal vector (or None) per Linear that consumes the row.
-    Returns ``(codes list, scales list, x_plus_r or None, h or None)``; with ``BLOCK_SCALE_ONLY`` the codes are None."""
+    Returns ``(codes list, scales list, x_plus_r or None, h or None)``; with ``BLOCK_SCALE_ONLY`` the codes are None.
+    ``r_ptr`` gives the addend as a raw device address with the row pitch of ``x`` (a multicast mapping when
+    ``r_multimem``); ``dst_multimem`` says that ``dst[0][0]`` is a multicast address."""
     dev = _require_cuda(x, r, norm_w, scale_in, *smooth_rcps)
     if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
         raise RuntimeError("block_quant takes a 2-D bf16 tensor with contiguous rows")
@@ -567,9 +572,10 @@ def block_quant(
         given_as_is = mode == L.BLOCK_GIVEN_SCALE and scale_in_parts <= 1
         scales = [scale_in if given_as_is else torch.empty((rows,), dtype=torch.float32, device=dev) for _ in range(nout)]
     x_out = None
-    if r is not None and sum_into is not None:
+    has_r = r is not None or r_ptr is not None
+    if has_r and sum_into is not None:
         x_out = sum_into
-    elif r is not None and store_sum:
+    elif has_r and store_sum:
         x_out = torch.empty((rows, cols), dtype=torch.bfloat16, device=dev)
     h_out = torch.empty((rows, cols), dtype=torch.bfloat16, device=dev) if want_h else None
     if rows == 0 or cols == 0:
@@ -578,14 +584,15 @@ def block_quant(
     i3 = C.c_int64 * 3
     pad = [None] * (3 - nout)
     args = L.BlockQuantArgs(
-        x=_ptr(x), r=_ptr(r), r_parts=int(r_parts), r_part_stride=int(r_part_stride), x_out=_ptr(x_out), h_out=_ptr(h_out),
+        x=_ptr(x), r=(int(r_ptr) if r_ptr is not None else _ptr(r)), r_parts=int(r_parts), r_part_stride=int(r_part_stride), x_out=_ptr(x_out), h_out=_ptr(h_out),
         norm_w=_ptr(norm_w),
         smooth_rcp=p3(*[_ptr(t) for t in list(smooth_rcps) + pad]), codes=p3(*[_ptr(t) for t in codes + pad]),
         scale_out=p3(*[(_ptr(t) if (mode != L.BLOCK_GIVEN_SCALE or scale_in_parts > 1) else None) for t in scales + pad]), scale_in=_ptr(scale_in), scale_in_parts=int(scale_in_parts), scale_in_stride=int(scale_in_stride),
-        ldx=x.stride(0), ldr=(r.stride(0) if r is not None else 0), ldxo=(x_out.stride(0) if x_out is not None else cols),
+        ldx=x.stride(0), ldr=(r.stride(0) if r is not None else (cols if r_ptr is not None else 0)), ldxo=(x_out.stride(0) if x_out is not None else cols),
         ldh=cols, ldq=i3(cols, cols, cols),
         rows=rows, cols=cols, nout=nout, prologue=int(prologue), mode=int(mode), qmax_levels=int(levels),
         norm_eps=float(norm_eps), dyn_eps=float(dyn_eps), max_ctas=int(max_ctas),
+        r_multimem=int(bool(r_multimem)), dst_multimem=int(bool(dst_multimem)),
     )  # fmt: skip
     ndst = 1
     if dst is not None:
@@ -594,7 +601,7 @@ def block_quant(
         args.codes_off = i3(*(list(dst[1]) + [0] * (3 - nout)))
         args.scale_off = i3(*(list(dst[2]) + [0] * (3 - nout)))
         args.ndst, args.dst_row0 = ndst, int(dst[3])
-    nbytes = rows * cols * (2 * (1 + (max(1, r_parts) if r is not None else 0) + (x_out is not None) + (h_out is not None))
+    nbytes = rows * cols * (2 * (1 + (max(1, r_parts) if has_r else 0) + (x_out is not None) + (h_out is not None))
                             + (0 if mode == L.BLOCK_SCALE_ONLY else nout * ndst))
     with torch.cuda.device(dev):
         rc = _timed("block_quant", float(nbytes), dev, lambda: L.load().qlin_block_quant(C.byref(args), _stream(dev)))

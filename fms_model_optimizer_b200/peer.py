@@ -84,11 +84,74 @@ class PeerArena:
         self._opened = []
 
 
+class SymmArena:
+    """The same arena interface over PyTorch's symmetric memory (``torch.distributed._symmetric_memory``): one
+    allocation per rank made with the driver's virtual-memory calls, exchanged between the processes and, where the
+    node has an NVLink switch, also bound to one multicast object.  ``mc_base`` is then the multicast mapping of the
+    arena: a ``multimem.st`` to ``mc_base + off`` lands at offset ``off`` of every rank's arena, and a
+    ``multimem.ld_reduce`` from it returns the sum of all ranks' values there.  ``mc_base`` is 0 when the node offers
+    no multicast.  PyTorch does the allocation and the handle exchange; the kernels of this library do every access."""
+
+    def __init__(self, nbytes: int, dev: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.dev = dev
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.nbytes = (int(nbytes) + 255) // 256 * 256
+        self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=dev)
+        self.handle = symm_mem.rendezvous(self.buf, self.group)
+        self.buf.zero_()
+        self.used = 0
+        self.base: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        if self.base[self.rank] != self.buf.data_ptr():
+            raise RuntimeError("symmetric memory: this rank's pointer differs from the tensor's address")
+        self.mc_base = int(self.handle.multicast_ptr or 0)
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=self.group)
+
+    alloc = PeerArena.alloc
+    addr = PeerArena.addr
+
+    def mc_addr(self, offset: int) -> int:
+        if not self.mc_base:
+            raise RuntimeError("this node offers no NVLink multicast")
+        return self.mc_base + offset
+
+    def close(self):
+        """Every rank must have stopped issuing work that touches the arena: a rank must never leave while another
+        still sends multicast traffic to the memory it had bound."""
+        torch.cuda.synchronize(self.dev)
+        dist.barrier(group=self.group)
+
+
+def make_arena(nbytes: int, dev: torch.device, want_multicast: bool, group=None):
+    """A SymmArena when ``want_multicast`` and the node provides it, otherwise the CUDA-IPC PeerArena.  All ranks take
+    the same branch (the decision is reduced over the group)."""
+    ok = 0
+    arena = None
+    if want_multicast:
+        try:
+            arena = SymmArena(nbytes, dev, group)
+            ok = 1 if arena.mc_base else 0
+        except Exception as e:  # noqa: BLE001 -- no symmetric memory on this node: every rank falls back together
+            print(f"# symmetric memory unavailable ({type(e).__name__}: {e}); using the CUDA-IPC arena", flush=True)
+            ok = 0
+        t = torch.tensor([ok], device=dev, dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+        ok = int(t.item())
+    if ok:
+        return arena
+    del arena
+    return PeerArena(nbytes, dev, group)
+
+
 class PeerBarrier:
     """``qlin_peer_barrier`` over flag words that live in a PeerArena.  Stream-ordered: work queued on the calling
     stream after ``wait()`` sees what the peers stored to this GPU before their ``wait()``."""
 
-    def __init__(self, arena: PeerArena):
+    def __init__(self, arena, timeout_s: float = 10.0):
         self.arena = arena
         self.off, flags = arena.alloc(256)
         self.flags = flags
@@ -97,10 +160,10 @@ class PeerBarrier:
             local_flags=arena.addr(arena.rank, self.off),
             peer_flags=(C.c_void_p * 8)(*([arena.addr(r, self.off) for r in range(arena.world)] + [None] * (8 - arena.world))),
             epoch=self.epoch.data_ptr(), status=ops.status_word(arena.dev).data_ptr(), rank=arena.rank, world=arena.world,
+            timeout_ns=int(timeout_s * 1e9),
         )  # fmt: skip
 
     def wait(self):
         dev = self.arena.dev
         with torch.cuda.device(dev):
-            L.check(L.load().qlin_peer_barrier(C.byref(self.args), ops._stream(dev)), "qlin_peer_barrier")
-        ops.LAUNCHES += 1
+            L.check(ops._timed("barrier", 0.0, dev, lambda: L.load().qlin_peer_barrier(C.byref(self.args), ops._stream(dev))), "qlin_peer_barrier")

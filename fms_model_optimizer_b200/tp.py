@@ -51,6 +51,16 @@ def shard_w8a8(weight_i8: torch.Tensor, w_scale: torch.Tensor, smooth: Optional[
     raise ValueError(f"unknown shard mode {mode!r}")
 
 
+class ScaleExchange:
+    """How the shards of a row-parallel Linear agree on the per-token scales without a collective: every shard stores
+    the scales of its slice of the row into slot ``rank`` of a ``[world][tokens]`` fp32 array on every GPU (plain stores
+    to the peers' arenas, or one ``multimem.st`` when ``bases`` holds the arena's multicast address), and after the
+    flag barrier each shard takes the maximum over the slots."""
+
+    def __init__(self, barrier, bases, slots_off: int, rank: int, slots: torch.Tensor, multimem: bool = False):
+        self.barrier, self.bases, self.slots_off, self.rank, self.slots, self.multimem = barrier, bases, slots_off, rank, slots, multimem
+
+
 class W8A8Linear:
     """A (possibly sharded) W8A8 Linear with per-token dynamic activation quantisation, SmoothQuant
     and per-channel weight scales: the arithmetic of QLinearINT8Deploy.forward
@@ -96,18 +106,17 @@ class W8A8Linear:
     def quantise_fused(self, x2: torch.Tensor, prologue: int = L.BLOCK_PLAIN, r: Optional[torch.Tensor] = None, exchange=None):
         """Per-token codes and scales of ``prologue(x2, r) / smooth`` for bf16 rows through the fused kernel
         (``ops.block_quant``); a row-parallel shard takes two passes around the MAX all-reduce of the scales.
-        ``exchange = (barrier, peer base addresses, byte offset of the [world][tokens] fp32 slots, rank, local slots)``
-        replaces that all-reduce: the first pass stores this shard's scales into slot ``rank`` on every GPU, and after
-        the barrier the second pass takes the maximum over the slots itself."""
+        ``exchange`` (a ``ScaleExchange``) replaces that all-reduce: the first pass stores this shard's scales into slot
+        ``rank`` on every GPU, and after the barrier the second pass takes the maximum over the slots itself."""
         rcp = [self.smooth_rcp]
-        if self.mode == "row" and self.world > 1 and exchange is not None:
-            bar, bases, slots_off, rank, slots = exchange
+        if exchange is not None:
             T = x2.shape[0]
+            world = exchange.barrier.arena.world
             ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_SCALE_ONLY,
-                            dst=(bases, [0], [slots_off + rank * T * 4], 0))
-            bar.wait()
+                            dst=(exchange.bases, [0], [exchange.slots_off + exchange.rank * T * 4], 0), dst_multimem=exchange.multimem)
+            exchange.barrier.wait()
             (codes,), (scale,), _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_GIVEN_SCALE,
-                                                       scale_in=slots, scale_in_parts=self.world, scale_in_stride=T)
+                                                       scale_in=exchange.slots, scale_in_parts=world, scale_in_stride=T)
             return codes, scale
         if self.mode == "row" and self.world > 1:
             _, (scale,), _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_SCALE_ONLY)
@@ -127,7 +136,7 @@ class W8A8Linear:
         self.gemm_fn(codes, self.weight, scale, self.w_scale, self.bias, act_dtype, prod_dtype, scatter=(bases, rows_per_rank, row0), **kw)
 
     def __call__(self, x2: Optional[torch.Tensor], quantised=None, act_dtype: Optional[torch.dtype] = None,
-                 reduce: bool = True) -> torch.Tensor:
+                 reduce: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``quantised=(codes, scale)`` skips the quantiser (a fused kernel upstream produced them for the
         activation dtype ``act_dtype``; for a row-parallel shard the scale must already be the maximum over ranks).
         ``reduce=False`` returns a row-parallel shard's partial output (the caller exchanges it)."""
@@ -135,6 +144,8 @@ class W8A8Linear:
         act_dtype = act_dtype if x2 is None else x2.dtype
         prod_dtype = torch.promote_types(act_dtype, self.w_scale_dtype)
         kw = {} if self.gemm_fn is not _cuda_gemm else {"max_ctas": self.max_ctas}
+        if out is not None:
+            kw["out"] = out
         out = self.gemm_fn(codes, self.weight, scale, self.w_scale, self.bias, act_dtype, prod_dtype, **kw)
         if reduce and self.mode == "row" and self.world > 1:
             dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)

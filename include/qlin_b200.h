@@ -426,6 +426,16 @@ typedef struct qlin_block_quant_args {
   float norm_eps, dyn_eps;
   int32_t max_ctas;     /* 0: fill the GPU; > 0: at most this many blocks, leaving SMs to kernels of other streams (a launch
                            whose replicated outputs are bound by the links anyway) */
+  /* NVLink-switch forms, for buffers that all GPUs of the node have bound to one multicast object (the addresses are
+     then the multicast mapping, not a peer pointer).
+     r_multimem != 0:   NORM only; r is read with multimem.ld_reduce: every 16-byte load returns the sum over all GPUs'
+                        copies of the buffer (bf16, accumulated in fp32 by the switch, rounded once): the reduction of a
+                        row-parallel Linear whose shards each wrote their partial output into their own copy.
+                        r_parts is ignored.
+     dst_multimem != 0: ndst must be 1 and dst_base[0] the multicast address: codes and scales are written with
+                        multimem.st, one store that lands in every GPU's copy. */
+  int32_t r_multimem;
+  int32_t dst_multimem;
 } qlin_block_quant_args;
 
 int qlin_block_quant(const qlin_block_quant_args* args, void* stream);
@@ -452,7 +462,7 @@ int qlin_rope(const qlin_rope_args* args, void* stream);
  *   qlin_ipc_open     maps a peer's allocation into this process (peer access is enabled on first use);
  *                     base_out is what qlin_ipc_close takes, ptr_out = base + offset.
  *   qlin_peer_barrier launches a one-warp kernel: rank stores the next epoch into slot `rank` of every
- *                     peer's flag array and waits (at most 10 s, then QLIN_ERR_TIMEOUT in *status) until all
+ *                     peer's flag array and waits (at most timeout_ns, then QLIN_ERR_TIMEOUT in *status) until all
  *                     `world` slots of its own array carry it.  Stores made to peer memory by earlier work of
  *                     the stream are visible to the peers' work after their barrier.  `epoch` is a device
  *                     counter owned by this barrier object; flag arrays and epoch start zeroed.
@@ -470,6 +480,7 @@ typedef struct qlin_peer_barrier_args {
   uint32_t* epoch;
   int32_t* status;
   int32_t rank, world;
+  int64_t timeout_ns;      /* longest wait in nanoseconds; 0 = the default of 10 s */
 } qlin_peer_barrier_args;
 
 int qlin_peer_barrier(const qlin_peer_barrier_args* args, void* stream);

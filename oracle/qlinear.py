@@ -217,3 +217,115 @@ def linear_fpx_backward(x, weight, grad_output, bias_dtype=None, trun_bits=0, ch
     grad_input = grad_input.reshape(grad_output.shape[:-1] + (in_dim,))
     grad_bias = gq.sum(0).to(bias_dtype) if bias_dtype is not None else None
     return grad_input, grad_weight, grad_bias
+
+
+# --------------------------------------------------------------------------------------------------
+# QLinearINT8Deploy beyond the per-token dynamic case
+# --------------------------------------------------------------------------------------------------
+def deploy_static_from_fms_mo(weight, bias, w_cv, a_cv, a_cvn, act_scale, alpha=0.5, native=True, sym_act=False, nbits=8):
+    """QLinearINT8Deploy.from_fms_mo (fms_mo/modules/linear.py:780-911) with ``use_dynamic_max_act_Qfunc=False``: static
+    per-tensor activation quantisation from the PACT clip values, in the "PT native" form (``use_PT_native_Qfunc=True``,
+    :832-834) or the older fms_mo form (:835-846).  Returns a dict of the module's buffers."""
+    w_levels = 2**nbits - 2
+    a_levels = 2**nbits - 1 - int(sym_act)
+    sq = torch.tensor([1.0], dtype=weight.dtype)
+    if act_scale is not None and torch.all(act_scale != 0).item():
+        w_sq = weight.abs().max(dim=0, keepdim=True)[0].clamp(min=1e-5)
+        alpha_t = torch.tensor([alpha], dtype=torch.float32).to(act_scale.dtype)
+        sq = (act_scale**alpha_t / w_sq ** (1.0 - alpha_t)).clamp(min=1e-5).to(act_scale.dtype)
+    st = dict(native=native, sym_act=sym_act, cvs=(a_cv, a_cvn), smoothq_scale=sq)
+    w_scale = w_cv * 2 / w_levels
+    if native:
+        input_scale = torch.tensor([(a_cv - a_cvn) / a_levels])
+        input_zp = torch.round(-a_cvn / input_scale)
+    else:
+        quant_scale = a_levels / torch.tensor([a_cv - a_cvn])
+        st["quant_stepsize"] = 1.0 / quant_scale
+        st["quant_zero_point"] = torch.round(a_cvn * quant_scale)
+        input_scale = st["quant_stepsize"]
+        input_zp = -st["quant_zero_point"]
+        w_scale = 1.0 / (w_levels / (w_cv * 2))
+    input_zp = input_zp.to(torch.int)
+    w_int8 = torch.round((weight * sq).t() / w_scale).clamp(-w_levels / 2, w_levels / 2).t().to(torch.int)
+    corr_int = 0 if sym_act else (input_zp - 128) * w_int8.sum(dim=1)
+    corr_term = corr_int * w_scale.float() * input_scale.float()
+    new_bias = (bias.float() - corr_term) if bias is not None else -corr_term
+    st.update(input_scale=input_scale, input_zp=input_zp, w_scale=w_scale, weight=w_int8.to(torch.int8), bias=new_bias.to(weight.dtype))
+    return st
+
+
+def deploy_static_codes(st, x2):
+    """qa_raw_qfunc / qa_fmo_mo_qfunc (fms_mo/modules/linear.py:1061-1083) after the SmoothQuant division of forward (:1330)."""
+    if torch.all(st["smoothq_scale"] != 1).item():
+        x2 = x2 / st["smoothq_scale"]
+    sym = int(st["sym_act"])
+    if st["native"]:
+        return torch.clamp((x2 / st["input_scale"] + st["input_zp"] - 128 + sym).round(), -128, 127).to(torch.int8)
+    return (torch.round(x2.clamp(st["cvs"][1], st["cvs"][0]) / st["quant_stepsize"] - st["quant_zero_point"]) - (128 - sym)).to(torch.int8)
+
+
+def deploy_static_forward(st, x, acc_dtype=torch.float16):
+    """QLinearINT8Deploy.forward + iaddmm_int (fms_mo/modules/linear.py:1309-1338, :1115-1188) for the static quantisers."""
+    org_dtype = x.dtype
+    tar_shape = tuple(x.shape[:-1]) + (st["weight"].shape[0],)
+    codes = deploy_static_codes(st, x.reshape(-1, x.shape[-1]))
+    acc = G.imatmul_chunk_truncate(codes, st["weight"].t())
+    out = (acc.float() * (st["input_scale"] * st["w_scale"]).to(torch.float16) + st["bias"]).to(acc_dtype)
+    return out.reshape(tar_shape).to(org_dtype)
+
+
+def deploy_zero_shift_from_fms_mo(weight, bias, w_cv, act_scale, zero_shift, alpha=0.5, nbits=8):
+    """from_fms_mo with ``0 < use_dynamic_max_act_Qfunc < 65``: dynamic per-tensor symmetric activations with a fake zero
+    shift (fms_mo/modules/linear.py:828-831, :886-906).  The partial correction ``zp * sum_k W`` is kept apart from the
+    bias because the input scale is only known at run time."""
+    w_levels = 2**nbits - 2
+    sq = torch.tensor([1.0], dtype=weight.dtype)
+    if act_scale is not None and torch.all(act_scale != 0).item():
+        w_sq = weight.abs().max(dim=0, keepdim=True)[0].clamp(min=1e-5)
+        alpha_t = torch.tensor([alpha], dtype=torch.float32).to(act_scale.dtype)
+        sq = (act_scale**alpha_t / w_sq ** (1.0 - alpha_t)).clamp(min=1e-5).to(act_scale.dtype)
+    w_scale = w_cv * 2 / w_levels
+    w_int8 = torch.round((weight * sq).t() / w_scale).clamp(-w_levels / 2, w_levels / 2).t().to(torch.int)
+    input_zp = torch.tensor(zero_shift)
+    corr_term = (input_zp * w_int8.sum(dim=1)) * w_scale.float() * torch.tensor(1.0).float()
+    new_bias = (bias.float() - corr_term) if bias is not None else -corr_term
+    new_bias = new_bias + corr_term
+    return dict(smoothq_scale=sq, w_scale=w_scale, weight=w_int8.to(torch.int8), input_zp=input_zp, corr_term=corr_term,
+                bias=new_bias.to(weight.dtype), nbits_a=nbits)
+
+
+def deploy_zero_shift_forward(st, x, acc_dtype=torch.float16):
+    """forward with qa_dyn_max_fake_zero_shift (fms_mo/modules/linear.py:1102-1113) and the bias update of iaddmm_int
+    (:1179-1182)."""
+    org_dtype = x.dtype
+    tar_shape = tuple(x.shape[:-1]) + (st["weight"].shape[0],)
+    x2 = x.reshape(-1, x.shape[-1])
+    if torch.all(st["smoothq_scale"] != 1).item():
+        x2 = x2 / st["smoothq_scale"]
+    amax = x2.abs().max()
+    levels = 2 ** (st["nbits_a"] - 1) - 1 - st["input_zp"]
+    input_scale = amax.clamp(min=1e-5) / levels
+    codes = (torch.round(x2 / input_scale) + st["input_zp"]).to(torch.int8)
+    acc = G.imatmul_chunk_truncate(codes, st["weight"].t())
+    updated_bias = st["bias"] - input_scale * st["corr_term"]
+    out = (acc.float() * (input_scale * st["w_scale"]).to(torch.float16) + updated_bias).to(acc_dtype)
+    return out.reshape(tar_shape).to(org_dtype)
+
+
+def deploy_from_torch_iW(weight_int, bias, a_cv, a_cvn, w_cv, zero_shift, native=True, acc_dtype=torch.float):
+    """QLinearINT8Deploy.from_torch_iW (fms_mo/modules/linear.py:922-1038): integer weights given, static activations."""
+    if native:
+        input_scale = torch.Tensor([(a_cv - a_cvn) / 255])
+        input_zp = torch.round(-a_cvn / input_scale).to(torch.int)
+        w_scale = torch.Tensor([w_cv * 2 / 254])
+        st = {}
+    else:
+        quant_scale = 255 / torch.Tensor([a_cv - a_cvn])
+        st = dict(quant_stepsize=1.0 / quant_scale, quant_zero_point=torch.round(a_cvn * quant_scale))
+        input_scale = st["quant_stepsize"]
+        input_zp = -st["quant_zero_point"]
+        w_scale = 1.0 / (254 / torch.Tensor([w_cv * 2]))
+    corr_term = (input_zp - 128) * torch.Tensor([zero_shift]) * w_scale * input_scale
+    st.update(native=native, sym_act=False, cvs=(a_cv, a_cvn), smoothq_scale=torch.tensor([1.0]), input_scale=input_scale,
+              input_zp=input_zp, w_scale=w_scale, weight=weight_int.to(torch.int8), bias=(bias - corr_term).to(acc_dtype))
+    return st

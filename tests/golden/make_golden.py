@@ -385,6 +385,101 @@ def gen_extra():
     save("extra.pt", out)
 
 
+def gen_deploy_more():
+    """QLinearINT8Deploy beyond the per-token dynamic case: the two static per-tensor quantisers (use_PT_native_Qfunc on and
+    off) with SmoothQuant, the fake zero-shift dynamic quantiser, from_torch_iW, and QLinearCublasI8I32NT.from_reference.
+    The reference's own iaddmm_int runs with an exact integer matmul as its matmul callable."""
+    torch.manual_seed(21)
+    imatmul_ops_reg("triton", mm_func=_dispatch_mm)
+    _mm["fn"] = lambda m1, m2: (m1.double() @ m2.double()).to(torch.int32)
+    out = {"static": [], "zero_shift": [], "torch_iW": [], "from_reference": []}
+    M, K, N = 36, 192, 80
+    for dtype in (torch.float32, torch.bfloat16, torch.float16):
+        x = make_x(M, K, dtype)
+        lin = ref_linear.QLinear(K, N, bias=True, num_bits_feature=8, qa_mode="pact+", num_bits_weight=8, qw_mode="maxperCh",
+                                 qcfg={"smoothq": True, "smoothq_alpha": 0.5}, device="cpu")  # fmt: skip
+        with torch.no_grad():
+            lin.weight.copy_(torch.randn(N, K) * 0.02)
+            lin.bias.copy_(torch.randn(N) * 0.01)
+            lin.quantize_feature.clip_val.fill_(2.37)
+            lin.quantize_feature.clip_valn.fill_(-1.93)
+        lin = lin.to(dtype)
+        lin.set_act_scale(x.float().abs().amax(0))
+        lin.train()
+        with torch.no_grad():
+            lin(x)
+        lin.eval()
+        base = dict(dtype=dtype, x=x, weight=lin.weight.detach().clone(), bias=lin.bias.detach().clone(),
+                    act_scale=lin.smoothq_act_scale.clone(), w_cv=lin.quantize_weight.clip_val.clone(),
+                    a_cv=lin.quantize_feature.clip_val.detach().clone(), a_cvn=lin.quantize_feature.clip_valn.detach().clone())  # fmt: skip
+        for native in (True, False):
+            dep = ref_linear.QLinearINT8Deploy.from_fms_mo(lin, use_int_kernel="cutlass", use_dynamic_max_act_Qfunc=False,
+                                                          use_PT_native_Qfunc=native, target_device="cpu")  # fmt: skip
+            dep.iaddmm = dep.iaddmm_int
+            y = dep(x.reshape(6, 6, K))
+            xs = x / dep.smoothq_scale if torch.all(dep.smoothq_scale != 1).item() else x
+            codes = (dep.qa_raw_qfunc(xs) if native else dep.qa_fmo_mo_qfunc(xs)).clone()
+            out["static"].append(dict(base, native=native, input_scale=dep.input_scale.clone(), input_zp=dep.input_zp.clone(),
+                                      w_scale=dep.w_scale.clone(), w_int8=dep.weight.detach().clone(), dep_bias=dep.bias.clone(),
+                                      smoothq_scale=dep.smoothq_scale.clone(), codes=codes, y=y.clone()))  # fmt: skip
+        # fake zero shift is meant for symmetric dynamic activations: a QLinear with per-token max activations
+        lin_sym = build_ref_qlinear(K, N, dtype, x)
+        lin_sym.train()
+        with torch.no_grad():
+            lin_sym(x)
+        lin_sym.eval()
+        base_sym = dict(dtype=dtype, x=x, weight=lin_sym.weight.detach().clone(), bias=lin_sym.bias.detach().clone(),
+                        act_scale=lin_sym.smoothq_act_scale.clone(), w_cv=lin_sym.quantize_weight.clip_val.clone())
+        for zs in (8, 40):
+            dep = ref_linear.QLinearINT8Deploy.from_fms_mo(lin_sym, use_int_kernel="cutlass", use_dynamic_max_act_Qfunc=zs, target_device="cpu")
+            dep.iaddmm = dep.iaddmm_int
+            y = dep(x.reshape(6, 6, K))
+            out["zero_shift"].append(dict(base_sym, zero_shift=zs, w_scale=dep.w_scale.clone(), w_int8=dep.weight.detach().clone(),
+                                          dep_bias=dep.bias.clone(), corr_term=dep.corr_term.clone(),
+                                          smoothq_scale=dep.smoothq_scale.clone(), y=y.clone()))  # fmt: skip
+    # from_torch_iW: an nn.Linear that already holds integer weights
+    for native in (True, False):
+        for dtype in (torch.float32, torch.float16):
+            nnlin = torch.nn.Linear(K, N, bias=True)
+            with torch.no_grad():
+                nnlin.weight.copy_(torch.randint(-127, 128, (N, K)).float())
+                nnlin.bias.copy_(torch.randn(N) * 0.05)
+            x = (torch.randn(M, K) * 1.2).to(dtype)
+            dep = ref_linear.QLinearINT8Deploy.from_torch_iW(nnlin, "int8", 3.1, -2.4, 0.21, 17.0, use_int_kernel="cutlass",
+                                                            use_PT_native_Qfunc=native, target_device="cpu")  # fmt: skip
+            # the reference's constructor leaves out four attributes its own forward reads; they are set here to the
+            # values that from_fms_mo gives an asymmetric static module without SmoothQuant
+            dep.useSymAct = False
+            dep.useDynMaxQfunc = False
+            dep.use_fake_zero_shift = False
+            dep.register_buffer("smoothq_scale", torch.tensor([1.0]))
+            dep.iaddmm = dep.iaddmm_int
+            y = dep(x)
+            out["torch_iW"].append(dict(dtype=dtype, native=native, x=x, weight=nnlin.weight.detach().clone(), bias=nnlin.bias.detach().clone(),
+                                        a_cv=3.1, a_cvn=-2.4, w_cv=0.21, zero_shift=17.0, dep_bias=dep.bias.detach().clone(),
+                                        input_scale=dep.input_scale.clone(), input_zp=dep.input_zp.clone(), w_scale=dep.w_scale.clone(),
+                                        y=y.clone()))  # fmt: skip
+    # QLinearCublasI8I32NT.from_reference: a torch.ao reference-quantized Linear as input
+    import torch.ao.nn.quantized.reference as nnqr
+
+    for force_sym in (False, True):
+        fl = torch.nn.Linear(K, N, bias=True)
+        with torch.no_grad():
+            fl.weight.copy_(torch.randn(N, K) * 0.05)
+        w_scales = fl.weight.detach().abs().amax(1) / 127
+        qparams = {"qscheme": torch.per_channel_affine, "dtype": torch.qint8, "scale": w_scales, "zero_point": torch.zeros(N, dtype=torch.int64), "axis": 0}
+        refq = nnqr.Linear.from_float(fl, qparams)
+        x = torch.randn(M, K) * 1.5
+        in_s, in_zp = torch.tensor(0.0237), torch.tensor(121)
+        dep = ref_linear.QLinearCublasI8I32NT.from_reference(refq, in_s.clone(), in_zp.clone(), torch.quint8, forceSymA=force_sym)
+        y = dep(x)
+        out["from_reference"].append(dict(x=x, weight=fl.weight.detach().clone(), bias=fl.bias.detach().clone(), w_scales=w_scales.clone(),
+                                          in_scale=in_s, in_zp=in_zp, force_sym=force_sym, dep_input_scale=dep.input_scale.clone(),
+                                          dep_input_zp=dep.input_zp.clone(), dep_bias=dep.bias.detach().clone(),
+                                          w_int8=dep.weight.detach().clone(), w_scale=dep.w_scale.clone(), y=y.clone()))  # fmt: skip
+    save("deploy_more.pt", out)
+
+
 if __name__ == "__main__":
     gen_quantizers()
     gen_qlinear()
@@ -392,3 +487,4 @@ if __name__ == "__main__":
     gen_fp8()
     gen_aiu_vectors()
     gen_extra()
+    gen_deploy_more()

@@ -311,3 +311,65 @@ def test_e5m2_codes_bit_exact_and_gemm_exact_on_small_sums(cuda_dev):
     b = torch.randint(-4, 5, (384, 128), generator=g).float().to(torch.float8_e5m2)
     out = ops.gemm(a.to(cuda_dev), b.to(cuda_dev))
     assert torch.equal(out.cpu(), a.float() @ b.float().t())
+
+
+def test_deploy_static_and_zero_shift_match_reference_outputs(cuda_dev):
+    """QLinearINT8Deploy with static per-tensor activation quantisation (both formulas) and SmoothQuant in fp32, bf16 and
+    fp16, with the fake zero-shift dynamic quantiser, and built by from_torch_iW: outputs equal the reference's own bit for
+    bit (golden deploy_more.pt, produced by the reference on CPU)."""
+    from test_host_logic import _ref_like_static
+
+    g = load_golden("deploy_more.pt")
+    for c in g["static"]:
+        q = QLinearINT8Deploy.from_fms_mo(_ref_like_static(c), use_dynamic_max_act_Qfunc=False, use_PT_native_Qfunc=c["native"],
+                                          target_device="cpu").to(cuda_dev)
+        y = q(c["x"].reshape(6, 6, -1).to(cuda_dev))
+        assert y.dtype == c["y"].dtype and torch.equal(y.cpu(), c["y"]), (c["dtype"], c["native"])
+    for c in g["zero_shift"]:
+        q = QLinearINT8Deploy.from_fms_mo(_RefLikeQLinear(c), use_dynamic_max_act_Qfunc=c["zero_shift"], target_device="cpu").to(cuda_dev)
+        y = q(c["x"].reshape(6, 6, -1).to(cuda_dev))
+        assert torch.equal(y.cpu(), c["y"]), (c["dtype"], c["zero_shift"], (y.cpu().float() - c["y"].float()).abs().max())
+    for c in g["torch_iW"]:
+        nnlin = torch.nn.Linear(c["weight"].shape[1], c["weight"].shape[0])
+        with torch.no_grad():
+            nnlin.weight.copy_(c["weight"])
+            nnlin.bias.copy_(c["bias"])
+        q = QLinearINT8Deploy.from_torch_iW(nnlin, "int8", c["a_cv"], c["a_cvn"], c["w_cv"], c["zero_shift"],
+                                            use_PT_native_Qfunc=c["native"], target_device="cpu").to(cuda_dev)
+        y = q(c["x"].to(cuda_dev))
+        assert torch.equal(y.cpu(), c["y"]), (c["dtype"], c["native"])
+
+
+def test_cublas_from_reference_matches_reference_outputs(cuda_dev):
+    import torch.ao.nn.quantized.reference as nnqr
+
+    from fms_model_optimizer_b200.modules import QLinearCublasI8I32NT
+
+    for c in load_golden("deploy_more.pt")["from_reference"]:
+        N, K = c["weight"].shape
+        fl = torch.nn.Linear(K, N)
+        with torch.no_grad():
+            fl.weight.copy_(c["weight"])
+            fl.bias.copy_(c["bias"])
+        qparams = {"qscheme": torch.per_channel_affine, "dtype": torch.qint8, "scale": c["w_scales"], "zero_point": torch.zeros(N, dtype=torch.int64), "axis": 0}
+        q = QLinearCublasI8I32NT.from_reference(nnqr.Linear.from_float(fl, qparams), c["in_scale"].clone(), c["in_zp"].clone(), torch.quint8,
+                                                forceSymA=c["force_sym"]).to(cuda_dev)
+        y = q(c["x"].to(cuda_dev))
+        assert torch.equal(y.cpu(), c["y"]), c["force_sym"]
+
+
+def test_deploy_module_sees_in_place_buffer_updates(cuda_dev):
+    """A forward, then load_state_dict with other scales and bias (same storage, new values), then a forward again: the
+    second result equals a fresh module's."""
+    c = load_golden("deploy_int8.pt")["cases"][0]
+    a = QLinearINT8Deploy.from_fms_mo(_RefLikeQLinear(c), use_dynamic_max_act_Qfunc=-1, target_device="cpu").to(cuda_dev)
+    x = c["x"].to(cuda_dev)
+    y0 = a(x)
+    sd = {k: v.clone() for k, v in a.state_dict().items()}
+    sd["w_scale"] = sd["w_scale"] * 2
+    sd["bias"] = sd["bias"] + 1
+    a.load_state_dict(sd)
+    b = QLinearINT8Deploy.from_fms_mo(_RefLikeQLinear(c), use_dynamic_max_act_Qfunc=-1, target_device="cpu").to(cuda_dev)
+    b.load_state_dict(sd)
+    y1 = a(x)
+    assert torch.equal(y1, b(x)) and not torch.equal(y1, y0)

@@ -104,3 +104,88 @@ def test_quantizer_factories_map_mode_strings_like_the_reference():
             Q.get_activation_quantizer(bad, nbits=8)
     with pytest.raises(ValueError):
         Q.to_fp8(8, q_mode="fp8_e5m2_sat")
+
+
+class _RefLikePact(torch.nn.Module):
+    """Stands in for the reference's PACT2 quantizer: only the clip values are read by from_fms_mo."""
+
+    def __init__(self, cv, cvn):
+        super().__init__()
+        self.clip_val = torch.nn.Parameter(cv.clone())
+        self.clip_valn = torch.nn.Parameter(cvn.clone())
+
+
+def _ref_like_static(c):
+    m = _RefLikeQLinear(c)
+    m.qa_mode = "pact+"
+    m.quantize_feature = _RefLikePact(c["a_cv"], c["a_cvn"])
+    return m
+
+
+def test_static_and_zero_shift_constructors_reproduce_reference_buffers():
+    g = load_golden("deploy_more.pt")
+    for c in g["static"]:
+        q = QLinearINT8Deploy.from_fms_mo(_ref_like_static(c), use_dynamic_max_act_Qfunc=False, use_PT_native_Qfunc=c["native"],
+                                          target_device="cpu")
+        assert torch.equal(q.weight, c["w_int8"]) and torch.equal(q.bias, c["dep_bias"]), (c["dtype"], c["native"])
+        assert torch.equal(q.input_scale, c["input_scale"]) and torch.equal(q.input_zp, c["input_zp"])
+        assert torch.equal(q.w_scale, c["w_scale"]) and torch.equal(q.smoothq_scale, c["smoothq_scale"])
+    for c in g["zero_shift"]:
+        q = QLinearINT8Deploy.from_fms_mo(_RefLikeQLinear(c), use_dynamic_max_act_Qfunc=c["zero_shift"], target_device="cpu")
+        assert q.use_fake_zero_shift and int(q.input_zp) == c["zero_shift"]
+        assert torch.equal(q.weight, c["w_int8"]) and torch.equal(q.bias, c["dep_bias"]) and torch.equal(q.corr_term, c["corr_term"])
+    for c in g["torch_iW"]:
+        nnlin = torch.nn.Linear(c["weight"].shape[1], c["weight"].shape[0])
+        with torch.no_grad():
+            nnlin.weight.copy_(c["weight"])
+            nnlin.bias.copy_(c["bias"])
+        q = QLinearINT8Deploy.from_torch_iW(nnlin, "int8", c["a_cv"], c["a_cvn"], c["w_cv"], c["zero_shift"],
+                                            use_PT_native_Qfunc=c["native"], target_device="cpu")
+        assert torch.equal(q.bias.detach(), c["dep_bias"]) and torch.equal(q.w_scale, c["w_scale"])
+        assert torch.equal(q.input_scale, c["input_scale"]) and torch.equal(q.input_zp, c["input_zp"])
+
+
+def test_from_reference_reproduces_reference_buffers():
+    import torch.ao.nn.quantized.reference as nnqr
+
+    from fms_model_optimizer_b200.modules import QLinearCublasI8I32NT
+
+    for c in load_golden("deploy_more.pt")["from_reference"]:
+        N, K = c["weight"].shape
+        fl = torch.nn.Linear(K, N)
+        with torch.no_grad():
+            fl.weight.copy_(c["weight"])
+            fl.bias.copy_(c["bias"])
+        qparams = {"qscheme": torch.per_channel_affine, "dtype": torch.qint8, "scale": c["w_scales"], "zero_point": torch.zeros(N, dtype=torch.int64), "axis": 0}
+        q = QLinearCublasI8I32NT.from_reference(nnqr.Linear.from_float(fl, qparams), c["in_scale"].clone(), c["in_zp"].clone(), torch.quint8,
+                                                forceSymA=c["force_sym"])
+        assert torch.equal(q.weight, c["w_int8"]) and torch.equal(q.w_scale, c["w_scale"])
+        assert torch.equal(q.input_scale, c["dep_input_scale"]) and torch.equal(q.input_zp, c["dep_input_zp"])
+        assert torch.equal(q.bias.detach(), c["dep_bias"])
+        assert q.input_dtype == (torch.qint8 if c["force_sym"] else torch.quint8)
+
+
+def test_lowering_default_arguments_leave_plain_linears_alone():
+    """With the default ``use_dyn_max_act=False`` no FP8 scaling mode follows from the arguments, so plain Linears stay;
+    with -1 they become FP8 Linears with per-token scales."""
+    from fms_model_optimizer_b200.modules import LinearFPxAcc
+    from fms_model_optimizer_b200.modules.linear import lower_qmodel_b200
+
+    c = load_golden("deploy_int8.pt")["cases"][0]
+
+    def toy():
+        m = torch.nn.Module()
+        m.q = _RefLikeQLinear(c)
+        type(m.q).__name__  # the lowering matches QLinear by class name
+        m.head = torch.nn.Linear(8, 4)
+        return m
+
+    class QLinear(_RefLikeQLinear):
+        pass
+
+    for dyn, head_type in ((False, torch.nn.Linear), (-1, LinearFPxAcc)):
+        m = toy()
+        m.q = QLinear(c)
+        lower_qmodel_b200(m, use_dyn_max_act=dyn)
+        assert type(m.q) is QLinearINT8Deploy
+        assert type(m.head) is head_type

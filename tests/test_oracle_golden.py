@@ -244,3 +244,23 @@ def test_fp8_linear_per_tensor_forward_backward_matches_reference():
                                             c["chunk"], c["dl16"])
         assert torch.equal(gx, c["gx"].reshape(gx.shape)) and torch.equal(gw, c["gw"])
         assert (gb is None and c["gb"] is None) or torch.equal(gb, c["gb"])
+
+
+def test_deploy_static_zero_shift_and_torch_iW_equal_reference_outputs():
+    """QLinearINT8Deploy with static per-tensor activations (both quantiser formulas, SmoothQuant on), with the fake
+    zero-shift dynamic quantiser, and built by from_torch_iW: buffers, codes and outputs equal the reference's."""
+    g = load_golden("deploy_more.pt")
+    for c in g["static"]:
+        st = OL.deploy_static_from_fms_mo(c["weight"], c["bias"], c["w_cv"], c["a_cv"], c["a_cvn"], c["act_scale"], 0.5, c["native"])
+        for k, ref in (("weight", "w_int8"), ("bias", "dep_bias"), ("input_scale", "input_scale"), ("w_scale", "w_scale"), ("input_zp", "input_zp")):
+            assert torch.equal(st[k], c[ref]), (c["dtype"], c["native"], k)
+        assert torch.equal(OL.deploy_static_codes(st, c["x"]), c["codes"])
+        assert torch.equal(OL.deploy_static_forward(st, c["x"].reshape(6, 6, -1)), c["y"])
+    for c in g["zero_shift"]:
+        st = OL.deploy_zero_shift_from_fms_mo(c["weight"], c["bias"], c["w_cv"], c["act_scale"], c["zero_shift"])
+        assert torch.equal(st["bias"], c["dep_bias"]) and torch.equal(st["corr_term"], c["corr_term"])
+        assert torch.equal(OL.deploy_zero_shift_forward(st, c["x"].reshape(6, 6, -1)), c["y"])
+    for c in g["torch_iW"]:
+        st = OL.deploy_from_torch_iW(c["weight"], c["bias"], c["a_cv"], c["a_cvn"], c["w_cv"], c["zero_shift"], c["native"])
+        assert torch.equal(st["bias"], c["dep_bias"]) and torch.equal(st["w_scale"], c["w_scale"])
+        assert torch.equal(OL.deploy_static_forward(st, c["x"], acc_dtype=torch.float), c["y"])
