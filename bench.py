@@ -274,7 +274,7 @@ def kernel_cases(dev, which):
         b = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev)
         out = torch.empty((M, N), dtype=torch.int32, device=dev)
         add(f"c2 int8 chunk-truncated GEMM {M}x{K}x{N}, chunk 64, 8 bits", "int8", "tensor", 2.0 * M * N * K,
-            lambda: ops.gemm(a, b, out=out, chunk_k=64, trun_bits=8))  # fmt: skip
+            lambda a=a, b=b, out=out: ops.gemm(a, b, out=out, chunk_k=64, trun_bits=8))  # fmt: skip
     if which in ("c3", "all"):
         torch.manual_seed(2)
         for M, K, N in ((1, 4096, 14336), (128, 4096, 4096), (8192, 4096, 14336), (8192, 14336, 4096)):
@@ -310,29 +310,29 @@ def kernel_cases(dev, which):
         rc = [ops.smooth_reciprocal((torch.rand(K, device=dev) + 0.5).bfloat16().float()) for _ in range(3)]
         sm = (torch.rand(K, device=dev) + 0.5).bfloat16().float()
         add(f"act_quant bf16 per-token int8 with SmoothQuant {M}x{K}", "bf16", "hbm", M * K * 3 + 4 * M + 4 * K,
-            lambda: ops.act_quant(x, mode=L.Q_I8_DYN, smooth=sm, native_chain=7))  # fmt: skip
+            lambda x=x, sm=sm: ops.act_quant(x, mode=L.Q_I8_DYN, smooth=sm, native_chain=7))  # fmt: skip
         add(f"block_quant add+RMSNorm+3 outputs {M}x{K}", "bf16", "hbm", M * K * (2 + 2 + 2 + 3) + 12 * M,
-            lambda: ops.block_quant(x, prologue=L.BLOCK_NORM, r=r, norm_w=nw, smooth_rcps=rc, store_sum=True))  # fmt: skip
+            lambda x=x, r=r, nw=nw, rc=rc: ops.block_quant(x, prologue=L.BLOCK_NORM, r=r, norm_w=nw, smooth_rcps=rc, store_sum=True))  # fmt: skip
         add(f"block_quant add+RMSNorm+2 outputs {M}x{K}", "bf16", "hbm", M * K * (2 + 2 + 2 + 2) + 8 * M,
-            lambda: ops.block_quant(x, prologue=L.BLOCK_NORM, r=r, norm_w=nw, smooth_rcps=rc[:2], store_sum=True))  # fmt: skip
+            lambda x=x, r=r, nw=nw, rc=rc: ops.block_quant(x, prologue=L.BLOCK_NORM, r=r, norm_w=nw, smooth_rcps=rc[:2], store_sum=True))  # fmt: skip
         add(f"block_quant SiLU*up+1 output {M}x{K}", "bf16", "hbm", M * K * (2 + 2 + 1) + 4 * M,
-            lambda: ops.block_quant(x, prologue=L.BLOCK_SILU_MUL, r=r, smooth_rcps=rc[:1]))  # fmt: skip
+            lambda x=x, r=r, rc=rc: ops.block_quant(x, prologue=L.BLOCK_SILU_MUL, r=r, smooth_rcps=rc[:1]))  # fmt: skip
         add(f"block_quant plain 1 output {M}x{K}", "bf16", "hbm", M * K * (2 + 1) + 4 * M,
-            lambda: ops.block_quant(x, prologue=L.BLOCK_PLAIN, smooth_rcps=rc[:1]))  # fmt: skip
+            lambda x=x, rc=rc: ops.block_quant(x, prologue=L.BLOCK_PLAIN, smooth_rcps=rc[:1]))  # fmt: skip
         for dt, name in ((torch.float32, "fp32"), (torch.bfloat16, "bf16")):
             xx = (torch.randn(M, K, device=dev) * 3).to(dt)
             gg = torch.randn(M, K, device=dev).to(dt)
             cv, cvn = torch.tensor([6.0], device=dev), torch.tensor([-6.0], device=dev)
             es = xx.element_size()
-            add(f"PACT+ forward {name} {M}x{K}", name, "hbm", 2 * es * M * K, lambda xx=xx: ops.pact2_fwd(xx, cv, cvn, 8, True))
-            add(f"PACT+ backward {name} {M}x{K}", name, "hbm", 3 * es * M * K, lambda xx=xx, gg=gg: ops.pact2_bwd(xx, gg, cv, cvn, 8, True))
+            add(f"PACT+ forward {name} {M}x{K}", name, "hbm", 2 * es * M * K, lambda xx=xx, cv=cv, cvn=cvn: ops.pact2_fwd(xx, cv, cvn, 8, True))
+            add(f"PACT+ backward {name} {M}x{K}", name, "hbm", 3 * es * M * K, lambda xx=xx, gg=gg, cv=cv, cvn=cvn: ops.pact2_bwd(xx, gg, cv, cvn, 8, True))
             w = (torch.randn(14336, 4096, device=dev) * 0.02).to(dt)
             add(f"SAWB+ per-channel weight fake-quant {name} 14336x4096", name, "hbm", 2 * es * w.numel(),
                 lambda w=w: ops.weight_fq_perch(w, num_bits=8, mode=L.W_SAWB, c0=SAWB_C[0], c1=SAWB_C[1]))  # fmt: skip
     return cases
 
 
-SAWB_C = (-12.80, 12.035)  # sawb_params_code coefficients for 8 bits (values only matter for timing here)
+SAWB_C = (31.76, -35.04)  # the 8-bit coefficients of sawb_params_code (fms_mo/quant/quantizers.py:639): clip = c0 * rms + c1 * mean|w|
 
 
 def comparator_cases(dev):
@@ -518,6 +518,8 @@ def run_c5(args, rank, world, dev):
         barrier()
         ops.check_status(dev)
 
+    timed_as = "eager launches" if graph is None else "CUDA graph replays"
+
     def step(ids=None):
         if graph is None:
             return model.forward(static_ids if ids is None else ids)
@@ -560,21 +562,23 @@ def run_c5(args, rank, world, dev):
     surfaces = None
     if world == 1 and args.surface == "both":
         # the same decoder by the drop-in route: QLinear -> lower_qmodel_b200 -> QLinearINT8Deploy, unfused norms
-        del graph
+        graph = None
         model.layers.clear()
         torch.cuda.empty_cache()
-        mod = W8A8Decoder(cfg, dev, 1, 0, layers=args.layers, surface="modules")
-        for _ in range(3):
-            mod.forward(ids_dev)
-        ops.LAUNCHES = 0
-        ms_mod = timed(lambda: mod.forward(ids_dev), max(2, args.steps // 2)) / max(2, args.steps // 2)
-        surfaces = {
-            "fused": {"tokens_per_s": tokens * args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps,
-                      "what": "tp.W8A8Linear fed by the fused block kernels (the headline)"},
-            "modules": {"tokens_per_s": tokens / (ms_mod * 1e-3), "ms_per_step": ms_mod,
-                        "what": "QLinear -> lower_qmodel_b200 -> QLinearINT8Deploy per Linear; RMSNorm, SiLU*up, residual adds as PyTorch ops"},
-        }  # fmt: skip
-        del mod
+        surfaces = {"fused": {"tokens_per_s": tokens * args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps,
+                              "what": "tp.W8A8Linear fed by the fused block kernels (the headline)"}}  # fmt: skip
+        try:
+            mod = W8A8Decoder(cfg, dev, 1, 0, layers=args.layers, surface="modules")
+            for _ in range(3):
+                mod.forward(ids_dev)
+            n_mod = max(2, args.steps // 2)
+            ms_mod = timed(lambda: mod.forward(ids_dev), n_mod) / n_mod
+            surfaces["modules"] = {"tokens_per_s": tokens / (ms_mod * 1e-3), "ms_per_step": ms_mod,
+                                   "what": "QLinear -> lower_qmodel_b200 -> QLinearINT8Deploy per Linear; RMSNorm, SiLU*up, residual adds "
+                                           "as PyTorch ops"}  # fmt: skip
+            del mod
+        except Exception as e:  # noqa: BLE001 -- the headline stands on its own
+            surfaces["modules"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
         torch.cuda.empty_cache()
     if world > 1:
         model.close()
@@ -614,8 +618,7 @@ def run_c5(args, rank, world, dev):
             "workload": "c5: Llama-3-8B-shaped decoder, all decoder Linears W8A8 SmoothQuant INT8, prefill 8x2048",
             "layers": nl, "global_batch": B, "seq_len": S, "parallelism": f"tp{world}", "sequence_groups_in_flight": groups,
             "surface": model.surface,
-            "timed_region": ("eager launches" if graph is None else "CUDA graph replays") +
-                            ", no instrumentation; per-launch CUDA events (roofline, shares) from the same number of eager steps right after",
+            "timed_region": timed_as + ", no instrumentation; per-launch CUDA events (roofline, shares) from the same number of eager steps right after",
             "shard_exchange": {"none": "none", "allreduce": "nccl all-reduce",
                                "multimem": "token-split residual stream; partial sums reduced in the NVLink switch (multimem.ld_reduce), "
                                            "codes replicated with multimem.st, flag barriers",
@@ -657,8 +660,10 @@ def run_c5(args, rank, world, dev):
     if surfaces is not None:
         line["surfaces"] = surfaces
     if world == 1 and not args.no_kernels:
-        k, c = measure_kernels(dev, "all", 5, 3)
-        line["kernels"], line["comparators"] = k, c
+        try:
+            line["kernels"], line["comparators"] = measure_kernels(dev, "all", 5, 3)
+        except Exception as e:  # noqa: BLE001 -- the headline stands on its own
+            line["kernels"] = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
     if world == 1 and not args.no_cpu_baseline:
         tps, per_step, threads, kind = cpu_layer_tokens_per_s(CPU_SAMPLE_TOKENS, 2, 1)
         line["cpu_baseline"] = {

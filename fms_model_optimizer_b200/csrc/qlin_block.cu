@@ -211,7 +211,10 @@ __global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams
         flip ^= 1;
         s = Elem<__nv_bfloat16>::rnd(__fdiv_rn(fmaxf(amax, eps), static_cast<float>(p.levels)));
         if (p.dst_multimem) {
-          if (threadIdx.x == 0) bq_store_f32_all(reinterpret_cast<float*>(p.dst_base[0] + p.scale_off[o]) + p.dst_row0 + row, s);
+          if (threadIdx.x == 0) {
+            bq_store_f32_all(reinterpret_cast<float*>(p.dst_base[0] + p.scale_off[o]) + p.dst_row0 + row, s);
+            if (p.ndst > 1) reinterpret_cast<float*>(p.dst_base[1] + p.scale_off[o])[p.dst_row0 + row] = s;
+          }
         } else if (p.ndst > 0) {
           if (static_cast<int>(threadIdx.x) < p.ndst)
             reinterpret_cast<float*>(p.dst_base[threadIdx.x] + p.scale_off[o])[p.dst_row0 + row] = s;
@@ -233,7 +236,11 @@ __global__ void __launch_bounds__(TPB) block_quant_kernel(const BlockQuantParams
       }
       const uint4 packed = make_uint4(out[0], out[1], out[2], out[3]);
       if (p.dst_multimem) {
-        bq_store16_all(p.dst_base[0] + p.codes_off[o] + static_cast<int64_t>(p.dst_row0 + row) * p.ldq[o] + ch * 16, packed);
+        const int64_t off = p.codes_off[o] + static_cast<int64_t>(p.dst_row0 + row) * p.ldq[o] + ch * 16;
+        bq_store16_all(p.dst_base[0] + off, packed);
+        // this GPU's own copy also gets a plain store: its own later kernels must not depend on the round trip of the
+        // multicast store through the switch (the copy that arrives that way carries the same bytes)
+        if (p.ndst > 1) *reinterpret_cast<uint4*>(p.dst_base[1] + off) = packed;
       } else if (p.ndst > 0) {
         const int64_t off = p.codes_off[o] + static_cast<int64_t>(p.dst_row0 + row) * p.ldq[o] + ch * 16;
         for (int d = 0; d < p.ndst; ++d) *reinterpret_cast<uint4*>(p.dst_base[d] + off) = packed;
@@ -341,7 +348,8 @@ extern "C" int qlin_block_quant(const qlin_block_quant_args* a, void* stream) {
   p.max_ctas = a->max_ctas;
   p.r_multimem = a->r_multimem != 0;
   p.dst_multimem = a->dst_multimem != 0;
-  if (p.dst_multimem && a->ndst != 1) return fail(QLIN_ERR_BAD_SHAPE, "qlin_block_quant: dst_multimem takes exactly one destination, the multicast address");
+  if (p.dst_multimem && a->ndst != 1 && a->ndst != 2)
+    return fail(QLIN_ERR_BAD_SHAPE, "qlin_block_quant: dst_multimem takes the multicast address and, optionally, this GPU's own buffer");
   if (p.r_multimem && (a->prologue != QLIN_BLOCK_NORM || a->r == nullptr))
     return fail(QLIN_ERR_UNSUPPORTED, "qlin_block_quant: r_multimem is the addend of the NORM prologue");
   if (a->r_parts < 0 || a->r_parts > 8 || (a->r_parts > 1 && a->r_part_stride % 8 != 0))

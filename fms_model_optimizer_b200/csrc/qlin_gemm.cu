@@ -35,8 +35,8 @@ constexpr int kTmemCols = 512;
 constexpr int kStageOutBytes = 4096;  // per epilogue warp: 32 rows x 128 bytes of output
 
 struct Aux {
-  uint64_t full[8];
-  uint64_t empty[8];
+  uint64_t full[12];
+  uint64_t empty[12];
   uint64_t tfull[4];
   uint64_t tempty[4];
   uint64_t drain;
@@ -46,15 +46,27 @@ struct Aux {
   float bias[256];
 };
 
-template <bool CHUNKED>
+// Tile configurations of the single-CTA kernel.
+//   kWide    128 x 256 tiles, the general unchunked case
+//   kChunked 128 x 128 tiles, per-chunk accumulators
+//   kNarrow64 / kNarrow32
+//            128 x 64 / 128 x 32 tiles for problems of at most 128 rows (one row block): such a problem is a stream
+//            over the weight matrix, and narrow tiles are what spreads that stream over all SMs (N / 32 tiles instead
+//            of N / 256) with a deep pipeline of small stages, so that it runs at HBM speed rather than at the speed
+//            at which a handful of SMs can pull their slices
+enum GemmMode { kWide = 0, kChunked = 1, kNarrow64 = 2, kNarrow32 = 3 };
+
+template <int MODE>
 struct Cfg {
-  static constexpr int BN = CHUNKED ? 128 : 256;
+  static constexpr bool CHUNKED = MODE == kChunked;
+  static constexpr bool NARROW = MODE == kNarrow64 || MODE == kNarrow32;
+  static constexpr int BN = MODE == kWide ? 256 : MODE == kChunked ? 128 : MODE == kNarrow64 ? 64 : 32;
   static constexpr int NBUF = CHUNKED ? 4 : 2;
-  static constexpr int STAGES = CHUNKED ? 5 : 4;
+  static constexpr int STAGES = MODE == kWide ? 4 : MODE == kChunked ? 5 : MODE == kNarrow64 ? 7 : 9;
   // Epilogue warps: w % 4 selects the 32 TMEM lanes a warp may read, w / 4 its column slice.  The
   // chunked kernel drains an accumulator per K-chunk, a chain of short dependent steps, and hides
   // that latency with twice as many, narrower warps.
-  static constexpr int EPI_WARPS = CHUNKED ? 16 : 8;
+  static constexpr int EPI_WARPS = CHUNKED ? 16 : MODE == kNarrow32 ? 4 : 8;
   static constexpr int PRODUCER_WARP = EPI_WARPS;
   static constexpr int MMA_WARP = EPI_WARPS + 1;
   static constexpr int THREADS = (EPI_WARPS + 2) * 32;
@@ -66,7 +78,10 @@ struct Cfg {
   static constexpr int AUX_OFFSET = OUT_OFFSET + EPI_WARPS * kStageOutBytes;
   static constexpr int SMEM_BYTES = AUX_OFFSET + static_cast<int>(sizeof(Aux));
 };
-static_assert(Cfg<false>::SMEM_BYTES <= 232448 && Cfg<true>::SMEM_BYTES <= 232448, "shared memory budget");
+static_assert(Cfg<kWide>::SMEM_BYTES <= 232448 && Cfg<kChunked>::SMEM_BYTES <= 232448 && Cfg<kNarrow64>::SMEM_BYTES <= 232448 &&
+                  Cfg<kNarrow32>::SMEM_BYTES <= 232448,
+              "shared memory budget");
+static_assert(Cfg<kNarrow32>::COLS_PER_WARP == 32 && Cfg<kNarrow64>::COLS_PER_WARP == 32, "narrow tiles drain 32 columns per warp");
 
 struct GemmParams {
   const void* c;
@@ -362,11 +377,12 @@ __device__ __forceinline__ void emit32(const GemmParams& p, const uint32_t (&v)[
   store_tile_coalesced(stage, w, g, p.ldd * 4, p.M - row0, lane);
 }
 
-template <bool F8, bool CHUNKED>
-__global__ void __launch_bounds__(Cfg<CHUNKED>::THREADS, 1)
+template <bool F8, int MODE>
+__global__ void __launch_bounds__(Cfg<MODE>::THREADS, 1)
 qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
-  using C = Cfg<CHUNKED>;
+  using C = Cfg<MODE>;
+  constexpr bool CHUNKED = C::CHUNKED;
   extern __shared__ __align__(1024) uint8_t smem[];
   Aux* aux = reinterpret_cast<Aux*>(smem + C::AUX_OFFSET);
   volatile int* abort_flag = &aux->abort_flag;
@@ -606,7 +622,30 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
         if (p.rs != nullptr && row < p.M) rs = p.rs[static_cast<int64_t>(row) * p.rs_stride];
       }
-      if constexpr (!CHUNKED) {
+      if constexpr (C::NARROW) {
+        const uint32_t buf = ebuf, bph = ebph;
+        if (++ebuf == C::NBUF) {
+          ebuf = 0;
+          ebph ^= 1u;
+        }
+        if (!warp_mbar_wait(&aux->tfull[buf], bph, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t v[32];
+        tmem_ld32(tmem_base + lane_base + buf * C::BN + half * C::COLS_PER_WARP, v);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&aux->tempty[buf]);  // the accumulator is in registers: the next tile may start
+        if (p.c != nullptr) {
+          uint32_t cv[32];
+          load_c_row<32>(p, cv, row, col_w);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = acc_add<F8>(cv[i], v[i]);
+        }
+        emit32<F8>(p, v, row0, lane, col_w, aux->cs, aux->bias, half * C::COLS_PER_WARP, rs, vec_ok, stage);
+      } else if constexpr (!CHUNKED) {
         const uint32_t buf = ebuf, bph = ebph;
         if (++ebuf == C::NBUF) {
           ebuf = 0;
@@ -981,15 +1020,15 @@ static int make_operand_map(CUtensorMap* tm, const void* base, int64_t rows, int
   return QLIN_OK;
 }
 
-template <bool F8, bool CHUNKED>
+template <bool F8, int MODE>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
-  using C = Cfg<CHUNKED>;
+  using C = Cfg<MODE>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return fail(QLIN_ERR_DEVICE, "device ordinal %d out of range", dev);
   if (!configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(qlin_gemm_kernel<F8, CHUNKED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(qlin_gemm_kernel<F8, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::SMEM_BYTES);
     if (e != cudaSuccess) return fail(QLIN_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured[dev] = true;
@@ -997,7 +1036,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   const int tiles = p.num_m * p.num_n;
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
-  qlin_gemm_kernel<F8, CHUNKED><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
+  qlin_gemm_kernel<F8, MODE><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
   QLIN_CHECK_LAUNCH("qlin_gemm");
   return QLIN_OK;
 }
@@ -1161,7 +1200,11 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   p.scatter_row0 = a->scatter_row0;
   p.f8_ab_format = a->kind == QLIN_DT_F8E5M2 ? 1 : 0;
   for (int i = 0; i < 8; ++i) p.scatter_d[i] = static_cast<uint8_t*>(a->scatter_d[i]);
-  const int bn = chunked ? Cfg<true>::BN : Cfg<false>::BN;
+  // At most 128 rows and no chunking: a stream over B.  Tiles of 32 columns unless that makes more than two waves of
+  // tiles whose A block (the same for all) would be re-read from L2 each time; then 64.
+  int mode = chunked ? kChunked : kWide;
+  if (!chunked && a->M <= kBM) mode = (a->M <= 16 || (a->N + 31) / 32 <= 2 * sm_count()) ? kNarrow32 : kNarrow64;
+  const int bn = mode == kWide ? Cfg<kWide>::BN : mode == kChunked ? Cfg<kChunked>::BN : mode == kNarrow64 ? Cfg<kNarrow64>::BN : Cfg<kNarrow32>::BN;
   p.num_m = (a->M + kBM - 1) / kBM;
   p.num_n = (a->N + bn - 1) / bn;
 
@@ -1179,6 +1222,14 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
     rc = f8 ? launch_pair<true>(ta, tb_half, p, s) : launch_pair<false>(ta, tb_half, p, s);
     if (rc <= 0) return rc;
   }
-  if (f8) return chunked ? launch<true, true>(ta, tb, p, s) : launch<true, false>(ta, tb, p, s);
-  return chunked ? launch<false, true>(ta, tb, p, s) : launch<false, false>(ta, tb, p, s);
+  switch (mode) {
+    case kChunked:
+      return f8 ? launch<true, kChunked>(ta, tb, p, s) : launch<false, kChunked>(ta, tb, p, s);
+    case kNarrow64:
+      return f8 ? launch<true, kNarrow64>(ta, tb, p, s) : launch<false, kNarrow64>(ta, tb, p, s);
+    case kNarrow32:
+      return f8 ? launch<true, kNarrow32>(ta, tb, p, s) : launch<false, kNarrow32>(ta, tb, p, s);
+    default:
+      return f8 ? launch<true, kWide>(ta, tb, p, s) : launch<false, kWide>(ta, tb, p, s);
+  }
 }

@@ -75,10 +75,13 @@ def w8a8_from_float(w, act, alpha=0.5):
     alpha = torch.tensor([alpha], dtype=act.dtype, device=act.device)  # the module keeps alpha as a one-element buffer
     smooth = (act**alpha / w_sq ** (1.0 - alpha)).clamp(min=1e-5).to(dtype)
     ws = w * smooth
-    w_cv = ws.abs().max(dim=1).values
-    w_scale = w_cv * 2 / 254
+    cv_new = ws.abs().max(dim=1).values
+    # the clip values a max-per-channel weight quantizer holds after its first training-mode forward: the fresh row
+    # maxima passed once through its moving average (fms_mo/quant/quantizers.py:3098-3128)
+    w_cv = (cv_new * (1.0 - 0.1) + cv_new * 0.1).to(dtype)
+    w_scale = w_cv * 2 / 254  # in the weight dtype, as the module's buffer would be
     codes = torch.round(ws.t() / w_scale).clamp(-127, 127).t().to(torch.int8).contiguous()
-    return codes, w_scale.float(), smooth.reshape(-1).float()
+    return codes, w_scale, smooth.reshape(-1).float()
 
 
 def synth_w8a8(n, k, seed, dev, dtype=torch.bfloat16):
@@ -172,26 +175,44 @@ class W8A8Decoder:
         hd, bf = cfg["head_dim"], torch.bfloat16
         x = F.embedding(ids, self.embed).view(B * S, -1)
         pending = None  # output of the last row-parallel Linear, added to the stream by the next fused kernel
+        tr = self.trace is not None
         for li, lin in enumerate(self.layers):
             # (x += pending) -> RMSNorm -> per-token int8 codes for q, k, v: one pass over the stream
-            cs, ss, xs, _ = ops.block_quant(x, prologue=L.BLOCK_NORM, r=pending, norm_w=lin["ln1"], store_sum=True,
+            cs, ss, xs, h = ops.block_quant(x, prologue=L.BLOCK_NORM, r=pending, norm_w=lin["ln1"], store_sum=True, want_h=tr,
                                             smooth_rcps=[lin["q"].smooth_rcp, lin["k"].smooth_rcp, lin["v"].smooth_rcp])  # fmt: skip
             x = xs if xs is not None else x
-            self._note("x_attn_in", li, x)
-            q = ops.rope_(lin["q"](None, (cs[0], ss[0]), bf).view(B * S, self.nq, hd), self.cos, self.sin, S)
-            k = ops.rope_(lin["k"](None, (cs[1], ss[1]), bf).view(B * S, self.nkv, hd), self.cos, self.sin, S)
+            q = lin["q"](None, (cs[0], ss[0]), bf)
+            k = lin["k"](None, (cs[1], ss[1]), bf)
             v = lin["v"](None, (cs[2], ss[2]), bf)
+            if tr:
+                for tag, t in (("x_attn_in", x), ("h_attn", h), ("q", q), ("k", k), ("v", v)):
+                    self._note(tag, li, t)
+                for name, c_, s_ in zip("qkv", cs, ss):
+                    self._note("codes_" + name, li, c_)
+                    self._note("scale_" + name, li, s_)
+            q = ops.rope_(q.view(B * S, self.nq, hd), self.cos, self.sin, S)
+            k = ops.rope_(k.view(B * S, self.nkv, hd), self.cos, self.sin, S)
             del cs, ss
             a = self._attention(q, k, v, B, S)
-            pending = lin["o"](None, lin["o"].quantise_fused(a), bf)
+            qa = lin["o"].quantise_fused(a)
+            pending = lin["o"](None, qa, bf)
+            if tr:
+                for tag, t in (("q_rope", q), ("k_rope", k), ("attn", a), ("codes_o", qa[0]), ("scale_o", qa[1]), ("o", pending)):
+                    self._note(tag, li, t)
             yield
-            cs, ss, x, _ = ops.block_quant(x, prologue=L.BLOCK_NORM, r=pending, norm_w=lin["ln2"], store_sum=True,
+            cs, ss, x, h = ops.block_quant(x, prologue=L.BLOCK_NORM, r=pending, norm_w=lin["ln2"], store_sum=True, want_h=tr,
                                            smooth_rcps=[lin["gate"].smooth_rcp, lin["up"].smooth_rcp])  # fmt: skip
-            self._note("x_mlp_in", li, x)
             g = lin["gate"](None, (cs[0], ss[0]), bf)
             u = lin["up"](None, (cs[1], ss[1]), bf)
+            keep = [] if tr else None
+            qd = lin["down"].quantise_fused(g, L.BLOCK_SILU_MUL, u, keep_h=keep)
+            pending = lin["down"](None, qd, bf)
+            if tr:
+                for tag, t in (("x_mlp_in", x), ("h_mlp", h), ("gate", g), ("up", u), ("codes_gate", cs[0]), ("scale_gate", ss[0]),
+                               ("codes_up", cs[1]), ("scale_up", ss[1]), ("h_down", keep[0]), ("codes_down", qd[0]), ("scale_down", qd[1]),
+                               ("down", pending)):  # fmt: skip
+                    self._note(tag, li, t)
             del cs, ss
-            pending = lin["down"](None, lin["down"].quantise_fused(g, L.BLOCK_SILU_MUL, u), bf)
             yield
         # only the last token of every sequence reaches the head
         x_last, p_last = x.view(B, S, -1)[:, -1].contiguous(), pending.view(B, S, -1)[:, -1].contiguous()
@@ -262,7 +283,8 @@ class W8A8Decoder:
                 g.scales.append(sc.view(torch.float32)[:T])
             g.sslot_off, sl = self.arena.alloc(4 * W * T)
             g.sslots = sl.view(torch.float32)[: W * T]
-            g.bases = [self.arena.mc_addr(0)] if mm else [self.arena.addr(r, 0) for r in range(W)]
+            # multimem: the multicast address, and this GPU's own arena for a plain copy of what its own kernels read next
+            g.bases = [self.arena.mc_addr(0), self.arena.addr(self.rank, 0)] if mm else [self.arena.addr(r, 0) for r in range(W)]
             g.part_bases = [self.arena.addr(r, g.part_off) for r in range(W)]
             g.my_part_mc = self.arena.mc_addr(g.part_off + self.rank * g.Ts * H * 2) if mm else 0
             self.sp.append(g)

@@ -7,6 +7,7 @@ from .linear import (
     QLinearCutlassI8I32NT,
     QLinearINT8Deploy,
     QLinearINT8Train,
+    lower_qmodel_b200,
 )
 
-__all__ = ["QLinear", "QLinearINT8Deploy", "QLinearINT8Train", "QLinearCublasI8I32NT", "QLinearCutlassI8I32NT", "LinearFPxAcc"]
+__all__ = ["QLinear", "QLinearINT8Deploy", "QLinearINT8Train", "QLinearCublasI8I32NT", "QLinearCutlassI8I32NT", "LinearFPxAcc", "lower_qmodel_b200"]

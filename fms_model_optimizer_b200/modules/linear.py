@@ -284,6 +284,10 @@ class QLinearINT8Deploy(nn.Linear):
                 kw["bias"] = prep["bias"] - in_scale * self.corr_term.detach().float().reshape(-1)
                 scale_dtype = self.w_scale.dtype if self.w_scale.dim() > 0 else chain  # a 0-dim scale takes the other operand's dtype
             elif self.usePTnativeQfunc:
+                # qa_raw_qfunc divides by the input_scale buffer: the chain runs in the promoted dtype of the two, which is
+                # the dtype of x for a module converted from a 16-bit model (its scale buffers carry the model's dtype)
+                st = _promote(chain, self.input_scale.dtype)
+                smooth_native |= 2 if (st == x2.dtype and st != torch.float32) else 0
                 codes, in_scale, _ = ops.act_quant(
                     x2, mode=L.Q_I8_STATIC, smooth=smooth, smooth_rcp=prep["smooth_rcp"], native_chain=smooth_native,
                     scale0=float(self.input_scale), zp0=float(self.input_zp), shift=128.0, add2=float(self.useSymAct),
@@ -291,6 +295,8 @@ class QLinearINT8Deploy(nn.Linear):
                 in_scale = self.input_scale.detach().float().reshape(-1)
                 scale_dtype = self.input_scale.dtype
             else:
+                st = _promote(chain, self.quant_stepsize.dtype)
+                smooth_native |= 2 if (st == x2.dtype and st != torch.float32) else 0
                 codes, in_scale, _ = ops.act_quant(
                     x2, mode=L.Q_I8_STATIC_CLAMP_FIRST, smooth=smooth, smooth_rcp=prep["smooth_rcp"], native_chain=smooth_native,
                     scale0=float(self.quant_stepsize), zp0=float(self.quant_zero_point), lo=float(self.cvs[1]), hi=float(self.cvs[0]),

@@ -103,27 +103,34 @@ class W8A8Linear:
             return codes, scale
         return self._q(x2, None)
 
-    def quantise_fused(self, x2: torch.Tensor, prologue: int = L.BLOCK_PLAIN, r: Optional[torch.Tensor] = None, exchange=None):
+    def quantise_fused(self, x2: torch.Tensor, prologue: int = L.BLOCK_PLAIN, r: Optional[torch.Tensor] = None, exchange=None,
+                       keep_h: Optional[list] = None):
         """Per-token codes and scales of ``prologue(x2, r) / smooth`` for bf16 rows through the fused kernel
         (``ops.block_quant``); a row-parallel shard takes two passes around the MAX all-reduce of the scales.
         ``exchange`` (a ``ScaleExchange``) replaces that all-reduce: the first pass stores this shard's scales into slot
-        ``rank`` on every GPU, and after the barrier the second pass takes the maximum over the slots itself."""
+        ``rank`` on every GPU, and after the barrier the second pass takes the maximum over the slots itself.
+        ``keep_h``: a list that receives the bf16 row the Linear sees (``prologue(x2, r)``), for tests."""
         rcp = [self.smooth_rcp]
+        want_h = keep_h is not None
         if exchange is not None:
             T = x2.shape[0]
             world = exchange.barrier.arena.world
             ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_SCALE_ONLY,
                             dst=(exchange.bases, [0], [exchange.slots_off + exchange.rank * T * 4], 0), dst_multimem=exchange.multimem)
             exchange.barrier.wait()
-            (codes,), (scale,), _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_GIVEN_SCALE,
-                                                       scale_in=exchange.slots, scale_in_parts=world, scale_in_stride=T)
+            (codes,), (scale,), _, h = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_GIVEN_SCALE,
+                                                       scale_in=exchange.slots, scale_in_parts=world, scale_in_stride=T, want_h=want_h)
+            if want_h:
+                keep_h.append(h)
             return codes, scale
         if self.mode == "row" and self.world > 1:
             _, (scale,), _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_SCALE_ONLY)
             dist.all_reduce(scale, op=dist.ReduceOp.MAX, group=self.group)
             (codes,), _, _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_GIVEN_SCALE, scale_in=scale)
             return codes, scale
-        (codes,), (scale,), _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp)
+        (codes,), (scale,), _, h = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, want_h=want_h)
+        if want_h:
+            keep_h.append(h)
         return codes, scale
 
     def scatter(self, quantised, bases, rows_per_rank: int, row0: int, act_dtype: torch.dtype) -> None:

@@ -432,8 +432,10 @@ typedef struct qlin_block_quant_args {
                         copies of the buffer (bf16, accumulated in fp32 by the switch, rounded once): the reduction of a
                         row-parallel Linear whose shards each wrote their partial output into their own copy.
                         r_parts is ignored.
-     dst_multimem != 0: ndst must be 1 and dst_base[0] the multicast address: codes and scales are written with
-                        multimem.st, one store that lands in every GPU's copy. */
+     dst_multimem != 0: dst_base[0] is the multicast address: codes and scales are written with multimem.st, one store
+                        that lands in every GPU's copy.  ndst is 1, or 2 with dst_base[1] = this GPU's own buffer, which
+                        then also gets a plain store, so that later kernels of this GPU need not wait for the store's
+                        round trip through the switch. */
   int32_t r_multimem;
   int32_t dst_multimem;
 } qlin_block_quant_args;

@@ -480,6 +480,53 @@ def gen_deploy_more():
     save("deploy_more.pt", out)
 
 
+C4_CFG = dict(num_hidden_layers=2, hidden_size=768, num_attention_heads=12, intermediate_size=3072, vocab_size=30522,
+              max_position_embeddings=128, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)  # no dropout: the step is deterministic
+C4_BATCH, C4_SEQ = 4, 32
+
+
+def gen_c4():
+    """The QAT workload as the reference prepares it: a random-init BERT encoder (BERT-base widths, two layers) through
+    ``qmodel_prep`` with the ``qat_int8`` recipe (PACT+ activations with clip values +-6, SAWB+ per-channel weights, no
+    calibration), one training-mode forward and backward in fp32 on CPU with the loss ``(out * G).sum()``.  The fixture
+    keeps the inputs' seeds, the output, every clip-value gradient, every bias gradient and, of every weight gradient,
+    its sum, its absolute sum and its leading 48 x 48 block (the full gradients would be 57 MB).  The test rebuilds the
+    same model from the same seed (transformers' BertModel initialiser on the CPU generator)."""
+    from transformers import BertConfig, BertModel
+
+    from fms_mo import qconfig_init, qmodel_prep
+
+    torch.manual_seed(3)
+    model = BertModel(BertConfig(**C4_CFG))
+    init_sd = {k: v.clone() for k, v in model.state_dict().items()}
+    ids = torch.randint(0, C4_CFG["vocab_size"], (C4_BATCH, C4_SEQ))
+    G = torch.randn(C4_BATCH, C4_SEQ, C4_CFG["hidden_size"])
+    qcfg = qconfig_init(recipe="qat_int8")
+    qcfg.update(qmodel_calibration=0, qw_mode="sawb+perCh", act_clip_init_val=6.0, act_clip_init_valn=-6.0)
+    qmodel_prep(model, (ids,), qcfg, use_dynamo=True)
+    qnames = [n for n, m in model.named_modules() if type(m).__name__ == "QLinear"]
+    model.train()
+    out = model(ids).last_hidden_state
+    (out * G).sum().backward()
+    grads = {}
+    for n, p in model.named_parameters():
+        if p.grad is None:
+            continue
+        g = p.grad.detach()
+        if "clip_val" in n or n.endswith(".bias") or g.numel() <= 4096:
+            grads[n] = g.clone()
+        else:
+            grads[n] = dict(sum=g.double().sum().item(), abs_sum=g.double().abs().sum().item(), norm=g.double().norm().item(),
+                            block=g.reshape(g.shape[0], -1)[:48, :48].clone())
+    w_clips = {n: model.get_submodule(n).quantize_weight.clip_val.detach().clone() for n in qnames}
+    # a checksum of the initial weights pins the test's rebuilt model to this one
+    init_sum = {k: v.double().sum().item() for k, v in init_sd.items() if v.dtype.is_floating_point}
+    save("c4_bert2.pt", dict(cfg=C4_CFG, batch=C4_BATCH, seq=C4_SEQ, ids=ids, G=G.bfloat16(), G_is="randn after ids, seed 3 (bf16 copy stored for a check)",
+                             qlinear_names=qnames, out=out.detach().clone(), grads=grads, w_clips=w_clips, init_sum=init_sum,
+                             qcfg={k: qcfg[k] for k in ("qa_mode", "qw_mode", "nbits_a", "nbits_w", "act_clip_init_val", "act_clip_init_valn")},
+                             align_zero=qcfg.get("align_zero", True)))
+
+
 if __name__ == "__main__":
     gen_quantizers()
     gen_qlinear()
@@ -488,3 +535,4 @@ if __name__ == "__main__":
     gen_aiu_vectors()
     gen_extra()
     gen_deploy_more()
+    gen_c4()

@@ -105,3 +105,31 @@ def test_product_never_imports_the_oracle():
     for f in pkg.rglob("*.py"):
         src = f.read_text()
         assert "import oracle" not in src and "from oracle" not in src, f
+
+
+def test_struct_sizes_and_offsets_match_a_c_compiler(tmp_path):
+    """The header compiled as plain C: sizeof and the offset of every field of every argument block equal the ctypes
+    mirror's (field order alone would not catch a wrong type)."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    assert gcc, "gcc is part of this build's toolchain"
+    structs = (("qlin_gemm_args", L.GemmArgs), ("qlin_quant_args", L.QuantArgs), ("qlin_pact2_args", L.Pact2Args),
+               ("qlin_wfq_args", L.WfqArgs), ("qlin_tensor_fq_args", L.TensorFqArgs), ("qlin_block_quant_args", L.BlockQuantArgs),
+               ("qlin_rope_args", L.RopeArgs), ("qlin_peer_barrier_args", L.PeerBarrierArgs))  # fmt: skip
+    lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {"]
+    for name, cls in structs:
+        lines.append(f'  printf("{name} %zu\\n", sizeof({name}));')
+        for field, _ in cls._fields_:
+            lines.append(f'  printf("{name}.{field} %zu\\n", offsetof({name}, {field}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-o", str(exe), str(src)], check=True)
+    got = dict(line.split() for line in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for name, cls in structs:
+        assert int(got[name]) == C.sizeof(cls), name
+        for field, _ in cls._fields_:
+            assert int(got[f"{name}.{field}"]) == getattr(cls, field).offset, f"{name}.{field}"

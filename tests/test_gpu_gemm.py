@@ -84,7 +84,7 @@ def test_reference_test_properties_int8(cuda_dev):
 
 
 def test_config2_full_size_sampled_and_checksum(cuda_dev):
-    """BASELINE config 2 at full size (4096 x 8192 x 4096, chunk 64, 8 truncated bits, seed 1):
+    """The chunk-truncated int8 GEMM at the full benchmark size (4096 x 8192 x 4096, chunk 64, 8 truncated bits, seed 1):
     (a) a random 48 x 40 sub-block of the output equals the oracle evaluated on those rows / columns
     (the truncation is elementwise per output, so a sub-block is exact parity);
     (b) for the untruncated product the checksum of checksums sum(D) == sum_k colsum(A)_k * colsum(B)_k."""

@@ -28,7 +28,7 @@ def test_deploy_int8_matches_reference_outputs(cuda_dev):
 
 
 def test_config1_shape_int8_linear_vs_oracle(cuda_dev):
-    """BASELINE config 1 (M=2048, K=4096, N=4096, bf16, 1% outlier channels x20, SmoothQuant 0.5,
+    """The single W8A8 INT8 Linear workload (M=2048, K=4096, N=4096, bf16, 1% outlier channels x20, SmoothQuant 0.5,
     seed 0) through QLinear -> lowering -> QLinearINT8Deploy, against the oracle: int8 codes,
     int32 accumulators and the bf16 output bit for bit; and within 0.25 abs / 2e-2 rel-Frobenius
     of the reference's bf16 fake-quant forward (the figures the two reference paths differ by)."""
@@ -91,7 +91,7 @@ def test_linear_fp8_matches_reference_outputs(cuda_dev):
 
 
 def test_config3_shapes_fp8_linear_vs_oracle(cuda_dev):
-    """BASELINE config 3 shapes (seed 2), bf16 in / out, against the oracle: relative Frobenius error
+    """The FP8 Linear sweep shapes (seed 2; the two large ones cut to 512 rows here, at full size in the next test), bf16 in / out, against the oracle: relative Frobenius error
     below 1e-3 (bf16 output rounding) and fewer than 1% of elements off by more than one bf16 ulp."""
     torch.manual_seed(2)
     for M, K, N in ((1, 4096, 14336), (128, 4096, 4096), (512, 4096, 14336), (512, 14336, 4096)):
@@ -107,6 +107,38 @@ def test_config3_shapes_fp8_linear_vs_oracle(cuda_dev):
         rel = torch.norm(y.float() - want.float()) / torch.norm(want.float())
         assert rel < 1e-3, (M, K, N, rel)
         assert ((y.float() - want.float()).abs() > 2**-6 * want.float().abs().clamp(min=1.0)).float().mean() < 0.01
+
+
+def test_fp8_linear_large_shapes_full_size_sampled(cuda_dev):
+    """The two large shapes of the FP8 sweep at their stated size, M = 8192 (8192 x 4096 x 14336 and 8192 x 14336 x 4096,
+    seed 2, bf16 in / out).  Per-token and per-channel scales make every output element a function of one row of x and one
+    row of W only, so the oracle evaluated on a random 64 x 48 choice of rows and columns is exact parity for those
+    elements: e4m3 codes and scales are bit exact, outputs within the bf16 rounding of an fp32 sum taken in another
+    order (at most one bf16 place, fewer than 1 % of elements differing at all)."""
+    from fms_model_optimizer_b200 import _lib as L
+
+    torch.manual_seed(2)
+    for M, K, N in ((8192, 4096, 14336), (8192, 14336, 4096)):
+        x = torch.randn(M, K).bfloat16()
+        w = torch.randn(N, K).bfloat16()
+        lin = torch.nn.Linear(K, N, bias=False).bfloat16()
+        with torch.no_grad():
+            lin.weight.copy_(w)
+        q = LinearFPxAcc.from_nn(lin.to(cuda_dev), trun_bits=0, chunk_size=64, dynamic_fp8="per_token")
+        with torch.no_grad():
+            y = q(x.to(cuda_dev)).cpu()
+        rows, cols = torch.randperm(M)[:64], torch.randperm(N)[:48]
+        want, xq, x_scale, wq, w_scale, _ = OL.linear_fpx_forward(x[rows], w[cols], None, chunk_size=64, return_parts=True)
+        got = y[rows][:, cols]
+        diff = (got.float() - want.float()).abs()
+        assert (diff <= 2.0**-7 * want.float().abs().clamp(min=1e-2)).all(), (M, K, N, diff.max())
+        assert (got != want).float().mean() < 0.01, (M, K, N)
+        # the codes and scales of the sampled rows, bit for bit
+        cq, cs, _ = ops.act_quant(x[rows].to(cuda_dev), mode=L.Q_F8_DYN, native_chain=3)
+        assert torch.equal(cq.cpu().view(torch.uint8), xq.to(torch.float8_e4m3fn).view(torch.uint8))
+        assert torch.equal(cs.cpu(), x_scale.reshape(-1).float())
+        del q, lin, y
+        torch.cuda.empty_cache()
 
 
 def test_qat_qlinear_forward_backward_vs_oracle(cuda_dev):
@@ -323,8 +355,24 @@ def test_deploy_static_and_zero_shift_match_reference_outputs(cuda_dev):
     for c in g["static"]:
         q = QLinearINT8Deploy.from_fms_mo(_ref_like_static(c), use_dynamic_max_act_Qfunc=False, use_PT_native_Qfunc=c["native"],
                                           target_device="cpu").to(cuda_dev)
+        # the int8 codes first (the reference's qa_raw_qfunc / qa_fmo_mo_qfunc on x / smoothq_scale), then the output
+        from fms_model_optimizer_b200 import _lib as L
+
+        prep = q._prepared(cuda_dev)
+        nat = 3 if c["dtype"] != torch.float32 else 0  # 16-bit models: smoothing and the quantiser chain both in the model dtype
+        xd = c["x"].to(cuda_dev)
+        if c["native"]:
+            codes, _, _ = ops.act_quant(xd, mode=L.Q_I8_STATIC, smooth=prep["smooth"], smooth_rcp=prep["smooth_rcp"], native_chain=nat,
+                                        scale0=float(q.input_scale), zp0=float(q.input_zp), shift=128.0, add2=0.0)
+        else:
+            codes, _, _ = ops.act_quant(xd, mode=L.Q_I8_STATIC_CLAMP_FIRST, smooth=prep["smooth"], smooth_rcp=prep["smooth_rcp"],
+                                        native_chain=nat, scale0=float(q.quant_stepsize), zp0=float(q.quant_zero_point),
+                                        lo=float(q.cvs[1]), hi=float(q.cvs[0]), shift=128.0)
+        bad = (codes.cpu() != c["codes"]).sum().item()
+        assert bad == 0, (c["dtype"], c["native"], "codes differ", bad, codes.numel())
         y = q(c["x"].reshape(6, 6, -1).to(cuda_dev))
-        assert y.dtype == c["y"].dtype and torch.equal(y.cpu(), c["y"]), (c["dtype"], c["native"])
+        assert y.dtype == c["y"].dtype
+        assert torch.equal(y.cpu(), c["y"]), (c["dtype"], c["native"], (y.cpu().float() - c["y"].float()).abs().max().item())
     for c in g["zero_shift"]:
         q = QLinearINT8Deploy.from_fms_mo(_RefLikeQLinear(c), use_dynamic_max_act_Qfunc=c["zero_shift"], target_device="cpu").to(cuda_dev)
         y = q(c["x"].reshape(6, 6, -1).to(cuda_dev))

@@ -1,0 +1,92 @@
+"""The QAT workload against the reference's own numbers: a two-layer BERT encoder with BERT-base widths whose twelve
+Linears are this package's ``QLinear`` (PACT+ activations, clip values +-6, SAWB+ per-channel weights), one training-mode
+forward and backward in fp32 with the loss ``(out * G).sum()``.
+
+The golden file was produced by fms-model-optimizer itself on CPU (``qmodel_prep`` with the ``qat_int8`` recipe,
+tests/golden/make_golden.py::gen_c4).  This test rebuilds the same random-init model from the same seed, swaps in this
+package's QLinear at the module names the reference quantised, runs the step on the GPU and compares the output, every
+clip-value gradient, every bias gradient and the sampled statistics of every weight gradient.
+
+Tolerances.  The quantizer kernels are bit exact given their inputs (tests/test_gpu_quant.py); what differs from the CPU
+run is the summation order of the fp32 GEMMs, LayerNorm / softmax / GELU of another library build, and the SAWB clip
+value (3e-5 relative, which moves fewer than 1 % of the weights by one quantisation level).  Those differences pass
+through 24 quantizers, where a value near a rounding boundary flips a level; hence relative Frobenius bounds of 5e-3 on
+the output and 2e-2 on gradients rather than ulps.
+"""
+
+import pytest
+import torch
+
+from conftest import load_golden
+from fms_model_optimizer_b200 import ops
+from fms_model_optimizer_b200.modules import QLinear
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.double() - b.double()).norm() / b.double().norm().clamp(min=1e-30)).item()
+
+
+def test_bert_two_layer_qat_step_matches_reference(cuda_dev):
+    from transformers import BertConfig, BertModel
+
+    g = load_golden("c4_bert2.pt")
+    torch.manual_seed(3)
+    model = BertModel(BertConfig(**g["cfg"]))
+    for k, v in model.state_dict().items():
+        if v.dtype.is_floating_point:
+            assert abs(v.double().sum().item() - g["init_sum"][k]) <= 1e-9 * max(1.0, abs(g["init_sum"][k])), f"initial weights differ: {k}"
+    ids = torch.randint(0, g["cfg"]["vocab_size"], (g["batch"], g["seq"]))
+    G = torch.randn(g["batch"], g["seq"], g["cfg"]["hidden_size"])
+    assert torch.equal(ids, g["ids"]) and torch.equal(G.bfloat16(), g["G"])
+    qc = g["qcfg"]
+    for name in g["qlinear_names"]:
+        lin = model.get_submodule(name)
+        q = QLinear(lin.in_features, lin.out_features, bias=lin.bias is not None, num_bits_feature=qc["nbits_a"], qa_mode=qc["qa_mode"],
+                    num_bits_weight=qc["nbits_w"], qw_mode=qc["qw_mode"], act_clip_init_val=qc["act_clip_init_val"],
+                    act_clip_init_valn=qc["act_clip_init_valn"], align_zero=g["align_zero"], device="cpu")  # fmt: skip
+        with torch.no_grad():
+            q.weight.copy_(lin.weight)
+            q.bias.copy_(lin.bias)
+        parent, _, leaf = name.rpartition(".")
+        setattr(model.get_submodule(parent), leaf, q)
+    model = model.to(cuda_dev)
+    model.train()
+    # fp32 attention through plain matmuls: the fused attention kernels take TF32 tensor-core shortcuts on fp32 inputs
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+
+    with sdpa_kernel(SDPBackend.MATH):
+        out = model(ids.to(cuda_dev)).last_hidden_state
+        (out * G.to(cuda_dev)).sum().backward()
+    torch.cuda.synchronize()
+    ops.check_status(cuda_dev)
+
+    clip_err = {}
+    for name in g["qlinear_names"]:
+        clip = model.get_submodule(name).quantize_weight.clip_val.detach().cpu().reshape(-1).double()
+        want = g["w_clips"][name].reshape(-1).double()
+        clip_err[name] = ((clip - want).abs() / want.abs()).max().item()
+    worst = {"out": _rel(out.detach().cpu(), g["out"]), "w_clip": max(clip_err.values())}
+    assert worst["w_clip"] < 1e-4, (worst, clip_err)
+    assert worst["out"] < 5e-3, worst
+    params = dict(model.named_parameters())
+    for n, want in g["grads"].items():
+        got = params[n].grad
+        assert got is not None, n
+        got = got.detach().cpu()
+        if isinstance(want, dict):
+            r_block = _rel(got.reshape(got.shape[0], -1)[:48, :48], want["block"])
+            r_norm = abs(got.double().norm().item() - want["norm"]) / max(want["norm"], 1e-30)
+            worst[n] = max(r_block, r_norm)
+            assert r_block < 2e-2 and r_norm < 1e-2, (n, r_block, r_norm)
+        elif "clip_val" in n:
+            # one scalar per quantizer: a sum of +-g over the elements outside the clip range and of g * rounding residue
+            # inside it; compare against the size of the terms it sums, not of the (cancelling) result
+            scale = max(abs(want.item()), 1e-3 * g["out"].numel() ** 0.5)
+            worst[n] = abs(got.item() - want.item()) / scale
+            assert worst[n] < 5e-2, (n, got.item(), want.item())
+        else:
+            worst[n] = _rel(got, want)
+            assert worst[n] < 2e-2, (n, worst[n])
+    print("largest relative differences:", sorted(worst.items(), key=lambda kv: -kv[1])[:6])

@@ -18,12 +18,12 @@ from fms_model_optimizer_b200 import _lib as L
 pytestmark = pytest.mark.gpu
 
 
-def _args(x, g, out, cv, cvn, grads, ws, nbits, variant=L.PACT_TWO_SIDED):
+def _args(x, g, out, cv, cvn, grads, ws, nbits, variant=L.PACT_TWO_SIDED, numel=None):
     dt = {torch.float32: L.DT_F32, torch.float16: L.DT_F16, torch.bfloat16: L.DT_BF16}[x.dtype]
     return L.Pact2Args(x=x.data_ptr(), grad_out=g.data_ptr(), out=out.data_ptr(), clip_val=cv.data_ptr(),
                        clip_valn=(cvn.data_ptr() if cvn is not None else None), grad_clip=grads.data_ptr(),
                        workspace=(ws.data_ptr() if ws is not None else None),
-                       numel=x.numel(), dtype=dt, num_bits=nbits, align_zero=1, variant=variant)
+                       numel=(x.numel() if numel is None else numel), dtype=dt, num_bits=nbits, align_zero=1, variant=variant)
 
 
 def test_noalloc_backward_equals_workspace_backward_twice(cuda_dev):
@@ -74,15 +74,17 @@ def test_noalloc_one_sided_and_symmetric_variants(cuda_dev, variant):
     cv = torch.tensor([1.75], device=cuda_dev)
     gen = torch.Generator(device=cuda_dev).manual_seed(5 + variant)
     for numel in (40003, 0):
-        x = (torch.randn(numel + 1, generator=gen, device=cuda_dev) * 2)[1:]
-        g = torch.randn(numel + 1, generator=gen, device=cuda_dev)[1:]
+        # buffers of numel + 2 elements viewed from their second element; the element count goes in explicitly, so
+        # the empty case still hands the library valid (non-NULL) pointers
+        x = (torch.randn(numel + 2, generator=gen, device=cuda_dev) * 2)[1:]
+        g = torch.randn(numel + 2, generator=gen, device=cuda_dev)[1:]
         ws = torch.empty(max(2, lib.qlin_pact2_bwd_workspace_bytes(numel) // 4), dtype=torch.float32, device=cuda_dev)
-        gx_ref, gc_ref = torch.empty(numel + 1, device=cuda_dev)[1:], torch.full((2,), float("nan"), device=cuda_dev)
-        gx_new, gc_new = torch.empty(numel + 1, device=cuda_dev)[1:], torch.full((2,), float("nan"), device=cuda_dev)
-        L.check(lib.qlin_pact2_bwd(C.byref(_args(x, g, gx_ref, cv, None, gc_ref, ws, 8, variant)), stream), "qlin_pact2_bwd")
-        L.check(lib.qlin_pact2_bwd_noalloc(C.byref(_args(x, g, gx_new, cv, None, gc_new, None, 8, variant)), stream), "noalloc")
+        gx_ref, gc_ref = torch.zeros(numel + 2, device=cuda_dev)[1:], torch.full((2,), float("nan"), device=cuda_dev)
+        gx_new, gc_new = torch.zeros(numel + 2, device=cuda_dev)[1:], torch.full((2,), float("nan"), device=cuda_dev)
+        L.check(lib.qlin_pact2_bwd(C.byref(_args(x, g, gx_ref, cv, None, gc_ref, ws, 8, variant, numel)), stream), "qlin_pact2_bwd")
+        L.check(lib.qlin_pact2_bwd_noalloc(C.byref(_args(x, g, gx_new, cv, None, gc_new, None, 8, variant, numel)), stream), "noalloc")
         torch.cuda.synchronize()
-        assert torch.equal(gx_new, gx_ref)
+        assert torch.equal(gx_new[:numel], gx_ref[:numel])
         assert torch.equal(gc_new, gc_ref), (gc_new, gc_ref)
         if numel == 0:
             assert gc_new.tolist() == [0.0, 0.0]
