@@ -309,8 +309,9 @@ def kernel_cases(dev, which):
         nw = torch.ones(K, device=dev, dtype=torch.bfloat16)
         rc = [ops.smooth_reciprocal((torch.rand(K, device=dev) + 0.5).bfloat16().float()) for _ in range(3)]
         sm = (torch.rand(K, device=dev) + 0.5).bfloat16().float()
+        smr = ops.smooth_reciprocal(sm)
         add(f"act_quant bf16 per-token int8 with SmoothQuant {M}x{K}", "bf16", "hbm", M * K * 3 + 4 * M + 4 * K,
-            lambda x=x, sm=sm: ops.act_quant(x, mode=L.Q_I8_DYN, smooth=sm, native_chain=7))  # fmt: skip
+            lambda x=x, sm=sm, smr=smr: ops.act_quant(x, mode=L.Q_I8_DYN, smooth=sm, smooth_rcp=smr, native_chain=7))  # fmt: skip
         add(f"block_quant add+RMSNorm+3 outputs {M}x{K}", "bf16", "hbm", M * K * (2 + 2 + 2 + 3) + 12 * M,
             lambda x=x, r=r, nw=nw, rc=rc: ops.block_quant(x, prologue=L.BLOCK_NORM, r=r, norm_w=nw, smooth_rcps=rc, store_sum=True))  # fmt: skip
         add(f"block_quant add+RMSNorm+2 outputs {M}x{K}", "bf16", "hbm", M * K * (2 + 2 + 2 + 2) + 8 * M,
@@ -412,7 +413,28 @@ def run_kernel_workload(args, dev):
 # ------------------------------------------------------------------------------------------------
 # c5: decoder prefill
 # ------------------------------------------------------------------------------------------------
-def _check_sharded_against_single(args, cfg, rank, world, dev, ids_dev, groups):
+def _calibrated_scales(args, cfg, world, dev, ids_dev, layers):
+    """SmoothQuant activation scales from one calibration forward of the float model on the first two sequences of the
+    batch (``decoder.calibrate_act_scales``); sharded runs take rank 0's vectors so that every shard smooths alike."""
+    from fms_model_optimizer_b200.decoder import calibrate_act_scales
+
+    if args.act_scales != "calibrated":
+        return None
+    scales = calibrate_act_scales(cfg, dev, ids_dev[:2], layers)
+    if world > 1:
+        keys = sorted(scales)
+        flat = torch.cat([scales[k] for k in keys])
+        dist.broadcast(flat, src=0)
+        off = 0
+        for k in keys:
+            n = scales[k].numel()
+            scales[k] = flat[off : off + n].clone()
+            off += n
+    torch.cuda.empty_cache()
+    return scales
+
+
+def _check_sharded_against_single(args, cfg, rank, world, dev, ids_dev, groups, scales):
     """Before timing a sharded run: a 2-layer decoder through the sharded path (eager and as a CUDA graph replay) and
     through the one-GPU path (every rank holds the full 2-layer weights), same ids.  Returns the relative Frobenius
     error of the final hidden states of the last tokens and whether the next-token ids agree; raises when the error is
@@ -420,11 +442,12 @@ def _check_sharded_against_single(args, cfg, rank, world, dev, ids_dev, groups):
     from fms_model_optimizer_b200 import ops
     from fms_model_optimizer_b200.decoder import W8A8Decoder
 
-    single = W8A8Decoder(cfg, dev, 1, 0, layers=2)
+    single = W8A8Decoder(cfg, dev, 1, 0, layers=2, calibrated_act_scales=scales)
     want_ids = single.forward(ids_dev)
     want_h = single.last_hidden.float().clone()
     del single
-    sharded = W8A8Decoder(cfg, dev, world, rank, layers=2, groups=groups, exchange=args.exchange, reserve_sms=args.reserve_sms)
+    sharded = W8A8Decoder(cfg, dev, world, rank, layers=2, groups=groups, exchange=args.exchange, reserve_sms=args.reserve_sms,
+                          calibrated_act_scales=scales)
     if sharded.exchange != "allreduce":
         sharded.enable_token_split(cfg["batch"] * cfg["seq"] // groups)
     res = {"exchange": sharded.exchange}
@@ -465,12 +488,13 @@ def run_c5(args, rank, world, dev):
     ids_dev = ids_host.to(dev)
     out_host = torch.empty(B, dtype=torch.int64).pin_memory()
 
+    scales = _calibrated_scales(args, cfg, world, dev, ids_dev, args.layers)
     check = None
     if world > 1 and not args.no_check:
-        check = _check_sharded_against_single(args, cfg, rank, world, dev, ids_dev, groups)
+        check = _check_sharded_against_single(args, cfg, rank, world, dev, ids_dev, groups, scales)
 
     model = W8A8Decoder(cfg, dev, world, rank, layers=args.layers, groups=groups, exchange=args.exchange, reserve_sms=args.reserve_sms,
-                        surface=("fused" if args.surface == "both" else args.surface))  # fmt: skip
+                        surface=("fused" if args.surface == "both" else args.surface), calibrated_act_scales=scales)  # fmt: skip
     if world > 1 and model.exchange != "allreduce":
         model.enable_token_split(tokens // groups)
     nl = len(model.layers)
@@ -559,6 +583,28 @@ def run_c5(args, rank, world, dev):
     launches = ops.LAUNCHES // args.steps
     ops.check_status(dev)
 
+    head_exchange, head_nvlink = model.exchange, getattr(model, "nvlink_bytes_per_forward", None)
+    sweep = []
+    if world > 1 and args.sweep and model.exchange != "allreduce":
+        # other settings of the sharded run on the same weights: "g<groups>r<reserved SMs>[s]" ("s": plain stores)
+        for spec in args.sweep.split(","):
+            gi, ri = spec.index("g"), spec.index("r")
+            sg, sr = int(spec[gi + 1 : ri]), int(spec[ri + 1 :].rstrip("s"))
+            graph = None
+            model.reconfigure(groups=sg, reserve_sms=sr, exchange=("stores" if spec.endswith("s") else "multimem"))
+            model.enable_token_split(tokens // sg)
+            for _ in range(3):
+                model.forward(ids_dev)
+            barrier()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                model.forward(static_ids)
+            gr.replay()
+            ms_v = timed(gr.replay, args.steps) / args.steps
+            ops.check_status(dev)
+            sweep.append({"groups": sg, "reserve_sms": sr, "exchange": model.exchange, "ms_per_step": ms_v, "tokens_per_s": tokens / (ms_v * 1e-3)})
+            del gr
+
     surfaces = None
     if world == 1 and args.surface == "both":
         # the same decoder by the drop-in route: QLinear -> lower_qmodel_b200 -> QLinearINT8Deploy, unfused norms
@@ -568,7 +614,7 @@ def run_c5(args, rank, world, dev):
         surfaces = {"fused": {"tokens_per_s": tokens * args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps,
                               "what": "tp.W8A8Linear fed by the fused block kernels (the headline)"}}  # fmt: skip
         try:
-            mod = W8A8Decoder(cfg, dev, 1, 0, layers=args.layers, surface="modules")
+            mod = W8A8Decoder(cfg, dev, 1, 0, layers=args.layers, surface="modules", calibrated_act_scales=scales)
             for _ in range(3):
                 mod.forward(ids_dev)
             n_mod = max(2, args.steps // 2)
@@ -618,11 +664,13 @@ def run_c5(args, rank, world, dev):
             "workload": "c5: Llama-3-8B-shaped decoder, all decoder Linears W8A8 SmoothQuant INT8, prefill 8x2048",
             "layers": nl, "global_batch": B, "seq_len": S, "parallelism": f"tp{world}", "sequence_groups_in_flight": groups,
             "surface": model.surface,
+            "smoothquant_act_scales": ("per-channel absmax from one calibration forward of the float model on 2 x 2048 tokens of the batch "
+                                       "(qlin_col_absmax)" if scales is not None else "synthetic: 4.0 with 1 % outlier channels x20"),
             "timed_region": timed_as + ", no instrumentation; per-launch CUDA events (roofline, shares) from the same number of eager steps right after",
             "shard_exchange": {"none": "none", "allreduce": "nccl all-reduce",
                                "multimem": "token-split residual stream; partial sums reduced in the NVLink switch (multimem.ld_reduce), "
                                            "codes replicated with multimem.st, flag barriers",
-                               "stores": "token-split residual stream; plain peer stores over NVLink, flag barriers"}[model.exchange],
+                               "stores": "token-split residual stream; plain peer stores over NVLink, flag barriers"}[head_exchange],
             "reserve_sms": args.reserve_sms,
             "l2": "inputs larger than L2 (activations 134 MB per Linear, weights 7 GB)",
             "linear_tops": decoder_linear_ops(cfg, tokens, nl) * args.steps / (ms * 1e-3) / 1e12,
@@ -646,8 +694,8 @@ def run_c5(args, rank, world, dev):
         "gpu_launches": launches * args.steps,
         "clocks": clocks,
     }  # fmt: skip
-    if world > 1 and model.exchange in ("multimem", "stores"):
-        out_b, in_b = model.nvlink_bytes_per_forward
+    if world > 1 and head_exchange in ("multimem", "stores"):
+        out_b, in_b = head_nvlink
         line["nvlink"] = {
             "bytes_out_per_step": out_b, "bytes_in_per_step": in_b,
             "achieved_gbs_in": in_b / (ms / args.steps * 1e-3) / 1e9, "achieved_gbs_out": out_b / (ms / args.steps * 1e-3) / 1e9,
@@ -657,6 +705,8 @@ def run_c5(args, rank, world, dev):
         }  # fmt: skip
     if check is not None:
         line["sharded_vs_single_gpu"] = check
+    if sweep:
+        line["sweep"] = sweep
     if surfaces is not None:
         line["surfaces"] = surfaces
     if world == 1 and not args.no_kernels:
@@ -804,8 +854,12 @@ def main():
     ap.add_argument("--groups", type=int, default=0, help="groups of sequences pipelined on separate streams (0: 2 on sharded runs, else 1)")
     ap.add_argument("--reserve-sms", type=int, default=-1, help="sharded runs with several groups: SMs left to the link-bound exchange "
                     "kernels, GEMMs capped at the rest (-1: 16 on more than two GPUs, else 0)")
+    ap.add_argument("--sweep", default="", help="sharded runs, development: further settings timed on the same weights after the headline, "
+                    "comma-separated g<groups>r<reserved SMs>[s], e.g. g2r0,g2r32,g1r0,g2r16s")
     ap.add_argument("--nccl-ctas", type=int, default=16, help="upper bound on the CTAs of a collective (sharded runs)")
     ap.add_argument("--c4-dtype", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--act-scales", default="calibrated", choices=["calibrated", "synthetic"],
+                    help="c5: SmoothQuant activation scales from a calibration forward of the float model, or synthetic ones")
     ap.add_argument("--breakdown", action="store_true", help="development: per-kernel-shape times on stderr")
     args = ap.parse_args()
 

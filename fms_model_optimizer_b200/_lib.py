@@ -57,6 +57,7 @@ EXPORTED_SYMBOLS = (
     "qlin_ipc_close",
     "qlin_peer_copy2d",
     "qlin_peer_barrier",
+    "qlin_col_absmax",
 )
 
 
@@ -241,6 +242,18 @@ class RopeArgs(C.Structure):
     ]
 
 
+class ColAbsmaxArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p),
+        ("amax_io", C.c_void_p),
+        ("ldx", C.c_int64),
+        ("rows", C.c_int32),
+        ("cols", C.c_int32),
+        ("dtype", C.c_int32),
+        ("accumulate", C.c_int32),
+    ]
+
+
 class PeerBarrierArgs(C.Structure):
     _fields_ = [
         ("local_flags", C.c_void_p),
@@ -282,6 +295,7 @@ def load() -> C.CDLL:
         ("qlin_block_quant", BlockQuantArgs),
         ("qlin_rope", RopeArgs),
         ("qlin_peer_barrier", PeerBarrierArgs),
+        ("qlin_col_absmax", ColAbsmaxArgs),
     ):
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(struct), C.c_void_p]

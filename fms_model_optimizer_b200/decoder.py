@@ -89,6 +89,47 @@ def synth_w8a8(n, k, seed, dev, dtype=torch.bfloat16):
     return w8a8_from_float(synth_weight(n, k, seed, dev, dtype), synth_act_scale(k, seed, dev, dtype))
 
 
+@torch.no_grad()
+def calibrate_act_scales(cfg, dev, ids, layers=None):
+    """The SmoothQuant calibration pass for the decoder: one forward of the float (bf16) model on ``ids`` [batch, seq] with
+    the per-input-channel absolute maxima of every Linear's input recorded on the device (``ops.col_absmax``, the
+    statistic of fms_mo/quant/ptq.py:2586-2596).  The float weights are the seeded ones the quantized decoder is built
+    from; they are generated layer by layer and dropped again.  Returns ``{(layer, name): fp32 [in_features]}``."""
+    B, S = ids.shape
+    H, hd = cfg["hidden"], cfg["head_dim"]
+    nl = layers if layers is not None else cfg["layers"]
+    g = torch.Generator(device=dev).manual_seed(4)
+    embed = (torch.randn(cfg["vocab"], H, generator=g, device=dev) * 0.02).bfloat16()
+    inv = 1.0 / (cfg["rope_theta"] ** (torch.arange(0, hd, 2, device=dev).float() / hd))
+    ang = torch.outer(torch.arange(S, device=dev).float(), inv)
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    ones = torch.ones(H, device=dev, dtype=torch.bfloat16)
+    x = F.embedding(ids, embed).view(B * S, H)
+    scales = {}
+    names = list(linear_shapes(cfg).items())
+    for li in range(nl):
+        w = {name: synth_weight(n, k, 1000 * li + ni, dev) for ni, (name, (n, k, _)) in enumerate(names)}
+        h = F.rms_norm(x, (H,), ones, 1e-5)
+        for name in ("q", "k", "v"):
+            scales[(li, name)] = ops.col_absmax(h)
+        q = ops.rope_(F.linear(h, w["q"]).view(B * S, cfg["q_heads"], hd), cos, sin, S)
+        k = ops.rope_(F.linear(h, w["k"]).view(B * S, cfg["kv_heads"], hd), cos, sin, S)
+        v = F.linear(h, w["v"])
+        a = F.scaled_dot_product_attention(q.view(B, S, -1, hd).transpose(1, 2), k.view(B, S, -1, hd).transpose(1, 2),
+                                           v.view(B, S, -1, hd).transpose(1, 2), is_causal=True, enable_gqa=True)  # fmt: skip
+        a = a.transpose(1, 2).reshape(B * S, -1)
+        scales[(li, "o")] = ops.col_absmax(a)
+        x = x + F.linear(a, w["o"])
+        h = F.rms_norm(x, (H,), ones, 1e-5)
+        scales[(li, "gate")] = ops.col_absmax(h)
+        scales[(li, "up")] = scales[(li, "gate")]
+        m = F.silu(F.linear(h, w["gate"])) * F.linear(h, w["up"])
+        scales[(li, "down")] = ops.col_absmax(m)
+        x = x + F.linear(m, w["down"])
+        del w
+    return scales
+
+
 class _Group:
     """Exchange buffers of one group of sequences (see W8A8Decoder.enable_token_split)."""
 
@@ -143,12 +184,35 @@ class W8A8Decoder:
         inv = 1.0 / (cfg["rope_theta"] ** (torch.arange(0, hd, 2, device=dev).float() / hd))
         ang = torch.outer(torch.arange(S, device=dev).float(), inv)
         self.cos, self.sin = ang.cos().contiguous(), ang.sin().contiguous()  # fp32 [S, hd / 2]
-        if world > 1 and surface == "fused" and reserve_sms > 0 and self.groups > 1:
-            sms = torch.cuda.get_device_properties(dev).multi_processor_count
-            link_bound = ("o", "down") if exchange == "stores" else ()
-            for lin in self.layers:
-                for name in LINEARS:
-                    lin[name].max_ctas = reserve_sms if name in link_bound else sms - reserve_sms
+        self._apply_sm_partition()
+
+    def _apply_sm_partition(self):
+        """With several groups in flight on a sharded run, GEMMs leave ``reserve_sms`` SMs to the exchange kernels of the
+        other group (in the plain-store scheme the row-parallel GEMMs are themselves link-bound and get that share)."""
+        if self.surface != "fused":
+            return
+        on = self.world > 1 and self.reserve_sms > 0 and self.groups > 1
+        sms = torch.cuda.get_device_properties(self.dev).multi_processor_count
+        link_bound = ("o", "down") if self.exchange == "stores" else ()
+        for lin in self.layers:
+            for name in LINEARS:
+                lin[name].max_ctas = None if not on else (self.reserve_sms if name in link_bound else sms - self.reserve_sms)
+
+    def reconfigure(self, groups=None, reserve_sms=None, exchange=None):
+        """Sharded runs: another number of sequence groups, SM partition or exchange scheme ("multimem" / "stores") on the
+        same weights.  Collective: every rank calls it with the same arguments; call ``enable_token_split`` afterwards."""
+        self.close()
+        self.sp = None
+        if groups is not None:
+            self.groups = max(1, groups)
+            self.streams = [torch.cuda.Stream(device=self.dev) for _ in range(self.groups)] if self.groups > 1 else []
+        if reserve_sms is not None:
+            self.reserve_sms = reserve_sms
+        if exchange is not None:
+            if "allreduce" in (exchange, self.exchange) and exchange != self.exchange:
+                raise RuntimeError("the NCCL all-reduce scheme shards the Linears differently: build another decoder")
+            self.exchange = exchange
+        self._apply_sm_partition()
 
     # ------------------------------------------------------------------------------------------------ helpers
     def _note(self, tag, layer, t):

@@ -625,6 +625,35 @@ def rope_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq_len: int) -
 
 
 # --------------------------------------------------------------------------------------------------
+# Calibration statistics
+# --------------------------------------------------------------------------------------------------
+def col_absmax(x: torch.Tensor, running: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-input-channel absolute maximum of ``x`` viewed as ``[-1, x.shape[-1]]`` (``qlin_col_absmax``): the statistic of
+    activation_stats (fms_mo/quant/ptq.py:2586-2596).  With ``running`` (fp32 ``[channels]``, on the device) the result
+    is folded into it in place -- the maximum over all batches seen -- and ``running`` is returned."""
+    dev = _require_cuda(x, running)
+    if x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        raise RuntimeError(f"unsupported dtype {x.dtype}")
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    rows, cols = x2.shape
+    if running is None:
+        out = torch.empty((cols,), dtype=torch.float32, device=dev)
+    else:
+        if running.dtype != torch.float32 or running.shape != (cols,) or not running.is_contiguous():
+            raise RuntimeError("running must be a contiguous fp32 vector with one entry per channel")
+        out = running
+    args = L.ColAbsmaxArgs(x=_ptr(x2), amax_io=_ptr(out), ldx=(x2.stride(0) if rows > 1 else cols), rows=rows, cols=cols, dtype=_DT[x2.dtype],
+                           accumulate=int(running is not None))  # fmt: skip
+    with torch.cuda.device(dev):
+        rc = _timed("col_absmax", float(rows * cols * x2.element_size() + 4 * cols), dev,
+                    lambda: L.load().qlin_col_absmax(C.byref(args), _stream(dev)))  # fmt: skip
+        L.check(rc, "qlin_col_absmax")
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
 # torch custom ops (namespace qlin_b200), the counterpart of the reference's fms_mo::* registrations
 # (fms_mo/custom_ext_kernels/utils.py:674-802).  Fake implementations give shapes and dtypes so the
 # ops can be traced.

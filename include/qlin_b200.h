@@ -442,6 +442,28 @@ typedef struct qlin_block_quant_args {
 
 int qlin_block_quant(const qlin_block_quant_args* args, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * qlin_col_absmax -- per-column (input-channel) absolute maximum of x [rows, cols], kept as a running maximum.
+ *
+ * Replaces: activation_stats of the SmoothQuant calibration pass (fms_mo/quant/ptq.py:2586-2596):
+ *           tensor.view(-1, hidden).abs().max(dim=0) followed by torch.max with the value kept so far; called from the
+ *           forward hooks get_act_scales installs on every Linear (fms_mo/quant/ptq.py:2609-2657).  The result feeds
+ *           QLinear.set_act_scale / the smoothq_act_scale buffer (fms_mo/modules/linear.py:345-368).
+ * amax_io [cols] fp32: with accumulate == 0 it is overwritten with max_r |x[r, c]|; with accumulate != 0 it receives
+ * max(amax_io[c], max_r |x[r, c]|) (its content must then be non-negative or NaN).  A NaN anywhere in a column makes that
+ * column's result NaN, as torch.max does.  The result is exact (a maximum does not depend on the order it is taken in).
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct qlin_col_absmax_args {
+  const void* x;
+  float* amax_io;
+  int64_t ldx;       /* elements between rows */
+  int32_t rows, cols;
+  int32_t dtype;     /* F32 / F16 / BF16 */
+  int32_t accumulate;
+} qlin_col_absmax_args;
+
+int qlin_col_absmax(const qlin_col_absmax_args* args, void* stream);
+
 /* qlin_rope -- rotary position embedding in place on x [tokens, heads, head_dim] bf16 (token pitch
  * ld_token elements), position = token % seq_len, cos / sin [seq_len, head_dim / 2] fp32, halves
  * rotated as (x[i], x[i + head_dim / 2]).  No counterpart in the reference (model plumbing between

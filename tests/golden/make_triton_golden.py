@@ -34,8 +34,21 @@ def main():
         from fms_mo.custom_ext_kernels.triton_kernels import tl_matmul_chunk_truncate as ref_mm
 
     dev = torch.device("cuda", 0)
-    out = {"cases": [], "timing": []}
+    out = {"cases": [], "timing": [], "errors": []}
 
+    def guarded(fn):
+        """A reference kernel that does not build with the installed Triton is recorded, not fatal: the other kernels
+        still give their vectors."""
+        def run(*args, **kw):
+            try:
+                return fn(*args, **kw)
+            except Exception as e:  # noqa: BLE001
+                msg = f"{type(e).__name__}: {str(e).strip().splitlines()[0] if str(e).strip() else ''}"
+                out["errors"].append(dict(what=f"{fn.__name__}{args}{kw}", error=msg[:400]))
+                print("FAILED", fn.__name__, args, kw, msg[:200], flush=True)
+        return run
+
+    @guarded
     def case(kind, M, K, N, seed, **kw):
         g = torch.Generator().manual_seed(seed)
         if kind == "int8":
@@ -67,10 +80,8 @@ def main():
     case("fp8", 96, 512, 80, 15, chunk_trun_bits=12, chunk_size=64, truncate_then_accumulate=False)
     case("fp8", 96, 512, 80, 16, chunk_trun_bits=8, chunk_size=128, with_c=True)
 
-    # the reference kernels as same-box comparator: time after warm-up with CUDA events
-    for kind, (M, K, N), kw in (("int8", (16384, 4096, 4096), dict(chunk_trun_bits=0, chunk_size=64)),
-                                ("int8", (4096, 8192, 4096), dict(chunk_trun_bits=8, chunk_size=64)),
-                                ("fp8", (8192, 4096, 14336), dict(chunk_trun_bits=0, chunk_size=64))):  # fmt: skip
+    @guarded
+    def timing(kind, M, K, N, **kw):
         if kind == "int8":
             a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
             b = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev)
@@ -91,6 +102,12 @@ def main():
         rec = dict(kind=kind, M=M, K=K, N=N, kw=kw, ms=ms, tops=2.0 * M * N * K / (ms * 1e-3) / 1e12)
         out["timing"].append(rec)
         print("timing", json.dumps(rec), flush=True)
+
+    # the reference kernels as same-box comparator: time after warm-up with CUDA events
+    timing("int8", 16384, 4096, 4096, chunk_trun_bits=0, chunk_size=64)
+    timing("int8", 4096, 8192, 4096, chunk_trun_bits=8, chunk_size=64)
+    timing("fp8", 8192, 4096, 14336, chunk_trun_bits=0, chunk_size=64)
+    timing("fp8", 4096, 8192, 4096, chunk_trun_bits=8, chunk_size=64)
     out["versions"] = dict(torch=torch.__version__, triton=__import__("triton").__version__, device=torch.cuda.get_device_name(0),
                            when=time.strftime("%Y-%m-%d"))
     torch.save(out, out_path)

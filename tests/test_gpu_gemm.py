@@ -132,6 +132,31 @@ def test_fp8_chunk_truncation_matches_oracle(cuda_dev):
         assert torch.norm(got - want) / torch.norm(want) < 1e-3  # reference bound with truncation, test_triton_mm.py:82
 
 
+def test_fp8_chunk_gemm_against_the_reference_triton_kernel(cuda_dev):
+    """The CUDA kernel against outputs of the reference's own Triton matmul_kernel on the same seeded operands (golden
+    triton_fp8_mm.pt, made on a B200 by tests/golden/make_triton_golden.py).  The tensor core sums a chunk's products in
+    its own order, so a chunk sum can differ in its last fp32 place before the truncation; after truncating 8 or more
+    mantissa bits almost every element is identical."""
+    from conftest import load_golden
+
+    for c in load_golden("triton_fp8_mm.pt")["cases"]:
+        g = torch.Generator().manual_seed(c["seed"])
+        a = torch.randn(c["M"], c["K"], generator=g).to(torch.float8_e4m3fn)
+        b = torch.randn(c["N"], c["K"], generator=g).to(torch.float8_e4m3fn)
+        cc = torch.randint(-1000, 1000, (c["M"], c["N"]), generator=g).to(torch.float32) if c["with_c"] else None
+        kw = c["kw"]
+        y = ops.tl_matmul_chunk_truncate(a.to(cuda_dev), b.to(cuda_dev).t(), c=(cc.to(cuda_dev) if cc is not None else None),
+                                         chunk_trun_bits=kw.get("chunk_trun_bits", 0), chunk_size=kw.get("chunk_size", 16),
+                                         truncate_then_accumulate=kw.get("truncate_then_accumulate", True),
+                                         clamp_acc_to_dl16=kw.get("clamp_acc_to_dl16", False)).cpu()  # fmt: skip
+        got, ref = (y[:64, :64], c["block"]) if "block" in c else (y, c["y"])
+        rel = (torch.norm(got - ref) / torch.norm(ref)).item()
+        trun = 14 if kw.get("clamp_acc_to_dl16", False) else kw.get("chunk_trun_bits", 0)
+        assert rel < max(1e-6, 2.0 ** (-(23 - trun))), (c["M"], kw, rel)
+        if trun >= 8:
+            assert (got == ref).float().mean() > 0.99, (c["M"], kw, (got == ref).float().mean().item())
+
+
 def test_dequant_epilogue_modes(cuda_dev):
     """Scaled epilogues against the same arithmetic in eager CPU PyTorch."""
     a, b = _i8((70, 192), 14), _i8((90, 192), 15)

@@ -264,3 +264,34 @@ def test_deploy_static_zero_shift_and_torch_iW_equal_reference_outputs():
         st = OL.deploy_from_torch_iW(c["weight"], c["bias"], c["a_cv"], c["a_cvn"], c["w_cv"], c["zero_shift"], c["native"])
         assert torch.equal(st["bias"], c["dep_bias"]) and torch.equal(st["w_scale"], c["w_scale"])
         assert torch.equal(OL.deploy_static_forward(st, c["x"], acc_dtype=torch.float), c["y"])
+
+
+def _triton_case_inputs(c):
+    g = torch.Generator().manual_seed(c["seed"])
+    a = torch.randn(c["M"], c["K"], generator=g).to(torch.float8_e4m3fn)
+    b = torch.randn(c["N"], c["K"], generator=g).to(torch.float8_e4m3fn)
+    cc = torch.randint(-1000, 1000, (c["M"], c["N"]), generator=g).to(torch.float32) if c["with_c"] else None
+    return a, b, cc
+
+
+def test_float_chunk_gemm_equals_the_reference_triton_kernel():
+    """The float chunk-truncating matmul of the oracle against outputs of the reference's own Triton kernel
+    (matmul_kernel / matmul_kernel_DABC through tl_matmul_chunk_truncate, run on a B200 by
+    tests/golden/make_triton_golden.py): bit for bit wherever a chunk function is applied (mantissa truncation, DL16
+    clamp, truncate-after-accumulate, initial accumulator); for the plain product, where the chunking only fixes an fp32
+    summation order, to 1e-7 relative."""
+    g = load_golden("triton_fp8_mm.pt")
+    assert len(g["cases"]) == 6
+    for c in g["cases"]:
+        a, b, cc = _triton_case_inputs(c)
+        kw = c["kw"]
+        y = OG.fmatmul_chunk_truncate(a, b.t(), c=cc, chunk_trun_bits=kw.get("chunk_trun_bits", 0), chunk_size=kw.get("chunk_size", 16),
+                                      truncate_then_accumulate=kw.get("truncate_then_accumulate", True),
+                                      clamp_acc_to_dl16=kw.get("clamp_acc_to_dl16", False))  # fmt: skip
+        got, ref = (y[:64, :64], c["block"]) if "block" in c else (y, c["y"])
+        if kw.get("chunk_trun_bits", 0) > 0 or kw.get("clamp_acc_to_dl16", False):
+            assert torch.equal(got, ref), (c["M"], kw)
+        else:
+            assert torch.norm(got - ref) / torch.norm(ref) < 1e-7, (c["M"], kw)
+        if "sum" in c:
+            assert abs(y.double().sum().item() - c["sum"]) <= 1e-6 * c["abs_sum"]
