@@ -58,6 +58,7 @@ EXPORTED_SYMBOLS = (
     "qlin_peer_copy2d",
     "qlin_peer_barrier",
     "qlin_col_absmax",
+    "qlin_shard_reduce",
 )
 
 
@@ -254,6 +255,20 @@ class ColAbsmaxArgs(C.Structure):
     ]
 
 
+class ShardReduceArgs(C.Structure):
+    _fields_ = [
+        ("src_multicast", C.c_void_p),
+        ("add", C.c_void_p),
+        ("out", C.c_void_p),
+        ("ld_src", C.c_int64),
+        ("ld_add", C.c_int64),
+        ("ld_out", C.c_int64),
+        ("rows", C.c_int32),
+        ("cols", C.c_int32),
+        ("max_ctas", C.c_int32),
+    ]
+
+
 class PeerBarrierArgs(C.Structure):
     _fields_ = [
         ("local_flags", C.c_void_p),
@@ -296,6 +311,7 @@ def load() -> C.CDLL:
         ("qlin_rope", RopeArgs),
         ("qlin_peer_barrier", PeerBarrierArgs),
         ("qlin_col_absmax", ColAbsmaxArgs),
+        ("qlin_shard_reduce", ShardReduceArgs),
     ):
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(struct), C.c_void_p]

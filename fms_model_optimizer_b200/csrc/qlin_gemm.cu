@@ -62,6 +62,10 @@ struct Cfg {
   static constexpr bool NARROW = MODE == kNarrow64 || MODE == kNarrow32;
   static constexpr int BN = MODE == kWide ? 256 : MODE == kChunked ? 128 : MODE == kNarrow64 ? 64 : 32;
   static constexpr int NBUF = CHUNKED ? 4 : 2;
+  // Narrow tiles spread the four MMAs of a K block over four accumulators (added up when drained): with so few columns an
+  // MMA is over long before the next one into the same accumulator may start, and independent chains hide that wait.
+  static constexpr int NACC = NARROW ? 4 : 1;
+  static constexpr int BUF_COLS = BN * NACC;  // TMEM columns per accumulator buffer
   static constexpr int STAGES = MODE == kWide ? 4 : MODE == kChunked ? 5 : MODE == kNarrow64 ? 7 : 9;
   // Epilogue warps: w % 4 selects the 32 TMEM lanes a warp may read, w / 4 its column slice.  The
   // chunked kernel drains an accumulator per K-chunk, a chain of short dependent steps, and hides
@@ -82,6 +86,9 @@ static_assert(Cfg<kWide>::SMEM_BYTES <= 232448 && Cfg<kChunked>::SMEM_BYTES <= 2
                   Cfg<kNarrow32>::SMEM_BYTES <= 232448,
               "shared memory budget");
 static_assert(Cfg<kNarrow32>::COLS_PER_WARP == 32 && Cfg<kNarrow64>::COLS_PER_WARP == 32, "narrow tiles drain 32 columns per warp");
+static_assert(Cfg<kNarrow64>::NBUF * Cfg<kNarrow64>::BUF_COLS <= kTmemCols && Cfg<kWide>::NBUF * Cfg<kWide>::BUF_COLS <= kTmemCols &&
+                  Cfg<kChunked>::NBUF * Cfg<kChunked>::BUF_COLS <= kTmemCols,
+              "tensor memory budget");
 
 struct GemmParams {
   const void* c;
@@ -437,10 +444,16 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t s = 0, ph = 0, issued = 0;
     bool ok = true;
     bool ready = false;
+    // Narrow tiles: every CTA reads the same A block, and CTAs that walk K in step all ask the same few L2 lines for it
+    // at the same moment.  Each tile therefore starts its walk at another K block (the order of the K blocks does not
+    // matter to the MMA warp: a sum).  Only when K is a whole number of blocks, so that no partial block moves from
+    // the end of the walk, where the MMA warp expects it.
+    const bool rotate_k = C::NARROW && (p.kbytes % kBK == 0);
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
       tile_coords(t, p.num_m, p.num_n, mb, nb);
       const int ya = mb * kBM, yb = nb * C::BN;
+      int kpos = rotate_k ? static_cast<int>((static_cast<unsigned>(t) * 7u) % static_cast<unsigned>(num_kb)) : 0;
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!ready) {
           ok = warp_mbar_wait(&aux->empty[s], ph ^ 1u, abort_flag);
@@ -450,7 +463,8 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint32_t nph = (ns == 0u) ? (ph ^ 1u) : ph;
         const uint32_t peek = warp_mbar_test_begin(&aux->empty[ns], nph ^ 1u);
         uint8_t* sa = smem + s * C::STAGE_BYTES;
-        tma_issue_stage(&aux->full[s], C::STAGE_BYTES, sa, &tmap_a, ya, sa + C::A_BYTES, &tmap_b, yb, kb * kBK);
+        tma_issue_stage(&aux->full[s], C::STAGE_BYTES, sa, &tmap_a, ya, sa + C::A_BYTES, &tmap_b, yb, kpos * kBK);
+        if (++kpos == num_kb) kpos = 0;
         ++issued;
         ready = warp_mbar_test_end(peek);
         s = ns;
@@ -511,7 +525,11 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               bph ^= 1u;
             }
           }
-          tc_mma4_release<F8 ? 1 : 0>(tmem_base + cur * C::BN, adesc, bdesc, idesc, accumulate, &aux->empty[s]);
+          if constexpr (C::NACC > 1) {
+            tc_mma4_release_split<F8 ? 1 : 0>(tmem_base + cur * C::BUF_COLS, C::BN, adesc, bdesc, idesc, accumulate, &aux->empty[s]);
+          } else {
+            tc_mma4_release<F8 ? 1 : 0>(tmem_base + cur * C::BUF_COLS, adesc, bdesc, idesc, accumulate, &aux->empty[s]);
+          }
           accumulate = 1;
           k32_left -= 4;
           if (k32_left == 0) tc_commit_elect(&aux->tfull[cur]);
@@ -563,7 +581,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 ++chunk_pos;
                 --k32_left;
                 const bool last_of_chunk = chunk_pos == p.chunk_k32 || k32_left == 0;
-                tc_mma1<F8 ? 1 : 0>(tmem_base + cur * C::BN, adesc + static_cast<uint64_t>(j * 2),
+                tc_mma1<F8 ? 1 : 0>(tmem_base + cur * C::BUF_COLS, adesc + static_cast<uint64_t>(j * 2),
                                     bdesc + static_cast<uint64_t>(j * 2), idesc, accumulate);
                 if (last_of_chunk) tc_commit_elect(&aux->tfull[cur]);
                 accumulate = 1;
@@ -634,7 +652,16 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         tc_fence_after();
         uint32_t v[32];
-        tmem_ld32(tmem_base + lane_base + buf * C::BN + half * C::COLS_PER_WARP, v);
+        tmem_ld32(tmem_base + lane_base + buf * C::BUF_COLS + half * C::COLS_PER_WARP, v);
+        if (total_k32 >= 4) {  // a K of less than one full block went to the first accumulator alone
+#pragma unroll 1
+          for (int acc = 1; acc < C::NACC; ++acc) {
+            uint32_t w[32];
+            tmem_ld32(tmem_base + lane_base + buf * C::BUF_COLS + acc * C::BN + half * C::COLS_PER_WARP, w);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = acc_add<F8>(v[i], w[i]);
+          }
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&aux->tempty[buf]);  // the accumulator is in registers: the next tile may start

@@ -150,6 +150,9 @@ class W8A8Decoder:
         self.sp: Optional[List[_Group]] = None
         self.arena = None
         self.last_hidden = None
+        # multimem exchange: read the shards' partial sums with a streaming kernel of its own ("split", many loads in
+        # flight per thread) before the fused norm + quantise kernel, or inside that kernel's prologue ("fused")
+        self.switch_reduce = "split"
         if exchange == "auto":
             exchange = "none" if world == 1 else "multimem"
         self.exchange = exchange
@@ -393,7 +396,9 @@ class W8A8Decoder:
             if n:
                 kw["dst"] = (g.bases, g.codes_off[:n], g.scale_off[:n], rank * Ts)
                 kw["dst_multimem"] = mm
-            if have_parts and mm:
+            if have_parts and mm and self.switch_reduce == "split":
+                ops.shard_reduce_(x, g.my_part_mc, max_ctas=2 * self.reserve_sms)
+            elif have_parts and mm:
                 kw.update(r_ptr=g.my_part_mc, r_multimem=True)
             elif have_parts:
                 kw.update(r=g.part[0], r_parts=W, r_part_stride=Ts * H)

@@ -624,6 +624,21 @@ def rope_(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, seq_len: int) -
     return x
 
 
+def shard_reduce_(x: torch.Tensor, src_multicast: int, max_ctas: int = 0) -> torch.Tensor:
+    """``x += sum over GPUs of their partial outputs`` for this GPU's block of rows, read through the multicast mapping at
+    ``src_multicast`` (row pitch = the row length of ``x``); in place on the bf16 ``x`` (``qlin_shard_reduce``)."""
+    dev = _require_cuda(x)
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.stride(1) != 1:
+        raise RuntimeError("shard_reduce_ takes a 2-D bf16 tensor with contiguous rows")
+    rows, cols = x.shape
+    args = L.ShardReduceArgs(src_multicast=int(src_multicast), add=_ptr(x), out=_ptr(x), ld_src=cols, ld_add=x.stride(0), ld_out=x.stride(0),
+                             rows=rows, cols=cols, max_ctas=int(max_ctas))  # fmt: skip
+    with torch.cuda.device(dev):
+        rc = _timed("shard_reduce", float(rows * cols * 2 * 3), dev, lambda: L.load().qlin_shard_reduce(C.byref(args), _stream(dev)))
+        L.check(rc, "qlin_shard_reduce")
+    return x
+
+
 # --------------------------------------------------------------------------------------------------
 # Calibration statistics
 # --------------------------------------------------------------------------------------------------

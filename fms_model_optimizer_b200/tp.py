@@ -126,7 +126,10 @@ class W8A8Linear:
         if self.mode == "row" and self.world > 1:
             _, (scale,), _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_SCALE_ONLY)
             dist.all_reduce(scale, op=dist.ReduceOp.MAX, group=self.group)
-            (codes,), _, _, _ = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_GIVEN_SCALE, scale_in=scale)
+            (codes,), _, _, h = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, mode=L.BLOCK_GIVEN_SCALE, scale_in=scale,
+                                                want_h=want_h)
+            if want_h:
+                keep_h.append(h)
             return codes, scale
         (codes,), (scale,), _, h = ops.block_quant(x2, prologue=prologue, r=r, smooth_rcps=rcp, want_h=want_h)
         if want_h:

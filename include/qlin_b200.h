@@ -498,6 +498,23 @@ int qlin_ipc_close(void* base);
  * a mapped peer address.  The copy engines carry it, so it overlaps kernels of other streams without taking SMs. */
 int qlin_peer_copy2d(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width, int64_t height, void* stream);
 
+/* qlin_shard_reduce -- the reduce-scatter half of a row-parallel Linear through the NVLink switch: every GPU holds its
+ * partial output in its own copy of a buffer bound to one multicast object; the owner of a block of rows reads the block
+ * through the multicast mapping (multimem.ld_reduce: the sum over all copies, accumulated in fp32, rounded to bf16 once),
+ * adds an optional local bf16 tensor in fp32 and writes bf16:  out = bf16(add + sum over GPUs of part).  All bf16,
+ * 16-byte aligned, cols and leading dimensions multiples of 8 elements; out may alias add.  max_ctas > 0 caps the grid
+ * (the kernel is bound by the links; a dozen CTAs carry it).  No counterpart in the reference. */
+typedef struct qlin_shard_reduce_args {
+  const void* src_multicast; /* multicast address of the first element of this GPU's block */
+  const void* add;           /* optional [rows, cols] local */
+  void* out;                 /* [rows, cols] local */
+  int64_t ld_src, ld_add, ld_out;
+  int32_t rows, cols;
+  int32_t max_ctas;
+} qlin_shard_reduce_args;
+
+int qlin_shard_reduce(const qlin_shard_reduce_args* args, void* stream);
+
 typedef struct qlin_peer_barrier_args {
   uint32_t* local_flags;
   uint32_t* peer_flags[8];

@@ -35,7 +35,7 @@ def test_struct_layouts_match_header_field_order():
                         ("qlin_pact2_args", L.Pact2Args), ("qlin_wfq_args", L.WfqArgs),
                         ("qlin_tensor_fq_args", L.TensorFqArgs), ("qlin_block_quant_args", L.BlockQuantArgs),
                         ("qlin_rope_args", L.RopeArgs), ("qlin_peer_barrier_args", L.PeerBarrierArgs),
-                        ("qlin_col_absmax_args", L.ColAbsmaxArgs)):
+                        ("qlin_col_absmax_args", L.ColAbsmaxArgs), ("qlin_shard_reduce_args", L.ShardReduceArgs)):
         body = re.search(r"typedef struct " + struct + r" \{(.*?)\} " + struct, text, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []
@@ -119,7 +119,7 @@ def test_struct_sizes_and_offsets_match_a_c_compiler(tmp_path):
     structs = (("qlin_gemm_args", L.GemmArgs), ("qlin_quant_args", L.QuantArgs), ("qlin_pact2_args", L.Pact2Args),
                ("qlin_wfq_args", L.WfqArgs), ("qlin_tensor_fq_args", L.TensorFqArgs), ("qlin_block_quant_args", L.BlockQuantArgs),
                ("qlin_rope_args", L.RopeArgs), ("qlin_peer_barrier_args", L.PeerBarrierArgs),
-               ("qlin_col_absmax_args", L.ColAbsmaxArgs))  # fmt: skip
+               ("qlin_col_absmax_args", L.ColAbsmaxArgs), ("qlin_shard_reduce_args", L.ShardReduceArgs))  # fmt: skip
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void) {"]
     for name, cls in structs:
         lines.append(f'  printf("{name} %zu\\n", sizeof({name}));')
