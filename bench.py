@@ -246,7 +246,7 @@ class KernelTimer:
         return tot / steps
 
 
-def kernel_cases(dev, which):
+def kernel_cases(dev, which, only=""):
     """(name, dtype, bound, work, unit_scale, fn) for the single-kernel workloads: work is operations for tensor-bound
     entries and algorithmic bytes for HBM-bound ones."""
     from fms_model_optimizer_b200 import _lib as L, ops, tp
@@ -258,16 +258,20 @@ def kernel_cases(dev, which):
     def add(name, dtype, bound, work, fn, graph=True):
         cases.append(dict(name=name, dtype=dtype, bound=bound, work=float(work), fn=fn, graph=graph))
 
+    def wanted(prefix):
+        """False when --only names another case: such a case is not even built (its set-up launches kernels too)."""
+        return not only or only.startswith(prefix) or prefix.startswith(only)
+
     if which in ("c1", "c5lin", "all"):
         for tag, (M, K, N) in (("c1", (2048, 4096, 4096)), ("c5lin", (16384, 4096, 4096))):
-            if which not in (tag, "all"):
+            if which not in (tag, "all") or not wanted(tag):
                 continue
             torch.manual_seed(0)
             x = torch.randn(M, K, device=dev).bfloat16()
             codes, w_scale, smooth = synth_w8a8(N, K, 0, dev)
             lin = tp.W8A8Linear(codes, w_scale, smooth, torch.zeros(N, device=dev))
             add(f"{tag} W8A8 INT8 Linear {M}x{K}x{N} (quantise + GEMM + dequantise)", "int8", "tensor", 2.0 * M * N * K, lambda lin=lin, x=x: lin(x))
-    if which in ("c2", "all"):
+    if which in ("c2", "all") and wanted("c2"):
         torch.manual_seed(1)
         M, K, N = 4096, 8192, 4096
         a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
@@ -278,6 +282,8 @@ def kernel_cases(dev, which):
     if which in ("c3", "all"):
         torch.manual_seed(2)
         for M, K, N in ((1, 4096, 14336), (128, 4096, 4096), (8192, 4096, 14336), (8192, 14336, 4096)):
+            if not wanted(f"c3 FP8 e4m3 Linear {M}x{K}x{N}"):
+                continue
             x = torch.randn(M, K, device=dev).bfloat16()
             lin = torch.nn.Linear(K, N, bias=False, device=dev, dtype=torch.bfloat16)
             with torch.no_grad():
@@ -358,7 +364,7 @@ def measure_kernels(dev, which="all", steps=5, warmup=3, with_comparators=True, 
     pk = peaks()
     timer = KernelTimer(dev)
     kernels, comps = [], []
-    for c in kernel_cases(dev, which):
+    for c in kernel_cases(dev, which, only):
         if only and only not in c["name"]:
             c["fn"] = None
             continue

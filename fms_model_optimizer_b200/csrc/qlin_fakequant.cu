@@ -27,6 +27,7 @@ struct PactParams {
 
 struct PactScalars {
   float cv, cvn, step, zp, n;
+  float rstep, rn;  // reciprocals for div_exact (NaN where the shortcut is not proven: those take the IEEE division)
   int variant;
 };
 
@@ -59,6 +60,8 @@ __device__ __forceinline__ PactScalars pact_scalars(const PactParams& p) {
     const float scale = Elem<XT>::rnd(__fmul_rn(Elem<XT>::rnd(__fdiv_rn(1.0f, two_cv)), s.n));
     s.step = Elem<XT>::rnd(__fdiv_rn(1.0f, scale));
   }
+  s.rstep = rcp_for_div(s.step);
+  s.rn = rcp_for_div(s.n);
   return s;
 }
 
@@ -67,28 +70,29 @@ __device__ __forceinline__ float pact_fwd_one(const PactScalars& s, float x) {
   if (s.variant == QLIN_PACT_TWO_SIDED) {
     float y = fminf(x, s.cv);
     y = fmaxf(y, s.cvn);
-    float t = Elem<XT>::rnd(__fdiv_rn(y, s.step));
+    float t = Elem<XT>::rnd(div_exact(y, s.step, s.rstep));
     t = Elem<XT>::rnd(__fsub_rn(t, s.zp));
-    const float q = rintf(t);
+    const float q = rint_small(t);  // |t| <= 2^16: y is clamped to the clip range
     return Elem<XT>::rnd(__fmul_rn(Elem<XT>::rnd(__fadd_rn(q, s.zp)), s.step));
   }
   if (s.variant == QLIN_PACT_ONE_SIDED) {
     // PACTplusSTE.forward: round(clamp(x, 0, cv) / step) * step
     const float y = fminf(fmaxf(x, 0.0f), s.cv);
-    return Elem<XT>::rnd(__fmul_rn(rintf(Elem<XT>::rnd(__fdiv_rn(y, s.step))), s.step));
+    return Elem<XT>::rnd(__fmul_rn(rint_small(Elem<XT>::rnd(div_exact(y, s.step, s.rstep))), s.step));
   }
   // PACTplusSymSTE_rev1.forward: round((clamp(x, -cv, cv) + cv) / step) * step - cv
   float y = x > s.cv ? s.cv : x;
   y = y < -s.cv ? -s.cv : y;
-  const float q = rintf(Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fadd_rn(y, s.cv)), s.step)));
+  const float q = rint_small(Elem<XT>::rnd(div_exact(Elem<XT>::rnd(__fadd_rn(y, s.cv)), s.step, s.rstep)));
   return Elem<XT>::rnd(__fsub_rn(Elem<XT>::rnd(__fmul_rn(q, s.step)), s.cv));
 }
 
 template <typename XT>
 __device__ __forceinline__ float pact_bwd_one(const PactScalars& s, float x, float g, float& ga, float& gan) {
   if (s.variant == QLIN_PACT_TWO_SIDED) {
-    const float z = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fsub_rn(x, s.cvn)), s.step));
-    const float delz = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fsub_rn(z, rintf(z))), s.n));
+    // lanes outside the clip range never use delz, so rint_small's range (|z| < 2^22) covers every lane that matters
+    const float z = Elem<XT>::rnd(div_exact(Elem<XT>::rnd(__fsub_rn(x, s.cvn)), s.step, s.rstep));
+    const float delz = Elem<XT>::rnd(div_exact(Elem<XT>::rnd(__fsub_rn(z, rint_small(z))), s.n, s.rn));
     const float inner = Elem<XT>::rnd(__fmul_rn(-g, delz));
     const bool hi = x >= s.cv, lo = x <= s.cvn;
     ga += hi ? g : (lo ? 0.0f : inner);
@@ -97,17 +101,17 @@ __device__ __forceinline__ float pact_bwd_one(const PactScalars& s, float x, flo
   }
   if (s.variant == QLIN_PACT_ONE_SIDED) {
     // PACTplusSTE.backward: z = x / step; delz = (z - round(z)) / n
-    const float z = Elem<XT>::rnd(__fdiv_rn(x, s.step));
-    const float delz = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fsub_rn(z, rintf(z))), s.n));
+    const float z = Elem<XT>::rnd(div_exact(x, s.step, s.rstep));
+    const float delz = Elem<XT>::rnd(div_exact(Elem<XT>::rnd(__fsub_rn(z, rint_small(z))), s.n, s.rn));
     const float inner = Elem<XT>::rnd(__fmul_rn(-g, delz));
     const bool hi = x >= s.cv, lo = x <= 0.0f;
     ga += hi ? g : (lo ? 0.0f : inner);
     return (hi || lo) ? 0.0f : g;
   }
   // PACTplusSymSTE_rev1.backward: z = (x + cv) / step; delz = 2 (round(z) - z) / n; +-1 outside
-  const float z = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fadd_rn(x, s.cv)), s.step));
-  const float d0 = Elem<XT>::rnd(__fsub_rn(rintf(z), z));
-  const float delz = Elem<XT>::rnd(__fdiv_rn(Elem<XT>::rnd(__fmul_rn(2.0f, d0)), s.n));
+  const float z = Elem<XT>::rnd(div_exact(Elem<XT>::rnd(__fadd_rn(x, s.cv)), s.step, s.rstep));
+  const float d0 = Elem<XT>::rnd(__fsub_rn(rint_small(z), z));
+  const float delz = Elem<XT>::rnd(div_exact(Elem<XT>::rnd(__fmul_rn(2.0f, d0)), s.n, s.rn));
   const bool hi = x >= s.cv, lo = x <= -s.cv;
   const float w = hi ? 1.0f : (lo ? -1.0f : delz);
   ga += Elem<XT>::rnd(__fmul_rn(w, g));

@@ -35,8 +35,8 @@ constexpr int kTmemCols = 512;
 constexpr int kStageOutBytes = 4096;  // per epilogue warp: 32 rows x 128 bytes of output
 
 struct Aux {
-  uint64_t full[12];
-  uint64_t empty[12];
+  uint64_t full[8];
+  uint64_t empty[8];
   uint64_t tfull[4];
   uint64_t tempty[4];
   uint64_t drain;
@@ -46,31 +46,15 @@ struct Aux {
   float bias[256];
 };
 
-// Tile configurations of the single-CTA kernel.
-//   kWide    128 x 256 tiles, the general unchunked case
-//   kChunked 128 x 128 tiles, per-chunk accumulators
-//   kNarrow64 / kNarrow32
-//            128 x 64 / 128 x 32 tiles for problems of at most 128 rows (one row block): such a problem is a stream
-//            over the weight matrix, and narrow tiles are what spreads that stream over all SMs (N / 32 tiles instead
-//            of N / 256) with a deep pipeline of small stages, so that it runs at HBM speed rather than at the speed
-//            at which a handful of SMs can pull their slices
-enum GemmMode { kWide = 0, kChunked = 1, kNarrow64 = 2, kNarrow32 = 3 };
-
-template <int MODE>
+template <bool CHUNKED>
 struct Cfg {
-  static constexpr bool CHUNKED = MODE == kChunked;
-  static constexpr bool NARROW = MODE == kNarrow64 || MODE == kNarrow32;
-  static constexpr int BN = MODE == kWide ? 256 : MODE == kChunked ? 128 : MODE == kNarrow64 ? 64 : 32;
+  static constexpr int BN = CHUNKED ? 128 : 256;
   static constexpr int NBUF = CHUNKED ? 4 : 2;
-  // Narrow tiles spread the four MMAs of a K block over four accumulators (added up when drained): with so few columns an
-  // MMA is over long before the next one into the same accumulator may start, and independent chains hide that wait.
-  static constexpr int NACC = NARROW ? 4 : 1;
-  static constexpr int BUF_COLS = BN * NACC;  // TMEM columns per accumulator buffer
-  static constexpr int STAGES = MODE == kWide ? 4 : MODE == kChunked ? 5 : MODE == kNarrow64 ? 7 : 9;
+  static constexpr int STAGES = CHUNKED ? 5 : 4;
   // Epilogue warps: w % 4 selects the 32 TMEM lanes a warp may read, w / 4 its column slice.  The
   // chunked kernel drains an accumulator per K-chunk, a chain of short dependent steps, and hides
   // that latency with twice as many, narrower warps.
-  static constexpr int EPI_WARPS = CHUNKED ? 16 : MODE == kNarrow32 ? 4 : 8;
+  static constexpr int EPI_WARPS = CHUNKED ? 16 : 8;
   static constexpr int PRODUCER_WARP = EPI_WARPS;
   static constexpr int MMA_WARP = EPI_WARPS + 1;
   static constexpr int THREADS = (EPI_WARPS + 2) * 32;
@@ -82,13 +66,7 @@ struct Cfg {
   static constexpr int AUX_OFFSET = OUT_OFFSET + EPI_WARPS * kStageOutBytes;
   static constexpr int SMEM_BYTES = AUX_OFFSET + static_cast<int>(sizeof(Aux));
 };
-static_assert(Cfg<kWide>::SMEM_BYTES <= 232448 && Cfg<kChunked>::SMEM_BYTES <= 232448 && Cfg<kNarrow64>::SMEM_BYTES <= 232448 &&
-                  Cfg<kNarrow32>::SMEM_BYTES <= 232448,
-              "shared memory budget");
-static_assert(Cfg<kNarrow32>::COLS_PER_WARP == 32 && Cfg<kNarrow64>::COLS_PER_WARP == 32, "narrow tiles drain 32 columns per warp");
-static_assert(Cfg<kNarrow64>::NBUF * Cfg<kNarrow64>::BUF_COLS <= kTmemCols && Cfg<kWide>::NBUF * Cfg<kWide>::BUF_COLS <= kTmemCols &&
-                  Cfg<kChunked>::NBUF * Cfg<kChunked>::BUF_COLS <= kTmemCols,
-              "tensor memory budget");
+static_assert(Cfg<false>::SMEM_BYTES <= 232448 && Cfg<true>::SMEM_BYTES <= 232448, "shared memory budget");
 
 struct GemmParams {
   const void* c;
@@ -107,6 +85,12 @@ struct GemmParams {
   int32_t scatter_rows, scatter_row0;
   uint8_t* scatter_d[8];
   int32_t f8_ab_format;  // float kinds: operand format of the instruction descriptor, 0 = e4m3, 1 = e5m2
+  // Split-K (unchunked problems of at most 128 rows): work item w = tile * split_k + split; split s owns K blocks
+  // [s * kb_per_split, ...).  Partial accumulators go to ws_part[s][M][N] (raw 32-bit words); the epilogue warp whose
+  // arrival on ws_count[tile * 8 + warp] is the last one adds the splits in index order and runs the real epilogue.
+  int32_t split_k, kb_per_split;
+  uint32_t* ws_part;
+  uint32_t* ws_count;
 };
 
 __device__ __forceinline__ float round_to(float y, int dt) {
@@ -384,12 +368,11 @@ __device__ __forceinline__ void emit32(const GemmParams& p, const uint32_t (&v)[
   store_tile_coalesced(stage, w, g, p.ldd * 4, p.M - row0, lane);
 }
 
-template <bool F8, int MODE>
-__global__ void __launch_bounds__(Cfg<MODE>::THREADS, 1)
+template <bool F8, bool CHUNKED>
+__global__ void __launch_bounds__(Cfg<CHUNKED>::THREADS, 1)
 qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
-  using C = Cfg<MODE>;
-  constexpr bool CHUNKED = C::CHUNKED;
+  using C = Cfg<CHUNKED>;
   extern __shared__ __align__(1024) uint8_t smem[];
   Aux* aux = reinterpret_cast<Aux*>(smem + C::AUX_OFFSET);
   volatile int* abort_flag = &aux->abort_flag;
@@ -434,6 +417,8 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int num_tiles = p.num_m * p.num_n;
   const int num_kb = (p.kbytes + kBK - 1) / kBK;
   const int total_k32 = (p.kbytes + 31) / 32;
+  const int split_k = CHUNKED ? 1 : max(1, p.split_k);
+  const int num_work = num_tiles * split_k;
   bool timed_out = false;
 
   if (warp == C::PRODUCER_WARP) {
@@ -444,17 +429,13 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t s = 0, ph = 0, issued = 0;
     bool ok = true;
     bool ready = false;
-    // Narrow tiles: every CTA reads the same A block, and CTAs that walk K in step all ask the same few L2 lines for it
-    // at the same moment.  Each tile therefore starts its walk at another K block (the order of the K blocks does not
-    // matter to the MMA warp: a sum).  Only when K is a whole number of blocks, so that no partial block moves from
-    // the end of the walk, where the MMA warp expects it.
-    const bool rotate_k = C::NARROW && (p.kbytes % kBK == 0);
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       int mb, nb;
+      const int t = w / split_k, sp = w - t * split_k;
       tile_coords(t, p.num_m, p.num_n, mb, nb);
       const int ya = mb * kBM, yb = nb * C::BN;
-      int kpos = rotate_k ? static_cast<int>((static_cast<unsigned>(t) * 7u) % static_cast<unsigned>(num_kb)) : 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
+      const int kb0 = sp * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!ready) {
           ok = warp_mbar_wait(&aux->empty[s], ph ^ 1u, abort_flag);
           if (!ok) break;
@@ -463,8 +444,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint32_t nph = (ns == 0u) ? (ph ^ 1u) : ph;
         const uint32_t peek = warp_mbar_test_begin(&aux->empty[ns], nph ^ 1u);
         uint8_t* sa = smem + s * C::STAGE_BYTES;
-        tma_issue_stage(&aux->full[s], C::STAGE_BYTES, sa, &tmap_a, ya, sa + C::A_BYTES, &tmap_b, yb, kpos * kBK);
-        if (++kpos == num_kb) kpos = 0;
+        tma_issue_stage(&aux->full[s], C::STAGE_BYTES, sa, &tmap_a, ya, sa + C::A_BYTES, &tmap_b, yb, kb * kBK);
         ++issued;
         ready = warp_mbar_test_end(peek);
         s = ns;
@@ -499,11 +479,13 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     bool tready = false;  // next accumulator buffer known to be drained
     // chunks that tile a 128-byte K block exactly (32, 64 or 128 elements, K a multiple of 128)
     const bool chunk_fast = CHUNKED && (p.chunk_k32 == 1 || p.chunk_k32 == 2 || p.chunk_k32 == 4) && (total_k32 % 4 == 0);
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       uint32_t accumulate = 0, cur = 0;
       int chunk_pos = 0;
-      int k32_left = total_k32;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int sp = w % split_k;
+      const int kb0 = sp * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
+      int k32_left = split_k > 1 ? min(total_k32 - kb0 * 4, (kb1 - kb0) * 4) : total_k32;
+      for (int kb = kb0; kb < kb1 && ok; ++kb) {
         if (!ready) {
           ok = warp_mbar_wait(&aux->full[s], ph, abort_flag);
           if (!ok) break;
@@ -515,7 +497,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
         const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
         if (!CHUNKED && k32_left >= 4) {
-          if (kb == 0) {
+          if (kb == kb0) {
             ok = warp_mbar_wait(&aux->tempty[buf], bph ^ 1u, abort_flag);
             if (!ok) break;
             tc_fence_after();
@@ -525,11 +507,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               bph ^= 1u;
             }
           }
-          if constexpr (C::NACC > 1) {
-            tc_mma4_release_split<F8 ? 1 : 0>(tmem_base + cur * C::BUF_COLS, C::BN, adesc, bdesc, idesc, accumulate, &aux->empty[s]);
-          } else {
-            tc_mma4_release<F8 ? 1 : 0>(tmem_base + cur * C::BUF_COLS, adesc, bdesc, idesc, accumulate, &aux->empty[s]);
-          }
+          tc_mma4_release<F8 ? 1 : 0>(tmem_base + cur * C::BN, adesc, bdesc, idesc, accumulate, &aux->empty[s]);
           accumulate = 1;
           k32_left -= 4;
           if (k32_left == 0) tc_commit_elect(&aux->tfull[cur]);
@@ -581,7 +559,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 ++chunk_pos;
                 --k32_left;
                 const bool last_of_chunk = chunk_pos == p.chunk_k32 || k32_left == 0;
-                tc_mma1<F8 ? 1 : 0>(tmem_base + cur * C::BUF_COLS, adesc + static_cast<uint64_t>(j * 2),
+                tc_mma1<F8 ? 1 : 0>(tmem_base + cur * C::BN, adesc + static_cast<uint64_t>(j * 2),
                                     bdesc + static_cast<uint64_t>(j * 2), idesc, accumulate);
                 if (last_of_chunk) tc_commit_elect(&aux->tfull[cur]);
                 accumulate = 1;
@@ -622,8 +600,9 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t ebuf = 0, ebph = 0;
     bool eready = false;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       int mb, nb;
+      const int t = w / split_k, sp = w - t * split_k;
       tile_coords(t, p.num_m, p.num_n, mb, nb);
       const int row0 = mb * kBM + q * 32;
       const int row = row0 + lane;
@@ -640,7 +619,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
         if (p.rs != nullptr && row < p.M) rs = p.rs[static_cast<int64_t>(row) * p.rs_stride];
       }
-      if constexpr (C::NARROW) {
+      if constexpr (!CHUNKED) {
         const uint32_t buf = ebuf, bph = ebph;
         if (++ebuf == C::NBUF) {
           ebuf = 0;
@@ -651,38 +630,57 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           break;
         }
         tc_fence_after();
-        uint32_t v[32];
-        tmem_ld32(tmem_base + lane_base + buf * C::BUF_COLS + half * C::COLS_PER_WARP, v);
-        if (total_k32 >= 4) {  // a K of less than one full block went to the first accumulator alone
+        if (split_k > 1) {
+          // Split-K: park this split's raw accumulators, then let the last split to arrive add them up in index order.
+          // Rows of this warp that lie outside M are skipped throughout (N is a multiple of 64 on this path).
+          const bool row_ok = row < p.M;
+          uint32_t* part = p.ws_part + (static_cast<int64_t>(sp) * p.M + row) * p.N + col_w;
 #pragma unroll 1
-          for (int acc = 1; acc < C::NACC; ++acc) {
-            uint32_t w[32];
-            tmem_ld32(tmem_base + lane_base + buf * C::BUF_COLS + acc * C::BN + half * C::COLS_PER_WARP, w);
+          for (int j = 0; j < C::COLS_PER_WARP; j += 64) {
+            uint32_t v[64];
+            tmem_ld64(tmem_base + lane_base + buf * C::BN + half * C::COLS_PER_WARP + j, v);
+            if (row_ok && col_w + j < p.N) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = acc_add<F8>(v[i], w[i]);
+              for (int i = 0; i < 64; i += 4) __stcg(reinterpret_cast<uint4*>(part + j + i), make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]));
+            }
           }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&aux->tempty[buf]);  // the accumulator is in registers: the next tile may start
-        if (p.c != nullptr) {
-          uint32_t cv[32];
-          load_c_row<32>(p, cv, row, col_w);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&aux->tempty[buf]);
+          __threadfence();
+          __syncwarp();
+          uint32_t arrived = 0;
+          if (lane == 0) arrived = atomicAdd(p.ws_count + t * C::EPI_WARPS + warp, 1u);
+          arrived = __shfl_sync(0xffffffffu, arrived, 0);
+          if (arrived == static_cast<uint32_t>(split_k - 1)) {
+            __threadfence();
+#pragma unroll 1
+            for (int j = 0; j < C::COLS_PER_WARP; j += 64) {
+              uint32_t v[64];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = acc_add<F8>(cv[i], v[i]);
-        }
-        emit32<F8>(p, v, row0, lane, col_w, aux->cs, aux->bias, half * C::COLS_PER_WARP, rs, vec_ok, stage);
-      } else if constexpr (!CHUNKED) {
-        const uint32_t buf = ebuf, bph = ebph;
-        if (++ebuf == C::NBUF) {
-          ebuf = 0;
-          ebph ^= 1u;
-        }
-        if (!warp_mbar_wait(&aux->tfull[buf], bph, abort_flag)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
+              for (int i = 0; i < 64; ++i) v[i] = 0u;
+              if (row_ok && col_w + j < p.N) {
+                for (int s2 = 0; s2 < split_k; ++s2) {
+                  const uint32_t* src = p.ws_part + (static_cast<int64_t>(s2) * p.M + row) * p.N + col_w + j;
+#pragma unroll
+                  for (int i = 0; i < 64; i += 4) {
+                    const uint4 u = __ldcg(reinterpret_cast<const uint4*>(src + i));
+                    v[i] = acc_add<F8>(v[i], u.x), v[i + 1] = acc_add<F8>(v[i + 1], u.y);
+                    v[i + 2] = acc_add<F8>(v[i + 2], u.z), v[i + 3] = acc_add<F8>(v[i + 3], u.w);
+                  }
+                }
+              }
+              if (p.c != nullptr) {
+                uint32_t cv[64];
+                load_c_row<64>(p, cv, row, col_w + j);
+#pragma unroll
+                for (int i = 0; i < 64; ++i) v[i] = acc_add<F8>(cv[i], v[i]);
+              }
+              emit64<F8>(p, v, row0, lane, col_w + j, aux->cs, aux->bias, half * C::COLS_PER_WARP + j, rs, vec_ok, stage);
+            }
+            if (lane == 0) p.ws_count[t * C::EPI_WARPS + warp] = 0u;  // the counters are left at zero for the next launch
+          }
+        } else {
 #pragma unroll 1
         for (int j = 0; j < C::COLS_PER_WARP; j += 64) {
           uint32_t v[64];
@@ -698,6 +696,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&aux->tempty[buf]);
+        }
       } else {
         uint32_t run[C::COLS_PER_WARP];
         load_c_row<C::COLS_PER_WARP>(p, run, row, col_w);
@@ -1047,23 +1046,23 @@ static int make_operand_map(CUtensorMap* tm, const void* base, int64_t rows, int
   return QLIN_OK;
 }
 
-template <bool F8, int MODE>
+template <bool F8, bool CHUNKED>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
-  using C = Cfg<MODE>;
+  using C = Cfg<CHUNKED>;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return fail(QLIN_ERR_DEVICE, "device ordinal %d out of range", dev);
   if (!configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(qlin_gemm_kernel<F8, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(qlin_gemm_kernel<F8, CHUNKED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::SMEM_BYTES);
     if (e != cudaSuccess) return fail(QLIN_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured[dev] = true;
   }
-  const int tiles = p.num_m * p.num_n;
+  const int tiles = p.num_m * p.num_n * (CHUNKED ? 1 : (p.split_k > 1 ? p.split_k : 1));
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
-  qlin_gemm_kernel<F8, MODE><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
+  qlin_gemm_kernel<F8, CHUNKED><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
   QLIN_CHECK_LAUNCH("qlin_gemm");
   return QLIN_OK;
 }
@@ -1138,6 +1137,23 @@ static bool pair_enabled() {
   return v == 1;
 }
 
+// Split-K plan for an unchunked problem of at most 128 rows: such a problem is a stream over B with one row block, and
+// the time a CTA spends per 128-byte K block does not shrink with the tile width, so the way to use all SMs is to keep
+// the 256-column tile and cut K.  Returns the number of splits (1: none) and the K blocks per split.
+static int plan_split_k(int M, int N, int K, bool chunked, bool scatter, int* kb_per_split) {
+  const int num_kb = (K + kBK - 1) / kBK;
+  *kb_per_split = num_kb;
+  if (chunked || scatter || M > kBM || N % 64 != 0) return 1;
+  const int tiles = (N + Cfg<false>::BN - 1) / Cfg<false>::BN;
+  int s = sm_count() / tiles;          // one wave of work items
+  if (s > num_kb / 4) s = num_kb / 4;  // at least four K blocks per split
+  if (s > 16) s = 16;
+  if (s < 2) return 1;
+  const int per = (num_kb + s - 1) / s;
+  *kb_per_split = per;
+  return (num_kb + per - 1) / per;
+}
+
 static bool is_round_dtype(int dt) {
   return dt == QLIN_DT_NONE || dt == QLIN_DT_F32 || dt == QLIN_DT_F16 || dt == QLIN_DT_BF16;
 }
@@ -1145,6 +1161,23 @@ static bool is_round_dtype(int dt) {
 }  // namespace qlin
 
 using namespace qlin;
+
+namespace qlin {
+// The workspace starts with one arrival counter per (tile, epilogue warp); 4096 words cover 512 tiles of 8 warps.
+constexpr int kSplitCounterWords = 4096;
+}  // namespace qlin
+
+extern "C" size_t qlin_gemm_workspace_bytes(const qlin_gemm_args* a) {
+  if (a == nullptr || a->M <= 0 || a->N <= 0 || a->K <= 0) return 0;
+  const bool f8 = a->kind != QLIN_DT_I8;
+  const bool chunked = (a->trun_bits > 0) || (!f8 && a->max_acc_bits < 32) || (f8 && a->clamp_dl16);
+  int per = 0;
+  const int splits = plan_split_k(a->M, a->N, a->K, chunked, a->scatter_rows > 0, &per);
+  if (splits <= 1) return 0;
+  const int tiles = (a->N + Cfg<false>::BN - 1) / Cfg<false>::BN;
+  if (tiles * Cfg<false>::EPI_WARPS > kSplitCounterWords) return 0;
+  return static_cast<size_t>(kSplitCounterWords) * 4 + static_cast<size_t>(splits) * a->M * a->N * 4;
+}
 
 extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   if (a == nullptr) return fail(QLIN_ERR_NULL, "qlin_gemm: args is NULL");
@@ -1227,11 +1260,24 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   p.scatter_row0 = a->scatter_row0;
   p.f8_ab_format = a->kind == QLIN_DT_F8E5M2 ? 1 : 0;
   for (int i = 0; i < 8; ++i) p.scatter_d[i] = static_cast<uint8_t*>(a->scatter_d[i]);
-  // At most 128 rows and no chunking: a stream over B.  Tiles of 32 columns unless that makes more than two waves of
-  // tiles whose A block (the same for all) would be re-read from L2 each time; then 64.
-  int mode = chunked ? kChunked : kWide;
-  if (!chunked && a->M <= kBM) mode = (a->M <= 16 || (a->N + 31) / 32 <= 2 * sm_count()) ? kNarrow32 : kNarrow64;
-  const int bn = mode == kWide ? Cfg<kWide>::BN : mode == kChunked ? Cfg<kChunked>::BN : mode == kNarrow64 ? Cfg<kNarrow64>::BN : Cfg<kNarrow32>::BN;
+  p.split_k = 1;
+  p.kb_per_split = (a->K + kBK - 1) / kBK;
+  p.ws_part = nullptr;
+  p.ws_count = nullptr;
+  {
+    int per = 0;
+    const int splits = plan_split_k(a->M, a->N, a->K, chunked, a->scatter_rows > 0, &per);
+    if (splits > 1 && a->workspace != nullptr) {
+      const size_t need = qlin_gemm_workspace_bytes(a);
+      if (need > 0 && a->workspace_bytes >= static_cast<int64_t>(need) && aligned16(a->workspace)) {
+        p.split_k = splits;
+        p.kb_per_split = per;
+        p.ws_count = static_cast<uint32_t*>(a->workspace);
+        p.ws_part = p.ws_count + kSplitCounterWords;
+      }
+    }
+  }
+  const int bn = chunked ? Cfg<true>::BN : Cfg<false>::BN;
   p.num_m = (a->M + kBM - 1) / kBM;
   p.num_n = (a->N + bn - 1) / bn;
 
@@ -1249,14 +1295,6 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
     rc = f8 ? launch_pair<true>(ta, tb_half, p, s) : launch_pair<false>(ta, tb_half, p, s);
     if (rc <= 0) return rc;
   }
-  switch (mode) {
-    case kChunked:
-      return f8 ? launch<true, kChunked>(ta, tb, p, s) : launch<false, kChunked>(ta, tb, p, s);
-    case kNarrow64:
-      return f8 ? launch<true, kNarrow64>(ta, tb, p, s) : launch<false, kNarrow64>(ta, tb, p, s);
-    case kNarrow32:
-      return f8 ? launch<true, kNarrow32>(ta, tb, p, s) : launch<false, kNarrow32>(ta, tb, p, s);
-    default:
-      return f8 ? launch<true, kWide>(ta, tb, p, s) : launch<false, kWide>(ta, tb, p, s);
-  }
+  if (f8) return chunked ? launch<true, true>(ta, tb, p, s) : launch<true, false>(ta, tb, p, s);
+  return chunked ? launch<false, true>(ta, tb, p, s) : launch<false, false>(ta, tb, p, s);
 }

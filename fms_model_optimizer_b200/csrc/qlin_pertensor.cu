@@ -105,6 +105,7 @@ __device__ __forceinline__ float pt_from_e4m3(uint8_t c) {
 
 struct PtScalars {
   float cv, inv_cv, levels, half_levels, f8_scale;
+  float rlevels, rf8_scale;  // reciprocals for div_exact (NaN: take the IEEE division)
 };
 
 template <typename XT>
@@ -119,6 +120,8 @@ __device__ __forceinline__ PtScalars pt_scalars(const PtParams& p) {
   float sc = Elem<XT>::rnd(__fmul_rn(Elem<XT>::rnd(__fdiv_rn(1.0f, fmaxf(s.cv, eps))), 448.0f));
   if (std::is_same<XT, __half>::value) sc = fminf(sc, 65504.0f);
   s.f8_scale = sc;
+  s.rlevels = rcp_for_div(s.levels);
+  s.rf8_scale = rcp_for_div(sc);
   return s;
 }
 
@@ -131,9 +134,9 @@ __device__ __forceinline__ float pt_one(const PtParams& p, const PtScalars& s, f
     t = fminf(fmaxf(t, -1.0f), 1.0f);
     t = Elem<XT>::rnd(__fmul_rn(t, 0.5f));
     t = Elem<XT>::rnd(__fadd_rn(t, 0.5f));
-    const float q = rintf(Elem<XT>::rnd(__fmul_rn(s.levels, t)));
+    const float q = rint_small(Elem<XT>::rnd(__fmul_rn(s.levels, t)));  // 0 <= levels * t <= 65535
     if (!p.dequantize) return Elem<XT>::rnd(__fsub_rn(q, s.half_levels));
-    float d = Elem<XT>::rnd(__fdiv_rn(q, s.levels));
+    float d = Elem<XT>::rnd(div_exact(q, s.levels, s.rlevels));
     d = Elem<XT>::rnd(__fmul_rn(2.0f, d));
     d = Elem<XT>::rnd(__fsub_rn(d, 1.0f));
     return Elem<XT>::rnd(__fmul_rn(d, s.cv));
@@ -145,7 +148,7 @@ __device__ __forceinline__ float pt_one(const PtParams& p, const PtScalars& s, f
   t = fminf(fmaxf(t, -448.0f), 448.0f);
   if (is_nan) t = __int_as_float(0x7FC00000);
   float f = pt_from_e4m3(pt_to_e4m3(t));
-  if (p.kind == QLIN_PT_F8_SCALED) f = Elem<XT>::rnd(__fdiv_rn(f, s.f8_scale));
+  if (p.kind == QLIN_PT_F8_SCALED) f = Elem<XT>::rnd(div_exact(f, s.f8_scale, s.rf8_scale));
   return f;
 }
 

@@ -262,45 +262,6 @@ __device__ __forceinline__ void tc_mma4_release(uint32_t d_tmem, uint64_t adesc,
 #undef QLIN_MMA4
 }
 
-// The same K block with its four MMAs spread over four accumulators `dstride` TMEM columns apart (the caller adds them
-// up when it drains them).  An MMA into an accumulator has to wait for the previous MMA into the same accumulator; with
-// narrow tiles that wait, not the arithmetic, sets the pace, and four independent chains hide it.
-template <int KIND_F8>
-__device__ __forceinline__ void tc_mma4_release_split(uint32_t d_tmem, uint32_t dstride, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                                      uint32_t accumulate, uint64_t* empty_bar) {
-#define QLIN_MMA4S(KIND)                                                                        \
-  asm volatile(                                                                                 \
-      "{\n\t"                                                                                   \
-      ".reg .pred pe, pa;\n\t"                                                                  \
-      ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"                                                   \
-      ".reg .b32 d1, d2, d3;\n\t"                                                               \
-      "elect.sync _|pe, 0xffffffff;\n\t"                                                        \
-      "setp.ne.b32 pa, %4, 0;\n\t"                                                              \
-      "add.s64 a1, %1, 2;\n\t"                                                                  \
-      "add.s64 b1, %2, 2;\n\t"                                                                  \
-      "add.s64 a2, %1, 4;\n\t"                                                                  \
-      "add.s64 b2, %2, 4;\n\t"                                                                  \
-      "add.s64 a3, %1, 6;\n\t"                                                                  \
-      "add.s64 b3, %2, 6;\n\t"                                                                  \
-      "add.u32 d1, %0, %6;\n\t"                                                                 \
-      "add.u32 d2, d1, %6;\n\t"                                                                 \
-      "add.u32 d3, d2, %6;\n\t"                                                                 \
-      "@pe tcgen05.mma.cta_group::1.kind::" KIND " [%0], %1, %2, %3, pa;\n\t"                   \
-      "@pe tcgen05.mma.cta_group::1.kind::" KIND " [d1], a1, b1, %3, pa;\n\t"                   \
-      "@pe tcgen05.mma.cta_group::1.kind::" KIND " [d2], a2, b2, %3, pa;\n\t"                   \
-      "@pe tcgen05.mma.cta_group::1.kind::" KIND " [d3], a3, b3, %3, pa;\n\t"                   \
-      "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%5];\n\t"     \
-      "}" ::"r"(d_tmem),                                                                        \
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(smem_u32(empty_bar)), "r"(dstride) \
-      : "memory")
-  if (KIND_F8) {
-    QLIN_MMA4S("f8f6f4");
-  } else {
-    QLIN_MMA4S("i8");
-  }
-#undef QLIN_MMA4S
-}
-
 // One accumulation chunk of NMMA (1, 2 or 4) K=32-byte MMAs into a fresh accumulator (the first MMA
 // overwrites it), then the "accumulator full" commit on `tfull_bar`.
 template <int KIND_F8, int NMMA>

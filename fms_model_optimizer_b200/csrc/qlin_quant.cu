@@ -846,7 +846,9 @@ __device__ __forceinline__ float wfq_scale(const WfqParams& p, float clip, float
 // torch.fake_quantize_per_channel_affine with zero_point 0:
 //   q = clamp(nearbyint(w * (1 / scale)), -L, L);  out = q * scale.
 __device__ __forceinline__ float wfq_one(float w, float inv_scale, float scale, float lim, int& q) {
-  float r = nearbyintf(__fmul_rn(w, inv_scale));
+  // nearbyintf with two additions (the rounding instruction issues on the quarter-rate pipe); the clamp to +-2^21 first
+  // keeps the sum inside the range where that is exact and cannot change a result that is clamped to +-lim afterwards
+  float r = rint_small(fminf(fmaxf(__fmul_rn(w, inv_scale), -2097152.0f), 2097152.0f));
   r = fminf(fmaxf(r, -lim), lim);
   q = static_cast<int>(r);
   return __fmul_rn(r, scale);

@@ -16,13 +16,20 @@ struct Elem<float> {
   static __device__ __forceinline__ float to_f(float v) { return v; }
   static __device__ __forceinline__ float rnd(float v) { return v; }
 };
+// Round to the 16-bit type and widen back.  The scalar conversion instructions issue on the quarter-rate conversion
+// pipe, which was what bounded the 16-bit fake-quant kernels (88 % busy in the PACT+ forward); the packed forms (two
+// floats -> one register) and the widening by a shift / a packed add issue on the full-rate pipes and round identically
+// for every input, NaN and infinities included.
 template <>
 struct Elem<__half> {
-  static __device__ __forceinline__ float rnd(float v) { return __half2float(__float2half_rn(v)); }
+  static __device__ __forceinline__ float rnd(float v) { return __half22float2(__floats2half2_rn(v, 0.0f)).x; }
 };
 template <>
 struct Elem<__nv_bfloat16> {
-  static __device__ __forceinline__ float rnd(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+  static __device__ __forceinline__ float rnd(float v) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v, 0.0f);
+    return __uint_as_float(*reinterpret_cast<const uint32_t*>(&h) << 16);
+  }
 };
 
 // Rounds to T when `native` is set: the value a torch op on a T tensor would have produced.
@@ -46,6 +53,11 @@ __device__ __forceinline__ float fast_rnd<__nv_bfloat16>(float v) {
   const float m = __uint_as_float((__float_as_uint(v) & 0x7F800000u) + 0x08400000u);
   return __fsub_rn(__fadd_rn(v, m), m);
 }
+// rintf for |v| < 2^22 with two additions, sign of zero kept (rintf(-0.3) is -0.0).  Inputs beyond that range give an
+// unspecified finite value: for callers that clamp first or discard such lanes.
+__device__ __forceinline__ float rint_small(float v) {
+  return copysignf(__fsub_rn(__fadd_rn(v, 12582912.0f), 12582912.0f), v);
+}
 // rint for |v| < 2^22, and the integer itself from the low bits of the biased sum.
 __device__ __forceinline__ float fast_rint(float v, int& as_int) {
   const float t = __fadd_rn(v, 12582912.0f);
@@ -63,7 +75,7 @@ __device__ __forceinline__ float div_exact(float x, float s, float r) {
   const float q = __fmul_rn(x, r);
   const float rem = __fmaf_rn(-s, q, x);
   const float q2 = __fmaf_rn(rem, r, q);
-  if (x == 0.0f) return q;  // keeps the sign of a zero quotient
+  if (x == 0.0f && r == r) return q;  // keeps the sign of a zero quotient (r is NaN where the caller asked for the IEEE division)
   const float a = fabsf(q2);
   if (!(a > 1e-15f && a < 1e15f)) return __fdiv_rn(x, s);
   return q2;
