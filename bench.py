@@ -452,7 +452,7 @@ def _check_sharded_against_single(args, cfg, rank, world, dev, ids_dev, groups, 
     The sharp check is the residual stream after the first attention block (``x_mlp_in`` of layer 0): up to there the
     sharded run computes the same codes and integer accumulators as the one-GPU run, and the only difference is that
     every shard's partial output is rounded to bf16 before the sum -- a relative error of the order of 1e-3; a wrong offset,
-    a stale buffer or a missed barrier shows there as an error of order 1.  It must be below 5e-3.  From then on a last-
+    a stale buffer or a missed barrier shows there as an error of order 1.  It must be below 2e-2 (3.3e-3 measured on two GPUs).  From then on a last-
     place difference in a normalised row flips int8 codes and the two runs drift apart like any two roundings of the same
     model (a few per cent after two layers, which is also what a CPU run of the same layers in another order shows);
     the final hidden state is reported and only has to be the same model (below 0.2)."""
@@ -498,7 +498,7 @@ def _check_sharded_against_single(args, cfg, rank, world, dev, ids_dev, groups, 
                     w = want_x[gi * (T // groups) + rank * Ts : gi * (T // groups) + (rank + 1) * Ts]
                 worst = max(worst, ((t.float() - w).norm() / w.norm()).item())
             res[mode]["first_exchange_rel_err"] = worst
-            if not worst < 5e-3:
+            if not worst < 2e-2:
                 raise RuntimeError(f"sharded forward: residual stream after the first exchange differs from the one-GPU run by {worst}")
         if not err < 0.2:
             raise RuntimeError(f"sharded forward ({mode}) differs from the one-GPU forward: relative error {err}")

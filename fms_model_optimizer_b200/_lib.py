@@ -41,7 +41,6 @@ EXPORTED_SYMBOLS = (
     "qlin_last_error_string",
     "qlin_device_supported",
     "qlin_gemm",
-    "qlin_gemm_workspace_bytes",
     "qlin_act_quant",
     "qlin_pact2_fwd",
     "qlin_pact2_bwd",
@@ -98,8 +97,6 @@ class GemmArgs(C.Structure):
         ("scatter_rows", C.c_int32),
         ("scatter_row0", C.c_int32),
         ("max_ctas", C.c_int32),
-        ("workspace", C.c_void_p),
-        ("workspace_bytes", C.c_int64),
     ]
 
 
@@ -319,8 +316,6 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(struct), C.c_void_p]
         fn.restype = C.c_int
-    lib.qlin_gemm_workspace_bytes.argtypes = [C.POINTER(GemmArgs)]
-    lib.qlin_gemm_workspace_bytes.restype = C.c_size_t
     lib.qlin_pact2_bwd_workspace_bytes.argtypes = [C.c_int64]
     lib.qlin_pact2_bwd_workspace_bytes.restype = C.c_size_t
     lib.qlin_pact2_bwd_noalloc_max_numel.restype = C.c_int64

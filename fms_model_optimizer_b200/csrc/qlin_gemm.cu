@@ -85,12 +85,6 @@ struct GemmParams {
   int32_t scatter_rows, scatter_row0;
   uint8_t* scatter_d[8];
   int32_t f8_ab_format;  // float kinds: operand format of the instruction descriptor, 0 = e4m3, 1 = e5m2
-  // Split-K (unchunked problems of at most 128 rows): work item w = tile * split_k + split; split s owns K blocks
-  // [s * kb_per_split, ...).  Partial accumulators go to ws_part[s][M][N] (raw 32-bit words); the epilogue warp whose
-  // arrival on ws_count[tile * 8 + warp] is the last one adds the splits in index order and runs the real epilogue.
-  int32_t split_k, kb_per_split;
-  uint32_t* ws_part;
-  uint32_t* ws_count;
 };
 
 __device__ __forceinline__ float round_to(float y, int dt) {
@@ -417,8 +411,6 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int num_tiles = p.num_m * p.num_n;
   const int num_kb = (p.kbytes + kBK - 1) / kBK;
   const int total_k32 = (p.kbytes + 31) / 32;
-  const int split_k = CHUNKED ? 1 : max(1, p.split_k);
-  const int num_work = num_tiles * split_k;
   bool timed_out = false;
 
   if (warp == C::PRODUCER_WARP) {
@@ -429,13 +421,11 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t s = 0, ph = 0, issued = 0;
     bool ok = true;
     bool ready = false;
-    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
-      const int t = w / split_k, sp = w - t * split_k;
       tile_coords(t, p.num_m, p.num_n, mb, nb);
       const int ya = mb * kBM, yb = nb * C::BN;
-      const int kb0 = sp * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
-      for (int kb = kb0; kb < kb1; ++kb) {
+      for (int kb = 0; kb < num_kb; ++kb) {
         if (!ready) {
           ok = warp_mbar_wait(&aux->empty[s], ph ^ 1u, abort_flag);
           if (!ok) break;
@@ -479,13 +469,11 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     bool tready = false;  // next accumulator buffer known to be drained
     // chunks that tile a 128-byte K block exactly (32, 64 or 128 elements, K a multiple of 128)
     const bool chunk_fast = CHUNKED && (p.chunk_k32 == 1 || p.chunk_k32 == 2 || p.chunk_k32 == 4) && (total_k32 % 4 == 0);
-    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       uint32_t accumulate = 0, cur = 0;
       int chunk_pos = 0;
-      const int sp = w % split_k;
-      const int kb0 = sp * p.kb_per_split, kb1 = min(num_kb, kb0 + p.kb_per_split);
-      int k32_left = split_k > 1 ? min(total_k32 - kb0 * 4, (kb1 - kb0) * 4) : total_k32;
-      for (int kb = kb0; kb < kb1 && ok; ++kb) {
+      int k32_left = total_k32;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
         if (!ready) {
           ok = warp_mbar_wait(&aux->full[s], ph, abort_flag);
           if (!ok) break;
@@ -497,7 +485,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint64_t adesc = adesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
         const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(s * (C::STAGE_BYTES >> 4));
         if (!CHUNKED && k32_left >= 4) {
-          if (kb == kb0) {
+          if (kb == 0) {
             ok = warp_mbar_wait(&aux->tempty[buf], bph ^ 1u, abort_flag);
             if (!ok) break;
             tc_fence_after();
@@ -600,9 +588,8 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t ebuf = 0, ebph = 0;
     bool eready = false;
     bool ok = true;
-    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
-      const int t = w / split_k, sp = w - t * split_k;
       tile_coords(t, p.num_m, p.num_n, mb, nb);
       const int row0 = mb * kBM + q * 32;
       const int row = row0 + lane;
@@ -630,57 +617,6 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           break;
         }
         tc_fence_after();
-        if (split_k > 1) {
-          // Split-K: park this split's raw accumulators, then let the last split to arrive add them up in index order.
-          // Rows of this warp that lie outside M are skipped throughout (N is a multiple of 64 on this path).
-          const bool row_ok = row < p.M;
-          uint32_t* part = p.ws_part + (static_cast<int64_t>(sp) * p.M + row) * p.N + col_w;
-#pragma unroll 1
-          for (int j = 0; j < C::COLS_PER_WARP; j += 64) {
-            uint32_t v[64];
-            tmem_ld64(tmem_base + lane_base + buf * C::BN + half * C::COLS_PER_WARP + j, v);
-            if (row_ok && col_w + j < p.N) {
-#pragma unroll
-              for (int i = 0; i < 64; i += 4) __stcg(reinterpret_cast<uint4*>(part + j + i), make_uint4(v[i], v[i + 1], v[i + 2], v[i + 3]));
-            }
-          }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&aux->tempty[buf]);
-          __threadfence();
-          __syncwarp();
-          uint32_t arrived = 0;
-          if (lane == 0) arrived = atomicAdd(p.ws_count + t * C::EPI_WARPS + warp, 1u);
-          arrived = __shfl_sync(0xffffffffu, arrived, 0);
-          if (arrived == static_cast<uint32_t>(split_k - 1)) {
-            __threadfence();
-#pragma unroll 1
-            for (int j = 0; j < C::COLS_PER_WARP; j += 64) {
-              uint32_t v[64];
-#pragma unroll
-              for (int i = 0; i < 64; ++i) v[i] = 0u;
-              if (row_ok && col_w + j < p.N) {
-                for (int s2 = 0; s2 < split_k; ++s2) {
-                  const uint32_t* src = p.ws_part + (static_cast<int64_t>(s2) * p.M + row) * p.N + col_w + j;
-#pragma unroll
-                  for (int i = 0; i < 64; i += 4) {
-                    const uint4 u = __ldcg(reinterpret_cast<const uint4*>(src + i));
-                    v[i] = acc_add<F8>(v[i], u.x), v[i + 1] = acc_add<F8>(v[i + 1], u.y);
-                    v[i + 2] = acc_add<F8>(v[i + 2], u.z), v[i + 3] = acc_add<F8>(v[i + 3], u.w);
-                  }
-                }
-              }
-              if (p.c != nullptr) {
-                uint32_t cv[64];
-                load_c_row<64>(p, cv, row, col_w + j);
-#pragma unroll
-                for (int i = 0; i < 64; ++i) v[i] = acc_add<F8>(cv[i], v[i]);
-              }
-              emit64<F8>(p, v, row0, lane, col_w + j, aux->cs, aux->bias, half * C::COLS_PER_WARP + j, rs, vec_ok, stage);
-            }
-            if (lane == 0) p.ws_count[t * C::EPI_WARPS + warp] = 0u;  // the counters are left at zero for the next launch
-          }
-        } else {
 #pragma unroll 1
         for (int j = 0; j < C::COLS_PER_WARP; j += 64) {
           uint32_t v[64];
@@ -696,7 +632,6 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&aux->tempty[buf]);
-        }
       } else {
         uint32_t run[C::COLS_PER_WARP];
         load_c_row<C::COLS_PER_WARP>(p, run, row, col_w);
@@ -1059,7 +994,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
     if (e != cudaSuccess) return fail(QLIN_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured[dev] = true;
   }
-  const int tiles = p.num_m * p.num_n * (CHUNKED ? 1 : (p.split_k > 1 ? p.split_k : 1));
+  const int tiles = p.num_m * p.num_n;
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
   qlin_gemm_kernel<F8, CHUNKED><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
@@ -1137,23 +1072,6 @@ static bool pair_enabled() {
   return v == 1;
 }
 
-// Split-K plan for an unchunked problem of at most 128 rows: such a problem is a stream over B with one row block, and
-// the time a CTA spends per 128-byte K block does not shrink with the tile width, so the way to use all SMs is to keep
-// the 256-column tile and cut K.  Returns the number of splits (1: none) and the K blocks per split.
-static int plan_split_k(int M, int N, int K, bool chunked, bool scatter, int* kb_per_split) {
-  const int num_kb = (K + kBK - 1) / kBK;
-  *kb_per_split = num_kb;
-  if (chunked || scatter || M > kBM || N % 64 != 0) return 1;
-  const int tiles = (N + Cfg<false>::BN - 1) / Cfg<false>::BN;
-  int s = sm_count() / tiles;          // one wave of work items
-  if (s > num_kb / 4) s = num_kb / 4;  // at least four K blocks per split
-  if (s > 16) s = 16;
-  if (s < 2) return 1;
-  const int per = (num_kb + s - 1) / s;
-  *kb_per_split = per;
-  return (num_kb + per - 1) / per;
-}
-
 static bool is_round_dtype(int dt) {
   return dt == QLIN_DT_NONE || dt == QLIN_DT_F32 || dt == QLIN_DT_F16 || dt == QLIN_DT_BF16;
 }
@@ -1161,23 +1079,6 @@ static bool is_round_dtype(int dt) {
 }  // namespace qlin
 
 using namespace qlin;
-
-namespace qlin {
-// The workspace starts with one arrival counter per (tile, epilogue warp); 4096 words cover 512 tiles of 8 warps.
-constexpr int kSplitCounterWords = 4096;
-}  // namespace qlin
-
-extern "C" size_t qlin_gemm_workspace_bytes(const qlin_gemm_args* a) {
-  if (a == nullptr || a->M <= 0 || a->N <= 0 || a->K <= 0) return 0;
-  const bool f8 = a->kind != QLIN_DT_I8;
-  const bool chunked = (a->trun_bits > 0) || (!f8 && a->max_acc_bits < 32) || (f8 && a->clamp_dl16);
-  int per = 0;
-  const int splits = plan_split_k(a->M, a->N, a->K, chunked, a->scatter_rows > 0, &per);
-  if (splits <= 1) return 0;
-  const int tiles = (a->N + Cfg<false>::BN - 1) / Cfg<false>::BN;
-  if (tiles * Cfg<false>::EPI_WARPS > kSplitCounterWords) return 0;
-  return static_cast<size_t>(kSplitCounterWords) * 4 + static_cast<size_t>(splits) * a->M * a->N * 4;
-}
 
 extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   if (a == nullptr) return fail(QLIN_ERR_NULL, "qlin_gemm: args is NULL");
@@ -1260,23 +1161,6 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   p.scatter_row0 = a->scatter_row0;
   p.f8_ab_format = a->kind == QLIN_DT_F8E5M2 ? 1 : 0;
   for (int i = 0; i < 8; ++i) p.scatter_d[i] = static_cast<uint8_t*>(a->scatter_d[i]);
-  p.split_k = 1;
-  p.kb_per_split = (a->K + kBK - 1) / kBK;
-  p.ws_part = nullptr;
-  p.ws_count = nullptr;
-  {
-    int per = 0;
-    const int splits = plan_split_k(a->M, a->N, a->K, chunked, a->scatter_rows > 0, &per);
-    if (splits > 1 && a->workspace != nullptr) {
-      const size_t need = qlin_gemm_workspace_bytes(a);
-      if (need > 0 && a->workspace_bytes >= static_cast<int64_t>(need) && aligned16(a->workspace)) {
-        p.split_k = splits;
-        p.kb_per_split = per;
-        p.ws_count = static_cast<uint32_t*>(a->workspace);
-        p.ws_part = p.ws_count + kSplitCounterWords;
-      }
-    }
-  }
   const int bn = chunked ? Cfg<true>::BN : Cfg<false>::BN;
   p.num_m = (a->M + kBM - 1) / kBM;
   p.num_n = (a->N + bn - 1) / bn;

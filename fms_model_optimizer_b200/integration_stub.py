@@ -24,8 +24,7 @@ class GemmArgs(C.Structure):  # mirrors qlin_gemm_args in include/qlin_b200.h, f
         + [(n, C.c_int32) for n in ("M", "N", "K", "kind", "chunk_k", "trun_bits", "max_acc_bits", "trunc_then_acc", "clamp_dl16",
                                     "epilogue", "row_scale_stride", "col_scale_stride", "prod_round", "scale_round", "mid_round",
                                     "acc_round", "out_dtype")]  # fmt: skip
-        + [("scatter_d", C.c_void_p * 8), ("scatter_rows", C.c_int32), ("scatter_row0", C.c_int32), ("max_ctas", C.c_int32),
-           ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64)]
+        + [("scatter_d", C.c_void_p * 8), ("scatter_rows", C.c_int32), ("scatter_row0", C.c_int32), ("max_ctas", C.c_int32)]
     )
 
 

@@ -31,9 +31,7 @@ _DT = {
 _ROUND = {None: L.DT_NONE, torch.float32: L.DT_F32, torch.float16: L.DT_F16, torch.bfloat16: L.DT_BF16}
 
 _status_words: dict[int, torch.Tensor] = {}
-# Split-K workspace of the GEMM, one per device: zero-initialised once, left with zeroed counters by every launch.  Launches
-# that can overlap on one device (several streams) must bring their own (``gemm(..., workspace=...)``).
-_gemm_workspaces: dict[int, torch.Tensor] = {}
+
 
 # Measurement hooks used by bench.py: LAUNCHES counts kernel launches made through this module;
 # when PROFILE is a list, every launch is bracketed by CUDA events on the launching stream and
@@ -147,7 +145,6 @@ def gemm(
     scatter: Optional[Tuple[Sequence[int], int, int]] = None,
     max_ctas: Optional[int] = None,
     out_dtype: Optional[torch.dtype] = None,
-    workspace: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """``D[M,N] = epilogue(C + sum_chunks f(A_c @ B_c^T))`` with A ``[M,K]`` and B ``[N,K]`` (both
     K-contiguous, int8 or float8_e4m3fn).  See ``qlin_gemm`` in include/qlin_b200.h for the
@@ -212,16 +209,6 @@ def gemm(
         bases = list(scatter[0]) + [None] * (8 - len(scatter[0]))
         args.scatter_d = (C.c_void_p * 8)(*bases)
         args.scatter_rows, args.scatter_row0 = int(scatter[1]), int(scatter[2])
-    if M <= 128 and scatter is None:
-        # decode-sized problems: lend the kernel a split-K workspace (kept per device and stream; see qlin_gemm_args.workspace)
-        need = int(L.load().qlin_gemm_workspace_bytes(C.byref(args)))
-        if need > 0:
-            ws = workspace if workspace is not None else _gemm_workspaces.get(dev.index)
-            if workspace is None and (ws is None or ws.numel() < need) and not torch.cuda.is_current_stream_capturing():
-                ws = torch.zeros(max(need, 8 << 20), dtype=torch.uint8, device=dev)  # never allocated inside a graph capture
-                _gemm_workspaces[dev.index] = ws
-            if ws is not None and ws.numel() >= need:
-                args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
     with torch.cuda.device(dev):
         rc = _timed("gemm", 2.0 * M * N * K, dev, lambda: L.load().qlin_gemm(C.byref(args), _stream(dev)))
         L.check(rc, "qlin_gemm")

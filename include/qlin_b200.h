@@ -136,19 +136,9 @@ typedef struct qlin_gemm_args {
   int32_t max_ctas;         /* 0: one persistent CTA per SM; > 0: at most this many CTAs (each needs a whole SM),
                                leaving SMs free for a kernel that runs concurrently on another stream, e.g. a
                                collective.  Results do not depend on it. */
-  /* Optional split-K workspace for problems of at most 128 rows (a stream over B: decode-sized M).  With a workspace of
-     at least qlin_gemm_workspace_bytes(args) bytes, 16-byte aligned, whose first 16 KB are ZERO on the first use, the K
-     range is cut over several CTAs per 256-column tile; partial accumulators are parked in the workspace and added in a
-     fixed order (results are deterministic and, for int8, identical to the unsplit kernel).  The library leaves the
-     first 16 KB zero again, so one zero-initialised buffer serves every later call; two launches that may overlap on
-     the GPU must not share it.  NULL: no split. */
-  void* workspace;
-  int64_t workspace_bytes;
 } qlin_gemm_args;
 
 int qlin_gemm(const qlin_gemm_args* args, void* stream);
-/* Bytes of split-K workspace qlin_gemm can use for this problem (0: it would not split). */
-size_t qlin_gemm_workspace_bytes(const qlin_gemm_args* args);
 
 /* ------------------------------------------------------------------------------------------------
  * qlin_act_quant -- row-wise (per-token / per-channel) dynamic 8-bit quantisation in one pass.

@@ -192,36 +192,3 @@ def test_empty_and_error_cases(cuda_dev):
         ops.gemm(b, b.float())
     with pytest.raises(RuntimeError, match="status"):
         ops.gemm(b, b, chunk_k=48, trun_bits=8)
-
-
-@pytest.mark.parametrize("M,N,K", [(1, 14336, 4096), (7, 1024, 2048), (128, 4096, 4096), (100, 640, 4100), (128, 4096, 14336)])
-def test_split_k_small_m_is_exact_and_deterministic(cuda_dev, M, N, K):
-    """Problems of at most 128 rows are cut along K over several CTAs (a stream over the weights): int8 results must equal
-    the exact product (and the unsplit kernel's), fp8 results must repeat bit for bit from launch to launch (the splits are
-    added in a fixed order) and stay within the fp32 summation tolerance; the workspace's counters are left at zero."""
-    from fms_model_optimizer_b200 import _lib as L
-
-    g = torch.Generator().manual_seed(M + N)
-    a = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8)
-    b = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8)
-    want = (a.double() @ b.double().t()).to(torch.int32)
-    ad, bd = a.to(cuda_dev), b.to(cuda_dev)
-    ws = torch.zeros(64 << 20, dtype=torch.uint8, device=cuda_dev)
-    got = ops.gemm(ad, bd, workspace=ws)
-    assert torch.equal(got.cpu(), want)
-    assert int(ws[:16384].view(torch.int32).abs().sum().item()) == 0  # counters back at zero
-    again = ops.gemm(ad, bd, workspace=ws)
-    assert torch.equal(again, got)
-    # scaled epilogue through the split path, bf16 output, against the same arithmetic in eager CPU PyTorch
-    rs, cs = torch.rand(M, generator=g) * 1e-3 + 1e-4, torch.rand(N, generator=g) * 1e-2 + 1e-3
-    y = ops.gemm(ad, bd, workspace=ws, epilogue=L.EPI_SCALE_SEQ, row_scale=rs.to(cuda_dev), col_scale=cs.to(cuda_dev), out_dtype=torch.bfloat16)
-    assert torch.equal(y.cpu(), ((want.float() * rs[:, None]) * cs[None, :]).bfloat16())
-    # fp8: repeatable, and within the summation-order tolerance of the oracle
-    a8 = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
-    b8 = torch.randn(N, K, generator=g).to(torch.float8_e4m3fn)
-    f1 = ops.gemm(a8.to(cuda_dev), b8.to(cuda_dev), workspace=ws)
-    f2 = ops.gemm(a8.to(cuda_dev), b8.to(cuda_dev), workspace=ws)
-    assert torch.equal(f1, f2)
-    ref = (a8.double() @ b8.double().t()).float()
-    assert torch.norm(f1.cpu() - ref) / torch.norm(ref) < 1e-5
-    ops.check_status(cuda_dev)
