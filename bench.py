@@ -215,13 +215,14 @@ def run_reference(args, rank):
 class KernelTimer:
     """Times one call as a CUDA graph replay (the way a serving loop issues it: for small shapes the launches of a
     Linear take less GPU time than the host needs to queue them), with a 256 MB write between replays so that nothing
-    is served from L2."""
+    is served from L2.  Cases that walk through several weight sets larger than L2 in one call need no such write
+    (flush=False): every set has been evicted, clean, by the time its turn comes again."""
 
     def __init__(self, dev):
         self.dev = dev
         self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
-    def __call__(self, fn, steps=5, warmup=3, graph=True):
+    def __call__(self, fn, steps=5, warmup=3, graph=True, flush=True):
         with torch.no_grad():
             for _ in range(max(warmup, 3)):
                 fn()
@@ -236,7 +237,8 @@ class KernelTimer:
                 torch.cuda.synchronize()
             tot = 0.0
             for _ in range(steps):
-                self.flush.zero_()
+                if flush:
+                    self.flush.zero_()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
                 run()
@@ -281,7 +283,7 @@ def kernel_cases(dev, which, only=""):
             lambda a=a, b=b, out=out: ops.gemm(a, b, out=out, chunk_k=64, trun_bits=8))  # fmt: skip
     if which in ("c3", "all"):
         torch.manual_seed(2)
-        for M, K, N in ((1, 4096, 14336), (128, 4096, 4096), (8192, 4096, 14336), (8192, 14336, 4096)):
+        for M, K, N in ((1, 4096, 14336), (1, 14336, 4096), (128, 4096, 4096), (128, 4096, 14336), (8192, 4096, 14336), (8192, 14336, 4096)):
             if not wanted(f"c3 FP8 e4m3 Linear {M}x{K}x{N}"):
                 continue
             x = torch.randn(M, K, device=dev).bfloat16()
@@ -292,10 +294,24 @@ def kernel_cases(dev, which, only=""):
             with torch.no_grad():
                 q(x)
             small = M <= 128
-            work = (N * K + M * K * 3 + M * N * 2) if small else 2.0 * M * N * K
-            add(f"c3 FP8 e4m3 Linear {M}x{K}x{N} (quantise + GEMM + dequantise)", "fp8", "hbm" if small else "tensor", work,
-                (lambda q=q, x=x: q(x)))  # fmt: skip
-            cases[-1]["ops"] = 2.0 * M * N * K
+            if small:
+                # decode-sized: the weights are the traffic.  One call walks through R independent Linears (R weight sets,
+                # together several times L2), so each launch streams its weights from HBM and the fixed cost of timing one
+                # tiny launch alone is spread over R of them; the figures are per Linear.
+                R = max(8, -(-3 * 126_000_000 // (N * K)))
+                qs = [q]
+                for _ in range(R - 1):
+                    with torch.no_grad():
+                        lin.weight.copy_(torch.randn(N, K, device=dev))
+                    qs.append(LinearFPxAcc.from_nn(lin, trun_bits=0, chunk_size=64, dynamic_fp8="per_token"))
+                    with torch.no_grad():
+                        qs[-1](x)
+                del lin
+                add(f"c3 FP8 e4m3 Linear {M}x{K}x{N} (quantise + GEMM + dequantise), {R} weight sets in rotation", "fp8", "hbm",
+                    N * K + M * K * 3 + M * N * 2, (lambda qs=qs, x=x: [qq(x) for qq in qs]))  # fmt: skip
+                cases[-1].update(ops=2.0 * M * N * K, calls=R, flush=False)
+                continue
+            add(f"c3 FP8 e4m3 Linear {M}x{K}x{N} (quantise + GEMM + dequantise)", "fp8", "tensor", 2.0 * M * N * K, (lambda q=q, x=x: q(x)))
     if which == "all":
         for M, K, N in ((16384, 4096, 4096), (8192, 8192, 8192)):
             for kind, dt in (("int8", torch.int8), ("fp8", torch.float8_e4m3fn)):
@@ -368,8 +384,10 @@ def measure_kernels(dev, which="all", steps=5, warmup=3, with_comparators=True, 
         if only and only not in c["name"]:
             c["fn"] = None
             continue
-        ms = timer(c["fn"], steps, warmup, c["graph"])
+        ms = timer(c["fn"], steps, warmup, c["graph"], c.get("flush", True)) / c.get("calls", 1)
         e = {"name": c["name"], "dtype": c["dtype"], "bound": c["bound"], "us": ms * 1e3}
+        if not c.get("flush", True):
+            e["l2"] = f"{c['calls']} weight sets (several times L2) used in rotation inside one CUDA graph; figures per Linear"
         if c["bound"] == "tensor":
             tops = c["work"] / (ms * 1e-3) / 1e12
             e.update(tops=tops, frac_of_2x_bf16_measured=tops / (2 * pk["bf16"]), frac_of_datasheet_8bit=tops / DATASHEET_8BIT_TOPS)
@@ -411,7 +429,7 @@ def run_kernel_workload(args, dev):
             "unit": "TOPS" if tensor else "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": e["us"] * 1e-3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": e["dtype"],
             "data": "synthetic",
-            "config": {"workload": e["name"], "l2": "256 MB flush between timed launches", "launch": "CUDA graph replay of the call"},
+            "config": {"workload": e["name"], "l2": e.get("l2", "256 MB flush between timed launches"), "launch": "CUDA graph replay of the call"},
             "roofline": {"bound": e["bound"], "achieved": val, "peak": peak, "unit": "TFLOP/s" if tensor else "GB/s", "frac": val / peak,
                          "traffic": C5LIN_DRAM_BYTES if args.workload == "c5lin" else None,
                          "peak_source": (f"2 x bf16_tflops (burst) of MEASURED_PEAKS.json ({pk['src']}); datasheet dense 8-bit "

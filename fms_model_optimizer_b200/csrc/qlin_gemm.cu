@@ -85,6 +85,7 @@ struct GemmParams {
   int32_t scatter_rows, scatter_row0;
   uint8_t* scatter_d[8];
   int32_t f8_ab_format;  // float kinds: operand format of the instruction descriptor, 0 = e4m3, 1 = e5m2
+  int32_t sk_mt, sk_split, sk_stages;  // few-row kernel: padded row count, K splits (= cluster size), pipeline stages
 };
 
 __device__ __forceinline__ float round_to(float y, int dt) {
@@ -947,6 +948,244 @@ qlin_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Few-row kernel (M <= 128, unchunked): the decode-time shapes, where the weight matrix is read once
+// and everything else is small.  The operands swap roles: 128 rows of the WEIGHT are the MMA's M
+// dimension and the M activation rows, padded to a multiple of 32, are its N dimension, so a K block
+// costs 128 x MT x 128 multiply-adds of tensor time instead of the 128 x 256 x 128 a weight-as-B tile
+// costs whatever M is, and the kernel runs at the rate the weights stream in.  One CTA per
+// (128 output channels, K split); the CTAs of one channel block form a cluster, park their partial
+// accumulators in their own shared memory, and after a cluster barrier CTA r sums rows r, r+S, ...
+// over the splits in split order through distributed shared memory (a fixed order: the result does not
+// depend on scheduling), dequantises and stores them.  Accumulator lane = output channel, so the
+// stores of one row are contiguous across the warp.
+//   warps 0-3  epilogue (TMEM lanes 32 w ..), warp 4 TMA producer, warp 5 MMA issuer / TMEM owner
+// ------------------------------------------------------------------------------------------------
+constexpr int kSkEpiWarps = 8;  // warp w reads TMEM lanes 32 (w % 4) .., half w / 4 of the 32-row groups
+constexpr int kSkProducerWarp = kSkEpiWarps;
+constexpr int kSkMmaWarp = kSkEpiWarps + 1;
+constexpr int kSkThreads = (kSkEpiWarps + 2) * 32;
+constexpr int kSkWBytes = kBM * kBK;  // 128 weight rows x 128 bytes of K per stage
+constexpr int kSkTmemCols = 128;
+
+template <bool F8>
+__device__ __forceinline__ void skinny_emit(const GemmParams& p, uint32_t v, int m, int n, float rs, float cs, float bias,
+                                            bool prod, bool has_bias) {
+  if (p.c != nullptr) v = acc_add<F8>(reinterpret_cast<const uint32_t*>(p.c)[static_cast<int64_t>(m) * p.ldc + n], v);
+  if (p.epilogue == QLIN_EPI_RAW) {
+    reinterpret_cast<uint32_t*>(p.d)[static_cast<int64_t>(m) * p.ldd + n] = v;
+    return;
+  }
+  const float y = dequant_one<F8>(p, v, rs, cs, bias, prod, has_bias);
+  if (p.out_dtype == QLIN_DT_F32) {
+    reinterpret_cast<float*>(p.d)[static_cast<int64_t>(m) * p.ldd + n] = y;
+  } else {
+    reinterpret_cast<uint16_t*>(p.d)[static_cast<int64_t>(m) * p.ldd + n] = static_cast<uint16_t>(pack16(p, y, 0.0f) & 0xFFFFu);
+  }
+}
+
+// Sum of one accumulator element over the NS splits, in split order; the loads are issued together.
+template <bool F8, int NS>
+__device__ __forceinline__ uint32_t skinny_sum_splits(const uint32_t* src) {
+  uint32_t t[NS];
+#pragma unroll
+  for (int q = 0; q < NS; ++q) t[q] = ld_cluster_u32(map_to_cta(src, static_cast<uint32_t>(q)));
+  uint32_t acc = t[0];
+#pragma unroll
+  for (int q = 1; q < NS; ++q) acc = acc_add<F8>(acc, t[q]);
+  return acc;
+}
+
+template <bool F8>
+__global__ void __launch_bounds__(kSkThreads, 1)
+qlin_gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                        const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int MT = p.sk_mt, S = p.sk_split, STG = p.sk_stages;
+  const int stage_bytes = kSkWBytes + MT * kBK;
+  Aux* aux = reinterpret_cast<Aux*>(smem + STG * stage_bytes);
+  volatile int* abort_flag = &aux->abort_flag;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tile = blockIdx.x / S;
+  const int sp = S > 1 ? static_cast<int>(cluster_cta_rank()) : 0;
+  const int num_kb = (p.kbytes + kBK - 1) / kBK;
+  const int kb0 = static_cast<int>(static_cast<int64_t>(sp) * num_kb / S);
+  const int kb1 = static_cast<int>(static_cast<int64_t>(sp + 1) * num_kb / S);
+  const bool scaled = p.epilogue != QLIN_EPI_RAW;
+  const bool prod = p.epilogue == QLIN_EPI_SCALE_PROD;
+  const bool has_bias = p.bias != nullptr;
+
+  // Every thread of every CTA of the cluster reaches the two cluster barriers below, whatever happens before them.
+  const bool bad = (smem_u32(smem) & 1023u) != 0;
+  if (bad && threadIdx.x == 0 && p.status != nullptr) atomicExch(p.status, static_cast<int32_t>(QLIN_ERR_BAD_ALIGN));
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STG; ++s) {
+      mbar_init(&aux->full[s], 1);
+      mbar_init(&aux->empty[s], 1);
+    }
+    mbar_init(&aux->tfull[0], 1);
+    mbar_init(&aux->drain, 1);
+    aux->abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async();
+  }
+  if (warp == kSkMmaWarp) {
+    tmem_alloc(&aux->tmem_base, kSkTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == kSkProducerWarp && lane == 0) {
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  // the row scales of the (at most 128) activation rows, read by every epilogue thread
+  float* s_rs = aux->cs;
+  if (threadIdx.x < MT) s_rs[threadIdx.x] = (scaled && p.rs != nullptr && static_cast<int>(threadIdx.x) < p.M) ? p.rs[static_cast<int64_t>(threadIdx.x) * p.rs_stride] : 1.0f;
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = aux->tmem_base;
+  bool timed_out = false;
+  uint32_t* part = reinterpret_cast<uint32_t*>(smem);  // [MT][128] partial accumulators, over the drained pipeline stages
+
+  if (bad) {
+    // nothing: fall through to the barriers
+  } else if (warp == kSkProducerWarp) {
+    // ------------------------------------------------------------------ TMA producer
+    uint32_t s = 0, ph = 0, issued = 0;
+    bool ok = true;
+    for (int kb = kb0; kb < kb1; ++kb) {
+      ok = warp_mbar_wait(&aux->empty[s], ph ^ 1u, abort_flag);
+      if (!ok) break;
+      uint8_t* sa = smem + s * stage_bytes;
+      tma_issue_stage(&aux->full[s], static_cast<uint32_t>(stage_bytes), sa, &tmap_w, tile * kBM, sa + kSkWBytes, &tmap_x, 0, kb * kBK);
+      ++issued;
+      if (++s == static_cast<uint32_t>(STG)) {
+        s = 0;
+        ph ^= 1u;
+      }
+    }
+    if (!ok) {
+      if (lane == 0) {
+        timed_out = !*abort_flag;
+        *abort_flag = 1;
+      }
+      for (uint32_t st = 0; st < static_cast<uint32_t>(STG); ++st) {
+        if (issued <= st) continue;
+        const uint32_t last = (issued - 1 - st) / static_cast<uint32_t>(STG);
+        mbar_wait_drain(&aux->full[st], last & 1u);
+      }
+    }
+    __syncwarp();
+  } else if (warp == kSkMmaWarp) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = F8 ? make_idesc(1u, static_cast<uint32_t>(p.f8_ab_format), kBM, static_cast<uint32_t>(MT))
+                              : make_idesc(2u, 1u, kBM, static_cast<uint32_t>(MT));
+    const uint64_t wdesc0 = make_smem_desc_sw128(smem_u32(smem));
+    const uint64_t xdesc0 = make_smem_desc_sw128(smem_u32(smem) + kSkWBytes);
+    uint32_t s = 0, ph = 0, accumulate = 0;
+    bool ok = true;
+    for (int kb = kb0; kb < kb1; ++kb) {
+      ok = warp_mbar_wait(&aux->full[s], ph, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint64_t off = static_cast<uint64_t>(s * (stage_bytes >> 4));
+      tc_mma4_release<F8 ? 1 : 0>(tmem_base, wdesc0 + off, xdesc0 + off, idesc, accumulate, &aux->empty[s]);
+      accumulate = 1;
+      if (++s == static_cast<uint32_t>(STG)) {
+        s = 0;
+        ph ^= 1u;
+      }
+    }
+    if (ok) tc_commit_elect(&aux->tfull[0]);
+    if (!ok && lane == 0) {
+      timed_out = !*abort_flag;
+      *abort_flag = 1;
+    }
+    tc_commit_elect(&aux->drain);
+    mbar_wait_drain(&aux->drain, 0);
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue warps, first half
+    const int q = warp & 3;
+    const int n_local = q * 32 + lane;
+    const int n = tile * kBM + n_local;
+    if (warp_mbar_wait(&aux->tfull[0], 0, abort_flag)) {
+      tc_fence_after();
+      const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+      float cs = 1.0f, bias = 0.0f;
+      if (S == 1 && n < p.N && scaled) {
+        if (p.cs != nullptr) cs = p.cs[static_cast<int64_t>(n) * p.cs_stride];
+        if (has_bias) bias = p.bias[n];
+      }
+#pragma unroll 1
+      for (int c = (warp >> 2) * 32; c < MT; c += 64) {
+        if (c >= p.M) break;
+        uint32_t v[32];
+        tmem_ld32(tmem_base + lane_base + c, v);
+        if (S == 1) {
+          if (n < p.N) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (c + j < p.M) skinny_emit<F8>(p, v[j], c + j, n, s_rs[c + j], cs, bias, prod, has_bias);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c + j < p.M) part[(c + j) * kBM + n_local] = v[j];
+        }
+      }
+      tc_fence_before();
+    } else if (lane == 0) {
+      timed_out = !*abort_flag;
+      *abort_flag = 1;
+    }
+    __syncwarp();
+  }
+
+  if (S > 1) {
+    __syncwarp();
+    cluster_arrive_wait();  // every split's partial tile is in its CTA's shared memory
+    if (!bad && warp < kSkEpiWarps) {
+      const int n_local = threadIdx.x & (kBM - 1);
+      const int n = tile * kBM + n_local;
+      if (n < p.N) {
+        float cs = 1.0f, bias = 0.0f;
+        if (scaled) {
+          if (p.cs != nullptr) cs = p.cs[static_cast<int64_t>(n) * p.cs_stride];
+          if (has_bias) bias = p.bias[n];
+        }
+        // this CTA's rows are sp, sp + S, ...; the two halves of the epilogue warps take every other one of them
+        // two rows per iteration: both rows' loads are in flight before the first sum is needed
+        auto sum_row = [&](int m) -> uint32_t {
+          const uint32_t* src = part + m * kBM + n_local;
+          if (S == 2) return skinny_sum_splits<F8, 2>(src);
+          if (S == 4) return skinny_sum_splits<F8, 4>(src);
+          return skinny_sum_splits<F8, 8>(src);
+        };
+        for (int m = sp + S * static_cast<int>(threadIdx.x >> 7); m < p.M; m += 4 * S) {
+          const int m2 = m + 2 * S;
+          const uint32_t acc = sum_row(m);
+          const uint32_t acc2 = m2 < p.M ? sum_row(m2) : 0u;
+          skinny_emit<F8>(p, acc, m, n, s_rs[m], cs, bias, prod, has_bias);
+          if (m2 < p.M) skinny_emit<F8>(p, acc2, m2, n, s_rs[m2], cs, bias, prod, has_bias);
+        }
+      }
+    }
+    __syncwarp();
+    cluster_arrive_wait();  // nobody leaves while a neighbour still reads its shared memory
+  }
+
+  if (timed_out && p.status != nullptr) atomicExch(p.status, static_cast<int32_t>(QLIN_ERR_TIMEOUT));
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kSkMmaWarp) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, kSkTmemCols);
+  }
+}
+
 // ---------------------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -1072,6 +1311,57 @@ static bool pair_enabled() {
   return v == 1;
 }
 
+// The few-row kernel is used for unchunked problems of at most 128 rows unless QLIN_GEMM_SKINNY=0.
+static bool skinny_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("QLIN_GEMM_SKINNY");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+template <bool F8>
+static int launch_skinny(const CUtensorMap& tw, const CUtensorMap& tx, GemmParams p, cudaStream_t stream) {
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return fail(QLIN_ERR_DEVICE, "device ordinal %d out of range", dev);
+  const int smem_max = 232448;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(qlin_gemm_skinny_kernel<F8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+    if (e != cudaSuccess) return fail(QLIN_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    configured[dev] = true;
+  }
+  const int stage_bytes = kSkWBytes + p.sk_mt * kBK;
+  int stages = (smem_max - static_cast<int>(sizeof(Aux))) / stage_bytes;
+  p.sk_stages = stages > 8 ? 8 : stages;
+  const int tiles = (p.N + kBM - 1) / kBM;
+  // K splits: the largest power of two that keeps one CTA per SM and at least four K blocks per split
+  const int num_kb = (p.kbytes + kBK - 1) / kBK;
+  int split = 1;
+  while (split < 8 && tiles * split * 2 <= sm_count() && num_kb / (split * 2) >= 4) split *= 2;
+  p.sk_split = split;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * split), 1, 1);
+  cfg.blockDim = dim3(kSkThreads, 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(p.sk_stages) * stage_bytes + sizeof(Aux);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(split);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, qlin_gemm_skinny_kernel<F8>, tw, tx, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(QLIN_ERR_LAUNCH, "qlin_gemm (few-row kernel): %s", cudaGetErrorString(e));
+  }
+  return QLIN_OK;
+}
+
 static bool is_round_dtype(int dt) {
   return dt == QLIN_DT_NONE || dt == QLIN_DT_F32 || dt == QLIN_DT_F16 || dt == QLIN_DT_BF16;
 }
@@ -1165,13 +1455,25 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   p.num_m = (a->M + kBM - 1) / kBM;
   p.num_n = (a->N + bn - 1) / bn;
 
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  p.sk_mt = p.sk_split = p.sk_stages = 0;
+  if (!chunked && a->M <= kBM && a->scatter_rows == 0 && a->max_ctas <= 0 && skinny_enabled()) {
+    // weight rows as the MMA's M dimension, the few activation rows (padded to 32) as its N dimension
+    p.sk_mt = (a->M + 31) / 32 * 32;
+    CUtensorMap tw, tx;
+    int rc = make_operand_map(&tw, a->b, a->N, a->K, a->ldb, kBM);
+    if (rc != QLIN_OK) return rc;
+    rc = make_operand_map(&tx, a->a, a->M, a->K, a->lda, p.sk_mt);
+    if (rc != QLIN_OK) return rc;
+    return f8 ? launch_skinny<true>(tw, tx, p, s) : launch_skinny<false>(tw, tx, p, s);
+  }
+
   CUtensorMap ta, tb;
   int rc = make_operand_map(&ta, a->a, a->M, a->K, a->lda, kBM);
   if (rc != QLIN_OK) return rc;
   rc = make_operand_map(&tb, a->b, a->N, a->K, a->ldb, bn);
   if (rc != QLIN_OK) return rc;
 
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (!chunked && a->M >= 2 * kBM && pair_enabled()) {
     CUtensorMap tb_half;  // each CTA of a pair loads 128 of the tile's 256 B rows
     rc = make_operand_map(&tb_half, a->b, a->N, a->K, a->ldb, PairCfg::BN / 2);

@@ -192,3 +192,49 @@ def test_empty_and_error_cases(cuda_dev):
         ops.gemm(b, b.float())
     with pytest.raises(RuntimeError, match="status"):
         ops.gemm(b, b, chunk_k=48, trun_bits=8)
+
+
+@pytest.mark.parametrize(
+    "M,N,K",
+    [(1, 14336, 4096), (1, 4096, 14336), (7, 1024, 2048), (16, 4096, 4096), (33, 200, 1000), (64, 128, 512), (96, 520, 4100),
+     (100, 2048, 8192), (128, 4096, 4096), (128, 300, 160), (128, 14336, 640)],
+)
+def test_few_row_gemm_is_exact_and_deterministic(cuda_dev, M, N, K):
+    """Problems of at most 128 rows run on the few-row kernel (weight rows as the MMA's M dimension, K split over a cluster
+    whose partial sums are added in split order).  The shapes cover one to eight splits, ragged rows, columns and K tails.
+    Integer results equal the exact product, raw and through a dequantising epilogue with an initial accumulator; the fp8
+    result is the same bits on every run (fixed summation order) and within the fp8 bound of the oracle."""
+    a, b = _i8((M, K), 21), _i8((N, K), 22, -128, 128)
+    acc = (a.double() @ b.double().t()).to(torch.int32)
+    ad, bd = a.to(cuda_dev), b.to(cuda_dev)
+    got = ops.gemm(ad, bd)
+    ops.check_status(cuda_dev)
+    assert torch.equal(got.cpu(), acc)
+    g = torch.Generator().manual_seed(23)
+    c = torch.randint(-1000, 1000, (M, N), dtype=torch.int32, generator=g)
+    got = ops.gemm(ad, bd, c=c.to(cuda_dev))
+    assert torch.equal(got.cpu(), acc + c)
+    rs = (torch.rand(M, generator=g) * 0.05 + 1e-3).bfloat16().float()
+    cs = torch.rand(N, generator=g) * 2e-4 + 1e-5
+    bias = torch.randn(N, generator=g).bfloat16().float() * 0.01
+    want = (acc.float() * (rs[:, None] * cs[None, :]).to(torch.float16) + bias).to(torch.float16).to(torch.bfloat16)
+    got = ops.gemm(ad, bd, epilogue=L.EPI_SCALE_PROD, row_scale=rs.to(cuda_dev), col_scale=cs.to(cuda_dev),
+                   bias=bias.to(cuda_dev), scale_round=torch.float16, acc_round=torch.float16, out_dtype=torch.bfloat16)  # fmt: skip
+    assert torch.equal(got.cpu(), want)
+    want = ((acc.float() * rs[:, None]) * cs[None, :]).bfloat16()
+    got = ops.gemm(ad, bd, epilogue=L.EPI_SCALE_SEQ, row_scale=rs.to(cuda_dev), col_scale=cs.to(cuda_dev), out_dtype=torch.bfloat16)
+    assert torch.equal(got.cpu(), want)
+    want32 = (acc.float() * rs[:, None]) * cs[None, :] + bias
+    got = ops.gemm(ad, bd, epilogue=L.EPI_SCALE_SEQ, row_scale=rs.to(cuda_dev), col_scale=cs.to(cuda_dev), bias=bias.to(cuda_dev),
+                   out_dtype=torch.float32)  # fmt: skip
+    assert torch.equal(got.cpu(), want32)
+
+    fa = torch.randn(M, K, generator=g).to(torch.float8_e4m3fn)
+    fb = torch.randn(N, K, generator=g).to(torch.float8_e4m3fn)
+    fad, fbd = fa.to(cuda_dev), fb.to(cuda_dev)
+    y1 = ops.gemm(fad, fbd)
+    y2 = ops.gemm(fad, fbd)
+    ops.check_status(cuda_dev)
+    assert torch.equal(y1, y2)
+    exact = fa.double() @ fb.double().t()
+    assert (torch.norm(y1.cpu().double() - exact) / torch.norm(exact)).item() < 1e-5
