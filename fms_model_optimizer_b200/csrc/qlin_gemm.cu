@@ -85,6 +85,7 @@ struct GemmParams {
   int32_t scatter_rows, scatter_row0;
   uint8_t* scatter_d[8];
   int32_t f8_ab_format;  // float kinds: operand format of the instruction descriptor, 0 = e4m3, 1 = e5m2
+  int32_t low_byte_mode;  // chunked int8, 8 truncated bits: the total on the tensor core, the chunks' low bytes on the ALU
   int32_t sk_mt, sk_split, sk_stages;  // few-row kernel: padded row count, K splits (= cluster size), pipeline stages
 };
 
@@ -470,8 +471,20 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     bool tready = false;  // next accumulator buffer known to be drained
     // chunks that tile a 128-byte K block exactly (32, 64 or 128 elements, K a multiple of 128)
     const bool chunk_fast = CHUNKED && (p.chunk_k32 == 1 || p.chunk_k32 == 2 || p.chunk_k32 == 4) && (total_k32 % 4 == 0);
+    // low-byte mode: the last accumulator holds the tile's untruncated total, the others rotate over the chunks
+    const bool low_mode = CHUNKED && !F8 && p.low_byte_mode != 0;
+    const uint32_t nbuf = low_mode ? C::NBUF - 1 : C::NBUF;
+    const uint32_t d_total = tmem_base + (C::NBUF - 1) * C::BN;
+    uint32_t tot_ph = 0;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       uint32_t accumulate = 0, cur = 0;
+      if (low_mode) {
+        // the epilogue warps must have read the previous tile's total before it is overwritten
+        ok = warp_mbar_wait(&aux->tempty[C::NBUF - 1], tot_ph ^ 1u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        tot_ph ^= 1u;
+      }
       int chunk_pos = 0;
       int k32_left = total_k32;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
@@ -510,11 +523,27 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               if (!ok) break;
             }
             tc_fence_after();
-            const uint32_t nb = (buf + 1 == C::NBUF) ? 0u : buf + 1;
+            const uint32_t nb = (buf + 1 == nbuf) ? 0u : buf + 1;
             const uint32_t nbph = (nb == 0u) ? (bph ^ 1u) : bph;
             const uint32_t tpeek = warp_mbar_test_begin(&aux->tempty[nb], nbph ^ 1u);
             const uint64_t off = static_cast<uint64_t>(c * p.chunk_k32 * 2);
             const uint32_t d = tmem_base + buf * C::BN;
+            if constexpr (CHUNKED && !F8) {
+              if (low_mode) {
+                const uint32_t acc_total = (kb == 0 && c == 0) ? 0u : 1u;
+                if (p.chunk_k32 == 1) {
+                  tc_mma_chunk_and_total_i8<1>(d, d_total, adesc + off, bdesc + off, idesc, acc_total, &aux->tfull[buf]);
+                } else if (p.chunk_k32 == 2) {
+                  tc_mma_chunk_and_total_i8<2>(d, d_total, adesc + off, bdesc + off, idesc, acc_total, &aux->tfull[buf]);
+                } else {
+                  tc_mma_chunk_and_total_i8<4>(d, d_total, adesc + off, bdesc + off, idesc, acc_total, &aux->tfull[buf]);
+                }
+                tready = warp_mbar_test_end(tpeek);
+                buf = nb;
+                bph = nbph;
+                continue;
+              }
+            }
             if (p.chunk_k32 == 1) {
               tc_mma_chunk<F8 ? 1 : 0, 1>(d, adesc + off, bdesc + off, idesc, &aux->tfull[buf]);
             } else if (p.chunk_k32 == 2) {
@@ -589,6 +618,8 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t ebuf = 0, ebph = 0;
     bool eready = false;
     bool ok = true;
+    const bool elow = CHUNKED && !F8 && p.low_byte_mode != 0;
+    const uint32_t enbuf = elow ? C::NBUF - 1 : C::NBUF;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
       tile_coords(t, p.num_m, p.num_n, mb, nb);
@@ -641,7 +672,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         while (k32_left > 0) {
           k32_left -= p.chunk_k32;
           const uint32_t buf = ebuf, bph = ebph;
-          if (++ebuf == C::NBUF) {
+          if (++ebuf == enbuf) {
             ebuf = 0;
             ebph ^= 1u;
           }
@@ -650,6 +681,24 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             break;
           }
           tc_fence_after();
+          if (elow) {
+            // ((p + 128) >> 8) << 8 = p - sext8(low byte of p): the sum of the chunks is the untruncated total (kept by
+            // the tensor core in its own accumulator) minus the sum of the sign-extended low bytes.  Only the low bits
+            // of the chunk's accumulator are read (two columns per register), one dp4a per element picks its byte.
+            uint32_t v16[C::COLS_PER_WARP / 2];
+            tmem_ld32_low16(tmem_base + lane_base + buf * C::BN + half * C::COLS_PER_WARP, v16);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&aux->tempty[buf]);
+            const uint32_t epeek = warp_mbar_test_begin(&aux->tfull[ebuf], ebph);
+#pragma unroll
+            for (int i = 0; i < C::COLS_PER_WARP / 2; ++i) {
+              run[2 * i] = static_cast<uint32_t>(__dp4a(static_cast<int>(v16[i]), 0x000000FF, static_cast<int>(run[2 * i])));
+              run[2 * i + 1] = static_cast<uint32_t>(__dp4a(static_cast<int>(v16[i]), 0x00FF0000, static_cast<int>(run[2 * i + 1])));
+            }
+            eready = warp_mbar_test_end(epeek);
+            continue;
+          }
           uint32_t v[C::COLS_PER_WARP];
           tmem_ld32(tmem_base + lane_base + buf * C::BN + half * C::COLS_PER_WARP, v);
           tc_fence_before();
@@ -671,6 +720,17 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               run[i] = chunk_round<F8>(acc_add<F8>(run[i], v[i]), clamp, lo, hi, rb, mask, dl16);
           }
           eready = warp_mbar_test_end(epeek);
+        }
+        if (!ok) break;
+        if (elow) {
+          // the last chunk's commit covers every MMA of the tile: the total is complete
+          uint32_t tot[C::COLS_PER_WARP];
+          tmem_ld32(tmem_base + lane_base + (C::NBUF - 1) * C::BN + half * C::COLS_PER_WARP, tot);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&aux->tempty[C::NBUF - 1]);
+#pragma unroll
+          for (int i = 0; i < C::COLS_PER_WARP; ++i) run[i] += tot[i];
         }
         if (!ok) break;
         emit32<F8>(p, run, row0, lane, col_w, aux->cs, aux->bias, half * C::COLS_PER_WARP, rs, vec_ok, stage);
@@ -1311,6 +1371,15 @@ static bool pair_enabled() {
   return v == 1;
 }
 
+static bool low_byte_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("QLIN_GEMM_LOWBYTE");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
 // The few-row kernel is used for unchunked problems of at most 128 rows unless QLIN_GEMM_SKINNY=0.
 static bool skinny_enabled() {
   static int v = -1;
@@ -1457,6 +1526,12 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
 
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   p.sk_mt = p.sk_split = p.sk_stages = 0;
+  // int8 chunks with the low byte rounded away, summed after rounding, no clamp, chunks of 32 / 64 / 128 that tile K:
+  // sum of ((p + 128) >> 8 << 8) = sum of p - sum of sext8(p), the first sum kept by the tensor core (QLIN_GEMM_LOWBYTE=0: off)
+  p.low_byte_mode = (chunked && !f8 && a->trun_bits == 8 && a->trunc_then_acc && a->max_acc_bits >= 32 &&
+                     (chunk_k32 == 1 || chunk_k32 == 2 || chunk_k32 == 4) && total_k32 % 4 == 0 && low_byte_enabled())
+                        ? 1
+                        : 0;
   if (!chunked && a->M <= kBM && a->scatter_rows == 0 && a->max_ctas <= 0 && skinny_enabled()) {
     // weight rows as the MMA's M dimension, the few activation rows (padded to 32) as its N dimension
     p.sk_mt = (a->M + 31) / 32 * 32;

@@ -306,6 +306,47 @@ __device__ __forceinline__ void tc_mma_chunk(uint32_t d_tmem, uint64_t adesc, ui
 #undef QLIN_CHUNK_HEAD
 }
 
+// One accumulation chunk of NMMA (1, 2 or 4) K=32-byte int8 MMAs issued twice: into a running total accumulator
+// (`accumulate_total` = 0 makes the first MMA overwrite it) and into a fresh per-chunk accumulator, then the
+// "accumulator full" commit on `tfull_bar` (it covers both).
+template <int NMMA>
+__device__ __forceinline__ void tc_mma_chunk_and_total_i8(uint32_t d_chunk, uint32_t d_total, uint64_t adesc, uint64_t bdesc,
+                                                          uint32_t idesc, uint32_t accumulate_total, uint64_t* tfull_bar) {
+#define QLIN_CT_HEAD                                      \
+  "{\n\t"                                                 \
+  ".reg .pred pe, pf, pt, pa;\n\t"                        \
+  ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"                 \
+  "elect.sync _|pe, 0xffffffff;\n\t"                      \
+  "setp.ne.b32 pt, %3, 0;\n\t"                            \
+  "setp.eq.b32 pf, %3, 0;\n\t"                            \
+  "setp.ne.b32 pa, %6, 0;\n\t"                            \
+  "add.s64 a1, %1, 2;\n\t"                                \
+  "add.s64 b1, %2, 2;\n\t"                                \
+  "add.s64 a2, %1, 4;\n\t"                                \
+  "add.s64 b2, %2, 4;\n\t"                                \
+  "add.s64 a3, %1, 6;\n\t"                                \
+  "add.s64 b3, %2, 6;\n\t"
+#define QLIN_CT_TAIL                                                                           \
+  "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%4];\n\t"        \
+  "}" ::"r"(d_chunk),                                                                          \
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(smem_u32(tfull_bar)), "r"(d_total), "r"(accumulate_total) \
+      : "memory"
+#define QLIN_MC(A, B, P) "@pe tcgen05.mma.cta_group::1.kind::i8 [%0], " A ", " B ", %3, " P ";\n\t"
+#define QLIN_MT(A, B, P) "@pe tcgen05.mma.cta_group::1.kind::i8 [%5], " A ", " B ", %3, " P ";\n\t"
+  if (NMMA == 1) {
+    asm volatile(QLIN_CT_HEAD QLIN_MT("%1", "%2", "pa") QLIN_MC("%1", "%2", "pf") QLIN_CT_TAIL);
+  } else if (NMMA == 2) {
+    asm volatile(QLIN_CT_HEAD QLIN_MT("%1", "%2", "pa") QLIN_MC("%1", "%2", "pf") QLIN_MT("a1", "b1", "pt") QLIN_MC("a1", "b1", "pt") QLIN_CT_TAIL);
+  } else {
+    asm volatile(QLIN_CT_HEAD QLIN_MT("%1", "%2", "pa") QLIN_MC("%1", "%2", "pf") QLIN_MT("a1", "b1", "pt") QLIN_MC("a1", "b1", "pt")
+                     QLIN_MT("a2", "b2", "pt") QLIN_MC("a2", "b2", "pt") QLIN_MT("a3", "b3", "pt") QLIN_MC("a3", "b3", "pt") QLIN_CT_TAIL);
+  }
+#undef QLIN_MT
+#undef QLIN_MC
+#undef QLIN_CT_TAIL
+#undef QLIN_CT_HEAD
+}
+
 // A single K=32-byte MMA, elected-lane form.
 template <int KIND_F8>
 __device__ __forceinline__ void tc_mma1(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
@@ -476,6 +517,19 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// The low 16 bits of 32 consecutive 32-bit columns, two columns per register (column 2i in the low half of r[i],
+// column 2i + 1 in the high half): half the register traffic of tmem_ld32 for callers that only need the low bits.
+__device__ __forceinline__ void tmem_ld32_low16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.pack::16b.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }

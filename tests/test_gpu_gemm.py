@@ -238,3 +238,18 @@ def test_few_row_gemm_is_exact_and_deterministic(cuda_dev, M, N, K):
     assert torch.equal(y1, y2)
     exact = fa.double() @ fb.double().t()
     assert (torch.norm(y1.cpu().double() - exact) / torch.norm(exact)).item() < 1e-5
+
+
+@pytest.mark.parametrize("M,N,K,chunk", [(300, 260, 512, 64), (128, 128, 256, 32), (1000, 2100, 1024, 128), (64, 4096, 8192, 64)])
+def test_low_byte_chunk_mode_is_bit_exact(cuda_dev, M, N, K, chunk):
+    """Eight truncated bits with chunks of 32 / 64 / 128 that tile K run with the untruncated total on the tensor core and
+    the chunks' low bytes summed on the ALU (sum of round-to-256 = total - sum of sign-extended low bytes).  Several tiles
+    per CTA, ragged edges and an initial accumulator; the result is the oracle's, bit for bit."""
+    a, b = _i8((M, K), 31), _i8((K, N), 32)
+    c = torch.randint(-100000, 100000, (M, N), dtype=torch.int32, generator=torch.Generator().manual_seed(33))
+    for cc in (None, c):
+        want = OG.imatmul_chunk_truncate(a, b, c=cc, chunk_trun_bits=8, chunk_size=chunk)
+        got = ops.tl_matmul_chunk_truncate(a.to(cuda_dev), b.to(cuda_dev), c=(cc.to(cuda_dev) if cc is not None else None),
+                                           chunk_trun_bits=8, chunk_size=chunk)  # fmt: skip
+        ops.check_status(cuda_dev)
+        assert torch.equal(got.cpu(), want)
