@@ -154,7 +154,9 @@ class W8A8Decoder:
         # flight per thread) before the fused norm + quantise kernel, or inside that kernel's prologue ("fused")
         self.switch_reduce = "split"
         if exchange == "auto":
-            exchange = "none" if world == 1 else "multimem"
+            # measured on 8 x B200: with two GPUs the plain-store scheme wins (every byte crosses one link once either
+            # way and the stores ride in the GEMM epilogue); from four GPUs on the switch's reduce / replicate does
+            exchange = "none" if world == 1 else ("stores" if world == 2 else "multimem")
         self.exchange = exchange
         H, hd = cfg["hidden"], cfg["head_dim"]
         self.nq, self.nkv = cfg["q_heads"] // world, cfg["kv_heads"] // world
