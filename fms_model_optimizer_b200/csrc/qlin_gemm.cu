@@ -15,6 +15,11 @@
 // tile i+1.  Chunked: BN=128, four 128-column accumulators; every K-chunk is a fresh accumulation
 // that the epilogue warps drain, round and add to a running sum held in registers.
 //
+// Three kernels share this file: the CTA-pair kernel (cta_group::2, unchunked problems of at least 256 rows), the
+// single-CTA kernel described above (chunked problems and the shapes in between), and the few-row kernel (at most
+// 128 rows: weight rows as the MMA's M dimension, K split over a thread-block cluster).  Environment switches for
+// A/B measurements: QLIN_GEMM_PAIR=0, QLIN_GEMM_SKINNY=0, QLIN_GEMM_LOWBYTE=0 select the kernel or mode each replaces.
+//
 // All mbarrier waits are bounded; a wait that runs out raises an abort flag, the CTA drains its
 // copies and MMAs, frees TMEM, writes QLIN_ERR_TIMEOUT to the status word and returns.
 #include <cstdlib>

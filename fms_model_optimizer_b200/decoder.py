@@ -337,6 +337,7 @@ class W8A8Decoder:
         for _ in range(self.groups):
             g = _Group()
             g.bar = PeerBarrier(self.arena, barrier_timeout_s)
+            g.side = torch.cuda.Stream(device=self.dev)
             g.T, g.Ts = T, T // W
             g.part_off, part = self.arena.alloc(T * H * 2)
             # multimem: my partial output for all tokens; stores: [world] receive slots for my tokens
@@ -419,9 +420,16 @@ class W8A8Decoder:
             self._note("x_attn_in", li, x)
             bar.wait()  # every rank's codes have landed here
             yield
+            # the shards of k and v are narrow (a quarter of q's columns with grouped-query attention): v's GEMM goes to a
+            # side stream so that it shares a wave of CTAs with k's instead of taking one of its own
+            cur = torch.cuda.current_stream()
+            g.side.wait_stream(cur)
+            with torch.cuda.stream(g.side):
+                v = lin["v"](None, (g.codes[2], g.scales[2]), bf)
             q = ops.rope_(lin["q"](None, (g.codes[0], g.scales[0]), bf).view(T, self.nq, hd), self.cos, self.sin, S)
             k = ops.rope_(lin["k"](None, (g.codes[1], g.scales[1]), bf).view(T, self.nkv, hd), self.cos, self.sin, S)
-            v = lin["v"](None, (g.codes[2], g.scales[2]), bf)
+            cur.wait_stream(g.side)
+            v.record_stream(cur)
             a = self._attention(q, k, v, B, S)
             row_parallel(lin["o"], lin["o"].quantise_fused(a, exchange=sx))
             have_parts = True
