@@ -41,6 +41,7 @@ EXPORTED_SYMBOLS = (
     "qlin_last_error_string",
     "qlin_device_supported",
     "qlin_gemm",
+    "qlin_gemm_batched",
     "qlin_act_quant",
     "qlin_pact2_fwd",
     "qlin_pact2_bwd",
@@ -316,6 +317,8 @@ def load() -> C.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = [C.POINTER(struct), C.c_void_p]
         fn.restype = C.c_int
+    lib.qlin_gemm_batched.argtypes = [C.POINTER(GemmArgs), C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]
+    lib.qlin_gemm_batched.restype = C.c_int
     lib.qlin_pact2_bwd_workspace_bytes.argtypes = [C.c_int64]
     lib.qlin_pact2_bwd_workspace_bytes.restype = C.c_size_t
     lib.qlin_pact2_bwd_noalloc_max_numel.restype = C.c_int64

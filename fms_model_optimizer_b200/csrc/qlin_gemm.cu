@@ -1564,3 +1564,20 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   if (f8) return chunked ? launch<true, true>(ta, tb, p, s) : launch<true, false>(ta, tb, p, s);
   return chunked ? launch<false, true>(ta, tb, p, s) : launch<false, false>(ta, tb, p, s);
 }
+
+extern "C" int qlin_gemm_batched(const qlin_gemm_args* a, int32_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, void* stream) {
+  if (a == nullptr) return fail(QLIN_ERR_NULL, "qlin_gemm_batched: args is NULL");
+  if (batch < 0 || stride_a < 0 || stride_b < 0 || stride_d < 0) return fail(QLIN_ERR_BAD_SHAPE, "qlin_gemm_batched: negative batch or stride");
+  if (a->c != nullptr || a->scatter_rows != 0) return fail(QLIN_ERR_UNSUPPORTED, "qlin_gemm_batched: no accumulator input and no row-block scatter");
+  if (batch > 1 && (stride_a % 16 != 0 || stride_b % 16 != 0)) return fail(QLIN_ERR_BAD_ALIGN, "qlin_gemm_batched: operand strides must be multiples of 16 bytes");
+  const int64_t out_elt = (a->epilogue == QLIN_EPI_RAW || a->out_dtype == QLIN_DT_F32) ? 4 : 2;
+  qlin_gemm_args one = *a;
+  for (int32_t i = 0; i < batch; ++i) {
+    one.a = static_cast<const uint8_t*>(a->a) + i * stride_a;
+    one.b = static_cast<const uint8_t*>(a->b) + i * stride_b;
+    one.d = static_cast<uint8_t*>(a->d) + i * stride_d * out_elt;
+    const int rc = qlin_gemm(&one, stream);
+    if (rc != QLIN_OK) return rc;
+  }
+  return QLIN_OK;
+}

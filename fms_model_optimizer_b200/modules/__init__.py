@@ -1,5 +1,6 @@
-"""Quantized Linear modules (mirror of fms_mo/modules/linear.py for the B200 path)."""
+"""Quantized Linear and batched-matmul modules (mirror of fms_mo/modules/linear.py and fms_mo/modules/bmm.py for the B200 path)."""
 
+from .bmm import QBmm, QBmmINT8Deploy
 from .linear import (
     LinearFPxAcc,
     QLinear,
@@ -10,4 +11,5 @@ from .linear import (
     lower_qmodel_b200,
 )
 
-__all__ = ["QLinear", "QLinearINT8Deploy", "QLinearINT8Train", "QLinearCublasI8I32NT", "QLinearCutlassI8I32NT", "LinearFPxAcc", "lower_qmodel_b200"]
+__all__ = ["QLinear", "QLinearINT8Deploy", "QLinearINT8Train", "QLinearCublasI8I32NT", "QLinearCutlassI8I32NT", "LinearFPxAcc", "lower_qmodel_b200",
+           "QBmm", "QBmmINT8Deploy"]  # fmt: skip

@@ -215,6 +215,38 @@ def gemm(
     return out
 
 
+def bmm_i8(a: torch.Tensor, b_nk: torch.Tensor) -> torch.Tensor:
+    """Batched int8 product: ``a [B, M, K]`` times ``b_nk [B, N, K]`` (both K-contiguous) -> int32 ``[B, M, N]``, exact.
+    One ``qlin_gemm_batched`` call (include/qlin_b200.h); the integer product QBmmINT8Deploy stands for
+    (fms_mo/modules/bmm.py:741-752 simulates it with a float matmul)."""
+    if a.dim() != 3 or b_nk.dim() != 3 or a.shape[0] != b_nk.shape[0] or a.shape[2] != b_nk.shape[2]:
+        raise RuntimeError("bmm_i8 takes a [B,M,K] and b_nk [B,N,K]")
+    if a.dtype != torch.int8 or b_nk.dtype != torch.int8 or not a.is_cuda or a.device != b_nk.device:
+        raise RuntimeError("bmm_i8 takes int8 CUDA tensors on one device")
+    B, M, K = a.shape
+    N = b_nk.shape[1]
+    dev = a.device
+    out = torch.empty((B, M, N), dtype=torch.int32, device=dev)
+    if B == 0 or M == 0 or N == 0:
+        return out
+    if K % 16 != 0:  # rows of the operands must start on 16-byte boundaries: zero columns add nothing
+        pad = 16 - K % 16
+        a, b_nk = torch.nn.functional.pad(a, (0, pad)), torch.nn.functional.pad(b_nk, (0, pad))
+    a, b_nk = a.contiguous(), b_nk.contiguous()
+    Kp = a.shape[2]
+    args = L.GemmArgs(
+        a=_ptr(a), b=_ptr(b_nk), c=None, d=_ptr(out), row_scale=None, col_scale=None, bias=None, status=_ptr(status_word(dev)),
+        lda=Kp, ldb=Kp, ldc=0, ldd=N, M=M, N=N, K=Kp, kind=L.DT_I8, chunk_k=0, trun_bits=0, max_acc_bits=32, trunc_then_acc=1,
+        clamp_dl16=0, epilogue=L.EPI_RAW, row_scale_stride=0, col_scale_stride=0, prod_round=_ROUND[None], scale_round=_ROUND[None],
+        mid_round=_ROUND[None], acc_round=_ROUND[None], out_dtype=L.DT_I32, max_ctas=int(GEMM_MAX_CTAS),
+    )  # fmt: skip
+    with torch.cuda.device(dev):
+        rc = _timed("gemm", 2.0 * B * M * N * K, dev,
+                    lambda: L.load().qlin_gemm_batched(C.byref(args), B, M * Kp, N * Kp, M * N, _stream(dev)))
+        L.check(rc, "qlin_gemm_batched")
+    return out
+
+
 def _as_nk(m2: torch.Tensor) -> torch.Tensor:
     """The reference passes B as a ``[k,n]`` tensor, normally the ``.t()`` view of a row-major
     ``[n,k]`` weight.  Returns the ``[n,k]`` K-contiguous operand, copying only when ``m2`` is not

@@ -140,6 +140,14 @@ typedef struct qlin_gemm_args {
 
 int qlin_gemm(const qlin_gemm_args* args, void* stream);
 
+/* qlin_gemm_batched -- the same problem `batch` times over operands that lie `stride_a`, `stride_b` (elements of
+ * the operand type) and `stride_d` (elements of the output type) apart: D[i] = epilogue(A[i] . B[i]^T).  The batched
+ * int8 product behind QBmmINT8Deploy (fms_mo/modules/bmm.py:719-752), where the reference itself "has not implemented
+ * any batched CUTLASS matmul" and simulates with torch.matmul on fp16 copies of the codes.  Scales, bias and the
+ * status word are shared by all problems; `c` must be NULL; row-block scatter is not provided.  One launch per
+ * problem on `stream`, in order. */
+int qlin_gemm_batched(const qlin_gemm_args* args, int32_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * qlin_act_quant -- row-wise (per-token / per-channel) dynamic 8-bit quantisation in one pass.
  *

@@ -527,6 +527,55 @@ def gen_c4():
                              align_zero=qcfg.get("align_zero", True)))
 
 
+def gen_bmm():
+    """QBmm (fake-quantized matmul) and QBmmINT8Deploy (fms_mo/modules/bmm.py:26-228, 607-758) on CPU.
+
+    The deploy forward subtracts a correction term whose sum runs over dimension 0 of m2's codes
+    (bmm.py:741-746), so it only evaluates where that term broadcasts against the product: the cases below use
+    m == k.  With a symmetric m1 the zero point is 128 and the term is zero; with an asymmetric m1 it is whatever
+    the reference computes, stored here as it came out."""
+    from fms_mo.modules.bmm import QBmm, QBmmINT8Deploy
+
+    cases = []
+    spec = [  # name, bits m1, mode m1, one-sided m1, mode m2, sym_7bits, dtype, (m, k, n)
+        ("sym8_fp32", 8, "pactsym+", False, "pactsym+", False, torch.float32, (32, 32, 48)),
+        ("sym8_bf16", 8, "pactsym+", False, "pactsym+", False, torch.bfloat16, (32, 32, 48)),
+        ("sym8_fp16", 8, "pactsym+", False, "pactsym+", False, torch.float16, (32, 32, 48)),
+        ("asym8_fp32", 8, "pact+", False, "pactsym+", False, torch.float32, (32, 32, 48)),
+        ("onesided7_fp32", 8, "pact+", True, "pactsym+", True, torch.float32, (48, 48, 16)),
+        ("sym8_fp32_bmm3d", 8, "pactsym+", False, "pactsym+", False, torch.float32, (64, 64, 64)),
+    ]
+    for i, (name, nb1, mode1, uni, mode2, sym7, dtype, (m, k, n)) in enumerate(spec):
+        g = torch.Generator().manual_seed(700 + i)
+        qcfg = {"use_PT_native_Qfunc": False, "sym_7bits_bmm": sym7}
+        cv1, cvn1, cv2 = (1.0, 0.0, 2.5) if uni else (3.0, -2.0, 2.5)
+        q = QBmm(num_bits_m1=nb1, qm1_mode=mode1, num_bits_m2=8, qm2_mode=mode2, m1_unidirectional=uni, replaceBmm=("bmm3d" not in name),
+                 qcfg=qcfg, m1_clip_init_val=cv1, m1_clip_init_valn=cvn1, m2_clip_init_val=cv2, m2_clip_init_valn=-cv2)  # fmt: skip
+        lead = (2, 2) if "bmm3d" in name else (2, 3)
+        m1 = torch.randn(*lead, m, k, generator=g)
+        m2 = torch.randn(*lead, k, n, generator=g)
+        if uni:
+            m1 = torch.softmax(m1 * 3, dim=-1)
+        q = q.to(dtype)
+        m1, m2 = m1.to(dtype), m2.to(dtype)
+        a = m1.clone().requires_grad_(True)
+        b = m2.clone().requires_grad_(True)
+        y = q(a, b)
+        go = torch.randn(y.shape, generator=g).to(dtype)
+        y.backward(go)
+        d = QBmmINT8Deploy.from_fms_mo(q, target_device="cpu")
+        yd = d(m1, m2)
+        cases.append(dict(name=name, kw=dict(num_bits_m1=nb1, qm1_mode=mode1, num_bits_m2=8, qm2_mode=mode2, m1_unidirectional=uni,
+                                             replaceBmm=("bmm3d" not in name), m1_clip_init_val=cv1, m1_clip_init_valn=cvn1,
+                                             m2_clip_init_val=cv2, m2_clip_init_valn=-cv2),
+                          qcfg=qcfg, dtype=dtype, m1=m1, m2=m2, grad_out=go, y=y.detach().clone(), grad_m1=a.grad.clone(), grad_m2=b.grad.clone(),
+                          clip_grads={n_: p_.grad.clone() for n_, p_ in q.named_parameters()},
+                          deploy_buffers={n_: b_.clone() for n_, b_ in d.named_buffers()}, y_deploy=yd.clone(),
+                          num_bits=(q.num_bits_m1, q.num_bits_m2)))  # fmt: skip
+        print(name, "fake vs deploy max diff", (yd.float() - y.float()).abs().max().item())
+    save("bmm.pt", dict(cases=cases))
+
+
 if __name__ == "__main__":
     gen_quantizers()
     gen_qlinear()
@@ -536,3 +585,4 @@ if __name__ == "__main__":
     gen_extra()
     gen_deploy_more()
     gen_c4()
+    gen_bmm()

@@ -295,3 +295,27 @@ def test_float_chunk_gemm_equals_the_reference_triton_kernel():
             assert torch.norm(got - ref) / torch.norm(ref) < 1e-7, (c["M"], kw)
         if "sum" in c:
             assert abs(y.double().sum().item() - c["sum"]) <= 1e-6 * c["abs_sum"]
+
+
+def test_bmm_oracle_matches_reference_fixture():
+    """oracle/bmm.py against QBmm / QBmmINT8Deploy run by the reference itself (bmm.pt): the fake-quantized product and
+    the deploy buffers bit for bit, the deploy output bit for bit including the infinities of its fp16 stage."""
+    from oracle import bmm as OB
+
+    for c in load_golden("bmm.pt")["cases"]:
+        kw, (nb1, nb2) = c["kw"], c["num_bits"]
+        dt = c["dtype"]
+        cv1 = torch.tensor([kw["m1_clip_init_val"]]).to(dt)
+        cvn1 = torch.tensor([kw["m1_clip_init_valn"]]).to(dt)
+        cv2 = torch.tensor([kw["m2_clip_init_val"]]).to(dt)
+        uni = kw["m1_unidirectional"]
+        q1 = dict(mode=kw["qm1_mode"], num_bits=nb1, clip_val=cv1, clip_valn=cvn1, one_sided=uni)
+        q2 = dict(mode=kw["qm2_mode"], num_bits=nb2, clip_val=cv2, clip_valn=None, one_sided=False)
+        y = OB.qbmm_fake(c["m1"], c["m2"], q1, q2, kw["replaceBmm"])
+        assert y.dtype == c["y"].dtype and torch.equal(y, c["y"]), c["name"]
+        buf = OB.deploy_buffers(cv1, cvn1, nb1, kw["qm1_mode"], cv2, nb2)
+        for k, v in c["deploy_buffers"].items():
+            assert buf[k].dtype == v.dtype and torch.equal(buf[k], v), (c["name"], k)
+        yd = OB.qbmm_int8_deploy(c["m1"], c["m2"], buf)
+        want = c["y_deploy"]
+        assert yd.dtype == want.dtype and torch.equal(torch.nan_to_num(yd.float(), nan=12345.0), torch.nan_to_num(want.float(), nan=12345.0)), c["name"]
