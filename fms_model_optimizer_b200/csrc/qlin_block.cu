@@ -15,6 +15,8 @@
 // bf16-valued smoothing / row scales, bf16(a * RN_f32(1 / b)) equals the reference's
 // bf16(RN_f32(a / b)) (a quotient of two 8-bit significands is never within 2^-18 of a bf16
 // rounding boundary).  Callers must pass correctly rounded reciprocals of bf16-valued scales.
+#include <cstdlib>
+
 #include <cuda_bf16.h>
 
 #include "qlin_internal.h"
@@ -293,6 +295,42 @@ __global__ void __launch_bounds__(256) rope_kernel(const RopeParams p) {
   }
 }
 
+template <int TPB>
+static int launch_block_quant_tpb(const BlockQuantParams& p, cudaStream_t s) {
+  static bool configured[64] = {};
+  constexpr int kSmemMax = TPB >= 1024 ? 98304 : 49152;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(block_quant_kernel<TPB>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax) != cudaSuccess)
+      return fail(QLIN_ERR_LAUNCH, "cudaFuncSetAttribute failed for qlin_block_quant");
+    configured[dev] = true;
+  }
+  // resident blocks per SM by registers (64 per thread): 1024 threads
+  const int per_sm = TPB >= 1024 ? 2 : (TPB >= 512 ? 2 : 2 * (1024 / TPB));
+  int grid = sm_count() * per_sm;
+  if (grid > p.rows) grid = p.rows;
+  if (p.max_ctas > 0) {  // the cap counts blocks of 256 threads
+    int cap = TPB >= 256 ? p.max_ctas : p.max_ctas * (256 / TPB);
+    if (cap < 1) cap = 1;
+    if (grid > cap) grid = cap;
+  }
+  const int smem = p.nout * p.cols * 4;
+  const bool in_smem = smem > 0 && smem <= kSmemMax && p.rows >= 4 * grid;
+  block_quant_kernel<TPB><<<grid, TPB, in_smem ? smem : 0, s>>>(p, in_smem ? 1 : 0);
+  QLIN_CHECK_LAUNCH("qlin_block_quant");
+  return QLIN_OK;
+}
+
+static int launch_block_quant(const BlockQuantParams& p, int nchunks, cudaStream_t s) {
+  if (nchunks <= 32) return launch_block_quant_tpb<32>(p, s);
+  if (nchunks <= 64) return launch_block_quant_tpb<64>(p, s);
+  if (nchunks <= 128) return launch_block_quant_tpb<128>(p, s);
+  if (nchunks <= 256) return launch_block_quant_tpb<256>(p, s);
+  if (nchunks <= 512) return launch_block_quant_tpb<512>(p, s);
+  return launch_block_quant_tpb<1024>(p, s);
+}
+
 }  // namespace qlin
 
 using namespace qlin;
@@ -374,34 +412,11 @@ extern "C" int qlin_block_quant(const qlin_block_quant_args* a, void* stream) {
   p.dyn_eps = a->dyn_eps;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int nchunks = p.cols / 16;
-  static bool configured[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(block_quant_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 49152) != cudaSuccess ||
-        cudaFuncSetAttribute(block_quant_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 98304) != cudaSuccess)
-      return fail(QLIN_ERR_LAUNCH, "cudaFuncSetAttribute failed for qlin_block_quant");
-    configured[dev] = true;
-  }
-  if (nchunks <= 256) {
-    int grid = sm_count() * 8;
-    if (grid > p.rows) grid = p.rows;
-    if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
-    // the vectors fit beside four resident blocks per SM: 3 outputs x 16 KB
-    const int smem = p.nout * p.cols * 4;
-    const bool in_smem = smem > 0 && smem <= 49152 && p.rows >= 4 * grid;
-    block_quant_kernel<256><<<grid, 256, in_smem ? smem : 0, s>>>(p, in_smem ? 1 : 0);
-  } else {
-    int grid = sm_count() * 2;
-    if (grid > p.rows) grid = p.rows;
-    if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
-    const int smem = p.nout * p.cols * 4;
-    const bool in_smem = smem > 0 && smem <= 98304 && p.rows >= 4 * grid;
-    block_quant_kernel<1024><<<grid, 1024, in_smem ? smem : 0, s>>>(p, in_smem ? 1 : 0);
-  }
-  QLIN_CHECK_LAUNCH("qlin_block_quant");
-  return QLIN_OK;
+  // One block per row at a time, one 16-element slice per thread: the block size is the smallest power of two that
+  // covers the row (a shard's rows can be a few hundred elements long; idle lanes still cost issue slots).
+  return launch_block_quant(p, nchunks, s);
 }
+
 
 extern "C" int qlin_rope(const qlin_rope_args* a, void* stream) {
   if (a == nullptr) return fail(QLIN_ERR_NULL, "qlin_rope: args is NULL");

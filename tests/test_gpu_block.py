@@ -153,3 +153,25 @@ def test_block_quant_partial_sums_and_replicated_outputs(cuda_dev):
             scales = d[offs_s[o] : offs_s[o] + 4 * R].view(torch.float32)
             assert torch.equal(codes[T:].cpu(), want_c) and not codes[:T].any()
             assert torch.equal(scales[T:].cpu(), want_s.float().reshape(-1)) and not scales[:T].any()
+
+
+@pytest.mark.parametrize("T,K", [(700, 512), (300, 1024), (260, 1792), (130, 2064), (90, 7168), (40, 9000 // 16 * 16)])
+def test_block_size_follows_the_row_length(cuda_dev, T, K):
+    """Rows of a few hundred to a few thousand elements (the shards of a row-parallel Linear's input) run with blocks of
+    32 to 1024 threads; every size class against the oracle, with enough rows for the persistent loop and the shared
+    reciprocal vectors."""
+    g = torch.Generator().manual_seed(T + K)
+    x = (torch.randn(T, K, generator=g) * 2).bfloat16()
+    r = torch.randn(T, K, generator=g).bfloat16()
+    sm = _smooth(K, 11)
+    rcp = ops.smooth_reciprocal(sm.float().to(cuda_dev))
+    codes, scales, _, h = ops.block_quant(x.to(cuda_dev), prologue=L.BLOCK_SILU_MUL, r=r.to(cuda_dev), smooth_rcps=[rcp], want_h=True)
+    ref = (F.silu(x.float()).bfloat16() * r)
+    assert _ulp_close(h.cpu(), ref, ulps=2)
+    want_c, want_s = OQ.qa_dynamic_max_qfunc(h.cpu() / sm)
+    assert torch.equal(codes[0].cpu(), want_c) and torch.equal(scales[0].cpu(), want_s.float().reshape(-1))
+    codes, scales, _, _ = ops.block_quant(x.to(cuda_dev), smooth_rcps=[rcp, None])
+    for c, s, m in zip(codes, scales, (sm, None)):
+        want_c, want_s = OQ.qa_dynamic_max_qfunc(x if m is None else x / m)
+        assert torch.equal(c.cpu(), want_c) and torch.equal(s.cpu(), want_s.float().reshape(-1))
+    ops.check_status(cuda_dev)
