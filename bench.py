@@ -324,6 +324,14 @@ def kernel_cases(dev, which, only=""):
                 add(f"GEMM {kind} {M}x{K}x{N}, bf16 output, scale epilogue", kind, "tensor", 2.0 * M * N * K,
                     lambda a=a, b=b, rs=rs, cs=cs, out=out: ops.gemm(a, b, out=out, epilogue=L.EPI_SCALE_SEQ, row_scale=rs, col_scale=cs,
                                                                       out_dtype=torch.bfloat16))  # fmt: skip
+        # batched integer matmul of attention shapes (QBmmINT8Deploy): 64 heads of one 2048-token sequence each
+        for tag, (Bh, M, N, K) in (("q.k^T", (64, 2048, 2048, 128)), ("p.v", (64, 2048, 128, 2048))):
+            a3 = torch.randint(-100, 100, (Bh, M, K), dtype=torch.int8, device=dev)
+            b3 = torch.randint(-100, 100, (Bh, N, K), dtype=torch.int8, device=dev)
+            byts = Bh * (M * K + N * K + 4 * M * N)
+            add(f"bmm_i8 {tag} {Bh}x{M}x{K}x{N}, int32 output, one launch", "int8", "hbm" if tag == "q.k^T" else "tensor",
+                byts if tag == "q.k^T" else 2.0 * Bh * M * N * K, lambda a3=a3, b3=b3: ops.bmm_i8(a3, b3))
+            cases[-1]["ops"] = 2.0 * Bh * M * N * K
         # HBM-bound kernels on c5 / c4 shaped tensors (larger than L2)
         M, K = 16384, 4096
         x = torch.randn(M, K, device=dev).bfloat16()

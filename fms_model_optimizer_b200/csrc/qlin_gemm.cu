@@ -90,6 +90,8 @@ struct GemmParams {
   int32_t scatter_rows, scatter_row0;
   uint8_t* scatter_d[8];
   int32_t f8_ab_format;  // float kinds: operand format of the instruction descriptor, 0 = e4m3, 1 = e5m2
+  int32_t batch;             // batched launch: problems stacked along the rows of A, B and along D (see qlin_gemm_batched)
+  int64_t batch_stride_d;    // elements of the output type between the problems' outputs
   int32_t low_byte_mode;  // chunked int8, 8 truncated bits: the total on the tensor core, the chunks' low bytes on the ALU
   int32_t sk_mt, sk_split, sk_stages;  // few-row kernel: padded row count, K splits (= cluster size), pipeline stages
 };
@@ -369,7 +371,11 @@ __device__ __forceinline__ void emit32(const GemmParams& p, const uint32_t (&v)[
   store_tile_coalesced(stage, w, g, p.ldd * 4, p.M - row0, lane);
 }
 
-template <bool F8, bool CHUNKED>
+// BATCHED: p.batch problems of the same shape whose operands are stacked along the rows (A is [batch * M, K], B is
+// [batch * N, K]); a tile of problem b starts at row b * M of A and row b * N of B, its rows and columns beyond the
+// problem's M and N belong to the next problem (or lie outside and read as zeros) and are dropped by the epilogue's
+// bounds checks, and its output goes to D + b * batch_stride_d.
+template <bool F8, bool CHUNKED, bool BATCHED = false>
 __global__ void __launch_bounds__(Cfg<CHUNKED>::THREADS, 1)
 qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
@@ -415,7 +421,8 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = aux->tmem_base;
 
-  const int num_tiles = p.num_m * p.num_n;
+  const int per_batch = p.num_m * p.num_n;
+  const int num_tiles = BATCHED ? per_batch * p.batch : per_batch;
   const int num_kb = (p.kbytes + kBK - 1) / kBK;
   const int total_k32 = (p.kbytes + 31) / 32;
   bool timed_out = false;
@@ -430,8 +437,9 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     bool ready = false;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
-      tile_coords(t, p.num_m, p.num_n, mb, nb);
-      const int ya = mb * kBM, yb = nb * C::BN;
+      const int bi = BATCHED ? t / per_batch : 0;
+      tile_coords(t - bi * per_batch, p.num_m, p.num_n, mb, nb);
+      const int ya = mb * kBM + bi * p.M, yb = nb * C::BN + bi * p.N;
       for (int kb = 0; kb < num_kb; ++kb) {
         if (!ready) {
           ok = warp_mbar_wait(&aux->empty[s], ph ^ 1u, abort_flag);
@@ -627,7 +635,16 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t enbuf = elow ? C::NBUF - 1 : C::NBUF;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       int mb, nb;
-      tile_coords(t, p.num_m, p.num_n, mb, nb);
+      const int bi = BATCHED ? t / per_batch : 0;
+      tile_coords(t - bi * per_batch, p.num_m, p.num_n, mb, nb);
+      GemmParams pb;
+      const GemmParams* pp = &p;
+      if constexpr (BATCHED) {
+        pb = p;
+        pb.d = static_cast<uint8_t*>(p.d) + static_cast<int64_t>(bi) * p.batch_stride_d * elt;
+        pp = &pb;
+      }
+      const GemmParams& pe = *pp;
       const int row0 = mb * kBM + q * 32;
       const int row = row0 + lane;
       const int col_w = nb * C::BN + half * C::COLS_PER_WARP;
@@ -664,7 +681,7 @@ qlin_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int i = 0; i < 64; ++i) v[i] = acc_add<F8>(cv[i], v[i]);
           }
-          emit64<F8>(p, v, row0, lane, col_w + j, aux->cs, aux->bias, half * C::COLS_PER_WARP + j, rs, vec_ok, stage);
+          emit64<F8>(pe, v, row0, lane, col_w + j, aux->cs, aux->bias, half * C::COLS_PER_WARP + j, rs, vec_ok, stage);
         }
         tc_fence_before();
         __syncwarp();
@@ -1285,7 +1302,7 @@ static int make_operand_map(CUtensorMap* tm, const void* base, int64_t rows, int
   return QLIN_OK;
 }
 
-template <bool F8, bool CHUNKED>
+template <bool F8, bool CHUNKED, bool BATCHED = false>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
   using C = Cfg<CHUNKED>;
   static bool configured[64] = {};
@@ -1293,15 +1310,15 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return fail(QLIN_ERR_DEVICE, "device ordinal %d out of range", dev);
   if (!configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(qlin_gemm_kernel<F8, CHUNKED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(qlin_gemm_kernel<F8, CHUNKED, BATCHED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::SMEM_BYTES);
     if (e != cudaSuccess) return fail(QLIN_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     configured[dev] = true;
   }
-  const int tiles = p.num_m * p.num_n;
-  int grid = tiles < sm_count() ? tiles : sm_count();
+  const int64_t tiles = static_cast<int64_t>(p.num_m) * p.num_n * (BATCHED ? p.batch : 1);
+  int grid = tiles < sm_count() ? static_cast<int>(tiles) : sm_count();
   if (p.max_ctas > 0 && grid > p.max_ctas) grid = p.max_ctas;
-  qlin_gemm_kernel<F8, CHUNKED><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
+  qlin_gemm_kernel<F8, CHUNKED, BATCHED><<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(ta, tb, p);
   QLIN_CHECK_LAUNCH("qlin_gemm");
   return QLIN_OK;
 }
@@ -1444,7 +1461,8 @@ static bool is_round_dtype(int dt) {
 
 using namespace qlin;
 
-extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
+// batch > 1: the problems' operands are stacked along the rows (dense), one launch of the batched single-CTA kernel.
+static int gemm_impl(const qlin_gemm_args* a, void* stream, int32_t batch, int64_t stride_d) {
   if (a == nullptr) return fail(QLIN_ERR_NULL, "qlin_gemm: args is NULL");
   if (a->a == nullptr || a->b == nullptr || (a->d == nullptr && a->scatter_rows <= 0))
     return fail(QLIN_ERR_NULL, "qlin_gemm: a, b or d is NULL");
@@ -1531,12 +1549,25 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
 
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   p.sk_mt = p.sk_split = p.sk_stages = 0;
+  p.batch = batch;
+  p.batch_stride_d = stride_d;
   // int8 chunks with the low byte rounded away, summed after rounding, no clamp, chunks of 32 / 64 / 128 that tile K:
   // sum of ((p + 128) >> 8 << 8) = sum of p - sum of sext8(p), the first sum kept by the tensor core (QLIN_GEMM_LOWBYTE=0: off)
   p.low_byte_mode = (chunked && !f8 && a->trun_bits == 8 && a->trunc_then_acc && a->max_acc_bits >= 32 &&
                      (chunk_k32 == 1 || chunk_k32 == 2 || chunk_k32 == 4) && total_k32 % 4 == 0 && low_byte_enabled())
                         ? 1
                         : 0;
+  if (batch > 1) {
+    if (chunked || a->c != nullptr || a->scatter_rows != 0) return fail(QLIN_ERR_UNSUPPORTED, "qlin_gemm_batched: one launch takes unchunked problems without accumulator input or scatter");
+    if (static_cast<int64_t>(batch) * a->M > 0x7fffffff || static_cast<int64_t>(batch) * a->N > 0x7fffffff)
+      return fail(QLIN_ERR_BAD_SHAPE, "qlin_gemm_batched: batch * rows exceeds the coordinate range");
+    CUtensorMap ta, tb;
+    int rc = make_operand_map(&ta, a->a, static_cast<int64_t>(batch) * a->M, a->K, a->lda, kBM);
+    if (rc != QLIN_OK) return rc;
+    rc = make_operand_map(&tb, a->b, static_cast<int64_t>(batch) * a->N, a->K, a->ldb, bn);
+    if (rc != QLIN_OK) return rc;
+    return f8 ? launch<true, false, true>(ta, tb, p, s) : launch<false, false, true>(ta, tb, p, s);
+  }
   if (!chunked && a->M <= kBM && a->scatter_rows == 0 && a->max_ctas <= 0 && skinny_enabled()) {
     // weight rows as the MMA's M dimension, the few activation rows (padded to 32) as its N dimension
     p.sk_mt = (a->M + 31) / 32 * 32;
@@ -1565,18 +1596,26 @@ extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) {
   return chunked ? launch<false, true>(ta, tb, p, s) : launch<false, false>(ta, tb, p, s);
 }
 
+extern "C" int qlin_gemm(const qlin_gemm_args* a, void* stream) { return gemm_impl(a, stream, 1, 0); }
+
 extern "C" int qlin_gemm_batched(const qlin_gemm_args* a, int32_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, void* stream) {
   if (a == nullptr) return fail(QLIN_ERR_NULL, "qlin_gemm_batched: args is NULL");
   if (batch < 0 || stride_a < 0 || stride_b < 0 || stride_d < 0) return fail(QLIN_ERR_BAD_SHAPE, "qlin_gemm_batched: negative batch or stride");
   if (a->c != nullptr || a->scatter_rows != 0) return fail(QLIN_ERR_UNSUPPORTED, "qlin_gemm_batched: no accumulator input and no row-block scatter");
   if (batch > 1 && (stride_a % 16 != 0 || stride_b % 16 != 0)) return fail(QLIN_ERR_BAD_ALIGN, "qlin_gemm_batched: operand strides must be multiples of 16 bytes");
+  if (batch == 0) return QLIN_OK;
   const int64_t out_elt = (a->epilogue == QLIN_EPI_RAW || a->out_dtype == QLIN_DT_F32) ? 4 : 2;
+  const bool needs_chunks = (a->trun_bits > 0) || (a->kind == QLIN_DT_I8 && a->max_acc_bits < 32) || (a->kind != QLIN_DT_I8 && a->clamp_dl16);
+  // dense stacks of unchunked problems: one launch whose tiles walk over all problems
+  if (batch > 1 && !needs_chunks && stride_a == static_cast<int64_t>(a->M) * a->lda && stride_b == static_cast<int64_t>(a->N) * a->ldb &&
+      (stride_d * out_elt) % 16 == 0 && a->M > 0 && a->N > 0)
+    return gemm_impl(a, stream, batch, stride_d);
   qlin_gemm_args one = *a;
   for (int32_t i = 0; i < batch; ++i) {
     one.a = static_cast<const uint8_t*>(a->a) + i * stride_a;
     one.b = static_cast<const uint8_t*>(a->b) + i * stride_b;
     one.d = static_cast<uint8_t*>(a->d) + i * stride_d * out_elt;
-    const int rc = qlin_gemm(&one, stream);
+    const int rc = gemm_impl(&one, stream, 1, 0);
     if (rc != QLIN_OK) return rc;
   }
   return QLIN_OK;

@@ -144,8 +144,9 @@ int qlin_gemm(const qlin_gemm_args* args, void* stream);
  * the operand type) and `stride_d` (elements of the output type) apart: D[i] = epilogue(A[i] . B[i]^T).  The batched
  * int8 product behind QBmmINT8Deploy (fms_mo/modules/bmm.py:719-752), where the reference itself "has not implemented
  * any batched CUTLASS matmul" and simulates with torch.matmul on fp16 copies of the codes.  Scales, bias and the
- * status word are shared by all problems; `c` must be NULL; row-block scatter is not provided.  One launch per
- * problem on `stream`, in order. */
+ * status word are shared by all problems; `c` must be NULL; row-block scatter is not provided.  Dense stacks of
+ * unchunked problems (stride_a = M * lda, stride_b = N * ldb, stride_d a multiple of 16 bytes) run as ONE launch whose
+ * tiles walk over all problems; anything else as one launch per problem on `stream`, in order. */
 int qlin_gemm_batched(const qlin_gemm_args* args, int32_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_d, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
