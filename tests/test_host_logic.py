@@ -189,3 +189,24 @@ def test_lowering_default_arguments_leave_plain_linears_alone():
         lower_qmodel_b200(m, use_dyn_max_act=dyn)
         assert type(m.q) is QLinearINT8Deploy
         assert type(m.head) is head_type
+
+
+def test_qbmm_deploy_buffers_equal_the_reference_fixture():
+    """QBmm's constructor surface and QBmmINT8Deploy.from_fms_mo are host logic: built on the CPU they must carry the
+    reference's parameter names, bit widths and buffers (bmm.pt, made by the reference's own classes)."""
+    from conftest import load_golden
+    from fms_model_optimizer_b200.modules import QBmm, QBmmINT8Deploy
+
+    for c in load_golden("bmm.pt")["cases"]:
+        q = QBmm(qcfg=dict(c["qcfg"]), **c["kw"]).to(c["dtype"])
+        assert (q.num_bits_m1, q.num_bits_m2) == tuple(c["num_bits"])
+        assert sorted(n for n, _ in q.named_parameters()) == sorted(c["clip_grads"])
+        d = QBmmINT8Deploy.from_fms_mo(q, target_device="cpu")
+        assert sorted(n for n, _ in d.named_buffers()) == sorted(c["deploy_buffers"])
+        for k, v in c["deploy_buffers"].items():
+            got = getattr(d, k)
+            assert got.dtype == v.dtype and torch.equal(got, v), (c["name"], k)
+    with pytest.raises(NotImplementedError):
+        QBmm(num_bits_m1=8, qm1_mode="pactsym+", num_bits_m2=8, qm2_mode="pactsym+", qcfg={"qmodel_calibration_new": 3})
+    with pytest.raises(RuntimeError, match="CUDA"):
+        QBmmINT8Deploy.from_fms_mo(q, target_device="cpu")(c["m1"], c["m2"])
