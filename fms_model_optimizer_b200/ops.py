@@ -12,6 +12,7 @@ of the file) so that modules call ``torch.ops.qlin_b200.*`` the way the referenc
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional, Sequence, Tuple
 
 import torch
@@ -43,9 +44,24 @@ PROFILE = None
 GEMM_MAX_CTAS = 0
 
 
+# QLIN_NVTX=1: every launch of this library sits inside an NVTX range named after its entry point, so that a timeline
+# tool shows the library's calls among PyTorch's (off by default: a range costs a little host time per launch).
+NVTX = os.environ.get("QLIN_NVTX", "0") == "1"
+
+
 def _timed(name: str, work: float, dev: torch.device, call):
     global LAUNCHES
     LAUNCHES += 1
+    if NVTX:
+        torch.cuda.nvtx.range_push(f"qlin_{name}")
+        try:
+            return _timed_inner(name, work, dev, call)
+        finally:
+            torch.cuda.nvtx.range_pop()
+    return _timed_inner(name, work, dev, call)
+
+
+def _timed_inner(name: str, work: float, dev: torch.device, call):
     if PROFILE is None:
         return call()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
