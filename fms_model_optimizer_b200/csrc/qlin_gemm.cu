@@ -1576,7 +1576,10 @@ static int gemm_impl(const qlin_gemm_args* a, void* stream, int32_t batch, int64
     if (rc != QLIN_OK) return rc;
     rc = make_operand_map(&tx, a->a, a->M, a->K, a->lda, p.sk_mt);
     if (rc != QLIN_OK) return rc;
-    return f8 ? launch_skinny<true>(tw, tx, p, s) : launch_skinny<false>(tw, tx, p, s);
+    rc = f8 ? launch_skinny<true>(tw, tx, p, s) : launch_skinny<false>(tw, tx, p, s);
+    // a device that cannot place the cluster (fewer SMs per GPC than the split needs): the wide tile below does the job
+    if (rc != QLIN_ERR_LAUNCH) return rc;
+    p.sk_mt = p.sk_split = p.sk_stages = 0;
   }
 
   CUtensorMap ta, tb;
