@@ -540,7 +540,8 @@ def run_c5(args, rank, world, dev):
     from fms_model_optimizer_b200.decoder import LLAMA3_8B, W8A8Decoder, decoder_linear_ops, linear_shapes
 
     cfg = dict(LLAMA3_8B)
-    groups = args.groups if args.groups > 0 else (2 if world > 1 else 1)
+    # measured on 8 x B200: two groups of sequences in flight up to four GPUs, four groups at eight
+    groups = args.groups if args.groups > 0 else (4 if world >= 8 else (2 if world > 1 else 1))
     B, S = cfg["batch"], cfg["seq"]
     tokens = B * S
     g = torch.Generator().manual_seed(4)
@@ -649,9 +650,10 @@ def run_c5(args, rank, world, dev):
         # other settings of the sharded run on the same weights: "g<groups>r<reserved SMs>[s]" ("s": plain stores)
         for spec in args.sweep.split(","):
             gi, ri = spec.index("g"), spec.index("r")
-            sg, sr = int(spec[gi + 1 : ri]), int(spec[ri + 1 :].rstrip("s"))
+            sg, sr = int(spec[gi + 1 : ri]), int(spec[ri + 1 :].rstrip("sf"))
             graph = None
             model.reconfigure(groups=sg, reserve_sms=sr, exchange=("stores" if spec.endswith("s") else "multimem"))
+            model.switch_reduce = "fused" if spec.endswith("f") else "split"  # "f": the switch reduce inside the norm + quantise kernel
             model.enable_token_split(tokens // sg)
             for _ in range(3):
                 model.forward(ids_dev)
@@ -662,7 +664,7 @@ def run_c5(args, rank, world, dev):
             gr.replay()
             ms_v = timed(gr.replay, args.steps) / args.steps
             ops.check_status(dev)
-            sweep.append({"groups": sg, "reserve_sms": sr, "exchange": model.exchange, "ms_per_step": ms_v, "tokens_per_s": tokens / (ms_v * 1e-3)})
+            sweep.append({"groups": sg, "reserve_sms": sr, "exchange": model.exchange, "switch_reduce": model.switch_reduce, "ms_per_step": ms_v, "tokens_per_s": tokens / (ms_v * 1e-3)})
             del gr
 
     surfaces = None
