@@ -650,11 +650,12 @@ def run_c5(args, rank, world, dev):
         # other settings of the sharded run on the same weights: "g<groups>r<reserved SMs>[s]" ("s": plain stores)
         for spec in args.sweep.split(","):
             gi, ri = spec.index("g"), spec.index("r")
-            sg, sr = int(spec[gi + 1 : ri]), int(spec[ri + 1 :].rstrip("sfn").split("t")[0])
+            sg, sr = int(spec[gi + 1 : ri]), int(spec[ri + 1 :].rstrip("sfnk").split("t")[0])
             graph = None
             model.reconfigure(groups=sg, reserve_sms=sr, exchange=("stores" if spec.endswith("s") else "multimem"))
             model.switch_reduce = "fused" if spec.endswith("f") else "split"  # "f": the switch reduce inside the norm + quantise kernel
-            model.stagger = 0 if spec.endswith("n") else (int(spec.split("t")[1].rstrip("sfn")) if "t" in spec else 1)  # "n": groups start together; "t<k>": k segments apart
+            model.k_on_side_stream = spec.endswith("k")  # "k": the k projection on a second side stream
+            model.stagger = 0 if spec.endswith("n") else (int(spec.split("t")[1].rstrip("sfnk")) if "t" in spec else 2)  # "n": groups start together; "t<k>": k segments apart
             model.enable_token_split(tokens // sg)
             for _ in range(3):
                 model.forward(ids_dev)
@@ -665,7 +666,7 @@ def run_c5(args, rank, world, dev):
             gr.replay()
             ms_v = timed(gr.replay, args.steps) / args.steps
             ops.check_status(dev)
-            sweep.append({"groups": sg, "reserve_sms": sr, "exchange": model.exchange, "switch_reduce": model.switch_reduce, "stagger": model.stagger, "ms_per_step": ms_v, "tokens_per_s": tokens / (ms_v * 1e-3)})
+            sweep.append({"groups": sg, "reserve_sms": sr, "exchange": model.exchange, "switch_reduce": model.switch_reduce, "stagger": model.stagger, "k_on_side_stream": model.k_on_side_stream, "ms_per_step": ms_v, "tokens_per_s": tokens / (ms_v * 1e-3)})
             del gr
 
     surfaces = None

@@ -157,6 +157,7 @@ class W8A8Decoder:
         # groups; two = the embedding and the first norm + quantise + exchange).  Measured at four GPUs: no difference with
         # two groups (46.3 ms either way), 45.6 against 47.9 ms with four.
         self.stagger = 2
+        self.k_on_side_stream = False
         if exchange == "auto":
             # measured on 8 x B200: with two GPUs the plain-store scheme wins (every byte crosses one link once either
             # way and the stores ride in the GEMM epilogue); from four GPUs on the switch's reduce / replicate does
@@ -342,6 +343,7 @@ class W8A8Decoder:
             g = _Group()
             g.bar = PeerBarrier(self.arena, barrier_timeout_s)
             g.side = torch.cuda.Stream(device=self.dev)
+            g.side2 = torch.cuda.Stream(device=self.dev)
             g.T, g.Ts = T, T // W
             g.part_off, part = self.arena.alloc(T * H * 2)
             # multimem: my partial output for all tokens; stores: [world] receive slots for my tokens
@@ -430,8 +432,16 @@ class W8A8Decoder:
             g.side.wait_stream(cur)
             with torch.cuda.stream(g.side):
                 v = lin["v"](None, (g.codes[2], g.scales[2]), bf)
+            if self.k_on_side_stream:  # with many small groups q's shard does not fill the GPU either: k beside it as well
+                g.side2.wait_stream(cur)
+                with torch.cuda.stream(g.side2):
+                    k = ops.rope_(lin["k"](None, (g.codes[1], g.scales[1]), bf).view(T, self.nkv, hd), self.cos, self.sin, S)
             q = ops.rope_(lin["q"](None, (g.codes[0], g.scales[0]), bf).view(T, self.nq, hd), self.cos, self.sin, S)
-            k = ops.rope_(lin["k"](None, (g.codes[1], g.scales[1]), bf).view(T, self.nkv, hd), self.cos, self.sin, S)
+            if self.k_on_side_stream:
+                cur.wait_stream(g.side2)
+                k.record_stream(cur)
+            else:
+                k = ops.rope_(lin["k"](None, (g.codes[1], g.scales[1]), bf).view(T, self.nkv, hd), self.cos, self.sin, S)
             cur.wait_stream(g.side)
             v.record_stream(cur)
             a = self._attention(q, k, v, B, S)
